@@ -1,0 +1,325 @@
+"""ctypes binding of include/h3q8.h.
+
+`Gpu` mirrors the reference's operator interface (src/gpu.h): the same operator
+names without the `h3_gpu_` prefix, the same argument order and meaning, the
+same 1/0 result convention turned into `H3Error` carrying `h3_gpu_error()`.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+MODE_BF16, MODE_W8A16, MODE_W8A8 = 0, 1, 2
+ACT_NONE, ACT_GELU_TANH = 0, 1
+KERNEL_AUTO, KERNEL_PLAIN, KERNEL_TCGEN05, KERNEL_TCGEN05_M256, KERNEL_TCGEN05_N128 = 0, 1, 2, 3, 4
+F32, BF16, I8, U32, F16 = 0, 1, 2, 3, 4
+HOST_VISIBLE, DEVICE_ONLY, HOST_PINNED = 0, 1, 2
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libh3q8.so")
+_lib = None
+
+
+class H3Error(RuntimeError):
+    pass
+
+
+class LinearDesc(C.Structure):
+    """h3q8_linear_desc"""
+    _fields_ = [
+        ("mode", C.c_uint32), ("rows", C.c_uint32), ("input_dim", C.c_uint32), ("output_dim", C.c_uint32),
+        ("input", C.c_void_p), ("weight", C.c_void_p), ("weight_scales", C.c_void_p), ("weight_group", C.c_uint32),
+        ("input_scales", C.c_void_p), ("bias", C.c_void_p), ("gate", C.c_void_p), ("residual", C.c_void_p),
+        ("activation", C.c_uint32), ("output", C.c_void_p), ("accumulators", C.c_void_p), ("kernel", C.c_uint32),
+    ]
+
+
+class Stats(C.Structure):
+    """h3_gpu_stats"""
+    _fields_ = ([(n, C.c_uint64) for n in ("q8_weights", "q8_source_bytes", "q8_storage_bytes", "q8_dispatches")] +
+                [("q8_load_seconds", C.c_double)] +
+                [(n, C.c_uint64) for n in ("allocated_bytes", "live_bytes", "peak_live_bytes", "tensor_allocations",
+                                           "direct_dispatches", "submissions", "linear_dispatches", "h2d_bytes",
+                                           "d2h_bytes", "d2d_bytes", "streamed_bytes", "stream_stalls", "pinned_bytes",
+                                           "stream_slot_bytes")] +
+                [("stream_wait_seconds", C.c_double), ("quant_conversion_seconds", C.c_double)] +
+                [(n, C.c_uint64) for n in ("quant_projection_dispatches", "quant_cache_hits", "quant_cache_misses",
+                                           "native_scratch_bytes", "native_scratch_allocations",
+                                           "native_scratch_reuses")])
+
+
+class Problem(C.Structure):
+    """h3_gpu_linear_problem"""
+    _fields_ = [("output", C.c_void_p), ("input", C.c_void_p), ("weight", C.c_void_p), ("bias", C.c_void_p),
+                ("gate", C.c_void_p), ("residual", C.c_void_p), ("rows", C.c_uint32), ("input_dim", C.c_uint32),
+                ("output_dim", C.c_uint32), ("activation", C.c_int)]
+
+
+def library():
+    """Loads the in-tree libh3q8.so; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise H3Error(f"{_LIB_PATH} is missing: run `python -m h3cli_b200.build` (needs nvcc); there is no CPU fallback")
+    lib = C.CDLL(_LIB_PATH)
+    vp, u32, u64, sz = C.c_void_p, C.c_uint32, C.c_uint64, C.c_size_t
+    sig = {
+        "h3_q8_layout": (C.c_int, [u32, u32, C.POINTER(sz), C.POINTER(sz)]),
+        "h3_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32]),
+        "h3q8_q8_layout": (C.c_int, [u32, u32, u32, C.POINTER(sz), C.POINTER(sz)]),
+        "h3q8_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32, u32]),
+        "h3q8_linear": (C.c_int, [C.POINTER(LinearDesc), vp]),
+        "h3q8_linear_grouped": (C.c_int, [C.POINTER(LinearDesc), u32, vp]),
+        "h3q8_quantize_rows": (C.c_int, [vp, vp, vp, u32, u32, u32, C.c_float, vp]),
+        "h3q8_q8_pack_rows_device": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
+        "h3q8_q8_dequant": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
+        "h3q8_device_status": (u32, [vp]),
+        "h3q8_last_error": (C.c_char_p, []),
+        "h3q8_kernel_launches": (u64, []),
+        "h3_gpu_create": (vp, [C.c_char_p, C.c_char_p, sz]),
+        "h3_gpu_free": (None, [vp]), "h3_gpu_cancel": (None, [vp]),
+        "h3_gpu_error": (C.c_char_p, [vp]),
+        "h3_gpu_get_stats": (C.c_int, [vp, C.POINTER(Stats)]),
+        "h3_gpu_backend_name": (C.c_char_p, [vp]), "h3_gpu_has_int8_mlp": (C.c_int, [vp]),
+        "h3_gpu_begin": (C.c_int, [vp]), "h3_gpu_continue": (C.c_int, [vp]),
+        "h3_gpu_submit": (C.c_int, [vp]), "h3_gpu_synchronize": (C.c_int, [vp]),
+        "h3_gpu_tensor_alloc": (vp, [vp, sz, C.c_int, C.c_int]),
+        "h3_gpu_tensor_contents": (vp, [vp]),
+        "h3_gpu_tensor_new_f32": (vp, [vp, sz]), "h3_gpu_tensor_new_bf16": (vp, [vp, sz]), "h3_gpu_tensor_new_i8": (vp, [vp, sz]),
+        "h3_gpu_tensor_from_f32": (vp, [vp, vp, sz]), "h3_gpu_tensor_from_bf16": (vp, [vp, vp, sz]),
+        "h3_gpu_tensor_from_u32": (vp, [vp, vp, sz]),
+        "h3_gpu_tensor_free": (None, [vp]), "h3_gpu_tensor_elements": (sz, [vp]), "h3_gpu_tensor_dtype": (C.c_int, [vp]),
+        "h3_gpu_tensor_read_f32": (C.c_int, [vp, vp, sz]), "h3_gpu_tensor_read_bf16": (C.c_int, [vp, vp, sz]),
+        "h3_gpu_tensor_read_u32": (C.c_int, [vp, vp, sz]), "h3_gpu_tensor_read_i8": (C.c_int, [vp, vp, sz]),
+        "h3_gpu_tensor_write_f32": (C.c_int, [vp, vp, sz]), "h3_gpu_tensor_write_bf16": (C.c_int, [vp, vp, sz]),
+        "h3_gpu_tensor_write_i8": (C.c_int, [vp, vp, sz]),
+        "h3_gpu_tensor_write_bf16_range": (C.c_int, [vp, sz, vp, sz]),
+        "h3_gpu_event_new": (vp, [vp]), "h3_gpu_event_record": (C.c_int, [vp, vp]),
+        "h3_gpu_event_wait": (C.c_int, [vp, vp]), "h3_gpu_event_free": (None, [vp]),
+        "h3_gpu_tensor_load_bf16": (vp, [vp, C.c_char_p, u64, sz]),
+        "h3_gpu_tensor_read_file_bf16": (C.c_int, [vp, C.c_char_p, u64, sz, C.c_char_p, sz]),
+        "h3_gpu_tensor_stream_file_bf16": (C.c_int, [vp, C.c_char_p, u64, sz, C.c_char_p, sz]),
+        "h3_gpu_plan_weights": (C.c_int, [vp, u64, u64]), "h3_gpu_release_weight_cache": (C.c_int, [vp]),
+        "h3_gpu_linear_bf16": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32]),
+        "h3_gpu_quant_configure": (C.c_int, [vp, C.c_int, C.c_char_p, u64, u64, C.c_int]),
+        "h3_gpu_quant_load": (vp, [vp, C.c_char_p, u64, u32, u32]),
+        "h3_gpu_q8_load": (vp, [vp, C.c_char_p, u64, u32, u32]),
+        "h3q8_gpu_set_group": (C.c_int, [vp, u32]),
+        "h3q8_gpu_tensor_device_pointer": (vp, [vp]), "h3q8_gpu_compute_stream": (vp, [vp]),
+        "h3q8_gpu_set_w8a16_scratch_rows": (C.c_int, [vp, u32]),
+        "h3q8_gpu_q8_from_host": (vp, [vp, vp, vp, u32, u32, u32]),
+        "h3_gpu_quantize_weight_int8": (C.c_int, [vp, vp, vp, vp, u32, u32]),
+        "h3_gpu_linear_int8_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
+        "h3_gpu_gelu_bf16": (C.c_int, [vp, vp, vp, u32, C.c_int]),
+        "h3_gpu_gate_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]),
+        "h3_gpu_add_bf16": (C.c_int, [vp, vp, vp, vp, u32]),
+        "h3_gpu_linear_fused_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
+        "h3_gpu_linear_grouped_bf16": (C.c_int, [vp, C.POINTER(Problem), u32]),
+    }
+    for name, (restype, argtypes) in sig.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = restype, argtypes
+    lib._signatures = sig
+    _lib = lib
+    return lib
+
+
+_NP = {F32: np.float32, BF16: np.uint16, I8: np.int8, U32: np.uint32}
+
+
+class Tensor:
+    """An h3_gpu_tensor; bf16 travels as uint16 bit patterns."""
+
+    def __init__(self, gpu, handle):
+        if not handle:
+            raise H3Error(gpu.error())
+        self.gpu, self.handle = gpu, handle
+
+    @property
+    def elements(self):
+        return library().h3_gpu_tensor_elements(self.handle)
+
+    @property
+    def dtype(self):
+        return library().h3_gpu_tensor_dtype(self.handle)
+
+    @property
+    def device_pointer(self):
+        return library().h3q8_gpu_tensor_device_pointer(self.handle)
+
+    def read(self, elements=None, dtype=None):
+        dtype = self.dtype if dtype is None else dtype
+        n = self.elements if elements is None else elements
+        out = np.empty(n, _NP[dtype])
+        fn = {F32: "read_f32", BF16: "read_bf16", I8: "read_i8", U32: "read_u32"}[dtype]
+        self.gpu._check(getattr(library(), "h3_gpu_tensor_" + fn)(self.handle, out.ctypes.data, n))
+        return out
+
+    def write(self, values):
+        values = np.ascontiguousarray(values)
+        fn = {F32: "write_f32", BF16: "write_bf16", I8: "write_i8"}[self.dtype]
+        self.gpu._check(getattr(library(), "h3_gpu_tensor_" + fn)(self.handle, values.ctypes.data, values.size))
+
+    def free(self):
+        if self.handle:
+            library().h3_gpu_tensor_free(self.handle)
+            self.handle = None
+
+
+def _h(t):
+    return None if t is None else t.handle
+
+
+class Gpu:
+    """An h3_gpu context (src/gpu.h): one per GPU, used by one thread at a time."""
+
+    def __init__(self, shader_path=""):
+        err = C.create_string_buffer(1024)
+        self.handle = library().h3_gpu_create(shader_path.encode(), err, len(err))
+        if not self.handle:
+            raise H3Error(err.value.decode() or "h3_gpu_create failed")
+
+    def error(self):
+        return library().h3_gpu_error(self.handle).decode()
+
+    def _check(self, ok):
+        if not ok:
+            raise H3Error(self.error())
+        return ok
+
+    def free(self):
+        if self.handle:
+            library().h3_gpu_free(self.handle)
+            self.handle = None
+
+    def cancel(self):
+        library().h3_gpu_cancel(self.handle)
+
+    def stats(self):
+        s = Stats()
+        self._check(library().h3_gpu_get_stats(self.handle, C.byref(s)))
+        return s
+
+    def backend_name(self):
+        return library().h3_gpu_backend_name(self.handle).decode()
+
+    def begin(self):
+        return self._check(library().h3_gpu_begin(self.handle))
+
+    def continue_(self):
+        return self._check(library().h3_gpu_continue(self.handle))
+
+    def submit(self):
+        return self._check(library().h3_gpu_submit(self.handle))
+
+    def synchronize(self):
+        return self._check(library().h3_gpu_synchronize(self.handle))
+
+    @property
+    def stream(self):
+        return library().h3q8_gpu_compute_stream(self.handle)
+
+    # tensors ------------------------------------------------------------
+    def tensor_alloc(self, elements, dtype, storage=DEVICE_ONLY):
+        return Tensor(self, library().h3_gpu_tensor_alloc(self.handle, elements, dtype, storage))
+
+    def tensor_new_bf16(self, n):
+        return Tensor(self, library().h3_gpu_tensor_new_bf16(self.handle, n))
+
+    def tensor_new_i8(self, n):
+        return Tensor(self, library().h3_gpu_tensor_new_i8(self.handle, n))
+
+    def tensor_new_f32(self, n):
+        return Tensor(self, library().h3_gpu_tensor_new_f32(self.handle, n))
+
+    def tensor_from_bf16(self, bits):
+        bits = np.ascontiguousarray(bits, np.uint16)
+        return Tensor(self, library().h3_gpu_tensor_from_bf16(self.handle, bits.ctypes.data, bits.size))
+
+    def tensor_from_f32(self, values):
+        values = np.ascontiguousarray(values, np.float32)
+        return Tensor(self, library().h3_gpu_tensor_from_f32(self.handle, values.ctypes.data, values.size))
+
+    def tensor_from_u32(self, values):
+        values = np.ascontiguousarray(values, np.uint32)
+        return Tensor(self, library().h3_gpu_tensor_from_u32(self.handle, values.ctypes.data, values.size))
+
+    def tensor_from_i8(self, values):
+        values = np.ascontiguousarray(values, np.int8)
+        t = self.tensor_new_i8(values.size)
+        t.write(values)
+        return t
+
+    def tensor_load_bf16(self, path, offset, elements):
+        return Tensor(self, library().h3_gpu_tensor_load_bf16(self.handle, path.encode(), offset, elements))
+
+    # quantised weights --------------------------------------------------
+    def quant_configure(self, mode, cache=None, bf16_weights=0, activations=0, force_stream=0):
+        return self._check(library().h3_gpu_quant_configure(self.handle, mode, cache.encode() if cache else None,
+                                                            bf16_weights, activations, force_stream))
+
+    def set_group(self, group):
+        return self._check(library().h3q8_gpu_set_group(self.handle, group))
+
+    def set_w8a16_scratch_rows(self, rows):
+        return self._check(library().h3q8_gpu_set_w8a16_scratch_rows(self.handle, rows))
+
+    def q8_load(self, path, offset, rows, columns):
+        return Tensor(self, library().h3_gpu_q8_load(self.handle, path.encode(), offset, rows, columns))
+
+    def quant_load(self, path, offset, rows, columns):
+        return Tensor(self, library().h3_gpu_quant_load(self.handle, path.encode(), offset, rows, columns))
+
+    def q8_from_host(self, weights, scales, group):
+        weights = np.ascontiguousarray(weights, np.int8)
+        scales = np.ascontiguousarray(scales, np.float32)
+        rows, columns = weights.shape
+        return Tensor(self, library().h3q8_gpu_q8_from_host(self.handle, weights.ctypes.data, scales.ctypes.data,
+                                                            rows, columns, group))
+
+    # operators ----------------------------------------------------------
+    def linear_bf16(self, output, input, weight, bias, rows, input_dim, output_dim):
+        return self._check(library().h3_gpu_linear_bf16(self.handle, _h(output), _h(input), _h(weight), _h(bias),
+                                                        rows, input_dim, output_dim))
+
+    def linear_fused_bf16(self, output, input, weight, bias, gate, residual, rows, input_dim, output_dim, activation):
+        return self._check(library().h3_gpu_linear_fused_bf16(self.handle, _h(output), _h(input), _h(weight), _h(bias),
+                                                              _h(gate), _h(residual), rows, input_dim, output_dim,
+                                                              activation))
+
+    def linear_grouped_bf16(self, problems):
+        array = (Problem * len(problems))(*[Problem(_h(p["output"]), _h(p["input"]), _h(p["weight"]), _h(p.get("bias")),
+                                                     _h(p.get("gate")), _h(p.get("residual")), p["rows"], p["input_dim"],
+                                                     p["output_dim"], p.get("activation", 0)) for p in problems])
+        return self._check(library().h3_gpu_linear_grouped_bf16(self.handle, array, len(problems)))
+
+    def quantize_weight_int8(self, output, scales, input, rows, columns):
+        return self._check(library().h3_gpu_quantize_weight_int8(self.handle, _h(output), _h(scales), _h(input), rows, columns))
+
+    def linear_int8_bf16(self, output, quantized_input, input_scales, input, weight, weight_scales, rows, input_dim,
+                         output_dim, use_slower_uncached_int8_scales=0):
+        return self._check(library().h3_gpu_linear_int8_bf16(self.handle, _h(output), _h(quantized_input), _h(input_scales),
+                                                             _h(input), _h(weight), _h(weight_scales), rows, input_dim,
+                                                             output_dim, use_slower_uncached_int8_scales))
+
+    def gelu_bf16(self, output, input, elements, approximate=1):
+        return self._check(library().h3_gpu_gelu_bf16(self.handle, _h(output), _h(input), elements, approximate))
+
+    def gate_bf16(self, output, residual, branch, modulation, row_map, rows, width, slots, gate_slot):
+        return self._check(library().h3_gpu_gate_bf16(self.handle, _h(output), _h(residual), _h(branch), _h(modulation),
+                                                      _h(row_map), rows, width, slots, gate_slot))
+
+    def add_bf16(self, output, left, right, elements):
+        return self._check(library().h3_gpu_add_bf16(self.handle, _h(output), _h(left), _h(right), elements))
+
+    # raw layer on this context's stream ------------------------------------
+    def raw_linear(self, **fields):
+        """h3q8_linear with Tensor / int fields; enqueues on the compute stream."""
+        d = LinearDesc()
+        for key, value in fields.items():
+            setattr(d, key, value.device_pointer if isinstance(value, Tensor) else value)
+        if not library().h3q8_linear(C.byref(d), self.stream):
+            raise H3Error(library().h3q8_last_error().decode())
+
+    def raw_status(self):
+        return library().h3q8_device_status(self.stream)

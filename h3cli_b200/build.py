@@ -1,0 +1,52 @@
+"""Compiles libh3q8.so in-tree for sm_100a with nvcc (cross-compiles without a GPU)."""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libh3q8.so")
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-pthread"]
+
+
+def _nvcc():
+    for candidate in (shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if candidate and os.path.exists(candidate):
+            return candidate
+    raise RuntimeError("nvcc not found: libh3q8 cannot be built")
+
+
+def _stale(target, sources):
+    if not os.path.exists(target):
+        return True
+    stamp = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > stamp for s in sources)
+
+
+def build(force=False, verbose=False):
+    """Builds h3cli_b200/libh3q8.so if any source is newer; returns its path."""
+    include = os.path.join(ROOT, "include")
+    sources = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC))] + [os.path.join(include, "h3q8.h"), __file__]
+    if not force and not _stale(LIB, sources):
+        return LIB
+    build_dir = os.path.join(HERE, "_build")
+    os.makedirs(build_dir, exist_ok=True)
+    pack_o = os.path.join(build_dir, "q8_pack.o")
+    run = lambda cmd: subprocess.run(cmd, check=True, stdout=None if verbose else subprocess.DEVNULL)
+    run(["gcc", "-O2", "-std=c11", "-fPIC", "-ffp-contract=off", "-I", include, "-c",
+         os.path.join(CSRC, "q8_pack.c"), "-o", pack_o])
+    objects = [pack_o]
+    for unit in ("h3q8_raw.cu", "h3_gpu.cu"):
+        obj = os.path.join(build_dir, unit.replace(".cu", ".o"))
+        run([_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-I", include, "-I", CSRC, "-c",
+             os.path.join(CSRC, unit), "-o", obj])
+        objects.append(obj)
+    run([_nvcc(), "-shared", "-o", LIB, *objects, "-lm"])
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,383 @@
+/* Persistent, warp-specialised tcgen05 GEMM for the q8 DiT linears (sm_100a).
+ *
+ *   out[M,N] = epilogue( X[M,K] . W[N,K]^T )
+ *
+ * Three operand modes share one pipeline:
+ *   MODE_BF16   X bf16, W bf16            TMA -> smem -> kind::f16 MMA  (fp32 in TMEM)
+ *   MODE_W8A16  X bf16, W int8 + scales   TMA -> smem -> dequant warps write
+ *                                         bf16(float(q)*scale) tiles -> kind::f16 MMA
+ *   MODE_W8A8   X int8, W int8            TMA -> smem -> kind::i8 MMA   (int32 in TMEM)
+ *
+ * One CTA per SM, static round-robin over output tiles of (128*MT) x BN.
+ * Warp roles: 0-3 epilogue (TMEM lane quadrant = warp index), 4 TMA producer,
+ * 5 MMA issuer and TMEM owner, 6-13 dequantisers (MODE_W8A16 only).
+ * Operand tiles are rows of 128 bytes in the 128-byte swizzle; one k-block is
+ * 64 bf16 or 128 int8 elements = four MMA instructions per 128-row sub-tile.
+ * Accumulators are double-buffered in TMEM whenever 2*MT*BN <= 512 columns so
+ * the epilogue of one tile overlaps the main loop of the next.
+ *
+ * No cluster launch and no TMA multicast: every CTA fetches its own tiles and
+ * tiles that share weights are co-scheduled so they meet in L2.
+ */
+#pragma once
+#include "epilogue.cuh"
+
+namespace h3q8 {
+
+enum : int { MODE_BF16 = 0, MODE_W8A16 = 1, MODE_W8A8 = 2 };
+
+enum : uint32_t {
+    STATUS_OK = 0,
+    STATUS_WAIT_PRODUCER = 1,  /* TMA producer gave up waiting for a free stage   */
+    STATUS_WAIT_MMA = 2,       /* MMA issuer gave up waiting for operands / TMEM  */
+    STATUS_WAIT_EPILOGUE = 3,  /* epilogue gave up waiting for an accumulator     */
+    STATUS_WAIT_DEQUANT = 4,   /* dequantiser gave up waiting                     */
+};
+
+struct GemmParams {
+    uint32_t M, N, K;
+    uint32_t scale_group;   /* K elements per weight scale; 0 = one scale per output channel */
+    uint32_t scale_groups;  /* scales per weight row                                         */
+    const float *w_scales;  /* [N, scale_groups] (MODE_W8A16, MODE_W8A8)                     */
+    const float *a_scales;  /* [M] per-token scales (MODE_W8A8)                              */
+    EpilogueParams ep;
+    uint16_t *out;          /* bf16 [M,N]                                                    */
+    int32_t *acc_dump;      /* optional int32 [M,N] raw accumulators (MODE_W8A8, ungrouped)  */
+    uint32_t *status;       /* device error word, 0 = ok                                     */
+    uint32_t m_blocks, n_blocks, tiles, band;
+};
+
+template <int MODE, int BN, int MT, bool GROUPED>
+struct GemmConfig {
+    static constexpr int BM = 128 * MT;
+    static constexpr int ROW_BYTES = 128;
+    static constexpr int BKE = MODE == MODE_W8A8 ? 128 : 64;   /* K elements per k-block */
+    static constexpr int A_BYTES = BM * ROW_BYTES;
+    static constexpr int B_BYTES = BN * ROW_BYTES;              /* MMA operand tile        */
+    static constexpr int RAW_BYTES = MODE == MODE_W8A16 ? BN * 64 : 0;
+    static constexpr int STAGE_BYTES = A_BYTES + (MODE == MODE_W8A16 ? RAW_BYTES : B_BYTES);
+    static constexpr int CONV_BUFFERS = MODE == MODE_W8A16 ? 2 : 0;
+    static constexpr int SMEM_BUDGET = 227 * 1024 - 2048;
+    static constexpr int STAGES_FIT = (SMEM_BUDGET - CONV_BUFFERS * B_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_FIT > 6 ? 6 : STAGES_FIT;
+    static constexpr int ACC_COLS = BN * MT;
+    static constexpr int ACC_BUFFERS = 512 / ACC_COLS >= 2 ? 2 : 1;
+    static constexpr int DEQUANT_WARPS = MODE == MODE_W8A16 ? 8 : 0;
+    static constexpr int WARPS = 6 + DEQUANT_WARPS;
+    static constexpr int THREADS = WARPS * 32;
+    static constexpr int BARRIERS = 2 * STAGES + 2 * CONV_BUFFERS + 2 * ACC_BUFFERS;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CONV_BUFFERS * B_BYTES + 1024 /* align */ + 256;
+    static constexpr uint32_t IDESC = MODE == MODE_W8A8 ? umma_idesc(2, 1, 128, BN) : umma_idesc(1, 1, 128, BN);
+    static_assert(STAGES >= 2, "pipeline needs at least two stages");
+    static_assert(ACC_COLS <= 512, "accumulator exceeds TMEM");
+    static_assert(!GROUPED || (MODE == MODE_W8A8 && BN == 128 && MT == 1), "grouped epilogue shape");
+};
+
+struct PipeState {
+    uint32_t index = 0, phase = 0;
+    __device__ __forceinline__ void advance(uint32_t count) {
+        if (++index == count) { index = 0; phase ^= 1; }
+    }
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long start = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int spin = 0; spin < 128; spin++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+
+/* Tile order: bands of `band` row blocks; inside a band the row block varies
+ * fastest, so the CTAs running at one time share a few weight column blocks
+ * and a few activation row blocks in L2. */
+__device__ __forceinline__ void tile_coordinates(const GemmParams &p, uint32_t tile, uint32_t &mb, uint32_t &nb) {
+    uint32_t per_band = p.band * p.n_blocks;
+    uint32_t b = tile / per_band, within = tile - b * per_band;
+    uint32_t first = b * p.band;
+    uint32_t height = p.m_blocks - first < p.band ? p.m_blocks - first : p.band;
+    nb = within / height;
+    mb = first + (within - nb * height);
+}
+
+/* int8 x4 -> four fp32 holding float(q)*scale, exactly as fp32 multiply rounds it.
+ * (q ^ 0x80) placed in the low mantissa byte of 2^23 gives 2^23 + q + 128. */
+__device__ __forceinline__ void dequant4(uint32_t packed, float scale, float (&f)[4]) {
+    uint32_t biased = packed ^ 0x80808080u;
+    f[0] = __fmul_rn(__fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7650)), 8388736.0f), scale);
+    f[1] = __fmul_rn(__fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7651)), 8388736.0f), scale);
+    f[2] = __fmul_rn(__fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7652)), 8388736.0f), scale);
+    f[3] = __fmul_rn(__fsub_rn(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7653)), 8388736.0f), scale);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+template <int MODE, int BN, int MT, bool GROUPED>
+__global__ void __launch_bounds__(GemmConfig<MODE, BN, MT, GROUPED>::THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmParams p) {
+    using C = GemmConfig<MODE, BN, MT, GROUPED>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *stages = smem;
+    uint8_t *conv = stages + C::STAGES * C::STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(conv + C::CONV_BUFFERS * C::B_BYTES);
+    uint64_t *full = bars, *empty = full + C::STAGES;
+    uint64_t *bfull = empty + C::STAGES, *bempty = bfull + C::CONV_BUFFERS;
+    uint64_t *tfull = bempty + C::CONV_BUFFERS, *tempty = tfull + C::ACC_BUFFERS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + C::ACC_BUFFERS);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t num_kb = (p.K + C::BKE - 1) / C::BKE;
+    /* k-blocks accumulated before the accumulator is handed to the epilogue */
+    const uint32_t kb_per_chunk = GROUPED ? p.scale_group / C::BKE : num_kb;
+    const uint32_t chunks = GROUPED ? (num_kb + kb_per_chunk - 1) / kb_per_chunk : 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], C::DEQUANT_WARPS); mbar_init(&bempty[s], 1); }
+        for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 4); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == 4 && lane == 0) { tma_prefetch_descriptor(&map_a); tma_prefetch_descriptor(&map_b); }
+    if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    uint32_t failure = STATUS_OK;
+
+    if (warp == 4) {
+        /* ------------------------------------------------ TMA producer */
+        if (lane == 0) {
+            PipeState st;
+            for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
+                uint32_t mb, nb;
+                tile_coordinates(p, tile, mb, nb);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!wait_or_abort(&empty[st.index], st.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
+                    uint8_t *stage = stages + st.index * C::STAGE_BYTES;
+                    mbar_arrive_expect_tx(&full[st.index], C::STAGE_BYTES);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++)
+                        tma_load_2d(stage + mt * 128 * C::ROW_BYTES, &map_a, &full[st.index],
+                                    (int32_t)(kb * C::BKE), (int32_t)(mb * C::BM + mt * 128));
+                    tma_load_2d(stage + C::A_BYTES, &map_b, &full[st.index], (int32_t)(kb * C::BKE), (int32_t)(nb * BN));
+                    st.advance(C::STAGES);
+                }
+            }
+        }
+    } else if (warp == 5) {
+        /* -------------------------------------------------- MMA issuer */
+        if (lane == 0) {
+            PipeState st, cv, acc;
+            for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
+                uint32_t kb = 0;
+                for (uint32_t chunk = 0; chunk < chunks && !failure; chunk++) {
+                    if (!wait_or_abort(&tempty[acc.index], acc.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                    tc_fence_after_sync();
+                    uint32_t last = kb + kb_per_chunk < num_kb ? kb + kb_per_chunk : num_kb;
+                    uint32_t accumulate = 0;
+                    for (; kb < last; kb++) {
+                        if (!wait_or_abort(&full[st.index], st.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                        uint8_t *stage = stages + st.index * C::STAGE_BYTES;
+                        uint8_t *b_tile = stage + C::A_BYTES;
+                        if (MODE == MODE_W8A16) {
+                            if (!wait_or_abort(&bfull[cv.index], cv.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                            b_tile = conv + cv.index * C::B_BYTES;
+                        }
+                        tc_fence_after_sync();
+                        const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(b_tile));
+#pragma unroll
+                        for (int mt = 0; mt < MT; mt++) {
+                            const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(stage + mt * 128 * C::ROW_BYTES));
+                            const uint32_t d = tmem_base + acc.index * C::ACC_COLS + mt * BN;
+#pragma unroll
+                            for (int k4 = 0; k4 < 4; k4++) {
+                                /* 32 bytes along K per instruction: +2 in 16-byte units */
+                                if (MODE == MODE_W8A8) umma_i8(d, a_desc + 2 * k4, b_desc + 2 * k4, C::IDESC, accumulate | k4);
+                                else umma_bf16(d, a_desc + 2 * k4, b_desc + 2 * k4, C::IDESC, accumulate | k4);
+                            }
+                        }
+                        accumulate = 1;
+                        umma_commit(&empty[st.index]);
+                        st.advance(C::STAGES);
+                        if (MODE == MODE_W8A16) { umma_commit(&bempty[cv.index]); cv.advance(C::CONV_BUFFERS); }
+                    }
+                    if (failure) break;
+                    umma_commit(&tfull[acc.index]);
+                    acc.advance(C::ACC_BUFFERS);
+                }
+            }
+        }
+    } else if (warp < 4) {
+        /* ---------------------------------------------------- epilogue */
+        PipeState acc;
+        const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
+        for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
+            uint32_t mb, nb;
+            tile_coordinates(p, tile, mb, nb);
+            const uint32_t n0 = nb * BN;
+            float totals[GROUPED ? BN : 1];
+            for (uint32_t chunk = 0; chunk < chunks && !failure; chunk++) {
+                bool ready = wait_or_abort(&tfull[acc.index], acc.phase, abort_flag);
+                if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_EPILOGUE; break; }
+                tc_fence_after_sync();
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    const uint32_t row = mb * C::BM + mt * 128 + warp * 32 + lane;
+                    const bool row_ok = row < p.M;
+                    float a_scale = 1.0f;
+                    if (MODE == MODE_W8A8) a_scale = row_ok ? p.a_scales[row] : 0.0f;
+#pragma unroll(GROUPED ? BN / 32 : 1)
+                    for (int c = 0; c < BN / 32; c++) {
+                        uint32_t v[32];
+                        tmem_load_32x32(tmem_base + ((warp * 32u) << 16) + acc.index * C::ACC_COLS + mt * BN + c * 32, v);
+                        tmem_load_wait();
+                        const uint32_t col0 = n0 + c * 32;
+                        if (GROUPED) {
+#pragma unroll
+                            for (int j = 0; j < 32; j++) {
+                                uint32_t col = col0 + j;
+                                float ws = col < p.N ? p.w_scales[(size_t)col * p.scale_groups + chunk] : 0.0f;
+                                float value = __fmul_rn(__fmul_rn((float)(int32_t)v[j], a_scale), ws);
+                                totals[c * 32 + j] = chunk ? __fadd_rn(totals[c * 32 + j], value) : value;
+                            }
+                            if (chunk + 1 < chunks) continue;
+                        }
+                        if (!row_ok) continue;
+                        if (MODE == MODE_W8A8 && !GROUPED && p.acc_dump) {
+#pragma unroll
+                            for (int j8 = 0; j8 < 4; j8++)
+                                if (col0 + j8 * 8 < p.N) {
+                                    int4 *dst = reinterpret_cast<int4 *>(p.acc_dump + (size_t)row * p.N + col0 + j8 * 8);
+                                    dst[0] = make_int4(v[j8 * 8 + 0], v[j8 * 8 + 1], v[j8 * 8 + 2], v[j8 * 8 + 3]);
+                                    dst[1] = make_int4(v[j8 * 8 + 4], v[j8 * 8 + 5], v[j8 * 8 + 6], v[j8 * 8 + 7]);
+                                }
+                        }
+#pragma unroll
+                        for (int j8 = 0; j8 < 4; j8++) {
+                            const uint32_t col = col0 + j8 * 8;
+                            if (col >= p.N) continue; /* N is a multiple of 8 on this path */
+                            float lin[8];
+                            if (MODE == MODE_W8A8 && !GROUPED) {
+                                float4 s0 = *reinterpret_cast<const float4 *>(p.w_scales + col);
+                                float4 s1 = *reinterpret_cast<const float4 *>(p.w_scales + col + 4);
+                                const float ws[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                                for (int j = 0; j < 8; j++)
+                                    lin[j] = __fmul_rn(__fmul_rn((float)(int32_t)v[j8 * 8 + j], a_scale), ws[j]);
+                            } else if (GROUPED) {
+#pragma unroll
+                                for (int j = 0; j < 8; j++) lin[j] = totals[c * 32 + j8 * 8 + j];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; j++) lin[j] = __uint_as_float(v[j8 * 8 + j]);
+                            }
+                            uint32_t bias[4] = {0, 0, 0, 0}, gate[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+                            uint32_t res[4] = {0, 0, 0, 0};
+                            if (p.ep.bias) *reinterpret_cast<uint4 *>(bias) = *reinterpret_cast<const uint4 *>(p.ep.bias + col);
+                            if (p.ep.gate) *reinterpret_cast<uint4 *>(gate) = *reinterpret_cast<const uint4 *>(p.ep.gate + col);
+                            if (p.ep.residual)
+                                *reinterpret_cast<uint4 *>(res) = *reinterpret_cast<const uint4 *>(p.ep.residual + (size_t)row * p.N + col);
+                            uint32_t packed[4];
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                uint32_t lo = epilogue_value(lin[2 * j], bf16_bits_to_f32(bias[j] & 0xffffu), p.ep.bias != nullptr,
+                                                             p.ep.activation, gated, bf16_bits_to_f32(gate[j] & 0xffffu),
+                                                             bf16_bits_to_f32(res[j] & 0xffffu));
+                                uint32_t hi = epilogue_value(lin[2 * j + 1], bf16_bits_to_f32(bias[j] >> 16), p.ep.bias != nullptr,
+                                                             p.ep.activation, gated, bf16_bits_to_f32(gate[j] >> 16),
+                                                             bf16_bits_to_f32(res[j] >> 16));
+                                packed[j] = lo | (hi << 16);
+                            }
+                            *reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + col) = *reinterpret_cast<uint4 *>(packed);
+                        }
+                    }
+                }
+                /* accumulator drained: hand the TMEM buffer back to the MMA issuer */
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&tempty[acc.index]);
+                acc.advance(C::ACC_BUFFERS);
+            }
+        }
+    } else if (MODE == MODE_W8A16) {
+        /* ------------------------------------------------- dequantisers */
+        /* 256 threads convert the BN x 64 int8 tile (64-byte rows, 64-byte swizzle)
+         * into a BN x 64 bf16 tile (128-byte rows, 128-byte swizzle). */
+        constexpr int THREADS_PER_ROW = 256 / BN;           /* 1 (BN=256) or 2 (BN=128) */
+        constexpr int CHUNKS = 4 / THREADS_PER_ROW;         /* 16-byte int8 chunks per thread */
+        const uint32_t d = threadIdx.x - 6 * 32;
+        const uint32_t r = d / THREADS_PER_ROW;
+        const uint32_t chunk0 = (d % THREADS_PER_ROW) * CHUNKS;
+        const uint32_t width = p.scale_group ? p.scale_group : p.K;
+        PipeState st, cv;
+        for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
+            uint32_t mb, nb;
+            tile_coordinates(p, tile, mb, nb);
+            const uint32_t n = nb * BN + r;
+            const float *row_scales = p.w_scales + (size_t)n * p.scale_groups;
+            for (uint32_t kb = 0; kb < num_kb; kb++) {
+                const float scale = n < p.N ? row_scales[(kb * C::BKE) / width] : 0.0f;
+                bool ready = wait_or_abort(&full[st.index], st.phase, abort_flag) &&
+                             wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
+                if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_DEQUANT; break; }
+                const uint8_t *raw = stages + st.index * C::STAGE_BYTES + C::A_BYTES;
+                uint8_t *dst = conv + cv.index * C::B_BYTES;
+#pragma unroll
+                for (int c = 0; c < CHUNKS; c++) {
+                    const uint32_t chunk = chunk0 + c;
+                    const uint4 q = *reinterpret_cast<const uint4 *>(raw + r * 64 + ((chunk ^ ((r >> 1) & 3)) << 4));
+                    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+                    uint32_t o[8];
+#pragma unroll
+                    for (int w = 0; w < 4; w++) {
+                        float f[4];
+                        dequant4(words[w], scale, f);
+                        o[2 * w] = pack_bf16x2(f[0], f[1]);
+                        o[2 * w + 1] = pack_bf16x2(f[2], f[3]);
+                    }
+                    uint8_t *row_dst = dst + r * 128;
+                    *reinterpret_cast<uint4 *>(row_dst + (((2 * chunk) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    *reinterpret_cast<uint4 *>(row_dst + (((2 * chunk + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bfull[cv.index]);
+                st.advance(C::STAGES);
+                cv.advance(C::CONV_BUFFERS);
+            }
+        }
+    }
+
+    /* ---------------------------------------------------------- teardown */
+    if (failure) {
+        *abort_flag = 1;
+        atomicCAS(p.status, 0u, failure | (blockIdx.x << 8));
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        /* Give any TMA copy still in flight time to land before the CTA's shared
+         * memory is released. */
+        long long start = clock64();
+        while (clock64() - start < 2000000ll) { }
+        __syncthreads();
+    }
+    if (warp == 5) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+} /* namespace h3q8 */

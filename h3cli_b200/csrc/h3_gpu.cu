@@ -1,0 +1,777 @@
+/* The h3_gpu_* operator layer of libh3q8: opaque context and tensors, command
+ * scope, file loading, and the linear operators that dispatch on a weight's
+ * q8 descriptor -- the subset of h3cli's src/gpu.h that the DiT block's linear
+ * path uses, with the reference's conventions:
+ *   - int results: 1 ok, 0 failure; the reason is kept per context (h3_gpu_error)
+ *   - operators need an open command scope (h3_gpu_begin), enqueue on the
+ *     context's compute stream and never block; h3_gpu_submit waits and reports
+ *     deferred errors (CUDA errors, a kernel's bounded wait that ran out,
+ *     non-finite activations seen by the quantiser)
+ *   - the caller owns tensors, the context owns scratch
+ * (src/cuda/gpu_cuda.cu:128-230, 429-489, 595-666 are the behaviour followed.) */
+#include <cerrno>
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fcntl.h>
+#include <mutex>
+#include <new>
+#include <sys/stat.h>
+#include <unistd.h>
+#include <vector>
+
+#include "h3q8.h"
+#include "h3q8_internal.h"
+#include "kernels_misc.cuh"
+
+using namespace h3q8;
+
+struct h3_gpu_tensor {
+    h3_gpu *owner = nullptr;
+    void *data = nullptr;
+    size_t elements = 0, bytes = 0;
+    h3_gpu_dtype dtype = H3_GPU_F32;
+    h3_gpu_storage storage = H3_GPU_DEVICE_ONLY;
+    cudaEvent_t ready = nullptr;    /* recorded on the copy stream after an async fill   */
+    cudaEvent_t released = nullptr; /* recorded on the compute stream after the last use */
+    bool ready_recorded = false, release_recorded = false;
+    /* q8 descriptor: int8 [n,k] at offset 0, fp32 scales [n, ceil(k/group)] at scale_offset */
+    int q8 = 0;
+    uint32_t q8_n = 0, q8_k = 0, q8_group = 0;
+    size_t q8_scale_offset = 0;
+};
+struct h3_gpu_event { h3_gpu *owner = nullptr; cudaEvent_t value = nullptr; bool recorded = false; };
+
+struct h3_gpu {
+    int device = 0;
+    cudaStream_t compute = nullptr, copy = nullptr;
+    bool active = false, deferred_error = false;
+    char error[1024] = {0};
+    h3_gpu_stats stats = {};
+    int quant_mode = 0;         /* 0 off, 1 W8A16, 2 W8A8 */
+    uint32_t group = 0;
+    bool group_set = false;
+    int w8a16_scratch_rows = 0; /* rows at or above which W8A16 dequantises to scratch first; 0 = never */
+    void *arena[3] = {nullptr, nullptr, nullptr}; /* 0 int8 activations, 1 activation scales, 2 bf16 weight scratch */
+    size_t arena_bytes[3] = {0, 0, 0};
+    uint32_t *flags = nullptr;  /* [0] kernel wait status, [1] non-finite seen */
+    void *bounce[2] = {nullptr, nullptr};
+    cudaEvent_t bounce_free[2] = {nullptr, nullptr};
+    bool bounce_used[2] = {false, false};
+    uint64_t allocation_budget = 0; /* H3_CUDA_TEST_MEMORY_BUDGET: fail allocations beyond this many live bytes */
+    std::mutex mutex, copy_mutex;
+    std::vector<h3_gpu_tensor *> accessed;
+};
+
+static const size_t BOUNCE_BYTES = 16u << 20; /* src/cuda/gpu_cuda.cu:79-82 */
+
+static double now_seconds() {
+    return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+static int set_error(h3_gpu *g, const char *format, ...) {
+    if (g) {
+        va_list args;
+        va_start(args, format);
+        vsnprintf(g->error, sizeof g->error, format, args);
+        va_end(args);
+    }
+    return 0;
+}
+static int checked(h3_gpu *g, cudaError_t e, const char *what, size_t bytes = 0) {
+    if (e == cudaSuccess) return 1;
+    if (g) g->deferred_error = true;
+    return set_error(g, "CUDA %s: %s (%zu bytes, device %d)", what, cudaGetErrorString(e), bytes, g ? g->device : -1);
+}
+static int selected(h3_gpu *g) { return g && checked(g, cudaSetDevice(g->device), "select device"); }
+static int launch_ready(h3_gpu *g) {
+    return selected(g) && (g->active || set_error(g, "CUDA operation requires h3_gpu_begin"));
+}
+static size_t item_size(h3_gpu_dtype t) { return t == H3_GPU_I8 ? 1 : (t == H3_GPU_BF16 || t == H3_GPU_F16) ? 2 : 4; }
+
+static int require(h3_gpu *g, const h3_gpu_tensor *t, h3_gpu_dtype dtype, size_t elements, const char *label) {
+    if (!t) return set_error(g, "%s: tensor is missing", label);
+    if (t->owner != g) return set_error(g, "%s: tensor belongs to another context", label);
+    if (t->dtype != dtype) return set_error(g, "%s: wrong element type", label);
+    if (t->elements < elements) return set_error(g, "%s: %zu elements, need %zu", label, t->elements, elements);
+    return 1;
+}
+/* Device pointer of a tensor for use on the compute stream: waits for an
+ * asynchronous fill, and notes the tensor so its 'released' event is recorded
+ * after the launch (src/cuda/gpu_cuda.cu:223-230, 208-220). */
+static void *pointer(const h3_gpu_tensor *t) {
+    if (!t) return nullptr;
+    h3_gpu *g = t->owner;
+    if (t->ready_recorded) cudaStreamWaitEvent(g->compute, t->ready, 0);
+    g->accessed.push_back(const_cast<h3_gpu_tensor *>(t));
+    return t->data;
+}
+static int launch_status(h3_gpu *g, const char *what, unsigned dispatches) {
+    g->stats.direct_dispatches += dispatches;
+    int ok = checked(g, cudaGetLastError(), what);
+    for (h3_gpu_tensor *t : g->accessed)
+        if (t->released) {
+            if (!checked(g, cudaEventRecord(t->released, g->compute), "tensor release event")) ok = 0;
+            else t->release_recorded = true;
+        }
+    g->accessed.clear();
+    return ok && !g->deferred_error;
+}
+static int arena(h3_gpu *g, int which, size_t bytes) {
+    if (g->arena_bytes[which] >= bytes) { g->stats.native_scratch_reuses++; return 1; }
+    if (g->arena[which]) {
+        cudaStreamSynchronize(g->compute);
+        cudaFree(g->arena[which]);
+        g->stats.live_bytes -= g->arena_bytes[which];
+        g->stats.native_scratch_bytes -= g->arena_bytes[which];
+        g->arena[which] = nullptr;
+        g->arena_bytes[which] = 0;
+    }
+    if (!checked(g, cudaMalloc(&g->arena[which], bytes), "scratch allocation", bytes)) return 0;
+    g->arena_bytes[which] = bytes;
+    g->stats.native_scratch_bytes += bytes;
+    g->stats.native_scratch_allocations++;
+    g->stats.live_bytes += bytes;
+    if (g->stats.live_bytes > g->stats.peak_live_bytes) g->stats.peak_live_bytes = g->stats.live_bytes;
+    return 1;
+}
+
+/* ------------------------------------------------------------------ context */
+extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
+    auto refuse = [&](const char *why) -> h3_gpu * {
+        if (error && error_size) snprintf(error, error_size, "%s", why);
+        return nullptr;
+    };
+    int device = 0, count = 0;
+    const char *chosen = getenv("H3_CUDA_DEVICE"); /* src/cuda/cuda_probe.c:31-40 */
+    if (cudaGetDeviceCount(&count) != cudaSuccess || !count) return refuse("no CUDA device: libh3q8 has no CPU path");
+    if (chosen && *chosen) {
+        char *end = nullptr;
+        long v = strtol(chosen, &end, 10);
+        if (*end || v < 0 || v >= count) return refuse("H3_CUDA_DEVICE is not a valid device index");
+        device = (int)v;
+    }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return refuse("cannot query the CUDA device");
+    if (prop.major != 10) return refuse("libh3q8 is built for sm_100a (B200) only");
+    h3_gpu *g = new (std::nothrow) h3_gpu;
+    if (!g) return refuse("out of host memory");
+    g->device = device;
+    const char *budget = getenv("H3_CUDA_TEST_MEMORY_BUDGET"); /* src/weights/residency.c:31-32 */
+    if (budget && *budget) g->allocation_budget = strtoull(budget, nullptr, 10);
+    const char *policy = getenv("H3Q8_W8A16_SCRATCH_ROWS");
+    g->w8a16_scratch_rows = policy && *policy ? atoi(policy) : 0;
+    bool ok = cudaSetDevice(device) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&g->compute, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&g->copy, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaMalloc(&g->flags, 2 * sizeof(uint32_t)) == cudaSuccess &&
+              cudaMemset(g->flags, 0, 2 * sizeof(uint32_t)) == cudaSuccess;
+    if (!ok) {
+        snprintf(error ? error : g->error, error ? error_size : sizeof g->error, "CUDA context setup failed: %s",
+                 cudaGetErrorString(cudaGetLastError()));
+        h3_gpu_free(g);
+        return nullptr;
+    }
+    return g;
+}
+
+extern "C" void h3_gpu_cancel(h3_gpu *g) {
+    if (!g) return;
+    cudaSetDevice(g->device);
+    cudaStreamSynchronize(g->compute);
+    cudaStreamSynchronize(g->copy);
+    cudaGetLastError();
+    if (g->flags) cudaMemset(g->flags, 0, 2 * sizeof(uint32_t));
+    g->accessed.clear();
+    g->active = false;
+    g->deferred_error = false;
+}
+
+extern "C" void h3_gpu_free(h3_gpu *g) {
+    if (!g) return;
+    h3_gpu_cancel(g);
+    for (int i = 0; i < 3; i++) if (g->arena[i]) cudaFree(g->arena[i]);
+    for (int i = 0; i < 2; i++) {
+        if (g->bounce[i]) cudaFreeHost(g->bounce[i]);
+        if (g->bounce_free[i]) cudaEventDestroy(g->bounce_free[i]);
+    }
+    if (g->flags) cudaFree(g->flags);
+    if (g->compute) cudaStreamDestroy(g->compute);
+    if (g->copy) cudaStreamDestroy(g->copy);
+    delete g;
+}
+
+extern "C" const char *h3_gpu_error(const h3_gpu *g) { return g ? g->error : "no GPU context"; }
+extern "C" int h3_gpu_get_stats(const h3_gpu *g, h3_gpu_stats *stats) {
+    if (!g || !stats) return 0;
+    *stats = g->stats;
+    return 1;
+}
+extern "C" const char *h3_gpu_backend_name(const h3_gpu *) { return "cuda-b200-q8"; }
+extern "C" int h3_gpu_has_int8_mlp(const h3_gpu *g) { return g != nullptr; }
+
+/* ------------------------------------------------------------ command scope */
+extern "C" int h3_gpu_begin(h3_gpu *g) {
+    if (!selected(g)) return 0;
+    if (g->active) return set_error(g, "command scope already active");
+    if (g->deferred_error) return set_error(g, "context has a pending error; call h3_gpu_cancel");
+    g->active = true;
+    return 1;
+}
+extern "C" int h3_gpu_continue(h3_gpu *g) {
+    return launch_ready(g) && !g->deferred_error;
+}
+static int drain(h3_gpu *g) {
+    if (!checked(g, cudaStreamSynchronize(g->compute), "synchronize")) return 0;
+    uint32_t flags[2] = {0, 0};
+    if (!checked(g, cudaMemcpy(flags, g->flags, sizeof flags, cudaMemcpyDeviceToHost), "read device flags")) return 0;
+    uint32_t shared_status = h3q8_device_status(g->compute);
+    if (flags[0] || flags[1] || shared_status) {
+        cudaMemset(g->flags, 0, sizeof flags);
+        g->deferred_error = true;
+        if (flags[1]) return set_error(g, "non-finite activation reached the int8 quantiser");
+        uint32_t code = flags[0] ? flags[0] : shared_status;
+        return set_error(g, "a linear kernel gave up a bounded wait (code %u, CTA %u)", code & 0xffu, code >> 8);
+    }
+    return 1;
+}
+extern "C" int h3_gpu_submit(h3_gpu *g) {
+    if (!launch_ready(g)) return 0;
+    g->active = false;
+    g->stats.submissions++;
+    int ok = drain(g);
+    return ok && !g->deferred_error;
+}
+extern "C" int h3_gpu_synchronize(h3_gpu *g) {
+    if (!selected(g)) return 0;
+    return checked(g, cudaStreamSynchronize(g->compute), "synchronize") &&
+           checked(g, cudaStreamSynchronize(g->copy), "synchronize copy stream");
+}
+
+/* ------------------------------------------------------------------ tensors */
+extern "C" h3_gpu_tensor *h3_gpu_tensor_alloc(h3_gpu *g, size_t elements, h3_gpu_dtype dtype, h3_gpu_storage storage) {
+    if (!selected(g) || !elements) { set_error(g, "tensor allocation: no elements"); return nullptr; }
+    size_t bytes = elements * item_size(dtype);
+    std::lock_guard<std::mutex> lock(g->mutex);
+    if (g->allocation_budget && g->stats.live_bytes + bytes > g->allocation_budget) {
+        set_error(g, "CUDA allocation: out of memory (test budget %llu, live %llu, requested %zu)",
+                  (unsigned long long)g->allocation_budget, (unsigned long long)g->stats.live_bytes, bytes);
+        return nullptr;
+    }
+    h3_gpu_tensor *t = new (std::nothrow) h3_gpu_tensor;
+    if (!t) return nullptr;
+    cudaError_t e = storage == H3_GPU_DEVICE_ONLY ? cudaMalloc(&t->data, bytes)
+                  : storage == H3_GPU_HOST_PINNED ? cudaMallocHost(&t->data, bytes)
+                                                  : cudaMallocManaged(&t->data, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        set_error(g, "CUDA allocation: %s; requested %zu bytes", cudaGetErrorString(e), bytes);
+        delete t;
+        return nullptr;
+    }
+    t->owner = g; t->elements = elements; t->bytes = bytes; t->dtype = dtype; t->storage = storage;
+    cudaEventCreateWithFlags(&t->ready, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&t->released, cudaEventDisableTiming);
+    g->stats.tensor_allocations++;
+    g->stats.allocated_bytes += bytes;
+    g->stats.live_bytes += bytes;
+    if (storage == H3_GPU_HOST_PINNED) g->stats.pinned_bytes += bytes;
+    if (g->stats.live_bytes > g->stats.peak_live_bytes) g->stats.peak_live_bytes = g->stats.live_bytes;
+    return t;
+}
+extern "C" void h3_gpu_tensor_free(h3_gpu_tensor *t) {
+    if (!t) return;
+    h3_gpu *g = t->owner;
+    cudaSetDevice(g->device);
+    { /* work in flight may still use it: cudaFree waits, host memory needs an explicit wait */
+        std::lock_guard<std::mutex> lock(g->mutex);
+        for (auto it = g->accessed.begin(); it != g->accessed.end();) it = *it == t ? g->accessed.erase(it) : it + 1;
+        if (t->storage == H3_GPU_HOST_PINNED) { cudaStreamSynchronize(g->compute); cudaStreamSynchronize(g->copy); cudaFreeHost(t->data); }
+        else { if (t->ready_recorded) cudaEventSynchronize(t->ready); cudaFree(t->data); }
+        g->stats.live_bytes -= t->bytes;
+        if (t->storage == H3_GPU_HOST_PINNED) g->stats.pinned_bytes -= t->bytes;
+    }
+    if (t->ready) cudaEventDestroy(t->ready);
+    if (t->released) cudaEventDestroy(t->released);
+    delete t;
+}
+extern "C" void *h3_gpu_tensor_contents(h3_gpu_tensor *t) {
+    if (!t || t->storage == H3_GPU_DEVICE_ONLY) return nullptr;
+    cudaSetDevice(t->owner->device);
+    cudaStreamSynchronize(t->owner->compute);
+    cudaStreamSynchronize(t->owner->copy);
+    return t->data;
+}
+extern "C" size_t h3_gpu_tensor_elements(const h3_gpu_tensor *t) { return t ? t->elements : 0; }
+extern "C" h3_gpu_dtype h3_gpu_tensor_dtype(const h3_gpu_tensor *t) { return t ? t->dtype : H3_GPU_F32; }
+extern "C" h3_gpu_tensor *h3_gpu_tensor_new_f32(h3_gpu *g, size_t n) { return h3_gpu_tensor_alloc(g, n, H3_GPU_F32, H3_GPU_DEVICE_ONLY); }
+extern "C" h3_gpu_tensor *h3_gpu_tensor_new_bf16(h3_gpu *g, size_t n) { return h3_gpu_tensor_alloc(g, n, H3_GPU_BF16, H3_GPU_DEVICE_ONLY); }
+extern "C" h3_gpu_tensor *h3_gpu_tensor_new_i8(h3_gpu *g, size_t n) { return h3_gpu_tensor_alloc(g, n, H3_GPU_I8, H3_GPU_DEVICE_ONLY); }
+
+/* Host <-> device copies order themselves after everything already enqueued on
+ * the compute stream and return when the bytes have moved. */
+static int upload(h3_gpu_tensor *t, size_t offset_bytes, const void *values, size_t bytes) {
+    h3_gpu *g = t->owner;
+    if (!selected(g)) return 0;
+    if (offset_bytes > t->bytes || bytes > t->bytes - offset_bytes) return set_error(g, "tensor write out of range");
+    if (!checked(g, cudaMemcpyAsync((char *)t->data + offset_bytes, values, bytes, cudaMemcpyDefault, g->compute), "host to device copy", bytes) ||
+        !checked(g, cudaStreamSynchronize(g->compute), "host to device copy wait")) return 0;
+    g->stats.h2d_bytes += bytes;
+    return 1;
+}
+static int download(const h3_gpu_tensor *t, void *values, size_t bytes) {
+    h3_gpu *g = t->owner;
+    if (!selected(g)) return 0;
+    if (bytes > t->bytes) return set_error(g, "tensor read out of range");
+    if (t->ready_recorded) cudaStreamWaitEvent(g->compute, t->ready, 0);
+    if (!checked(g, cudaMemcpyAsync(values, t->data, bytes, cudaMemcpyDefault, g->compute), "device to host copy", bytes) ||
+        !checked(g, cudaStreamSynchronize(g->compute), "device to host copy wait")) return 0;
+    g->stats.d2h_bytes += bytes;
+    return 1;
+}
+static h3_gpu_tensor *from_host(h3_gpu *g, const void *values, size_t elements, h3_gpu_dtype dtype) {
+    if (!values) { set_error(g, "tensor upload: no source"); return nullptr; }
+    h3_gpu_tensor *t = h3_gpu_tensor_alloc(g, elements, dtype, H3_GPU_DEVICE_ONLY);
+    if (t && !upload(t, 0, values, t->bytes)) { h3_gpu_tensor_free(t); t = nullptr; }
+    return t;
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_f32(h3_gpu *g, const float *v, size_t n) { return from_host(g, v, n, H3_GPU_F32); }
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_bf16(h3_gpu *g, const uint16_t *v, size_t n) { return from_host(g, v, n, H3_GPU_BF16); }
+extern "C" h3_gpu_tensor *h3_gpu_tensor_from_u32(h3_gpu *g, const uint32_t *v, size_t n) { return from_host(g, v, n, H3_GPU_U32); }
+#define TYPED_IO(name, ctype, dt)                                                                              \
+    extern "C" int h3_gpu_tensor_read_##name(const h3_gpu_tensor *t, ctype *values, size_t elements) {        \
+        if (!t || !values) return 0;                                                                           \
+        if (t->dtype != dt) return set_error(t->owner, "tensor read: wrong element type");                     \
+        return download(t, values, elements * sizeof(ctype));                                                  \
+    }                                                                                                          \
+    extern "C" int h3_gpu_tensor_write_##name(h3_gpu_tensor *t, const ctype *values, size_t elements) {       \
+        if (!t || !values) return 0;                                                                           \
+        if (t->dtype != dt) return set_error(t->owner, "tensor write: wrong element type");                    \
+        return upload(t, 0, values, elements * sizeof(ctype));                                                 \
+    }
+TYPED_IO(f32, float, H3_GPU_F32)
+TYPED_IO(bf16, uint16_t, H3_GPU_BF16)
+TYPED_IO(i8, int8_t, H3_GPU_I8)
+extern "C" int h3_gpu_tensor_read_u32(const h3_gpu_tensor *t, uint32_t *values, size_t elements) {
+    if (!t || !values) return 0;
+    if (t->dtype != H3_GPU_U32) return set_error(t->owner, "tensor read: wrong element type");
+    return download(t, values, elements * 4);
+}
+extern "C" int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *t, size_t offset, const uint16_t *values, size_t elements) {
+    if (!t || !values) return 0;
+    if (t->dtype != H3_GPU_BF16) return set_error(t->owner, "tensor write: wrong element type");
+    return upload(t, offset * 2, values, elements * 2);
+}
+
+extern "C" h3_gpu_event *h3_gpu_event_new(h3_gpu *g) {
+    if (!selected(g)) return nullptr;
+    h3_gpu_event *e = new (std::nothrow) h3_gpu_event;
+    if (e && cudaEventCreateWithFlags(&e->value, cudaEventDisableTiming) != cudaSuccess) { delete e; e = nullptr; }
+    if (e) e->owner = g;
+    return e;
+}
+extern "C" int h3_gpu_event_record(h3_gpu *g, h3_gpu_event *e) {
+    if (!selected(g) || !e || e->owner != g) return 0;
+    e->recorded = true;
+    return checked(g, cudaEventRecord(e->value, g->compute), "event record");
+}
+extern "C" int h3_gpu_event_wait(h3_gpu *g, h3_gpu_event *e) {
+    if (!selected(g) || !e || !e->recorded) return 0;
+    return checked(g, cudaStreamWaitEvent(g->compute, e->value, 0), "event wait");
+}
+extern "C" void h3_gpu_event_free(h3_gpu_event *e) {
+    if (!e) return;
+    cudaEventDestroy(e->value);
+    delete e;
+}
+
+/* ---------------------------------------------------------------- file I/O */
+/* pread -> pinned bounce buffer -> cudaMemcpyAsync on the copy stream, two
+ * bounce buffers in rotation, each guarded by a reuse event.  Safe to call from
+ * an I/O thread while the owner thread enqueues compute: only the copy stream
+ * and the copy mutex are touched (src/cuda/gpu_cuda.cu:761-841). */
+static int file_into(h3_gpu_tensor *t, size_t dst_offset, const char *path, uint64_t file_offset, size_t bytes,
+                     char *error, size_t error_size) {
+    h3_gpu *g = t->owner;
+    auto refuse = [&](const char *format, ...) {
+        char text[512];
+        va_list args;
+        va_start(args, format);
+        vsnprintf(text, sizeof text, format, args);
+        va_end(args);
+        if (error && error_size) snprintf(error, error_size, "%s", text);
+        set_error(g, "%s", text);
+        return 0;
+    };
+    if (dst_offset > t->bytes || bytes > t->bytes - dst_offset) return refuse("file read exceeds the tensor");
+    std::lock_guard<std::mutex> lock(g->copy_mutex);
+    if (cudaSetDevice(g->device) != cudaSuccess) return refuse("cannot select the CUDA device");
+    int fd = open(path, O_RDONLY);
+    if (fd < 0) return refuse("cannot open %s: %s", path, strerror(errno));
+    /* a slot that compute may still be reading must not be overwritten */
+    if (t->release_recorded) cudaStreamWaitEvent(g->copy, t->released, 0);
+    double start = now_seconds();
+    size_t done = 0;
+    int slot = 0, ok = 1;
+    while (ok && done < bytes) {
+        if (!g->bounce[slot]) {
+            if (cudaMallocHost(&g->bounce[slot], BOUNCE_BYTES) != cudaSuccess ||
+                cudaEventCreateWithFlags(&g->bounce_free[slot], cudaEventDisableTiming) != cudaSuccess) {
+                ok = refuse("cannot allocate a pinned staging buffer");
+                break;
+            }
+            g->stats.pinned_bytes += BOUNCE_BYTES;
+        }
+        if (g->bounce_used[slot]) cudaEventSynchronize(g->bounce_free[slot]);
+        size_t chunk = bytes - done < BOUNCE_BYTES ? bytes - done : BOUNCE_BYTES, got = 0;
+        while (got < chunk) {
+            ssize_t r = pread(fd, (char *)g->bounce[slot] + got, chunk - got, (off_t)(file_offset + done + got));
+            if (r < 0 && errno == EINTR) continue;
+            if (r <= 0) { ok = refuse("short read from %s at offset %llu", path, (unsigned long long)(file_offset + done + got)); break; }
+            got += (size_t)r;
+        }
+        if (!ok) break;
+        if (cudaMemcpyAsync((char *)t->data + dst_offset + done, g->bounce[slot], chunk, cudaMemcpyDefault, g->copy) != cudaSuccess ||
+            cudaEventRecord(g->bounce_free[slot], g->copy) != cudaSuccess) {
+            ok = refuse("CUDA copy from the staging buffer failed: %s", cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        g->bounce_used[slot] = true;
+        done += chunk;
+        slot ^= 1;
+    }
+    close(fd);
+    if (ok) {
+        cudaEventRecord(t->ready, g->copy);
+        t->ready_recorded = true;
+        g->stats.h2d_bytes += bytes;
+        g->stats.streamed_bytes += bytes;
+        g->stats.stream_wait_seconds += now_seconds() - start;
+    }
+    return ok;
+}
+extern "C" int h3_gpu_tensor_read_file_bf16(h3_gpu_tensor *t, const char *path, uint64_t offset, size_t elements,
+                                            char *error, size_t error_size) {
+    if (!t || !path || t->dtype != H3_GPU_BF16) return 0;
+    return file_into(t, 0, path, offset, elements * 2, error, error_size);
+}
+extern "C" int h3_gpu_tensor_stream_file_bf16(h3_gpu_tensor *t, const char *path, uint64_t offset, size_t elements,
+                                              char *error, size_t error_size) {
+    return h3_gpu_tensor_read_file_bf16(t, path, offset, elements, error, error_size);
+}
+extern "C" h3_gpu_tensor *h3_gpu_tensor_load_bf16(h3_gpu *g, const char *path, uint64_t offset, size_t elements) {
+    h3_gpu_tensor *t = h3_gpu_tensor_new_bf16(g, elements);
+    if (t && !file_into(t, 0, path, offset, elements * 2, nullptr, 0)) { h3_gpu_tensor_free(t); t = nullptr; }
+    return t;
+}
+
+/* ---------------------------------------------------------------- planning */
+/* 0 resident, 1 streamed (two layer slots), -1 not even that.  The reserve is
+ * max(1 GiB, total/10) as in src/cuda/gpu_cuda.cu:548-568. */
+extern "C" int h3_gpu_plan_weights(h3_gpu *g, uint64_t weights, uint64_t activations) {
+    if (!selected(g)) return -1;
+    size_t free_bytes = 0, total = 0;
+    if (!checked(g, cudaMemGetInfo(&free_bytes, &total), "memory query")) return -1;
+    if (g->allocation_budget) {
+        uint64_t left = g->allocation_budget > g->stats.live_bytes ? g->allocation_budget - g->stats.live_bytes : 0;
+        if (left < free_bytes) free_bytes = left;
+    }
+    uint64_t reserve = total / 10 > (1ull << 30) ? total / 10 : (1ull << 30);
+    if (g->allocation_budget) reserve = 0;
+    uint64_t fixed = activations + reserve;
+    if (free_bytes >= fixed && weights <= free_bytes - fixed) return 0;
+    if (free_bytes >= fixed) return 1;
+    set_error(g, "insufficient CUDA capacity for activations plus reserve");
+    return -1;
+}
+extern "C" int h3_gpu_release_weight_cache(h3_gpu *g) { return g != nullptr; }
+
+/* -------------------------------------------------------- quantised weights */
+extern "C" int h3q8_gpu_set_group(h3_gpu *g, uint32_t group) {
+    if (!g) return 0;
+    if (group && group % 16) return set_error(g, "scale group must be 0 (per channel) or a multiple of 16");
+    g->group = group;
+    g->group_set = true;
+    return 1;
+}
+extern "C" void *h3q8_gpu_tensor_device_pointer(const h3_gpu_tensor *t) { return t ? t->data : nullptr; }
+extern "C" void *h3q8_gpu_compute_stream(h3_gpu *g) { return g ? (void *)g->compute : nullptr; }
+extern "C" int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *g, uint32_t rows) {
+    if (!g) return 0;
+    g->w8a16_scratch_rows = (int)rows;
+    return 1;
+}
+extern "C" int h3_gpu_quant_configure(h3_gpu *g, int mode, const char *, uint64_t weights, uint64_t activations, int force_stream) {
+    if (!g) return 0;
+    if (mode < 0 || mode > 2) return set_error(g, "quantisation mode must be 0 (off), 1 (W8A16) or 2 (W8A8)");
+    if (!mode) return 1;
+    if (g->quant_mode) return set_error(g, "quantized GPU context already configured");
+    if (weights || activations) {
+        int plan = h3_gpu_plan_weights(g, weights / 2, activations);
+        if (plan < 0) return 0;
+        (void)force_stream;
+    }
+    if (!g->group_set) {
+        const char *env = getenv("H3Q8_GROUP");
+        g->group = env && *env ? (uint32_t)strtoul(env, nullptr, 10) : 0;
+    }
+    g->quant_mode = mode;
+    return 1;
+}
+
+static h3_gpu_tensor *q8_blob(h3_gpu *g, uint32_t rows, uint32_t columns, uint32_t group) {
+    size_t offset, bytes;
+    if (!h3q8_q8_layout(rows, columns, group, &offset, &bytes)) {
+        set_error(g, "q8 weight %ux%u: invalid or too large shape", rows, columns);
+        return nullptr;
+    }
+    /* scales start on a 16-byte boundary so kernels can fetch them as vectors */
+    size_t aligned = (offset + 15) & ~(size_t)15;
+    h3_gpu_tensor *t = h3_gpu_tensor_alloc(g, aligned + (bytes - offset), H3_GPU_I8, H3_GPU_DEVICE_ONLY);
+    if (!t) return nullptr;
+    t->elements = (size_t)rows * columns;
+    t->q8 = 1; t->q8_n = rows; t->q8_k = columns; t->q8_group = group; t->q8_scale_offset = aligned;
+    return t;
+}
+
+static h3_gpu_tensor *q8_load_file(h3_gpu *g, const char *path, uint64_t offset, uint32_t rows, uint32_t columns, uint32_t group) {
+    if (!selected(g) || !path) return nullptr;
+    if (offset & 1) { set_error(g, "q8 load: bf16 payload offset must be even"); return nullptr; }
+    double start = now_seconds();
+    h3_gpu_tensor *t = q8_blob(g, rows, columns, group);
+    if (!t) return nullptr;
+    /* Bounded staging: bf16 rows pass through a device buffer of at most 32 MiB
+     * (src/metal/q8_host.inc:3-51 bounds its staging the same way). */
+    size_t row_bytes = (size_t)columns * 2;
+    uint32_t chunk_rows = (uint32_t)((32u << 20) / row_bytes);
+    if (!chunk_rows) chunk_rows = 1;
+    if (chunk_rows > rows) chunk_rows = rows;
+    h3_gpu_tensor *staging = h3_gpu_tensor_new_bf16(g, (size_t)chunk_rows * columns);
+    const uint32_t width = group ? group : columns;
+    const uint32_t groups = (uint32_t)(((uint64_t)columns + width - 1) / width);
+    int ok = staging != nullptr;
+    cudaMemsetAsync(t->data, 0, t->bytes, g->compute);
+    for (uint32_t r = 0; ok && r < rows; r += chunk_rows) {
+        uint32_t n = rows - r < chunk_rows ? rows - r : chunk_rows;
+        /* the previous chunk's pack kernel must be done with the staging buffer */
+        cudaEventRecord(staging->released, g->compute);
+        staging->release_recorded = true;
+        ok = file_into(staging, 0, path, offset + (uint64_t)r * row_bytes, (size_t)n * row_bytes, nullptr, 0);
+        if (!ok) break;
+        cudaStreamWaitEvent(g->compute, staging->ready, 0);
+        const uint64_t items = (uint64_t)n * groups;
+        q8_pack_rows_kernel<<<(unsigned)((items + 7) / 8), 256, 0, g->compute>>>(
+            (const uint16_t *)staging->data, (int8_t *)t->data + (size_t)r * columns,
+            (float *)((char *)t->data + t->q8_scale_offset) + (size_t)r * groups, n, columns, width, groups, g->flags + 1);
+        count_launch(1);
+        ok = checked(g, cudaGetLastError(), "q8 pack launch");
+    }
+    uint32_t nonfinite = 0;
+    if (ok) ok = checked(g, cudaStreamSynchronize(g->compute), "q8 pack wait") &&
+                 checked(g, cudaMemcpy(&nonfinite, g->flags + 1, 4, cudaMemcpyDeviceToHost), "q8 pack flag");
+    if (ok && nonfinite) {
+        cudaMemset(g->flags + 1, 0, 4);
+        ok = set_error(g, "q8 load: non-finite weight in %s", path);
+    }
+    h3_gpu_tensor_free(staging);
+    if (!ok) { h3_gpu_tensor_free(t); return nullptr; }
+    g->stats.q8_weights++;
+    g->stats.q8_source_bytes += (uint64_t)rows * row_bytes;
+    g->stats.q8_storage_bytes += t->bytes;
+    g->stats.q8_load_seconds += now_seconds() - start;
+    g->stats.quant_conversion_seconds += now_seconds() - start;
+    return t;
+}
+extern "C" h3_gpu_tensor *h3_gpu_q8_load(h3_gpu *g, const char *path, uint64_t offset, uint32_t rows, uint32_t columns) {
+    return q8_load_file(g, path, offset, rows, columns, g && g->group_set ? g->group : H3_Q8_GROUP);
+}
+extern "C" h3_gpu_tensor *h3_gpu_quant_load(h3_gpu *g, const char *path, uint64_t offset, uint32_t rows, uint32_t columns) {
+    if (!g) return nullptr;
+    if (!g->quant_mode || !rows || !columns || rows % 128 || columns % 128 || (uint64_t)rows * columns > UINT32_MAX) {
+        set_error(g, "quantized weight shape must be nonzero and a multiple of 128"); /* src/cuda/cuda_quant.cuh:293-295 */
+        return nullptr;
+    }
+    h3_gpu_tensor *t = q8_load_file(g, path, offset, rows, columns, g->group);
+    if (t) g->stats.quant_cache_misses++;
+    return t;
+}
+extern "C" h3_gpu_tensor *h3q8_gpu_q8_from_host(h3_gpu *g, const int8_t *weights, const float *scales,
+                                                uint32_t rows, uint32_t columns, uint32_t group) {
+    if (!selected(g) || !weights || !scales) return nullptr;
+    h3_gpu_tensor *t = q8_blob(g, rows, columns, group);
+    if (!t) return nullptr;
+    const uint32_t width = group ? group : columns;
+    const size_t groups = ((size_t)columns + width - 1) / width;
+    if (!upload(t, 0, weights, (size_t)rows * columns) ||
+        !upload(t, t->q8_scale_offset, scales, (size_t)rows * groups * sizeof(float))) { h3_gpu_tensor_free(t); return nullptr; }
+    g->stats.q8_weights++;
+    g->stats.q8_storage_bytes += t->bytes;
+    return t;
+}
+
+/* ------------------------------------------------------------------ linears */
+static int linear_dispatch(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *in, const h3_gpu_tensor *w,
+                           const h3_gpu_tensor *bias, const h3_gpu_tensor *gate, const h3_gpu_tensor *residual,
+                           uint32_t rows, uint32_t k, uint32_t n, int activation) {
+    if (!launch_ready(g)) return 0;
+    if (!rows || !k || !n) return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
+    if (!w || w->owner != g) return set_error(g, "linear %ux%ux%u: weight is missing or foreign", rows, n, k);
+    if (!require(g, in, H3_GPU_BF16, (size_t)rows * k, "linear input") ||
+        !require(g, out, H3_GPU_BF16, (size_t)rows * n, "linear output")) return 0;
+    if (bias && !require(g, bias, H3_GPU_BF16, n, "linear bias")) return 0;
+    if (gate && !require(g, gate, H3_GPU_BF16, n, "linear gate")) return 0;
+    if (residual && !require(g, residual, H3_GPU_BF16, (size_t)rows * n, "linear residual")) return 0;
+    if (out == in || out == w) return set_error(g, "linear %ux%ux%u: output aliases an operand", rows, n, k);
+    if (activation < 0 || activation > H3Q8_ACT_GELU_TANH) return set_error(g, "linear: unknown activation %d", activation);
+    h3q8_linear_desc d = {};
+    d.rows = rows; d.input_dim = k; d.output_dim = n;
+    d.bias = bias ? (const uint16_t *)pointer(bias) : nullptr;
+    d.gate = gate ? (const uint16_t *)pointer(gate) : nullptr;
+    d.residual = residual ? (const uint16_t *)pointer(residual) : nullptr;
+    d.activation = (uint32_t)activation;
+    d.output = (uint16_t *)pointer(out);
+    d.input = pointer(in);
+    d.weight = pointer(w);
+    unsigned dispatches = 1;
+    if (w->q8) {
+        if (w->q8_n != n || w->q8_k != k) return set_error(g, "linear %ux%ux%u: q8 weight is %ux%u", rows, n, k, w->q8_n, w->q8_k);
+        d.weight_scales = (const float *)((const char *)w->data + w->q8_scale_offset);
+        d.weight_group = w->q8_group;
+        if (g->quant_mode == 2) { /* W8A8: per-token quantise into context scratch, then the int8 GEMM */
+            uint32_t padded = (rows + 127u) & ~127u;
+            if (!arena(g, 0, (size_t)padded * k) || !arena(g, 1, (size_t)padded * sizeof(float))) return 0;
+            quantize_rows_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)d.input, (int8_t *)g->arena[0], (float *)g->arena[1],
+                                                                 rows, k, 1.0f, g->flags + 1);
+            count_launch(1);
+            dispatches++;
+            d.mode = H3Q8_MODE_W8A8;
+            d.input = g->arena[0];
+            d.input_scales = (const float *)g->arena[1];
+        } else if (g->w8a16_scratch_rows && rows >= (uint32_t)g->w8a16_scratch_rows && k % 16 == 0) {
+            /* policy 0 of the reference: dequantise once, then a bf16 GEMM (src/metal/q8_host.inc:75-88) */
+            if (!arena(g, 2, (size_t)n * k * 2)) return 0;
+            if (!h3q8_q8_dequant((const int8_t *)d.weight, d.weight_scales, (uint16_t *)g->arena[2], n, k, d.weight_group, g->compute))
+                return set_error(g, "%s", h3q8_last_error());
+            dispatches++;
+            d.mode = H3Q8_MODE_BF16;
+            d.weight = g->arena[2];
+            d.weight_scales = nullptr;
+            d.weight_group = 0;
+        } else d.mode = H3Q8_MODE_W8A16;
+        g->stats.q8_dispatches++;
+        g->stats.quant_projection_dispatches++;
+    } else {
+        if (w->dtype != H3_GPU_BF16 || w->elements < (size_t)n * k) return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
+        d.mode = H3Q8_MODE_BF16;
+    }
+    if (!h3q8_linear(&d, g->compute)) { g->accessed.clear(); return set_error(g, "%s", h3q8_last_error()); }
+    g->stats.linear_dispatches++;
+    return launch_status(g, "linear", dispatches);
+}
+
+extern "C" int h3_gpu_linear_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *in, const h3_gpu_tensor *w,
+                                  const h3_gpu_tensor *bias, uint32_t rows, uint32_t k, uint32_t n) {
+    return linear_dispatch(g, out, in, w, bias, nullptr, nullptr, rows, k, n, H3Q8_ACT_NONE);
+}
+extern "C" int h3_gpu_linear_fused_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *in, const h3_gpu_tensor *w,
+                                        const h3_gpu_tensor *bias, const h3_gpu_tensor *gate, const h3_gpu_tensor *residual,
+                                        uint32_t rows, uint32_t k, uint32_t n, int activation) {
+    return linear_dispatch(g, out, in, w, bias, gate, residual, rows, k, n, activation);
+}
+extern "C" int h3_gpu_linear_grouped_bf16(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count) {
+    if (!g || !problems || !count) return set_error(g, "grouped linear: no problems");
+    for (uint32_t i = 0; i < count; i++) {
+        const h3_gpu_linear_problem &p = problems[i];
+        if (!linear_dispatch(g, p.output, p.input, p.weight, p.bias, p.gate, p.residual, p.rows, p.input_dim, p.output_dim, p.activation))
+            return 0;
+    }
+    return 1;
+}
+
+extern "C" int h3_gpu_quantize_weight_int8(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_tensor *scales, const h3_gpu_tensor *in,
+                                           uint32_t rows, uint32_t columns) {
+    if (!launch_ready(g)) return 0;
+    if (!rows || !columns || !require(g, in, H3_GPU_BF16, (size_t)rows * columns, "BF16 weight to quantize") ||
+        !require(g, out, H3_GPU_I8, (size_t)rows * columns, "int8 quantized output") ||
+        !require(g, scales, H3_GPU_F32, rows, "int8 quantization scales")) return 0;
+    quantize_rows_kernel<<<rows, 256, 0, g->compute>>>((const uint16_t *)pointer(in), (int8_t *)pointer(out), (float *)pointer(scales),
+                                                       rows, columns, 1.0f, g->flags + 1);
+    count_launch(1);
+    return launch_status(g, "weight quantiser", 1);
+}
+
+/* src/metal/gpu.m:3183-3249: quantise the rows (padded to 128) into the caller's
+ * scratch tensors, then the int8 GEMM with the dequantising epilogue. */
+extern "C" int h3_gpu_linear_int8_bf16(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_tensor *qin, h3_gpu_tensor *in_scales,
+                                       const h3_gpu_tensor *in, const h3_gpu_tensor *w, const h3_gpu_tensor *w_scales,
+                                       uint32_t rows, uint32_t k, uint32_t n, int) {
+    if (!launch_ready(g)) return 0;
+    uint32_t padded = (rows + 127u) & ~127u;
+    if (rows < 128 || k % 128 || n % 128) return set_error(g, "int8 linear needs rows >= 128 and K, N multiples of 128");
+    if (!require(g, w, H3_GPU_I8, (size_t)n * k, "int8 linear weight") || !require(g, w_scales, H3_GPU_F32, n, "int8 linear weight scales") ||
+        !require(g, out, H3_GPU_BF16, (size_t)rows * n, "int8 linear output") || !require(g, in, H3_GPU_BF16, (size_t)rows * k, "int8 linear input") ||
+        !require(g, qin, H3_GPU_I8, (size_t)padded * k, "int8 quantized output") ||
+        !require(g, in_scales, H3_GPU_F32, padded, "int8 quantization scales")) return 0;
+    quantize_rows_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)pointer(in), (int8_t *)pointer(qin), (float *)pointer(in_scales),
+                                                         rows, k, 1.0f, g->flags + 1);
+    count_launch(1);
+    h3q8_linear_desc d = {};
+    d.mode = H3Q8_MODE_W8A8; d.rows = rows; d.input_dim = k; d.output_dim = n;
+    d.input = qin->data; d.input_scales = (const float *)in_scales->data;
+    d.weight = pointer(w); d.weight_scales = (const float *)pointer(w_scales);
+    d.output = (uint16_t *)pointer(out);
+    if (!h3q8_linear(&d, g->compute)) { g->accessed.clear(); return set_error(g, "%s", h3q8_last_error()); }
+    g->stats.linear_dispatches++;
+    return launch_status(g, "int8 linear", 2);
+}
+
+/* ------------------------------------------- unfused epilogue operators */
+static __global__ void gelu_kernel(const uint16_t *in, uint16_t *out, uint32_t count) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = (uint16_t)f32_to_bf16_bits(gelu_tanh_f32(bf16_bits_to_f32(in[i])));
+}
+static __global__ void gate_kernel(const uint16_t *residual, const uint16_t *branch, const uint16_t *modulation, const uint32_t *row_map,
+                            uint16_t *out, uint32_t rows, uint32_t width, uint32_t slots, uint32_t gate_slot) {
+    uint32_t c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c >= width || r >= rows) return;
+    size_t base = (size_t)(row_map ? row_map[r] : 0) * slots * width;
+    float gate = bf16_bits_to_f32(modulation[base + (size_t)gate_slot * width + c]);
+    size_t i = (size_t)r * width + c;
+    out[i] = (uint16_t)f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(residual[i]), __fmul_rn(bf16_bits_to_f32(branch[i]), gate)));
+}
+static __global__ void add_kernel(const uint16_t *a, const uint16_t *b, uint16_t *out, uint32_t count) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) out[i] = (uint16_t)f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(a[i]), bf16_bits_to_f32(b[i])));
+}
+extern "C" int h3_gpu_gelu_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *in, uint32_t elements, int approximate) {
+    if (!launch_ready(g)) return 0;
+    if (!approximate) return set_error(g, "only the tanh GELU is on this path");
+    if (!elements || !require(g, in, H3_GPU_BF16, elements, "gelu input") || !require(g, out, H3_GPU_BF16, elements, "gelu output")) return 0;
+    gelu_kernel<<<(elements + 255) / 256, 256, 0, g->compute>>>((const uint16_t *)pointer(in), (uint16_t *)pointer(out), elements);
+    count_launch(1);
+    return launch_status(g, "gelu", 1);
+}
+extern "C" int h3_gpu_gate_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *residual, const h3_gpu_tensor *branch,
+                                const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
+                                uint32_t slots, uint32_t gate_slot) {
+    if (!launch_ready(g)) return 0;
+    size_t n = (size_t)rows * width;
+    if (!rows || !width || !slots || gate_slot >= slots || rows > 65535 ||
+        !require(g, residual, H3_GPU_BF16, n, "gate residual") || !require(g, branch, H3_GPU_BF16, n, "gate branch") ||
+        !require(g, out, H3_GPU_BF16, n, "gate output") || !require(g, modulation, H3_GPU_BF16, (size_t)slots * width, "gate modulation") ||
+        (row_map && !require(g, row_map, H3_GPU_U32, rows, "gate row map"))) return set_error(g, "gate: invalid arguments");
+    gate_kernel<<<dim3((width + 255) / 256, rows), 256, 0, g->compute>>>(
+        (const uint16_t *)pointer(residual), (const uint16_t *)pointer(branch), (const uint16_t *)pointer(modulation),
+        row_map ? (const uint32_t *)pointer(row_map) : nullptr, (uint16_t *)pointer(out), rows, width, slots, gate_slot);
+    count_launch(1);
+    return launch_status(g, "gate", 1);
+}
+extern "C" int h3_gpu_add_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *a, const h3_gpu_tensor *b, uint32_t elements) {
+    if (!launch_ready(g)) return 0;
+    if (!elements || !require(g, a, H3_GPU_BF16, elements, "add left") || !require(g, b, H3_GPU_BF16, elements, "add right") ||
+        !require(g, out, H3_GPU_BF16, elements, "add output")) return 0;
+    add_kernel<<<(elements + 255) / 256, 256, 0, g->compute>>>((const uint16_t *)pointer(a), (const uint16_t *)pointer(b), (uint16_t *)pointer(out), elements);
+    count_launch(1);
+    return launch_status(g, "add", 1);
+}

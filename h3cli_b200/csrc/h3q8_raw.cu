@@ -1,0 +1,270 @@
+/* Raw C entry points of libh3q8: validation, kernel selection, TMA descriptor
+ * construction and launches.  Device pointers in, work enqueued on the caller's
+ * stream, nothing allocated per call (one 4-byte status word per device is
+ * allocated on first use).  See include/h3q8.h for the contract. */
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "h3q8.h"
+#include "h3q8_internal.h"
+#include "kernels_misc.cuh"
+
+namespace h3q8 {
+
+static thread_local char last_error[512];
+static std::atomic<uint64_t> launches{0};
+
+int fail(const char *format, ...) {
+    va_list args;
+    va_start(args, format);
+    vsnprintf(last_error, sizeof last_error, format, args);
+    va_end(args);
+    return 0;
+}
+void count_launch(unsigned n) { launches.fetch_add(n, std::memory_order_relaxed); }
+
+static int cuda_ok(cudaError_t e, const char *what) {
+    return e == cudaSuccess ? 1 : fail("CUDA %s: %s", what, cudaGetErrorString(e));
+}
+
+/* ------------------------------------------------------------ per-device state */
+struct DeviceState {
+    bool ready = false;
+    int sms = 0;
+    uint32_t *status = nullptr;
+};
+static DeviceState devices[64];
+static std::mutex device_mutex;
+typedef CUresult (*encode_tiled_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static encode_tiled_fn encode_tiled = nullptr;
+
+static DeviceState *device_state() {
+    int device = 0;
+    if (!cuda_ok(cudaGetDevice(&device), "get device")) return nullptr;
+    if (device < 0 || device >= 64) { fail("device index %d out of range", device); return nullptr; }
+    std::lock_guard<std::mutex> lock(device_mutex);
+    DeviceState &d = devices[device];
+    if (d.ready) return &d;
+    cudaDeviceProp prop;
+    if (!cuda_ok(cudaGetDeviceProperties(&prop, device), "device properties")) return nullptr;
+    if (prop.major != 10) {
+        fail("libh3q8 needs an sm_100 GPU (B200); device %d is sm_%d%d", device, prop.major, prop.minor);
+        return nullptr;
+    }
+    d.sms = prop.multiProcessorCount;
+    if (!cuda_ok(cudaMalloc(&d.status, sizeof(uint32_t)), "status word") ||
+        !cuda_ok(cudaMemset(d.status, 0, sizeof(uint32_t)), "status word clear")) return nullptr;
+    if (!encode_tiled) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (!cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &result), "driver entry point") ||
+            result != cudaDriverEntryPointSuccess || !fn) {
+            fail("cuTensorMapEncodeTiled is not available from this driver");
+            return nullptr;
+        }
+        encode_tiled = (encode_tiled_fn)fn;
+    }
+    d.ready = true;
+    return &d;
+}
+
+uint32_t *device_status_word() {
+    DeviceState *d = device_state();
+    return d ? d->status : nullptr;
+}
+
+/* 2-D row-major [rows, columns] tensor, box = [box_rows, box_bytes worth of columns] */
+static int make_map(CUtensorMap *map, const void *base, uint32_t element_bytes, uint64_t rows, uint64_t columns,
+                    uint32_t box_columns, uint32_t box_rows, CUtensorMapSwizzle swizzle) {
+    cuuint64_t dims[2] = {columns, rows};
+    cuuint64_t strides[1] = {columns * element_bytes};
+    cuuint32_t box[2] = {box_columns, box_rows};
+    cuuint32_t element_strides[2] = {1, 1};
+    CUresult r = encode_tiled(map, element_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                              const_cast<void *>(base), dims, strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 1 : fail("cuTensorMapEncodeTiled failed (%d) for a %llu x %llu tensor", (int)r,
+                                        (unsigned long long)rows, (unsigned long long)columns);
+}
+
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+/* ------------------------------------------------------------------ launches */
+template <int MODE, int BN, int MT, bool GROUPED>
+static int launch_tcgen05(const h3q8_linear_desc &d, GemmParams p, DeviceState *dev, cudaStream_t stream) {
+    using C = GemmConfig<MODE, BN, MT, GROUPED>;
+    CUtensorMap map_a, map_b;
+    const uint32_t a_bytes = MODE == MODE_W8A8 ? 1 : 2, b_bytes = MODE == MODE_BF16 ? 2 : 1;
+    if (!make_map(&map_a, d.input, a_bytes, d.rows, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    if (!make_map(&map_b, d.weight, b_bytes, d.output_dim, d.input_dim, C::BKE, BN,
+                  MODE == MODE_W8A16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    p.m_blocks = (d.rows + C::BM - 1) / C::BM;
+    p.n_blocks = (d.output_dim + BN - 1) / BN;
+    p.tiles = p.m_blocks * p.n_blocks;
+    p.band = p.m_blocks < 16 ? p.m_blocks : 16;
+    auto kernel = gemm_tcgen05_kernel<MODE, BN, MT, GROUPED>;
+    static bool configured[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (!configured[device]) {
+        if (!cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
+                     "shared memory opt-in")) return 0;
+        configured[device] = true;
+    }
+    const uint32_t grid = p.tiles < (uint32_t)dev->sms ? p.tiles : (uint32_t)dev->sms;
+    kernel<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(map_a, map_b, p);
+    count_launch(1);
+    return cuda_ok(cudaGetLastError(), "tcgen05 linear launch");
+}
+
+template <int MODE>
+static int launch_plain(const h3q8_linear_desc &d, const GemmParams &p, cudaStream_t stream) {
+    dim3 grid((d.output_dim + 63) / 64, (d.rows + 63) / 64);
+    linear_plain_kernel<MODE><<<grid, 256, 0, stream>>>(d.input, d.weight, p);
+    count_launch(1);
+    return cuda_ok(cudaGetLastError(), "plain linear launch");
+}
+
+template <int MODE>
+static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t kernel, DeviceState *dev, cudaStream_t stream) {
+    const bool grouped8 = MODE == MODE_W8A8 && d.weight_group != 0;
+    if (kernel == H3Q8_KERNEL_PLAIN) return launch_plain<MODE>(d, p, stream);
+    if (grouped8) {
+        if (MODE == MODE_W8A8) return launch_tcgen05<MODE_W8A8, 128, 1, true>(d, p, dev, stream);
+        return fail("grouped W8A8 reached a non-W8A8 launch");
+    }
+    if (kernel == H3Q8_KERNEL_TCGEN05_M256) return launch_tcgen05<MODE, 256, 2, false>(d, p, dev, stream);
+    if (kernel == H3Q8_KERNEL_TCGEN05_N128) return launch_tcgen05<MODE, 128, 1, false>(d, p, dev, stream);
+    return launch_tcgen05<MODE, 256, 1, false>(d, p, dev, stream);
+}
+
+static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
+    if (!d.rows || !d.input_dim || !d.output_dim) return fail("linear %ux%ux%u: empty dimension", d.rows, d.output_dim, d.input_dim);
+    if (!d.input || !d.weight || !d.output) return fail("linear %ux%ux%u: null operand", d.rows, d.output_dim, d.input_dim);
+    if (d.mode > H3Q8_MODE_W8A8) return fail("linear: unknown mode %u", d.mode);
+    if (d.activation > H3Q8_ACT_GELU_TANH) return fail("linear: unknown activation %u", d.activation);
+    if (d.mode != H3Q8_MODE_BF16 && !d.weight_scales) return fail("linear: int8 weights need weight_scales");
+    if (d.mode == H3Q8_MODE_W8A8 && !d.input_scales) return fail("linear: W8A8 needs per-token input_scales");
+    if (d.accumulators && (d.mode != H3Q8_MODE_W8A8 || d.weight_group))
+        return fail("linear: the int32 dump exists only for W8A8 with per-channel weight scales");
+    if ((uint64_t)d.output_dim * d.input_dim > UINT32_MAX - 31u) return fail("linear: weight exceeds 32-bit indexing");
+    if (static_cast<const void *>(d.output) == d.input) return fail("linear: output aliases the input");
+    DeviceState *dev = device_state();
+    if (!dev) return 0;
+
+    const uint32_t width = d.weight_group ? d.weight_group : d.input_dim;
+    GemmParams p = {};
+    p.M = d.rows; p.N = d.output_dim; p.K = d.input_dim;
+    p.scale_group = d.mode == H3Q8_MODE_BF16 ? 0 : d.weight_group;
+    p.scale_groups = d.mode == H3Q8_MODE_BF16 ? 1 : (d.input_dim + width - 1) / width;
+    p.w_scales = d.weight_scales; p.a_scales = d.input_scales;
+    p.ep.bias = d.bias; p.ep.gate = d.gate; p.ep.residual = d.residual; p.ep.activation = d.activation;
+    p.out = d.output; p.acc_dump = d.accumulators; p.status = dev->status;
+
+    /* What the TMA path needs: 16-byte aligned bases and row pitches, output rows
+     * that take 16-byte stores, scale groups that align with the k-blocks. */
+    const uint32_t k_multiple = d.mode == H3Q8_MODE_BF16 ? 8 : 16;
+    bool tma_ok = d.input_dim % k_multiple == 0 && d.output_dim % 8 == 0 && aligned16(d.input) && aligned16(d.weight) &&
+                  aligned16(d.output) && (!d.bias || aligned16(d.bias)) && (!d.gate || aligned16(d.gate)) &&
+                  (!d.residual || aligned16(d.residual)) && (!d.accumulators || aligned16(d.accumulators)) &&
+                  (d.mode != H3Q8_MODE_W8A8 || aligned16(d.weight_scales));
+    if (d.mode == H3Q8_MODE_W8A16 && d.weight_group && d.weight_group % 64) tma_ok = false;
+    if (d.mode == H3Q8_MODE_W8A8 && d.weight_group && d.weight_group % 128) tma_ok = false;
+    uint32_t kernel = d.kernel;
+    if (kernel > H3Q8_KERNEL_TCGEN05_N128) return fail("linear: unknown kernel selector %u", kernel);
+    if (kernel == H3Q8_KERNEL_AUTO) {
+        const bool tiny = (uint64_t)d.rows * d.input_dim * d.output_dim <= (1u << 22);
+        kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128 : H3Q8_KERNEL_TCGEN05;
+    } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {
+        return fail("linear %ux%ux%u: shape or alignment not supported by the tcgen05 kernel "
+                    "(K %% %u, N %% 8, 16-byte aligned operands, scale group %% 64/128)",
+                    d.rows, d.output_dim, d.input_dim, k_multiple);
+    }
+    if (kernel == H3Q8_KERNEL_PLAIN && d.mode == H3Q8_MODE_W8A8 && d.weight_group % 16)
+        return fail("linear: W8A8 weight scale group must be a multiple of 16");
+    switch (d.mode) {
+    case H3Q8_MODE_BF16: return launch_mode<MODE_BF16>(d, p, kernel, dev, stream);
+    case H3Q8_MODE_W8A16: return launch_mode<MODE_W8A16>(d, p, kernel, dev, stream);
+    default: return launch_mode<MODE_W8A8>(d, p, kernel, dev, stream);
+    }
+}
+
+} /* namespace h3q8 */
+
+using namespace h3q8;
+
+extern "C" int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream) {
+    if (!desc) return fail("linear: null descriptor");
+    return linear_one(*desc, (cudaStream_t)cuda_stream);
+}
+
+extern "C" int h3q8_linear_grouped(const h3q8_linear_desc *problems, uint32_t count, void *cuda_stream) {
+    if (!problems || !count) return fail("grouped linear: no problems");
+    for (uint32_t i = 0; i < count; i++)
+        if (!linear_one(problems[i], (cudaStream_t)cuda_stream)) return 0;
+    return 1;
+}
+
+extern "C" int h3q8_quantize_rows(const uint16_t *input, int8_t *output, float *scales, uint32_t rows,
+                                  uint32_t dispatch_rows, uint32_t columns, float clip, void *cuda_stream) {
+    if (!input || !output || !scales || !rows || !columns || dispatch_rows < rows)
+        return fail("quantize rows: invalid arguments");
+    if (!(clip > 0.0f) || clip > 1.0f) return fail("quantize rows: clip must be in (0, 1]");
+    uint32_t *status = device_status_word();
+    if (!status) return 0;
+    quantize_rows_kernel<<<dispatch_rows, 256, 0, (cudaStream_t)cuda_stream>>>(input, output, scales, rows, columns, clip, nullptr);
+    count_launch(1);
+    return cuda_ok(cudaGetLastError(), "quantize rows launch");
+}
+
+extern "C" int h3q8_q8_pack_rows_device(const uint16_t *source, int8_t *weights, float *scales, uint32_t rows,
+                                        uint32_t columns, uint32_t group, void *cuda_stream) {
+    size_t offset, bytes;
+    if (!source || !weights || !scales || !h3q8_q8_layout(rows, columns, group, &offset, &bytes))
+        return fail("q8 pack: invalid arguments");
+    if (!device_status_word()) return 0;
+    const uint32_t width = group ? group : columns;
+    const uint32_t groups = (uint32_t)(((uint64_t)columns + width - 1) / width);
+    const uint64_t items = (uint64_t)rows * groups;
+    q8_pack_rows_kernel<<<(unsigned)((items + 7) / 8), 256, 0, (cudaStream_t)cuda_stream>>>(source, weights, scales, rows, columns,
+                                                                                           width, groups, nullptr);
+    count_launch(1);
+    return cuda_ok(cudaGetLastError(), "q8 pack launch");
+}
+
+extern "C" int h3q8_q8_dequant(const int8_t *weights, const float *scales, uint16_t *output, uint32_t rows,
+                               uint32_t columns, uint32_t group, void *cuda_stream) {
+    if (!weights || !scales || !output || !rows || !columns) return fail("q8 dequant: invalid arguments");
+    if (!device_status_word()) return 0;
+    const uint32_t width = group ? group : columns;
+    const uint32_t groups = (uint32_t)(((uint64_t)columns + width - 1) / width);
+    unsigned per_row = (columns / 16 + 255) / 256;
+    if (!per_row) per_row = 1;
+    q8_dequant_kernel<<<dim3(per_row, rows), 256, 0, (cudaStream_t)cuda_stream>>>(weights, scales, output, rows, columns, width, groups);
+    count_launch(1);
+    return cuda_ok(cudaGetLastError(), "q8 dequant launch");
+}
+
+extern "C" uint32_t h3q8_device_status(void *cuda_stream) {
+    uint32_t *word = device_status_word();
+    if (!word) return 0xffffffffu;
+    uint32_t value = 0;
+    if (cudaStreamSynchronize((cudaStream_t)cuda_stream) != cudaSuccess ||
+        cudaMemcpy(&value, word, sizeof value, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        fail("CUDA error while reading the device status: %s", cudaGetErrorString(cudaGetLastError()));
+        return 0xffffffffu;
+    }
+    if (value) {
+        cudaMemset(word, 0, sizeof value);
+        fail("a kernel gave up a bounded wait: code %u in CTA %u", value & 0xffu, value >> 8);
+    }
+    return value;
+}
+
+extern "C" const char *h3q8_last_error(void) { return last_error; }
+extern "C" uint64_t h3q8_kernel_launches(void) { return launches.load(); }

@@ -1,0 +1,252 @@
+/* Memory-bound helper kernels around the tcgen05 GEMM, plus a plain CUDA-core
+ * linear used for shapes the TMA path cannot take (K not a multiple of 16, N
+ * not a multiple of 8) and as an on-device cross-check.
+ *
+ * All of them are single-pass, coalesced, 16-byte-vectorised where the shape
+ * allows, one CTA of 256 threads per row (or per 64x64 output tile for the
+ * plain linear).  Rounding follows the reference bit for bit:
+ *   per-token quantiser   src/metal/shaders.metal:1391-1460
+ *   group weight packer   src/weights/q8.c:26-56
+ *   weight dequantiser    src/metal/shaders.metal:788-794
+ */
+#pragma once
+#include <float.h>
+#include "gemm_tcgen05.cuh"
+
+namespace h3q8 {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+/* max over a 256-thread CTA; every thread gets the result */
+__device__ __forceinline__ float block_max_256(float v, float *scratch8) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) scratch8[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = scratch8[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) r = fmaxf(r, scratch8[i]);
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ int quantize_one(float x, float inverse) {
+    int q = __float2int_rn(__fmul_rn(x, inverse)); /* rint: ties to even */
+    return q < -127 ? -127 : q > 127 ? 127 : q;
+}
+
+/* Per-token (per-row) dynamic int8 quantiser.  Rows >= rows are padding: zero
+ * bytes and scale 1.  One CTA per dispatched row.  Sets *nonfinite when a row
+ * maximum is Inf/NaN. */
+static __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_t *__restrict__ in, int8_t *__restrict__ out,
+                                                            float *__restrict__ scales, uint32_t rows, uint32_t columns,
+                                                            float clip, uint32_t *nonfinite) {
+    __shared__ float scratch[8];
+    const uint32_t row = blockIdx.x;
+    int8_t *q = out + (size_t)row * columns;
+    const bool vec = (columns & 7u) == 0;
+    if (row >= rows) {
+        if (vec) for (uint32_t c = threadIdx.x; c < columns / 8; c += 256) reinterpret_cast<uint2 *>(q)[c] = make_uint2(0, 0);
+        else for (uint32_t c = threadIdx.x; c < columns; c += 256) q[c] = 0;
+        if (threadIdx.x == 0) scales[row] = 1.0f;
+        return;
+    }
+    const uint16_t *x = in + (size_t)row * columns;
+    float peak = 0.0f;
+    uint4 held[2]; /* up to 4096 columns stay in registers between the two passes */
+    const uint32_t vectors = columns / 8;
+    if (vec) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            uint32_t c = threadIdx.x + i * 256;
+            held[i] = c < vectors ? reinterpret_cast<const uint4 *>(x)[c] : make_uint4(0, 0, 0, 0);
+            const uint32_t w[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                peak = fmaxf(peak, fmaxf(fabsf(bf16_bits_to_f32(w[j] & 0xffffu)), fabsf(bf16_bits_to_f32(w[j] >> 16))));
+        }
+        for (uint32_t c = threadIdx.x + 512; c < vectors; c += 256) {
+            uint4 v = reinterpret_cast<const uint4 *>(x)[c];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                peak = fmaxf(peak, fmaxf(fabsf(bf16_bits_to_f32(w[j] & 0xffffu)), fabsf(bf16_bits_to_f32(w[j] >> 16))));
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < columns; c += 256) peak = fmaxf(peak, fabsf(bf16_bits_to_f32(x[c])));
+    }
+    peak = block_max_256(peak, scratch);
+    const float clipped = __fmul_rn(peak, clip);
+    const float scale = clipped > 0.0f ? __fdiv_rn(clipped, 127.0f) : __fdiv_rn(1.0f, 127.0f);
+    const float inverse = clipped > 0.0f ? __fdiv_rn(127.0f, clipped) : 127.0f;
+    if (threadIdx.x == 0) {
+        scales[row] = scale;
+        if (!(peak <= FLT_MAX) && nonfinite) atomicOr(nonfinite, 1u);
+    }
+    if (vec) {
+        for (uint32_t c = threadIdx.x, i = 0; c < vectors; c += 256, i++) {
+            uint4 v = i == 0 ? held[0] : i == 1 ? held[1] : reinterpret_cast<const uint4 *>(x)[c];
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            uint32_t o[2] = {0, 0};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t lo = (uint32_t)quantize_one(bf16_bits_to_f32(w[j] & 0xffffu), inverse) & 0xffu;
+                uint32_t hi = (uint32_t)quantize_one(bf16_bits_to_f32(w[j] >> 16), inverse) & 0xffu;
+                o[j >> 1] |= (lo | (hi << 8)) << ((j & 1) * 16);
+            }
+            reinterpret_cast<uint2 *>(q)[c] = make_uint2(o[0], o[1]);
+        }
+    } else {
+        for (uint32_t c = threadIdx.x; c < columns; c += 256) q[c] = (int8_t)quantize_one(bf16_bits_to_f32(x[c]), inverse);
+    }
+}
+
+/* Weight-only Q8 group packer on the device: one warp per (row, K-group).
+ * scale = max==0 ? 1 : max(max/127, FLT_MIN); q = round-half-even(w/scale). */
+static __global__ void __launch_bounds__(256) q8_pack_rows_kernel(const uint16_t *__restrict__ src, int8_t *__restrict__ q,
+                                                           float *__restrict__ scales, uint32_t rows, uint32_t columns,
+                                                           uint32_t width, uint32_t groups, uint32_t *nonfinite) {
+    const uint64_t item = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= (uint64_t)rows * groups) return;
+    const uint32_t row = (uint32_t)(item / groups), g = (uint32_t)(item % groups), lane = threadIdx.x & 31;
+    const uint32_t first = g * width, last = columns - first < width ? columns : first + width;
+    const uint16_t *x = src + (size_t)row * columns;
+    float peak = 0.0f;
+    for (uint32_t k = first + lane; k < last; k += 32) peak = fmaxf(peak, fabsf(bf16_bits_to_f32(x[k])));
+    peak = warp_max(peak);
+    if (!(peak <= FLT_MAX) && lane == 0 && nonfinite) atomicOr(nonfinite, 1u);
+    const float scale = peak == 0.0f ? 1.0f : fmaxf(__fdiv_rn(peak, 127.0f), FLT_MIN);
+    if (lane == 0) scales[(size_t)row * groups + g] = scale;
+    for (uint32_t k = first + lane; k < last; k += 32) {
+        int v = __float2int_rn(__fdiv_rn(bf16_bits_to_f32(x[k]), scale));
+        q[(size_t)row * columns + k] = (int8_t)(v < -127 ? -127 : v > 127 ? 127 : v);
+    }
+}
+
+/* bf16(float(q) * scale[n, k/width]) for the whole matrix (dequant-to-scratch policy). */
+static __global__ void __launch_bounds__(256) q8_dequant_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
+                                                         uint16_t *__restrict__ out, uint32_t rows, uint32_t columns,
+                                                         uint32_t width, uint32_t groups) {
+    const uint32_t row = blockIdx.y;
+    const int8_t *src = q + (size_t)row * columns;
+    uint16_t *dst = out + (size_t)row * columns;
+    const float *s = scales + (size_t)row * groups;
+    if ((columns & 15u) == 0 && (width & 15u) == 0) {
+        for (uint32_t c = blockIdx.x * 256 + threadIdx.x; c < columns / 16; c += gridDim.x * 256) {
+            const uint4 v = reinterpret_cast<const uint4 *>(src)[c];
+            const float scale = s[(c * 16) / width];
+            const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+            uint32_t o[8];
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                float f[4];
+                dequant4(words[w], scale, f);
+                o[2 * w] = pack_bf16x2(f[0], f[1]);
+                o[2 * w + 1] = pack_bf16x2(f[2], f[3]);
+            }
+            reinterpret_cast<uint4 *>(dst)[2 * c] = make_uint4(o[0], o[1], o[2], o[3]);
+            reinterpret_cast<uint4 *>(dst)[2 * c + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+    } else {
+        for (uint32_t c = blockIdx.x * 256 + threadIdx.x; c < columns; c += gridDim.x * 256)
+            dst[c] = (uint16_t)f32_to_bf16_bits(__fmul_rn((float)src[c], s[c / width]));
+    }
+}
+
+/* Plain CUDA-core linear with the same operand modes and epilogue as the
+ * tcgen05 kernel: 64x64 output tile, 16x16 threads, 4x4 outputs per thread,
+ * K slabs of 16 staged through shared memory as fp32 / int32. */
+template <int MODE>
+__global__ void __launch_bounds__(256) linear_plain_kernel(const void *__restrict__ xin, const void *__restrict__ win,
+                                                           const GemmParams p) {
+    using acc_t = typename std::conditional<MODE == MODE_W8A8, int32_t, float>::type;
+    __shared__ acc_t xs[16][65];
+    __shared__ acc_t ws[16][65];
+    const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const uint32_t row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
+    const uint32_t width = p.scale_group ? p.scale_group : p.K;
+    const bool grouped8 = MODE == MODE_W8A8 && p.scale_group != 0;
+    acc_t acc[4][4];
+    float totals[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) { acc[i][j] = 0; totals[i][j] = 0.0f; }
+    for (uint32_t k0 = 0; k0 < p.K; k0 += 16) {
+        for (uint32_t e = threadIdx.x; e < 64 * 16; e += 256) {
+            const uint32_t r = e >> 4, k = e & 15;
+            const uint32_t gr = row0 + r, gc = col0 + r, gk = k0 + k;
+            acc_t xv = 0, wv = 0;
+            if (gk < p.K) {
+                if (gr < p.M) {
+                    if (MODE == MODE_W8A8) xv = (acc_t)reinterpret_cast<const int8_t *>(xin)[(size_t)gr * p.K + gk];
+                    else xv = (acc_t)bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(xin)[(size_t)gr * p.K + gk]);
+                }
+                if (gc < p.N) {
+                    if (MODE == MODE_BF16) wv = (acc_t)bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(win)[(size_t)gc * p.K + gk]);
+                    else {
+                        const int qv = reinterpret_cast<const int8_t *>(win)[(size_t)gc * p.K + gk];
+                        if (MODE == MODE_W8A8) wv = (acc_t)qv;
+                        else wv = (acc_t)bf16_bits_to_f32(f32_to_bf16_bits(
+                                 __fmul_rn((float)qv, p.w_scales[(size_t)gc * p.scale_groups + gk / width])));
+                    }
+                }
+            }
+            xs[k][r] = xv;
+            ws[k][r] = wv;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            acc_t a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { a[i] = xs[k][ty * 4 + i]; b[i] = ws[k][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (MODE == MODE_W8A8) acc[i][j] += a[i] * b[j];
+                    else acc[i][j] = (acc_t)fmaf((float)a[i], (float)b[j], (float)acc[i][j]);
+                }
+        }
+        __syncthreads();
+        /* grouped W8A8: close the K-group -- scale its exact int32 sum and add in fp32 */
+        if (grouped8 && ((k0 + 16) % width == 0 || k0 + 16 >= p.K)) {
+            const uint32_t g = k0 / width;
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint32_t r = row0 + ty * 4 + i, c = col0 + tx * 4 + j;
+                    if (r < p.M && c < p.N) {
+                        float value = __fmul_rn(__fmul_rn((float)acc[i][j], p.a_scales[r]), p.w_scales[(size_t)c * p.scale_groups + g]);
+                        totals[i][j] = g ? __fadd_rn(totals[i][j], value) : value;
+                    }
+                    acc[i][j] = 0;
+                }
+        }
+    }
+    const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t r = row0 + ty * 4 + i, c = col0 + tx * 4 + j;
+            if (r >= p.M || c >= p.N) continue;
+            float linear;
+            if (MODE == MODE_W8A8) {
+                if (grouped8) linear = totals[i][j];
+                else {
+                    if (p.acc_dump) p.acc_dump[(size_t)r * p.N + c] = (int32_t)acc[i][j];
+                    linear = __fmul_rn(__fmul_rn((float)acc[i][j], p.a_scales[r]), p.w_scales[c]);
+                }
+            } else linear = (float)acc[i][j];
+            const uint32_t y = epilogue_value(linear, p.ep.bias ? bf16_bits_to_f32(p.ep.bias[c]) : 0.0f, p.ep.bias != nullptr,
+                                              p.ep.activation, gated, p.ep.gate ? bf16_bits_to_f32(p.ep.gate[c]) : 1.0f,
+                                              p.ep.residual ? bf16_bits_to_f32(p.ep.residual[(size_t)r * p.N + c]) : 0.0f);
+            p.out[(size_t)r * p.N + c] = (uint16_t)y;
+        }
+}
+
+} /* namespace h3q8 */

@@ -1,0 +1,160 @@
+/* Thin inline-PTX wrappers for the sm_100a features the GEMM kernels use:
+ * mbarrier, TMA (cp.async.bulk.tensor, never multicast), tcgen05 MMA / TMEM,
+ * and the UMMA shared-memory and instruction descriptors.
+ *
+ * Every wait is bounded: a wait that sees no progress for WAIT_LIMIT_CYCLES
+ * returns false and the caller unwinds to the kernel's common exit, where the
+ * error word is set and TMEM is freed.  Nothing here traps or spins forever. */
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace h3q8 {
+
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll; /* about two seconds */
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+/* ---------------------------------------------------------------- mbarrier */
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+/* Orders generic-proxy shared-memory writes before async-proxy (TMA / UMMA) reads. */
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+/* Bounded wait.  False means "gave up": the caller must stop using the pipeline. */
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    long long start = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int spin = 0; spin < 256; spin++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+
+/* --------------------------------------------------------------------- TMA */
+__device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+/* 2-D tiled load global -> this CTA's shared memory; x is the innermost
+ * coordinate and must make x * element_size a multiple of 16 bytes. */
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar,
+                                            int32_t x, int32_t y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+
+/* ----------------------------------------------------------------- tcgen05 */
+__device__ __forceinline__ void tmem_alloc(uint32_t *dst_smem, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(dst_smem)), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after_sync() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+/* Arrive (count one) on an mbarrier once every MMA issued so far by this thread is done. */
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+/* D[tmem] (+)= A[smem] . B[smem]^T, bf16 x bf16 -> fp32 */
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+/* D[tmem] (+)= A[smem] . B[smem]^T, int8 x int8 -> int32 */
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                        uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+/* 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane
+ * (taddr.lane + t), columns taddr.column .. +31. */
+__device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_load_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+/* ------------------------------------------------------------- descriptors */
+/* Shared-memory matrix descriptor for a K-major operand tile stored as rows of
+ * 128 bytes with the 128-byte swizzle (what TMA SWIZZLE_128B writes): 8-row
+ * groups are 1024 bytes apart (stride byte offset), the leading byte offset is
+ * unused for swizzled K-major and set to its canonical 1, descriptor version 1
+ * (Blackwell), layout type 2 (SWIZZLE_128B).  The tile base must be 1024-byte
+ * aligned; stepping along K inside the 128-byte row adds the byte offset / 16
+ * to the start-address field. */
+__device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr) {
+    uint64_t desc = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    desc |= (uint64_t)1 << 16;                  /* leading byte offset (ignored) */
+    desc |= (uint64_t)(1024 >> 4) << 32;        /* stride byte offset            */
+    desc |= (uint64_t)1 << 46;                  /* descriptor version            */
+    desc |= (uint64_t)2 << 61;                  /* SWIZZLE_128B                  */
+    return desc;
+}
+/* Instruction descriptor: dense, K-major A and B, no negate, no saturate.
+ * c_format: 1 = F32, 2 = S32.  ab_format: kind::f16 -> 1 = BF16; kind::i8 -> 1 = signed. */
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t c_format, uint32_t ab_format,
+                                                  uint32_t m, uint32_t n) {
+    return (c_format << 4) | (ab_format << 7) | (ab_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+/* --------------------------------------------------------------- bf16 bits */
+/* Same bit recipe as the reference (src/metal/shaders.metal:15-19). */
+__device__ __forceinline__ uint32_t f32_to_bf16_bits(float v) {
+    uint32_t b = __float_as_uint(v);
+    return (b + 0x7fffu + ((b >> 16) & 1u)) >> 16;
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t b) { return __uint_as_float(b << 16); }
+
+} /* namespace h3q8 */

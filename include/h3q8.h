@@ -1,0 +1,241 @@
+/* libh3q8 -- B200 (sm_100a) implementation of the int8-weight ("q8") linear
+ * layers of the MiniMax-H3 DiT, as a drop-in behind h3cli's GPU operator
+ * interface (greg31337/h3cli, src/gpu.h).
+ *
+ * Two layers, both plain C:
+ *   1. h3_gpu_*   the subset of src/gpu.h that the DiT block's linear path
+ *                 uses: opaque context + tensors, command scope, and the linear
+ *                 operators.  Names, argument meaning, return convention
+ *                 (1 = ok, 0 = failure, message via h3_gpu_error) follow the
+ *                 reference; each declaration cites the line it replaces.
+ *   2. h3q8_*     the raw entry points underneath: device pointers, sizes and
+ *                 a CUDA stream, for callers that manage memory themselves.
+ *
+ * There is no CPU path: every operator runs CUDA kernels or fails with a reason.
+ */
+#ifndef H3Q8_H
+#define H3Q8_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* =====================================================================
+ * Host-side weight packing (no GPU involved)
+ * ===================================================================== */
+#define H3_Q8_VERSION 1 /* src/weights/q8.h:11 -- recipe id, bump when rounding/layout changes */
+#define H3_Q8_GROUP 64  /* src/weights/q8.h:12 */
+/* src/weights/q8.h:13-16 (src/weights/q8.c:6-56): storage is int8[N,K], zero
+ * padding to 4 bytes, float[N, ceil(K/64)]. */
+int h3_q8_layout(uint32_t rows, uint32_t columns, size_t *scale_offset, size_t *bytes);
+int h3_q8_pack_rows(const uint16_t *source, int8_t *weights, float *scales,
+                    uint32_t rows, uint32_t columns);
+/* Same recipe with the group width as a parameter (0 = one group per row). */
+int h3q8_q8_layout(uint32_t rows, uint32_t columns, uint32_t group, size_t *scale_offset, size_t *bytes);
+int h3q8_q8_pack_rows(const uint16_t *source, int8_t *weights, float *scales,
+                      uint32_t rows, uint32_t columns, uint32_t group);
+
+/* =====================================================================
+ * Layer 2: raw entry points (device pointers, caller-owned memory)
+ * ===================================================================== */
+enum { H3Q8_MODE_BF16 = 0, H3Q8_MODE_W8A16 = 1, H3Q8_MODE_W8A8 = 2 };
+enum { H3Q8_ACT_NONE = 0, H3Q8_ACT_GELU_TANH = 1 };
+enum { /* kernel selection; AUTO picks by shape */
+    H3Q8_KERNEL_AUTO = 0,
+    H3Q8_KERNEL_PLAIN = 1,     /* CUDA-core kernel, any shape                       */
+    H3Q8_KERNEL_TCGEN05 = 2,   /* tcgen05/TMA kernel, 128 x 256 tiles               */
+    H3Q8_KERNEL_TCGEN05_M256 = 3, /* tcgen05/TMA kernel, 256 x 256 tiles            */
+    H3Q8_KERNEL_TCGEN05_N128 = 4  /* tcgen05/TMA kernel, 128 x 128 tiles            */
+};
+
+/* out[M,N] = epilogue(input[M,K] . weight[N,K]^T), everything row-major.
+ * Replaces the body of gemm()/quant_gemm() (src/cuda/gpu_cuda.cu:927-1005,
+ * src/cuda/cuda_quant.cuh:339-398) and the Metal kernels h3_linear_q8_bf16 /
+ * h3_linear_int8_nax_r128 (src/metal/shaders.metal:799-857, 2417-2466), with the
+ * separate bias / GELU / gate kernels (src/cuda/cuda_kernels.cuh:879-902,
+ * 973-986) folded into the epilogue. */
+typedef struct {
+    uint32_t mode;            /* H3Q8_MODE_*                                               */
+    uint32_t rows;            /* M                                                         */
+    uint32_t input_dim;       /* K                                                         */
+    uint32_t output_dim;      /* N                                                         */
+    const void *input;        /* bf16 [M,K] (BF16, W8A16) or int8 [M,K] (W8A8)             */
+    const void *weight;       /* bf16 [N,K] (BF16) or int8 [N,K]                           */
+    const float *weight_scales; /* [N, ceil(K/group)] fp32; unused for BF16                */
+    uint32_t weight_group;    /* K elements per weight scale; 0 = per output channel       */
+    const float *input_scales;/* [M] per-token fp32 scales (W8A8)                          */
+    const uint16_t *bias;     /* bf16 [N] or NULL                                          */
+    const uint16_t *gate;     /* bf16 [N] or NULL (adaLN gate vector)                      */
+    const uint16_t *residual; /* bf16 [M,N] or NULL                                        */
+    uint32_t activation;      /* H3Q8_ACT_*                                                */
+    uint16_t *output;         /* bf16 [M,N]                                                */
+    int32_t *accumulators;    /* optional int32 [M,N] dump (W8A8, per-channel scales)      */
+    uint32_t kernel;          /* H3Q8_KERNEL_*                                             */
+} h3q8_linear_desc;
+int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream);
+
+/* Several independent problems in one call (video + audio streams of the DiT):
+ * every problem is enqueued back to back on the stream with no host sync. */
+int h3q8_linear_grouped(const h3q8_linear_desc *problems, uint32_t count, void *cuda_stream);
+
+/* Per-token dynamic int8 quantiser (src/metal/shaders.metal:1391-1460):
+ * scale = max|x|/127 (1/127 for a zero row), q = clamp(rint(x * (127/max))).
+ * Rows in [rows, dispatch_rows) are padding: zero bytes, scale 1. */
+int h3q8_quantize_rows(const uint16_t *input, int8_t *output, float *scales, uint32_t rows,
+                       uint32_t dispatch_rows, uint32_t columns, float clip, void *cuda_stream);
+/* Device version of h3q8_q8_pack_rows (bf16 [N,K] -> int8 [N,K] + scales). */
+int h3q8_q8_pack_rows_device(const uint16_t *source, int8_t *weights, float *scales, uint32_t rows,
+                             uint32_t columns, uint32_t group, void *cuda_stream);
+/* bf16(float(q)*scale) for a whole matrix (src/metal/shaders.metal:788-794). */
+int h3q8_q8_dequant(const int8_t *weights, const float *scales, uint16_t *output, uint32_t rows,
+                    uint32_t columns, uint32_t group, void *cuda_stream);
+/* Reads and clears the device error word of the current device (0 = ok);
+ * synchronises the stream first.  Non-zero: a bounded wait inside a kernel ran
+ * out (code in the low byte, CTA index above it). */
+uint32_t h3q8_device_status(void *cuda_stream);
+/* Message of the last failed h3q8_* call on this thread. */
+const char *h3q8_last_error(void);
+/* Launch counter: kernels this library has launched in this process. */
+uint64_t h3q8_kernel_launches(void);
+
+/* =====================================================================
+ * Layer 1: the reference's GPU operator interface (subset)
+ * ===================================================================== */
+typedef struct h3_gpu h3_gpu;               /* src/gpu.h:12 */
+typedef struct h3_gpu_tensor h3_gpu_tensor; /* src/gpu.h:13 */
+typedef struct h3_gpu_event h3_gpu_event;   /* src/gpu.h:14 */
+typedef enum { H3_GPU_F32 = 0, H3_GPU_BF16, H3_GPU_I8, H3_GPU_U32, H3_GPU_F16 } h3_gpu_dtype; /* src/gpu.h:16-22 */
+typedef enum { H3_GPU_HOST_VISIBLE, H3_GPU_DEVICE_ONLY, H3_GPU_HOST_PINNED } h3_gpu_storage;   /* src/gpu.h:24-25 */
+typedef enum { H3_WEIGHT_BF16 = 0, H3_WEIGHT_Q8 = 1 } h3_weight_format;                        /* src/backend.h:9 */
+
+/* Counters of src/gpu.h:99-142 that this path maintains (same names; the
+ * reference struct has more fields -- an integrating build copies these). */
+typedef struct {
+    uint64_t q8_weights, q8_source_bytes, q8_storage_bytes, q8_dispatches;
+    double q8_load_seconds;
+    uint64_t allocated_bytes, live_bytes, peak_live_bytes, tensor_allocations;
+    uint64_t direct_dispatches, submissions, linear_dispatches;
+    uint64_t h2d_bytes, d2h_bytes, d2d_bytes, streamed_bytes, stream_stalls;
+    uint64_t pinned_bytes, stream_slot_bytes;
+    double stream_wait_seconds, quant_conversion_seconds;
+    uint64_t quant_projection_dispatches, quant_cache_hits, quant_cache_misses;
+    uint64_t native_scratch_bytes, native_scratch_allocations, native_scratch_reuses;
+} h3_gpu_stats;
+
+/* Context -- src/gpu.h:144-145, 180-182, 203, 207, 267-268 */
+h3_gpu *h3_gpu_create(const char *shader_source_path, char *error, size_t error_size);
+void h3_gpu_free(h3_gpu *gpu);
+void h3_gpu_cancel(h3_gpu *gpu);
+const char *h3_gpu_error(const h3_gpu *gpu);
+int h3_gpu_get_stats(const h3_gpu *gpu, h3_gpu_stats *stats);
+const char *h3_gpu_backend_name(const h3_gpu *gpu);
+int h3_gpu_has_int8_mlp(const h3_gpu *gpu);
+/* Command scope -- src/gpu.h:260-266 */
+int h3_gpu_begin(h3_gpu *gpu);
+int h3_gpu_continue(h3_gpu *gpu);
+int h3_gpu_submit(h3_gpu *gpu);
+int h3_gpu_synchronize(h3_gpu *gpu);
+/* Tensors -- src/gpu.h:26-33, 209-258 */
+h3_gpu_tensor *h3_gpu_tensor_alloc(h3_gpu *gpu, size_t elements, h3_gpu_dtype dtype, h3_gpu_storage storage);
+void *h3_gpu_tensor_contents(h3_gpu_tensor *tensor);
+h3_gpu_tensor *h3_gpu_tensor_new_f32(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_new_bf16(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_new_i8(h3_gpu *gpu, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_f32(h3_gpu *gpu, const float *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_bf16(h3_gpu *gpu, const uint16_t *values, size_t elements);
+h3_gpu_tensor *h3_gpu_tensor_from_u32(h3_gpu *gpu, const uint32_t *values, size_t elements);
+void h3_gpu_tensor_free(h3_gpu_tensor *tensor);
+size_t h3_gpu_tensor_elements(const h3_gpu_tensor *tensor);
+h3_gpu_dtype h3_gpu_tensor_dtype(const h3_gpu_tensor *tensor);
+int h3_gpu_tensor_read_f32(const h3_gpu_tensor *tensor, float *values, size_t elements);
+int h3_gpu_tensor_read_bf16(const h3_gpu_tensor *tensor, uint16_t *values, size_t elements);
+int h3_gpu_tensor_read_u32(const h3_gpu_tensor *tensor, uint32_t *values, size_t elements);
+int h3_gpu_tensor_write_f32(h3_gpu_tensor *tensor, const float *values, size_t elements);
+int h3_gpu_tensor_write_bf16(h3_gpu_tensor *tensor, const uint16_t *values, size_t elements);
+int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *tensor, size_t destination_offset,
+                                   const uint16_t *values, size_t elements);
+/* Byte-typed transfers for int8 tensors (no reference twin: its int8 tensors
+ * are only ever produced on the device). */
+int h3_gpu_tensor_read_i8(const h3_gpu_tensor *tensor, int8_t *values, size_t elements);
+int h3_gpu_tensor_write_i8(h3_gpu_tensor *tensor, const int8_t *values, size_t elements);
+h3_gpu_event *h3_gpu_event_new(h3_gpu *gpu);
+int h3_gpu_event_record(h3_gpu *gpu, h3_gpu_event *event);
+int h3_gpu_event_wait(h3_gpu *gpu, h3_gpu_event *event);
+void h3_gpu_event_free(h3_gpu_event *event);
+/* File I/O -- src/gpu.h:221-236.  stream_file may run on an I/O thread while
+ * the owner thread enqueues compute (src/cuda/gpu_cuda.cu:761-841). */
+h3_gpu_tensor *h3_gpu_tensor_load_bf16(h3_gpu *gpu, const char *path, uint64_t file_offset, size_t elements);
+int h3_gpu_tensor_read_file_bf16(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
+                                 size_t elements, char *error, size_t error_size);
+int h3_gpu_tensor_stream_file_bf16(h3_gpu_tensor *tensor, const char *path, uint64_t file_offset,
+                                   size_t elements, char *error, size_t error_size);
+/* Planning -- src/gpu.h:34-36, 48-50: 0 resident, 1 streamed, -1 insufficient. */
+int h3_gpu_plan_weights(h3_gpu *gpu, uint64_t weights, uint64_t activations);
+int h3_gpu_release_weight_cache(h3_gpu *gpu);
+
+/* Linear -- src/gpu.h:501-505.  A weight that carries a q8 descriptor (made by
+ * h3_gpu_q8_load / h3_gpu_quant_load) is routed to the int8-weight kernels, as
+ * src/cuda/gpu_cuda.cu:927-931 and src/metal/gpu.m:2672-2673 do. */
+int h3_gpu_linear_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                       const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                       uint32_t rows, uint32_t input_dim, uint32_t output_dim);
+/* Quantised weights -- src/gpu.h:44-47, 74-75.
+ * mode: 0 off, 1 W8A16 (int8 weights, bf16 activations), 2 W8A8.  The scale
+ * group width comes from H3Q8_GROUP (default 64 for q8_load, per-channel
+ * otherwise) or h3q8_gpu_set_group(). */
+int h3_gpu_quant_configure(h3_gpu *gpu, int mode, const char *cache, uint64_t bf16_weights,
+                           uint64_t activations, int force_stream);
+h3_gpu_tensor *h3_gpu_quant_load(h3_gpu *gpu, const char *path, uint64_t offset, uint32_t rows, uint32_t columns);
+h3_gpu_tensor *h3_gpu_q8_load(h3_gpu *gpu, const char *path, uint64_t offset, uint32_t rows, uint32_t columns);
+int h3q8_gpu_set_group(h3_gpu *gpu, uint32_t group);
+/* Bridges between the two layers: the device address behind a tensor and the
+ * context's compute stream (a cudaStream_t), for callers that mix h3_gpu
+ * tensors with the raw h3q8_* entry points. */
+void *h3q8_gpu_tensor_device_pointer(const h3_gpu_tensor *tensor);
+void *h3q8_gpu_compute_stream(h3_gpu *gpu);
+/* Rows at or above which a W8A16 linear first dequantises the weight into
+ * context scratch and runs the bf16 GEMM (the reference's policy 0,
+ * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop. */
+int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *gpu, uint32_t rows);
+/* Same descriptor built from int8 weights + scales already in host memory. */
+h3_gpu_tensor *h3q8_gpu_q8_from_host(h3_gpu *gpu, const int8_t *weights, const float *scales,
+                                     uint32_t rows, uint32_t columns, uint32_t group);
+/* W8A8 family -- src/gpu.h:523-537 */
+int h3_gpu_quantize_weight_int8(h3_gpu *gpu, h3_gpu_tensor *output, h3_gpu_tensor *scales,
+                                const h3_gpu_tensor *input, uint32_t rows, uint32_t columns);
+int h3_gpu_linear_int8_bf16(h3_gpu *gpu, h3_gpu_tensor *output, h3_gpu_tensor *quantized_input,
+                            h3_gpu_tensor *input_scales, const h3_gpu_tensor *input,
+                            const h3_gpu_tensor *weight, const h3_gpu_tensor *weight_scales,
+                            uint32_t rows, uint32_t input_dim, uint32_t output_dim,
+                            int use_slower_uncached_int8_scales);
+/* Unfused epilogue operators kept for comparison -- src/gpu.h:575-577, 612-617, 750-752 */
+int h3_gpu_gelu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input, uint32_t elements, int approximate);
+int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+                     const h3_gpu_tensor *branch, const h3_gpu_tensor *modulation,
+                     const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width, uint32_t slots, uint32_t gate_slot);
+int h3_gpu_add_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *left,
+                    const h3_gpu_tensor *right, uint32_t elements);
+
+/* The fused projection: linear + bias + GELU-tanh | gate*branch + residual in
+ * one kernel.  No counterpart in src/gpu.h; modelled on its fused wrappers
+ * (h3_gpu_adaln_linear_bf16 :600-611, h3_gpu_gate_adaln_bf16 :618-629).
+ * weight may be bf16 or carry a q8 descriptor; with W8A8 configured the
+ * activations are quantised per token into context-owned scratch first.
+ * bias, gate, residual may be NULL.  activation: H3Q8_ACT_*. */
+int h3_gpu_linear_fused_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
+                             const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
+                             const h3_gpu_tensor *gate, const h3_gpu_tensor *residual,
+                             uint32_t rows, uint32_t input_dim, uint32_t output_dim, int activation);
+typedef struct {
+    h3_gpu_tensor *output;
+    const h3_gpu_tensor *input, *weight, *bias, *gate, *residual;
+    uint32_t rows, input_dim, output_dim;
+    int activation;
+} h3_gpu_linear_problem;
+int h3_gpu_linear_grouped_bf16(h3_gpu *gpu, const h3_gpu_linear_problem *problems, uint32_t count);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,151 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes binding of the CPU checker.
+
+`oracle/h3q8_oracle.c` restates the reference's q8 linear arithmetic on the CPU;
+`oracle/_ref/libh3q8_ref.so` is the reference's own `src/weights/q8.c` compiled
+unmodified.  Only the test-suite, the smoke check and the benchmark's CPU
+baseline may import this package; the shipped library never does.
+"""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = os.path.join(_HERE, "_build", "libh3q8_oracle.so")
+_REF = os.path.join(_HERE, "_ref", "libh3q8_ref.so")
+
+MODE_BF16, MODE_W8A16, MODE_W8A8 = 0, 1, 2
+ACT_NONE, ACT_GELU_TANH = 0, 1
+
+
+def build():
+    """Compile the checker (and, when the reference tree is present, `_ref`)."""
+    subprocess.run(["make", "-s", "-C", _HERE], check=True)
+
+
+class _Args(ctypes.Structure):
+    _fields_ = [
+        ("mode", ctypes.c_uint32), ("rows", ctypes.c_uint32),
+        ("input_dim", ctypes.c_uint32), ("output_dim", ctypes.c_uint32),
+        ("input", ctypes.c_void_p), ("weight", ctypes.c_void_p),
+        ("weight_scales", ctypes.c_void_p), ("weight_group", ctypes.c_uint32),
+        ("input_scales", ctypes.c_void_p),
+        ("bias", ctypes.c_void_p), ("gate", ctypes.c_void_p), ("residual", ctypes.c_void_p),
+        ("activation", ctypes.c_uint32),
+        ("output", ctypes.c_void_p), ("accumulators", ctypes.c_void_p),
+        ("fast", ctypes.c_int),
+    ]
+
+
+_lib = None
+_ref = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB):
+            build()
+        _lib = ctypes.CDLL(_LIB)
+        _lib.h3o_q8_layout.argtypes = [ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
+                                       ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+        _lib.h3o_q8_pack_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32]
+        _lib.h3o_q8_dequant.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32]
+        _lib.h3o_quantize_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                           ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_float]
+        _lib.h3o_gelu_tanh_bf16.argtypes = [ctypes.c_uint16]
+        _lib.h3o_gelu_tanh_bf16.restype = ctypes.c_uint16
+        _lib.h3o_gate_residual_bf16.argtypes = [ctypes.c_uint16] * 3
+        _lib.h3o_gate_residual_bf16.restype = ctypes.c_uint16
+        _lib.h3o_f32_to_bf16.argtypes = [ctypes.c_float]
+        _lib.h3o_f32_to_bf16.restype = ctypes.c_uint16
+        _lib.h3o_bf16_to_f32.argtypes = [ctypes.c_uint16]
+        _lib.h3o_bf16_to_f32.restype = ctypes.c_float
+        _lib.h3o_linear.argtypes = [ctypes.POINTER(_Args)]
+    return _lib
+
+
+def reference_q8():
+    """The reference's own packer (src/weights/q8.c), or None if it was never built."""
+    global _ref
+    if _ref is None and os.path.exists(_REF):
+        _ref = ctypes.CDLL(_REF)
+        _ref.h3_q8_layout.argtypes = [ctypes.c_uint32, ctypes.c_uint32,
+                                      ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]
+        _ref.h3_q8_pack_rows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                         ctypes.c_uint32, ctypes.c_uint32]
+    return _ref
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data
+
+
+def f32_to_bf16(x):
+    """Vectorised src/metal/shaders.metal:15-19."""
+    bits = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFFFFFF
+    return (bits >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(b):
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def q8_layout(rows, cols, group):
+    off, total = ctypes.c_size_t(), ctypes.c_size_t()
+    ok = lib().h3o_q8_layout(rows, cols, group, ctypes.byref(off), ctypes.byref(total))
+    return (off.value, total.value) if ok else None
+
+
+def q8_pack_rows(src_bf16, group):
+    rows, cols = src_bf16.shape
+    width = group or cols
+    groups = (cols + width - 1) // width
+    src = np.ascontiguousarray(src_bf16, dtype=np.uint16)
+    q = np.empty((rows, cols), np.int8)
+    s = np.empty((rows, groups), np.float32)
+    if not lib().h3o_q8_pack_rows(_ptr(src), _ptr(q), _ptr(s), rows, cols, group):
+        return None
+    return q, s
+
+
+def q8_dequant(q, s, group):
+    rows, cols = q.shape
+    out = np.empty((rows, cols), np.uint16)
+    lib().h3o_q8_dequant(_ptr(np.ascontiguousarray(q)), _ptr(np.ascontiguousarray(s)), _ptr(out), rows, cols, group)
+    return out
+
+
+def quantize_rows(x_bf16, dispatch_rows=None, clip=1.0):
+    rows, cols = x_bf16.shape
+    dispatch_rows = dispatch_rows or rows
+    x = np.ascontiguousarray(x_bf16, dtype=np.uint16)
+    q = np.empty((dispatch_rows, cols), np.int8)
+    s = np.empty((dispatch_rows,), np.float32)
+    lib().h3o_quantize_rows(_ptr(x), _ptr(q), _ptr(s), rows, dispatch_rows, cols, clip)
+    return q, s
+
+
+def gelu_tanh_bf16(b):
+    f = lib().h3o_gelu_tanh_bf16
+    return np.array([f(int(v)) for v in np.asarray(b, np.uint16).ravel()], np.uint16).reshape(np.shape(b))
+
+
+def linear(mode, x, w, w_scales=None, group=0, x_scales=None, bias=None, gate=None,
+           residual=None, activation=ACT_NONE, fast=False, want_acc=False):
+    """out[M,N] (bf16 bits) = epilogue(x . w^T); see h3o_linear_args."""
+    M, K = x.shape
+    N = w.shape[0]
+    keep = [np.ascontiguousarray(a) if a is not None else None
+            for a in (x, w, w_scales, x_scales, bias, gate, residual)]
+    out = np.empty((M, N), np.uint16)
+    acc = np.empty((M, N), np.int32) if want_acc else None
+    a = _Args(mode, M, K, N, _ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2]), group, _ptr(keep[3]),
+              _ptr(keep[4]), _ptr(keep[5]), _ptr(keep[6]), activation, _ptr(out), _ptr(acc), int(fast))
+    if not lib().h3o_linear(ctypes.byref(a)):
+        raise ValueError("oracle rejected the arguments")
+    return (out, acc) if want_acc else out
