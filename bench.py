@@ -1,0 +1,314 @@
+#!/usr/bin/env python
+"""Benchmark of the q8 DiT linear stack (one DiT block's four projections).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A step is one pass of QKV (3072->9216), attention-output (3072->3072, gate *
+branch + residual), FFN-up (3072->12288, GELU-tanh) and FFN-down (12288->3072,
+gate * branch + residual) over M = 32,400 tokens per GPU with int8 weights and
+per-channel fp32 scales (W8A16), synthetic seeded data.  With N > 1 every rank
+runs the same rows-sharded step on its own GPU (weights replicated, no
+collective); the job value is total TFLOP/s with the slowest rank's device time.
+
+Prints one JSON line (rank 0): `value` with operands resident in HBM, `e2e`
+through the h3_gpu_* operator interface with host buffers, `roofline` of the
+GEMM kernel from CUDA events, `cpu_baseline` = the CPU restatement on a bounded
+row slab.  `--impl reference` times only that CPU restatement (the reference has
+no CPU or CUDA int8 linear of its own to run).
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M_TOKENS, HIDDEN, FFN = 32400, 3072, 12288
+# name, K, N, epilogue
+LAYERS = [("qkv", HIDDEN, 3 * HIDDEN, ""), ("attn_out", HIDDEN, HIDDEN, "gr"),
+          ("ffn_up", HIDDEN, FFN, "a"), ("ffn_down", FFN, HIDDEN, "gr")]
+FLOP_PER_STEP = sum(2.0 * M_TOKENS * k * n for _, k, n, _ in LAYERS)
+METRIC = "q8_dit_block_linear_tflops"
+UNIT = "TFLOP/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_tcgen05_kernel launch, from the ncu
+# capture summarised in profiles/ (null until a capture exists for the bench workload)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            peaks = json.load(f)
+        return float(peaks["bf16_tflops"]), float(peaks.get("bf16_tflops_sustained", 0.0)), "measured"
+    except Exception:
+        return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz, self.stop_flag = index, [], set(), None, False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv, self.handle = pynvml, pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.nv:
+            return
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+        while not self.stop_flag:
+            try:
+                self.samples.append(self.nv.nvmlDeviceGetClockInfo(self.handle, self.nv.NVML_CLOCK_SM))
+                try:
+                    bits = self.nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    bits = self.nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.reasons.update(n for b, n in names.items() if bits & b)
+            except Exception:
+                break
+            time.sleep(0.002)
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def oracle_slab(rows, steps, warmup):
+    """Times the CPU restatement (oracle fast path, all host threads) on `rows` rows of each GEMM shape."""
+    import oracle
+    oracle.build()
+    rng = np.random.default_rng(0)
+    work = []
+    for name, k, n, spec in LAYERS:
+        x = oracle.f32_to_bf16(rng.standard_normal((rows, k), dtype=np.float32)).reshape(rows, k)
+        wq = rng.integers(-127, 128, (n, k), dtype=np.int8)
+        ws = np.exp(rng.normal(np.log(0.01), 0.3, (n, 1))).astype(np.float32)
+        gate = oracle.f32_to_bf16((rng.standard_normal(n, dtype=np.float32) * np.float32(0.1) + 1)) if "g" in spec else None
+        res = oracle.f32_to_bf16(rng.standard_normal((rows, n), dtype=np.float32)).reshape(rows, n) if "r" in spec else None
+        work.append((x, wq, ws, gate, res, 1 if "a" in spec else 0))
+    flop = sum(2.0 * rows * k * n for _, k, n, _ in LAYERS)
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        for x, wq, ws, gate, res, act in work:
+            oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0, gate=gate, residual=res, activation=act, fast=True)
+        if i >= warmup:
+            times.append(time.perf_counter() - t0)
+    seconds = float(np.mean(times))
+    return flop / seconds / 1e12, seconds, oracle.lib().h3o_threads()
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    rows = 512
+    value, seconds, cores = oracle_slab(rows, args.steps, args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{rows}-row slab of each of the 4 GEMM shapes per step (the reference has no CPU linear; "
+                                   "this is the CPU restatement of its shader arithmetic, blocked fp32 + OpenMP)"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config():
+    return {"workload": "DiT block linear stack (BASELINE config 2): M=32400 tokens per GPU, hidden 3072, FFN 12288, "
+                        "W8A16 int8 weights with per-channel fp32 scales; QKV, attn-out(+gate,+residual), "
+                        "FFN-up(GELU-tanh), FFN-down(+gate,+residual)",
+            "rows_per_gpu": M_TOKENS, "hidden": HIDDEN, "ffn": FFN, "l2": "inputs_exceed_l2 (>= 199 MB per operand vs 126 MB L2)",
+            "parallelism": "token-row sharding, weights replicated, no collective"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="h3q8")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank)
+
+    import torch
+    import torch.distributed as dist
+    os.environ["H3_CUDA_DEVICE"] = str(local)
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import h3cli_b200 as h
+    from h3cli_b200 import api
+
+    gpu = h.Gpu()
+    gpu.quant_configure(1)
+    gpu.set_w8a16_scratch_rows(int(os.environ.get("H3Q8_W8A16_SCRATCH_ROWS", "1024")))
+    stream = torch.cuda.ExternalStream(gpu.stream, device=local)
+    lib = h.library()
+
+    class _Span:
+        """Zero-copy torch view of an h3_gpu tensor (CUDA array interface)."""
+
+        def __init__(self, pointer, count):
+            self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<i2", "data": (pointer, False), "version": 2}
+
+    def device_bf16(rows, cols, mean=0.0, std=1.0, seed=0):
+        """A resident h3_gpu bf16 tensor filled on the device with seeded normals."""
+        gen = torch.Generator(device="cuda").manual_seed(1000 * rank + seed)
+        t = gpu.tensor_new_bf16(rows * cols)
+        view = torch.as_tensor(_Span(t.device_pointer, rows * cols), device=f"cuda:{local}").view(torch.bfloat16)
+        chunk = 4096
+        for r0 in range(0, rows, chunk):
+            r1 = min(rows, r0 + chunk)
+            block = torch.randn(r1 - r0, cols, generator=gen, device="cuda", dtype=torch.float32) * std + mean
+            view[r0 * cols:r1 * cols].copy_(block.to(torch.bfloat16).reshape(-1))
+        torch.cuda.synchronize()
+        return t
+
+    # ---- operands (weights replicated on every rank: same seed) ----------------------------------
+    weights, inputs, outputs, gates, residuals = {}, {}, {}, {}, {}
+    wgen = np.random.default_rng(42)
+    for name, k, n, spec in LAYERS:
+        wq = wgen.integers(-127, 128, (n, k), dtype=np.int8)
+        ws = np.exp(wgen.normal(np.log(0.01), 0.3, (n, 1))).astype(np.float32)
+        weights[name] = gpu.q8_from_host(wq, ws, 0)
+        outputs[name] = gpu.tensor_new_bf16(M_TOKENS * n)
+    x = device_bf16(M_TOKENS, HIDDEN, seed=1)
+    hidden = device_bf16(M_TOKENS, FFN, seed=2)
+    residual = device_bf16(M_TOKENS, HIDDEN, seed=3)
+    gate = device_bf16(1, HIDDEN, 1.0, 0.1, seed=4)
+    inputs = {"qkv": x, "attn_out": x, "ffn_up": x, "ffn_down": hidden}
+
+    def enqueue_step():
+        for name, k, n, spec in LAYERS:
+            gpu.linear_fused_bf16(outputs[name], inputs[name], weights[name], None, gate if "g" in spec else None,
+                                  residual if "r" in spec else None, M_TOKENS, k, n, 1 if "a" in spec else 0)
+        gpu.continue_()      # commit without waiting, as the reference's block loop does between blocks
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- value: operands resident in HBM -----------------------------------------------------------
+    gpu.begin()
+    for _ in range(args.warmup):
+        enqueue_step()
+    gpu.submit()
+    gpu.set_profiling(True)
+    before = gpu.stats()
+    launches_before = lib.h3q8_kernel_launches()
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gpu.begin()
+    start.record(stream)
+    for _ in range(args.steps):
+        enqueue_step()
+    stop.record(stream)
+    barrier()
+    sampler.stop_flag = True
+    gpu.submit()            # waits (already idle) and harvests the per-kernel events
+    seconds = start.elapsed_time(stop) * 1e-3
+    after = gpu.stats()
+    launches = lib.h3q8_kernel_launches() - launches_before
+    gpu.set_profiling(False)
+    t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    job_seconds = float(t.item())
+    value = world * FLOP_PER_STEP * args.steps / job_seconds / 1e12
+
+    gemm_seconds = after.linear_seconds - before.linear_seconds
+    gemm_launches = after.linear_kernel_launches - before.linear_kernel_launches
+    burst, sustained, which = measured_peak()
+    achieved = FLOP_PER_STEP * args.steps / gemm_seconds / 1e12 if gemm_seconds > 0 else None
+
+    # ---- e2e: the same four operators, host buffers in, host buffer out ------------------------------
+    # Chain as a DiT block calls them: x -> qkv; x -> attn_out (+gate, residual x) -> ffn_up (GELU) ->
+    # ffn_down (+gate, residual h1).  Per step the block input crosses PCIe in and the block output out.
+    host_x = torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory()
+    host_y = torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory()
+    lib.h3_gpu_tensor_read_bf16(x.handle, host_x.data_ptr(), M_TOKENS * HIDDEN)
+    h1 = gpu.tensor_new_bf16(M_TOKENS * HIDDEN)
+
+    def step_e2e():
+        lib.h3_gpu_tensor_write_bf16(x.handle, host_x.data_ptr(), M_TOKENS * HIDDEN)
+        gpu.begin()
+        gpu.linear_fused_bf16(outputs["qkv"], x, weights["qkv"], None, None, None, M_TOKENS, HIDDEN, 3 * HIDDEN, 0)
+        gpu.linear_fused_bf16(h1, x, weights["attn_out"], None, gate, x, M_TOKENS, HIDDEN, HIDDEN, 0)
+        gpu.linear_fused_bf16(outputs["ffn_up"], h1, weights["ffn_up"], None, None, None, M_TOKENS, HIDDEN, FFN, 1)
+        gpu.linear_fused_bf16(outputs["ffn_down"], outputs["ffn_up"], weights["ffn_down"], None, gate, h1, M_TOKENS, FFN, HIDDEN, 0)
+        gpu.submit()
+        lib.h3_gpu_tensor_read_bf16(outputs["ffn_down"].handle, host_y.data_ptr(), M_TOKENS * HIDDEN)
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record(stream)
+    wall = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    e_stop.record(stream)
+    barrier()
+    e_seconds = max(e_start.elapsed_time(e_stop) * 1e-3, time.perf_counter() - wall if world == 1 else 0.0)
+    t = torch.tensor([e_seconds], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * FLOP_PER_STEP * args.steps / float(t.item()) / 1e12
+
+    if rank == 0:
+        cpu_value, cpu_seconds, cores = (None, None, None)
+        if world == 1:
+            cpu_value, cpu_seconds, cores = oracle_slab(1024, 2, 1)
+        clocks = sampler.summary()
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": job_seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(),
+            "dit_block_linear_ms": job_seconds / args.steps * 1e3,
+            "tensor_peak_fraction_per_gpu": value / world / burst,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": M_TOKENS * HIDDEN * 2,
+                    "d2h_bytes_per_step": M_TOKENS * HIDDEN * 2,
+                    "path": "h3_gpu_tensor_write_bf16 -> 4 x h3_gpu_linear_fused_bf16 (chained as the DiT block calls them) "
+                            "-> h3_gpu_submit -> h3_gpu_tensor_read_bf16, pinned host buffers"},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16, 128x256> after q8_dequant_kernel",
+                         "achieved": achieved, "peak": burst, "unit": UNIT, "frac": achieved / burst if achieved else None,
+                         "peak_source": f"bf16_tflops (burst) of {which}", "frac_of_sustained": achieved / sustained if achieved and sustained else None,
+                         "launches": int(gemm_launches), "avg_launch_ms": gemm_seconds / max(gemm_launches, 1) * 1e3,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+            "cpu_baseline": None if cpu_value is None else {
+                "value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
+                "sample": "1024-row slab of each of the 4 GEMM shapes (0.232 TFLOP), blocked fp32 OpenMP restatement"},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    gpu.free()
+
+
+if __name__ == "__main__":
+    main()

@@ -44,7 +44,9 @@ class Stats(C.Structure):
                 [("stream_wait_seconds", C.c_double), ("quant_conversion_seconds", C.c_double)] +
                 [(n, C.c_uint64) for n in ("quant_projection_dispatches", "quant_cache_hits", "quant_cache_misses",
                                            "native_scratch_bytes", "native_scratch_allocations",
-                                           "native_scratch_reuses")])
+                                           "native_scratch_reuses")] +
+                [("linear_seconds", C.c_double), ("linear_kernel_launches", C.c_uint64),
+                 ("conversion_kernel_launches", C.c_uint64)])
 
 
 class Problem(C.Structure):
@@ -107,6 +109,7 @@ def library():
         "h3q8_gpu_set_group": (C.c_int, [vp, u32]),
         "h3q8_gpu_tensor_device_pointer": (vp, [vp]), "h3q8_gpu_compute_stream": (vp, [vp]),
         "h3q8_gpu_set_w8a16_scratch_rows": (C.c_int, [vp, u32]),
+        "h3q8_gpu_set_profiling": (C.c_int, [vp, C.c_int]),
         "h3q8_gpu_q8_from_host": (vp, [vp, vp, vp, u32, u32, u32]),
         "h3_gpu_quantize_weight_int8": (C.c_int, [vp, vp, vp, vp, u32, u32]),
         "h3_gpu_linear_int8_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
@@ -263,6 +266,9 @@ class Gpu:
 
     def set_w8a16_scratch_rows(self, rows):
         return self._check(library().h3q8_gpu_set_w8a16_scratch_rows(self.handle, rows))
+
+    def set_profiling(self, enabled):
+        return self._check(library().h3q8_gpu_set_profiling(self.handle, int(enabled)))
 
     def q8_load(self, path, offset, rows, columns):
         return Tensor(self, library().h3_gpu_q8_load(self.handle, path.encode(), offset, rows, columns))

@@ -33,7 +33,11 @@ __device__ __forceinline__ float gelu_tanh_f32(float v) {
     float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(v, cube));
     if (inner <= -10.0f) return 0.0f;
     if (inner >= 10.0f) return v;
-    return __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.0f, tanhf(inner)));
+    /* 0.5 v (1 + tanh u) == v / (1 + exp(-2u)).  The exponential and the division
+     * use the hardware approximations (relative error about 1e-6), far inside the
+     * bf16 rounding that follows; against a correctly rounded tanhf the stored
+     * bf16 differs by one step for a few outputs in ten thousand. */
+    return __fdividef(v, 1.0f + __expf(-2.0f * inner));
 }
 
 /* linear: fp32 linear result before bias.  Returns the final bf16 bits. */

@@ -9,8 +9,8 @@
  *   MODE_W8A8   X int8, W int8            TMA -> smem -> kind::i8 MMA   (int32 in TMEM)
  *
  * One CTA per SM, static round-robin over output tiles of (128*MT) x BN.
- * Warp roles: 0-3 epilogue (TMEM lane quadrant = warp index), 4 TMA producer,
- * 5 MMA issuer and TMEM owner, 6-13 dequantisers (MODE_W8A16 only).
+ * Warp roles: 0-7 epilogue (TMEM lane quadrant = warp % 4, column half = warp / 4),
+ * 8 TMA producer, 9 MMA issuer and TMEM owner, 10-17 dequantisers (MODE_W8A16 only).
  * Operand tiles are rows of 128 bytes in the 128-byte swizzle; one k-block is
  * 64 bf16 or 128 int8 elements = four MMA instructions per 128-row sub-tile.
  * Accumulators are double-buffered in TMEM whenever 2*MT*BN <= 512 columns so
@@ -63,7 +63,9 @@ struct GemmConfig {
     static constexpr int ACC_COLS = BN * MT;
     static constexpr int ACC_BUFFERS = 512 / ACC_COLS >= 2 ? 2 : 1;
     static constexpr int DEQUANT_WARPS = MODE == MODE_W8A16 ? 8 : 0;
-    static constexpr int WARPS = 6 + DEQUANT_WARPS;
+    static constexpr int EPILOGUE_WARPS = 8;
+    static constexpr int PRODUCER_WARP = EPILOGUE_WARPS, MMA_WARP = EPILOGUE_WARPS + 1, FIRST_DEQUANT_WARP = EPILOGUE_WARPS + 2;
+    static constexpr int WARPS = EPILOGUE_WARPS + 2 + DEQUANT_WARPS;
     static constexpr int THREADS = WARPS * 32;
     static constexpr int BARRIERS = 2 * STAGES + 2 * CONV_BUFFERS + 2 * ACC_BUFFERS;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CONV_BUFFERS * B_BYTES + 1024 /* align */ + 256;
@@ -143,20 +145,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], C::DEQUANT_WARPS); mbar_init(&bempty[s], 1); }
-        for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 4); }
+        for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], C::EPILOGUE_WARPS); }
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    if (warp == 4 && lane == 0) { tma_prefetch_descriptor(&map_a); tma_prefetch_descriptor(&map_b); }
-    if (warp == 5) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == C::PRODUCER_WARP && lane == 0) { tma_prefetch_descriptor(&map_a); tma_prefetch_descriptor(&map_b); }
+    if (warp == C::MMA_WARP) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     uint32_t failure = STATUS_OK;
 
-    if (warp == 4) {
+    if (warp == C::PRODUCER_WARP) {
         /* ------------------------------------------------ TMA producer */
         if (lane == 0) {
             PipeState st;
@@ -176,7 +178,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == C::MMA_WARP) {
         /* -------------------------------------------------- MMA issuer */
         if (lane == 0) {
             PipeState st, cv, acc;
@@ -219,29 +221,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             }
         }
-    } else if (warp < 4) {
+    } else if (warp < C::EPILOGUE_WARPS) {
         /* ---------------------------------------------------- epilogue */
+        /* warp w reads TMEM lanes 32*(w%4).. (its hardware quadrant) and the column half w/4 */
+        constexpr int HALF_CHUNKS = BN / 64;
+        const uint32_t quadrant = warp & 3, half = warp >> 2;
         PipeState acc;
         const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
         for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
             uint32_t mb, nb;
             tile_coordinates(p, tile, mb, nb);
             const uint32_t n0 = nb * BN;
-            float totals[GROUPED ? BN : 1];
+            float totals[GROUPED ? BN / 2 : 1];
             for (uint32_t chunk = 0; chunk < chunks && !failure; chunk++) {
                 bool ready = wait_or_abort(&tfull[acc.index], acc.phase, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_EPILOGUE; break; }
                 tc_fence_after_sync();
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
-                    const uint32_t row = mb * C::BM + mt * 128 + warp * 32 + lane;
+                    const uint32_t row = mb * C::BM + mt * 128 + quadrant * 32 + lane;
                     const bool row_ok = row < p.M;
                     float a_scale = 1.0f;
                     if (MODE == MODE_W8A8) a_scale = row_ok ? p.a_scales[row] : 0.0f;
-#pragma unroll(GROUPED ? BN / 32 : 1)
-                    for (int c = 0; c < BN / 32; c++) {
+#pragma unroll(GROUPED ? HALF_CHUNKS : 1)
+                    for (int hc = 0; hc < HALF_CHUNKS; hc++) {
+                        const int c = half * HALF_CHUNKS + hc;
                         uint32_t v[32];
-                        tmem_load_32x32(tmem_base + ((warp * 32u) << 16) + acc.index * C::ACC_COLS + mt * BN + c * 32, v);
+                        tmem_load_32x32(tmem_base + ((quadrant * 32u) << 16) + acc.index * C::ACC_COLS + mt * BN + c * 32, v);
                         tmem_load_wait();
                         const uint32_t col0 = n0 + c * 32;
                         if (GROUPED) {
@@ -250,7 +256,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 uint32_t col = col0 + j;
                                 float ws = col < p.N ? p.w_scales[(size_t)col * p.scale_groups + chunk] : 0.0f;
                                 float value = __fmul_rn(__fmul_rn((float)(int32_t)v[j], a_scale), ws);
-                                totals[c * 32 + j] = chunk ? __fadd_rn(totals[c * 32 + j], value) : value;
+                                totals[hc * 32 + j] = chunk ? __fadd_rn(totals[hc * 32 + j], value) : value;
                             }
                             if (chunk + 1 < chunks) continue;
                         }
@@ -278,7 +284,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                     lin[j] = __fmul_rn(__fmul_rn((float)(int32_t)v[j8 * 8 + j], a_scale), ws[j]);
                             } else if (GROUPED) {
 #pragma unroll
-                                for (int j = 0; j < 8; j++) lin[j] = totals[c * 32 + j8 * 8 + j];
+                                for (int j = 0; j < 8; j++) lin[j] = totals[hc * 32 + j8 * 8 + j];
                             } else {
 #pragma unroll
                                 for (int j = 0; j < 8; j++) lin[j] = __uint_as_float(v[j8 * 8 + j]);
@@ -317,7 +323,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
          * into a BN x 64 bf16 tile (128-byte rows, 128-byte swizzle). */
         constexpr int THREADS_PER_ROW = 256 / BN;           /* 1 (BN=256) or 2 (BN=128) */
         constexpr int CHUNKS = 4 / THREADS_PER_ROW;         /* 16-byte int8 chunks per thread */
-        const uint32_t d = threadIdx.x - 6 * 32;
+        const uint32_t d = threadIdx.x - C::FIRST_DEQUANT_WARP * 32;
         const uint32_t r = d / THREADS_PER_ROW;
         const uint32_t chunk0 = (d % THREADS_PER_ROW) * CHUNKS;
         const uint32_t width = p.scale_group ? p.scale_group : p.K;
@@ -374,7 +380,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         while (clock64() - start < 2000000ll) { }
         __syncthreads();
     }
-    if (warp == 5) {
+    if (warp == C::MMA_WARP) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
     }

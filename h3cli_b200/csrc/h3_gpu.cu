@@ -63,7 +63,46 @@ struct h3_gpu {
     uint64_t allocation_budget = 0; /* H3_CUDA_TEST_MEMORY_BUDGET: fail allocations beyond this many live bytes */
     std::mutex mutex, copy_mutex;
     std::vector<h3_gpu_tensor *> accessed;
+    /* profiling: event pairs per kernel, category 0 = GEMM, 7 = conversion */
+    bool profiling = false;
+    struct Span { cudaEvent_t start, stop; int category; };
+    std::vector<Span> spans;
+    std::vector<cudaEvent_t> spare_events;
 };
+
+/* Brackets kernel launches on the compute stream with an event pair while
+ * profiling; the pairs are read back after the next synchronising submit. */
+struct ProfileScope {
+    h3_gpu *g;
+    h3_gpu::Span span{};
+    bool live = false;
+    static cudaEvent_t event(h3_gpu *g) {
+        cudaEvent_t e = nullptr;
+        if (!g->spare_events.empty()) { e = g->spare_events.back(); g->spare_events.pop_back(); }
+        else cudaEventCreate(&e);
+        return e;
+    }
+    ProfileScope(h3_gpu *gpu, int category) : g(gpu) {
+        if (!g->profiling) return;
+        span.start = event(g); span.stop = event(g); span.category = category;
+        live = span.start && span.stop && cudaEventRecord(span.start, g->compute) == cudaSuccess;
+    }
+    ~ProfileScope() {
+        if (live && cudaEventRecord(span.stop, g->compute) == cudaSuccess) g->spans.push_back(span);
+    }
+};
+static void harvest_profile(h3_gpu *g) {
+    for (auto &s : g->spans) {
+        float ms = 0;
+        if (cudaEventElapsedTime(&ms, s.start, s.stop) == cudaSuccess) {
+            if (s.category == 0) { g->stats.linear_seconds += ms * 1e-3; g->stats.linear_kernel_launches++; }
+            else { g->stats.quant_conversion_seconds += ms * 1e-3; g->stats.conversion_kernel_launches++; }
+        }
+        g->spare_events.push_back(s.start);
+        g->spare_events.push_back(s.stop);
+    }
+    g->spans.clear();
+}
 
 static const size_t BOUNCE_BYTES = 16u << 20; /* src/cuda/gpu_cuda.cu:79-82 */
 
@@ -160,6 +199,7 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
     g->device = device;
     const char *budget = getenv("H3_CUDA_TEST_MEMORY_BUDGET"); /* src/weights/residency.c:31-32 */
     if (budget && *budget) g->allocation_budget = strtoull(budget, nullptr, 10);
+    g->profiling = getenv("H3_PROFILE") != nullptr;
     const char *policy = getenv("H3Q8_W8A16_SCRATCH_ROWS");
     g->w8a16_scratch_rows = policy && *policy ? atoi(policy) : 0;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
@@ -184,6 +224,7 @@ extern "C" void h3_gpu_cancel(h3_gpu *g) {
     cudaGetLastError();
     if (g->flags) cudaMemset(g->flags, 0, 2 * sizeof(uint32_t));
     g->accessed.clear();
+    harvest_profile(g);
     g->active = false;
     g->deferred_error = false;
 }
@@ -191,6 +232,7 @@ extern "C" void h3_gpu_cancel(h3_gpu *g) {
 extern "C" void h3_gpu_free(h3_gpu *g) {
     if (!g) return;
     h3_gpu_cancel(g);
+    for (cudaEvent_t e : g->spare_events) cudaEventDestroy(e);
     for (int i = 0; i < 3; i++) if (g->arena[i]) cudaFree(g->arena[i]);
     for (int i = 0; i < 2; i++) {
         if (g->bounce[i]) cudaFreeHost(g->bounce[i]);
@@ -224,6 +266,7 @@ extern "C" int h3_gpu_continue(h3_gpu *g) {
 }
 static int drain(h3_gpu *g) {
     if (!checked(g, cudaStreamSynchronize(g->compute), "synchronize")) return 0;
+    harvest_profile(g);
     uint32_t flags[2] = {0, 0};
     if (!checked(g, cudaMemcpy(flags, g->flags, sizeof flags, cudaMemcpyDeviceToHost), "read device flags")) return 0;
     uint32_t shared_status = h3q8_device_status(g->compute);
@@ -497,6 +540,11 @@ extern "C" int h3q8_gpu_set_group(h3_gpu *g, uint32_t group) {
 }
 extern "C" void *h3q8_gpu_tensor_device_pointer(const h3_gpu_tensor *t) { return t ? t->data : nullptr; }
 extern "C" void *h3q8_gpu_compute_stream(h3_gpu *g) { return g ? (void *)g->compute : nullptr; }
+extern "C" int h3q8_gpu_set_profiling(h3_gpu *g, int enabled) {
+    if (!g) return 0;
+    g->profiling = enabled != 0;
+    return 1;
+}
 extern "C" int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *g, uint32_t rows) {
     if (!g) return 0;
     g->w8a16_scratch_rows = (int)rows;
@@ -641,8 +689,11 @@ static int linear_dispatch(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *i
         if (g->quant_mode == 2) { /* W8A8: per-token quantise into context scratch, then the int8 GEMM */
             uint32_t padded = (rows + 127u) & ~127u;
             if (!arena(g, 0, (size_t)padded * k) || !arena(g, 1, (size_t)padded * sizeof(float))) return 0;
-            quantize_rows_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)d.input, (int8_t *)g->arena[0], (float *)g->arena[1],
-                                                                 rows, k, 1.0f, g->flags + 1);
+            {
+                ProfileScope timing(g, 7);
+                quantize_rows_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)d.input, (int8_t *)g->arena[0], (float *)g->arena[1],
+                                                                     rows, k, 1.0f, g->flags + 1);
+            }
             count_launch(1);
             dispatches++;
             d.mode = H3Q8_MODE_W8A8;
@@ -651,6 +702,7 @@ static int linear_dispatch(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *i
         } else if (g->w8a16_scratch_rows && rows >= (uint32_t)g->w8a16_scratch_rows && k % 16 == 0) {
             /* policy 0 of the reference: dequantise once, then a bf16 GEMM (src/metal/q8_host.inc:75-88) */
             if (!arena(g, 2, (size_t)n * k * 2)) return 0;
+            ProfileScope timing(g, 7);
             if (!h3q8_q8_dequant((const int8_t *)d.weight, d.weight_scales, (uint16_t *)g->arena[2], n, k, d.weight_group, g->compute))
                 return set_error(g, "%s", h3q8_last_error());
             dispatches++;
@@ -665,7 +717,10 @@ static int linear_dispatch(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *i
         if (w->dtype != H3_GPU_BF16 || w->elements < (size_t)n * k) return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
         d.mode = H3Q8_MODE_BF16;
     }
-    if (!h3q8_linear(&d, g->compute)) { g->accessed.clear(); return set_error(g, "%s", h3q8_last_error()); }
+    {
+        ProfileScope timing(g, 0);
+        if (!h3q8_linear(&d, g->compute)) { g->accessed.clear(); return set_error(g, "%s", h3q8_last_error()); }
+    }
     g->stats.linear_dispatches++;
     return launch_status(g, "linear", dispatches);
 }

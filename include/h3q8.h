@@ -121,6 +121,11 @@ typedef struct {
     double stream_wait_seconds, quant_conversion_seconds;
     uint64_t quant_projection_dispatches, quant_cache_hits, quant_cache_misses;
     uint64_t native_scratch_bytes, native_scratch_allocations, native_scratch_reuses;
+    /* H3_PROFILE categories 0 (GEMM) and 7 (quant conversion) of
+     * src/cuda/gpu_cuda.cu:231-273: CUDA-event time of the linear kernels and of
+     * the quantise / dequantise kernels, harvested at submit while profiling is on. */
+    double linear_seconds;
+    uint64_t linear_kernel_launches, conversion_kernel_launches;
 } h3_gpu_stats;
 
 /* Context -- src/gpu.h:144-145, 180-182, 203, 207, 267-268 */
@@ -198,6 +203,8 @@ void *h3q8_gpu_compute_stream(h3_gpu *gpu);
  * context scratch and runs the bf16 GEMM (the reference's policy 0,
  * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop. */
 int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *gpu, uint32_t rows);
+/* Per-kernel CUDA-event timing into h3_gpu_stats (on when H3_PROFILE is set). */
+int h3q8_gpu_set_profiling(h3_gpu *gpu, int enabled);
 /* Same descriptor built from int8 weights + scales already in host memory. */
 h3_gpu_tensor *h3q8_gpu_q8_from_host(h3_gpu *gpu, const int8_t *weights, const float *scales,
                                      uint32_t rows, uint32_t columns, uint32_t group);

@@ -21,7 +21,7 @@ ACT_NONE, ACT_GELU_TANH = 0, 1
 
 def build():
     """Compile the checker (and, when the reference tree is present, `_ref`)."""
-    subprocess.run(["make", "-s", "-C", _HERE], check=True)
+    subprocess.run(["make", "-s", "-C", _HERE], check=True, stdout=subprocess.DEVNULL)
 
 
 class _Args(ctypes.Structure):

@@ -1,0 +1,551 @@
+"""Parity of the CUDA path with the oracle, through the C-ABI (ctypes), on a B200.
+
+The bar: bit-exact for integer work (quantised bytes, scales, int32
+accumulators) and for exactly representable patterns; bf16 outputs within
+rel-L2 <= 2e-3 and max |delta| <= 2 bf16 ulp (ulp floor: see tests/parity.py).
+Cases follow h3cli's own operator tests (tests/metal_q8.c, tests/quant_native.c)
+and the benchmark configurations.
+"""
+import os
+import tempfile
+
+import numpy as np
+import pytest
+
+import h3cli_b200 as h
+from h3cli_b200 import synth
+from parity import bf16_to_f32, check_bf16, rel_l2
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TC_KERNELS = [h.KERNEL_TCGEN05, h.KERNEL_TCGEN05_M256, h.KERNEL_TCGEN05_N128]
+GUARD = 64
+
+
+def upload(gpu, **arrays):
+    out = {}
+    for name, a in arrays.items():
+        if a is None:
+            continue
+        a = np.ascontiguousarray(a)
+        out[name] = (gpu.tensor_from_bf16(a) if a.dtype == np.uint16 else gpu.tensor_from_i8(a) if a.dtype == np.int8
+                     else gpu.tensor_from_f32(a))
+    return out
+
+
+def raw_linear(gpu, mode, x, w, ws=None, group=0, xs=None, bias=None, gate=None, residual=None, activation=0,
+               kernel=h.KERNEL_AUTO, want_acc=False):
+    """One h3q8_linear call on fresh tensors; returns bf16 bits [M,N] (and int32 accumulators)."""
+    M, K = x.shape
+    N = w.shape[0]
+    t = upload(gpu, input=x, weight=w, weight_scales=ws, input_scales=xs, bias=bias, gate=gate, residual=residual)
+    out = gpu.tensor_from_bf16(np.full(M * N + GUARD, 0x3F80, np.uint16))
+    fields = dict(mode=mode, rows=M, input_dim=K, output_dim=N, weight_group=group, activation=activation, kernel=kernel,
+                  output=out, **t)
+    acc = None
+    if want_acc:
+        acc = gpu.tensor_alloc(M * N, 3)
+        fields["accumulators"] = acc
+    gpu.raw_linear(**fields)
+    assert gpu.raw_status() == 0
+    got = out.read()
+    assert (got[M * N:] == 0x3F80).all(), "wrote past the end of the output"
+    result = got[:M * N].reshape(M, N)
+    accv = acc.read(dtype=3).view(np.int32).reshape(M, N) if want_acc else None
+    for tensor in list(t.values()) + [out] + ([acc] if acc else []):
+        tensor.free()
+    return (result, accv) if want_acc else result
+
+
+def operands(seed, M, N, K, group, outliers=False):
+    width = group or K
+    x = synth.activations(seed, 1, M, K, outliers=synth.outlier_channels(seed, K) if outliers else None).reshape(M, K)
+    wq = synth.int8_weights(seed, 2, N, K)
+    ws = synth.lognormal_scales(seed, 3, N, (K + width - 1) // width)
+    return x, wq, ws
+
+
+def epilogue_operands(seed, M, N, spec):
+    bias = synth.bf16_normal(seed, 4, 1, N, 0, 0.02)[0] if "b" in spec else None
+    gate = synth.bf16_normal(seed, 5, 1, N, 1, 0.1)[0] if "g" in spec else None
+    res = synth.bf16_normal(seed, 6, M, N, 0, 1).reshape(M, N) if "r" in spec else None
+    return bias, gate, res, (1 if "a" in spec else 0)
+
+
+# --------------------------------------------------------------------------- quantisers
+@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 7), (33, 100), (130, 128), (300, 3072), (17, 5000), (5, 12288)])
+def test_row_quantiser_bit_exact(gpu, oracle, rows, cols):
+    x = synth.activations(11, 1, rows, cols, outliers=synth.outlier_channels(11, cols)).reshape(rows, cols)
+    x[0] = 0  # zero row: scale 1/127
+    padded = (rows + 127) // 128 * 128
+    tx, q, s = gpu.tensor_from_bf16(x), gpu.tensor_new_i8(padded * cols), gpu.tensor_new_f32(padded)
+    lib = h.library()
+    assert lib.h3q8_quantize_rows(tx.device_pointer, q.device_pointer, s.device_pointer, rows, padded, cols, 1.0, gpu.stream)
+    gpu.synchronize()
+    want_q, want_s = oracle.quantize_rows(x, padded)
+    assert (q.read().reshape(padded, cols) == want_q).all()
+    assert (s.read().view(np.uint32) == want_s.view(np.uint32)).all()
+    assert not lib.h3q8_quantize_rows(tx.device_pointer, q.device_pointer, s.device_pointer, rows, rows - 1, cols, 1.0, gpu.stream)
+    for t in (tx, q, s):
+        t.free()
+
+
+@pytest.mark.parametrize("group", [0, 64, 128])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (35, 65), (67, 129), (256, 256), (96, 3072)])
+def test_device_packer_and_dequant_bit_exact(gpu, oracle, rows, cols, group):
+    w = synth.bf16_normal(13, 2, rows, cols, 0, 0.125).reshape(rows, cols)
+    w[0, 0] = 0
+    want_q, want_s = oracle.q8_pack_rows(w, group)
+    tw, q, s = gpu.tensor_from_bf16(w), gpu.tensor_new_i8(rows * cols), gpu.tensor_new_f32(want_s.size)
+    lib = h.library()
+    assert lib.h3q8_q8_pack_rows_device(tw.device_pointer, q.device_pointer, s.device_pointer, rows, cols, group, gpu.stream)
+    gpu.synchronize()
+    assert (q.read().reshape(rows, cols) == want_q).all()
+    assert (s.read().view(np.uint32) == want_s.ravel().view(np.uint32)).all()
+    d = gpu.tensor_new_bf16(rows * cols)
+    assert lib.h3q8_q8_dequant(q.device_pointer, s.device_pointer, d.device_pointer, rows, cols, group, gpu.stream)
+    gpu.synchronize()
+    assert (d.read().reshape(rows, cols) == oracle.q8_dequant(want_q, want_s, group)).all()
+    for t in (tw, q, s, d):
+        t.free()
+
+
+def test_gelu_operator_all_bf16_inputs(gpu, oracle):
+    """Every finite bf16 input through h3_gpu_gelu_bf16 against the oracle's tanh-GELU."""
+    bits = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    finite = np.isfinite(bf16_to_f32(bits))
+    tin, tout = gpu.tensor_from_bf16(bits), gpu.tensor_new_bf16(65536)
+    gpu.begin()
+    gpu.gelu_bf16(tout, tin, 65536, 1)
+    gpu.submit()
+    got = tout.read()
+    want = oracle.gelu_tanh_bf16(bits)
+    # device tanhf and libm tanhf may differ in the last fp32 bit: allow one bf16 step, rarely
+    step = np.abs(got[finite].astype(np.int32) - want[finite].astype(np.int32))
+    assert step.max() <= 1 and (step != 0).mean() < 2e-3
+    tin.free(), tout.free()
+
+
+# --------------------------------------------------------------------------- the reference's operator test
+@pytest.mark.parametrize("index", [0, 1, 2, 3])
+def test_q8_load_and_linear_like_the_reference(oracle, index):
+    """tests/metal_q8.c:89-175: load bf16 from a file into Q8, stored bytes equal
+    the CPU packer's, linear + bias against the FP64 oracle, guard words, rejects,
+    dispatch counters."""
+    pack, lin = np.load(os.path.join(GOLDEN, "q8_pack.npz")), np.load(os.path.join(GOLDEN, "linear.npz"))
+    src, want_q, want_s = pack[f"src{index}"], pack[f"q{index}"], pack[f"s{index}"]
+    x, bias, want = lin[f"x{index}"], lin[f"bias{index}"], lin[f"out{index}"]
+    n, k = src.shape
+    m = x.shape[0]
+    gpu = h.Gpu()
+    with tempfile.NamedTemporaryFile(suffix=".bf16") as f:
+        f.write(src.tobytes())
+        f.flush()
+        w = gpu.q8_load(f.name, 0, n, k)
+        with pytest.raises(h.H3Error):
+            gpu.q8_load(f.name, 1, n, k)
+        with pytest.raises(h.H3Error):
+            gpu.q8_load(f.name, 0, 0xFFFFFFFF, 0xFFFFFFFF)
+        with pytest.raises(h.H3Error):
+            gpu.q8_load(f.name, 2, n, k)  # short read
+    offset = ((n * k + 3) & ~3) + 15 & ~15
+    blob = w.read(offset + want_s.size * 4, dtype=2)
+    assert (blob[:n * k].reshape(n, k) == want_q).all()
+    assert (blob[offset:].view(np.float32).view(np.uint32) == want_s.ravel().view(np.uint32)).all()
+    tx, tb = gpu.tensor_from_bf16(x), gpu.tensor_from_bf16(bias)
+    out = gpu.tensor_from_bf16(np.full(m * n + GUARD, 0x3F80, np.uint16))
+    for repeat in range(2):
+        gpu.begin()
+        gpu.linear_bf16(out, tx, w, tb, m, k, n)
+        gpu.submit()
+    got = out.read()
+    assert (got[m * n:] == 0x3F80).all()
+    assert rel_l2(got[:m * n], want.ravel()) < 0.006          # the reference's own gate
+    check_bf16(got[:m * n], want.ravel())
+    gpu.begin()
+    with pytest.raises(h.H3Error):
+        gpu.linear_bf16(out, tx, w, None, m, k, n + 1)
+    with pytest.raises(h.H3Error):
+        gpu.linear_bf16(tx, tx, w, None, m, k, n)
+    gpu.cancel()
+    assert (tx.read() == x.ravel()).all()
+    stats = gpu.stats()
+    assert stats.q8_weights == 1 and stats.q8_dispatches == 2
+    gpu.free()
+
+
+@pytest.mark.parametrize("scratch_rows", [0, 1])
+def test_queued_linears_share_scratch(scratch_rows):
+    """tests/metal_q8.c:42-87: distinct diagonal matrices queued in one command
+    scope; with the dequant-to-scratch policy they share one scratch buffer, so a
+    missing producer/consumer dependency would show as a wrong (exact) answer."""
+    gpu = h.Gpu()
+    gpu.set_w8a16_scratch_rows(scratch_rows)
+    with tempfile.NamedTemporaryFile(suffix=".bf16") as f:
+        for j in range(2):
+            f.write(synth.to_bf16(np.eye(64, dtype=np.float32) * (j + 1)).tobytes())
+        f.flush()
+        w = [gpu.q8_load(f.name, j * 64 * 64 * 2, 64, 64) for j in range(2)]
+    x = synth.to_bf16(np.arange(3 * 64, dtype=np.float32) - 100.0)
+    tx = gpu.tensor_from_bf16(x)
+    outs = [gpu.tensor_new_bf16(3 * 64) for _ in range(6)]
+    warm = None
+    for repeat in range(3):
+        gpu.begin()
+        for j in range(6):
+            gpu.linear_bf16(outs[j], tx, w[(j + repeat) % 2], None, 3, 64, 64)
+            if repeat and j % 2:
+                gpu.continue_()
+        gpu.submit()
+        for j in range(6):
+            want = synth.to_bf16(synth.from_bf16(x) * np.float32(1 + (j + repeat) % 2))
+            assert (outs[j].read() == want).all()
+        stats = gpu.stats()
+        if not repeat:
+            warm = stats
+        else:
+            assert stats.tensor_allocations == warm.tensor_allocations
+            assert stats.native_scratch_bytes == warm.native_scratch_bytes
+            if scratch_rows:
+                assert stats.native_scratch_reuses > warm.native_scratch_reuses
+    assert gpu.stats().q8_weights == 2 and gpu.stats().q8_dispatches == 18
+    gpu.free()
+
+
+# --------------------------------------------------------------------------- exact patterns
+def exact_pattern(M, N, K):
+    """Operands whose products and sums are exactly representable (the design of
+    tests/quant_native.c:30-52): powers of two by row/column bands."""
+    r, c, k = np.arange(M)[:, None], np.arange(N)[:, None], np.arange(K)[None, :]
+    x = (2.0 ** ((r + k) % 3 - 1)) * np.where((r + k) % 2, -1.0, 1.0)
+    wq = (2 ** ((c + k) % 4)).astype(np.int8) * np.where((c + 2 * k) % 3 == 0, -1, 1).astype(np.int8)
+    ws = (2.0 ** (-(np.arange(N) % 3) - 4)).astype(np.float32)[:, None]
+    return synth.to_bf16(x.astype(np.float32)).reshape(M, K), wq, ws
+
+
+@pytest.mark.parametrize("rows", [1, 3, 17, 129])
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS)
+def test_exact_patterns_bit_exact(gpu, oracle, rows, kernel):
+    N, K = 256, 512
+    x, wq, ws = exact_pattern(rows, N, K)
+    want = oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0)
+    assert (raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, kernel=kernel) == want).all()
+    wb = oracle.q8_dequant(wq, ws, 0)
+    assert (raw_linear(gpu, h.MODE_BF16, x, wb, kernel=kernel) == want).all()
+    xq, xs = oracle.quantize_rows(x)
+    want8, acc8 = oracle.linear(oracle.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, x_scales=xs, want_acc=True)
+    got8, gacc = raw_linear(gpu, h.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, xs=xs, kernel=kernel, want_acc=True)
+    assert (gacc == acc8).all() and (got8 == want8).all()
+
+
+def test_all_zero_input(gpu, oracle):
+    x = np.zeros((129, 256), np.uint16)
+    _, wq, ws = operands(3, 129, 128, 256, 0)
+    for kernel in (h.KERNEL_PLAIN, h.KERNEL_TCGEN05):
+        assert (raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, kernel=kernel) == 0).all()
+
+
+# --------------------------------------------------------------------------- randomised parity, ragged shapes
+SHAPES = [(1, 8, 16), (17, 40, 80), (129, 256, 256), (300, 520, 512), (128, 256, 64), (257, 264, 1040), (64, 3072, 3072)]
+
+
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("group,spec", [(0, ""), (64, "b"), (128, "ba"), (0, "gr"), (64, "bgra")])
+def test_w8a16_parity(gpu, oracle, M, N, K, group, spec, kernel):
+    x, wq, ws = operands(21, M, N, K, group)
+    bias, gate, res, act = epilogue_operands(21, M, N, spec)
+    want = oracle.linear(oracle.MODE_W8A16, x, wq, ws, group, bias=bias, gate=gate, residual=res, activation=act)
+    got = raw_linear(gpu, h.MODE_W8A16, x, wq, ws, group, bias=bias, gate=gate, residual=res, activation=act, kernel=kernel)
+    check_bf16(got, want)
+
+
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS)
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_bf16_parity(gpu, oracle, M, N, K, kernel):
+    x, wq, ws = operands(22, M, N, K, 64)
+    wb = oracle.q8_dequant(wq, ws, 64)
+    bias, gate, res, act = epilogue_operands(22, M, N, "bgr")
+    want = oracle.linear(oracle.MODE_BF16, x, wb, bias=bias, gate=gate, residual=res)
+    check_bf16(raw_linear(gpu, h.MODE_BF16, x, wb, bias=bias, gate=gate, residual=res, kernel=kernel), want)
+
+
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS)
+@pytest.mark.parametrize("M,N,K", [(1, 8, 16), (40, 24, 128), (130, 128, 256), (300, 520, 512), (257, 264, 1040), (64, 3072, 3072)])
+@pytest.mark.parametrize("spec", ["", "ba", "gr"])
+def test_w8a8_int32_exact_and_epilogue(gpu, oracle, M, N, K, spec, kernel):
+    x, wq, ws = operands(23, M, N, K, 0, outliers=True)
+    xq, xs = oracle.quantize_rows(x)
+    bias, gate, res, act = epilogue_operands(23, M, N, spec)
+    want, acc = oracle.linear(oracle.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, x_scales=xs, bias=bias, gate=gate, residual=res,
+                              activation=act, want_acc=True, fast=True)
+    got, gacc = raw_linear(gpu, h.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, xs=xs, bias=bias, gate=gate, residual=res,
+                           activation=act, kernel=kernel, want_acc=True)
+    assert (gacc == acc).all(), "int32 accumulators differ"
+    if act:
+        check_bf16(got, want)           # tanhf may differ in its last fp32 bit
+    else:
+        assert (got == want).all()      # identical accumulators and identical fp32 epilogue: identical bits
+
+
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN, h.KERNEL_TCGEN05])
+@pytest.mark.parametrize("M,N,K", [(40, 24, 256), (130, 128, 256), (300, 520, 512), (64, 3072, 3072)])
+def test_w8a8_group128_weight_scales(gpu, oracle, M, N, K, kernel):
+    """Config 3(b): per-group-128 weight scales.  No reference implementation
+    exists; pinned by exact int32 group sums combined in fp32 in ascending group
+    order (the order of src/metal/shaders.metal:2701-2741)."""
+    x, wq, ws = operands(24, M, N, K, 128, outliers=True)
+    xq, xs = oracle.quantize_rows(x)
+    bias = synth.bf16_normal(24, 4, 1, N, 0, 0.02)[0]
+    want = oracle.linear(oracle.MODE_W8A8, xq, wq, ws, 128, x_scales=xs, bias=bias, fast=True)
+    got = raw_linear(gpu, h.MODE_W8A8, xq, wq, ws, 128, xs=xs, bias=bias, kernel=kernel)
+    assert (got == want).all()
+
+
+def test_fixture_w8a8(gpu):
+    g = np.load(os.path.join(GOLDEN, "w8a8.npz"))
+    for i in range(3):
+        got, acc = raw_linear(gpu, h.MODE_W8A8, g[f"xq{i}"], g[f"wq{i}"], g[f"ws{i}"], 0, xs=g[f"xs{i}"], want_acc=True)
+        assert (acc == g[f"acc{i}"]).all() and (got == g[f"out{i}"]).all()
+
+
+# --------------------------------------------------------------------------- properties at benchmark size
+def sample_rows(M, count, seed):
+    rows = np.unique(np.concatenate([[0, M - 1, M // 2, 127, 128], np.random.default_rng(seed).integers(0, M, count)]))
+    return rows[rows < M]
+
+
+def test_config1_single_w8a16(gpu, oracle):
+    """X bf16 [4096,3072] N(0,1), W int8 [3072,3072], per-channel log-normal scales,
+    bf16 bias: sampled rows against the FP64 oracle, the whole output against the
+    plain kernel, and exact properties (doubling the input, row sharding)."""
+    M = N = K = 3072
+    M = 4096
+    x, wq, ws = operands(1, M, N, K, 0)
+    bias = synth.bf16_normal(1, 4, 1, N, 0, 0.02)[0]
+    got = raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, bias=bias, kernel=h.KERNEL_TCGEN05)
+    rows = sample_rows(M, 48, 1)
+    want = oracle.linear(oracle.MODE_W8A16, x[rows], wq, ws, 0, bias=bias)
+    check_bf16(got[rows], want)
+    plain = raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, bias=bias, kernel=h.KERNEL_PLAIN)
+    check_bf16(got, plain)
+    # doubling a bf16 input is exact, so without bias the output doubles exactly
+    base = raw_linear(gpu, h.MODE_W8A16, x[:512], wq, ws, 0, kernel=h.KERNEL_TCGEN05)
+    twice = raw_linear(gpu, h.MODE_W8A16, synth.to_bf16(synth.from_bf16(x[:512]) * np.float32(2)).reshape(512, K), wq, ws, 0,
+                       kernel=h.KERNEL_TCGEN05)
+    assert (synth.to_bf16(synth.from_bf16(base) * np.float32(2)).reshape(base.shape) == twice).all()
+    # token-row sharding: any split of the rows gives the same bits as the whole
+    for shards in (2, 8):
+        bounds = [M * i // shards for i in range(shards + 1)]
+        parts = [raw_linear(gpu, h.MODE_W8A16, x[a:b], wq, ws, 0, bias=bias, kernel=h.KERNEL_TCGEN05) for a, b in zip(bounds, bounds[1:])]
+        assert (np.concatenate(parts) == got).all()
+
+
+def test_config3_w8a8_outliers(oracle):
+    """W8A8 variant of config 1 through the operator layer: activation outliers,
+    per-token quantisation in a fused call, (a) per-channel and (b) group-128
+    weight scales, bias + GELU in the epilogue."""
+    M, N, K = 4096, 3072, 3072
+    x, wq, ws_group = operands(3, M, N, K, 128, outliers=True)
+    ws_channel = synth.lognormal_scales(3, 7, N, 1)
+    bias = synth.bf16_normal(3, 4, 1, N, 0, 0.02)[0]
+    xq, xs = oracle.quantize_rows(x)
+    for ws, group in ((ws_channel, 0), (ws_group, 128)):
+        gpu = h.Gpu()
+        gpu.quant_configure(2)
+        w = gpu.q8_from_host(wq, ws, group)
+        tx, tb, out = gpu.tensor_from_bf16(x), gpu.tensor_from_bf16(bias), gpu.tensor_new_bf16(M * N)
+        gpu.begin()
+        gpu.linear_fused_bf16(out, tx, w, tb, None, None, M, K, N, h.ACT_GELU_TANH)
+        gpu.submit()
+        got = out.read().reshape(M, N)
+        want = oracle.linear(oracle.MODE_W8A8, xq, wq, ws if group else ws[:, 0].copy(), group, x_scales=xs, bias=bias,
+                             activation=1, fast=True)
+        check_bf16(got, want)
+        assert (got != want).mean() < 1e-3   # only tanhf's last bit may differ
+        gpu.free()
+
+
+def test_config2_block_stack(oracle):
+    """One DiT block's four linears at M = 32,400 (hidden 3072, FFN 12288), W8A16
+    per-channel, fused epilogues, through the operator layer; sampled rows against
+    the oracle and both W8A16 policies against each other."""
+    M, H, F = 32400, 3072, 12288
+    rng = np.random.default_rng(2)
+    bf = lambda shape, mean=0.0, std=1.0: synth.to_bf16((rng.standard_normal(shape, dtype=np.float32) * np.float32(std) + np.float32(mean))).reshape(shape)
+    x, hidden, res = bf((M, H)), bf((M, F)), bf((M, H))
+    gate = bf((H,), 1.0, 0.1)
+    layers = [("qkv", x, 3 * H, None, None, 0), ("out", x, H, gate, res, 0), ("up", x, F, None, None, 1), ("down", hidden, H, gate, res, 0)]
+    rows = sample_rows(M, 24, 2)
+    results = {}
+    for policy_rows in (0, 1):
+        gpu = h.Gpu()
+        gpu.set_w8a16_scratch_rows(policy_rows)
+        for name, inp, n, g, r, act in layers:
+            k = inp.shape[1]
+            wq = rng.integers(-127, 128, (n, k), dtype=np.int8) if policy_rows == 0 else results[name][1]
+            ws = synth.lognormal_scales(2, hash(name) % 1000, n, 1) if policy_rows == 0 else results[name][2]
+            w = gpu.q8_from_host(wq, ws, 0)
+            tx, out = gpu.tensor_from_bf16(inp), gpu.tensor_new_bf16(M * n)
+            tg = gpu.tensor_from_bf16(g) if g is not None else None
+            tr = gpu.tensor_from_bf16(r) if r is not None else None
+            gpu.begin()
+            gpu.linear_fused_bf16(out, tx, w, None, tg, tr, M, k, n, act)
+            gpu.submit()
+            got = out.read().reshape(M, n)
+            if policy_rows == 0:
+                want = oracle.linear(oracle.MODE_W8A16, inp[rows], wq, ws, 0, gate=g, residual=None if r is None else r[rows], activation=act)
+                check_bf16(got[rows], want)
+                results[name] = (got, wq, ws)
+            else:
+                check_bf16(got, results[name][0])
+            for t in (w, tx, out, tg, tr):
+                if t is not None:
+                    t.free()
+        gpu.free()
+
+
+def test_config4_grouped_call(gpu, oracle):
+    """Video (K=N=3072) and audio (K=N=1536) problems with separate weight sets in
+    one grouped call (row counts scaled down; the two shapes are what matters)."""
+    specs = [(2 * 1296, 3072, 3072), (2 * 1152, 1536, 1536)]
+    problems, wants = [], []
+    for i, (M, N, K) in enumerate(specs):
+        x, wq, ws = operands(40 + i, M, N, K, 0)
+        w = gpu.q8_from_host(wq, ws, 0)
+        tx, out = gpu.tensor_from_bf16(x), gpu.tensor_new_bf16(M * N)
+        problems.append(dict(output=out, input=tx, weight=w, rows=M, input_dim=K, output_dim=N))
+        rows = sample_rows(M, 16, i)
+        wants.append((rows, oracle.linear(oracle.MODE_W8A16, x[rows], wq, ws, 0), M, N))
+    gpu.begin()
+    gpu.linear_grouped_bf16(problems)
+    gpu.submit()
+    for p, (rows, want, M, N) in zip(problems, wants):
+        check_bf16(p["output"].read().reshape(M, N)[rows], want)
+        for key in ("output", "input", "weight"):
+            p[key].free()
+
+
+def test_fused_equals_unfused_chain(gpu):
+    """linear -> gelu and linear -> gate as separate operators give the same bits
+    as the fused projection (the fused epilogue rounds where the chain rounds)."""
+    M, N, K = 300, 520, 512
+    x, wq, ws = operands(50, M, N, K, 64)
+    bias, gate, res, _ = epilogue_operands(50, M, N, "bgr")
+    w = gpu.q8_from_host(wq, ws, 64)
+    tx, tb, tg, tr = (gpu.tensor_from_bf16(a) for a in (x, bias, gate, res))
+    lin, act, chain, fused = (gpu.tensor_new_bf16(M * N) for _ in range(4))
+    gpu.begin()
+    gpu.linear_bf16(lin, tx, w, tb, M, K, N)
+    gpu.gelu_bf16(act, lin, M * N, 1)
+    gpu.gate_bf16(chain, tr, act, tg, None, M, N, 1, 0)
+    gpu.linear_fused_bf16(fused, tx, w, tb, tg, tr, M, K, N, h.ACT_GELU_TANH)
+    gpu.submit()
+    assert (chain.read() == fused.read()).all()
+    for t in (w, tx, tb, tg, tr, lin, act, chain, fused):
+        t.free()
+
+
+# --------------------------------------------------------------------------- interface behaviour
+def test_int8_operator_family_like_the_reference(oracle):
+    """h3_gpu_quantize_weight_int8 + h3_gpu_linear_int8_bf16 (src/metal/gpu.m:3174-3249):
+    per-channel weight scales from the row quantiser, caller-owned scratch padded
+    to 128 rows, rejects rows < 128 and K/N not multiples of 128."""
+    M, N, K = 200, 256, 384
+    x = synth.activations(60, 1, M, K).reshape(M, K)
+    wb = synth.bf16_normal(60, 2, N, K, 0, 0.05).reshape(N, K)
+    gpu = h.Gpu()
+    tw, wq, wsc = gpu.tensor_from_bf16(wb), gpu.tensor_new_i8(N * K), gpu.tensor_new_f32(N)
+    tx, out = gpu.tensor_from_bf16(x), gpu.tensor_new_bf16(M * N)
+    qin, qs = gpu.tensor_new_i8(256 * K), gpu.tensor_new_f32(256)
+    gpu.begin()
+    gpu.quantize_weight_int8(wq, wsc, tw, N, K)
+    gpu.linear_int8_bf16(out, qin, qs, tx, wq, wsc, M, K, N)
+    gpu.submit()
+    want_wq, want_ws = oracle.quantize_rows(wb)
+    assert (wq.read().reshape(N, K) == want_wq).all() and (wsc.read() == want_ws).all()
+    want_xq, want_xs = oracle.quantize_rows(x, 256)
+    assert (qin.read().reshape(256, K) == want_xq).all() and (qs.read() == want_xs).all()
+    want = oracle.linear(oracle.MODE_W8A8, want_xq[:M], want_wq, want_ws, 0, x_scales=want_xs[:M])
+    assert (out.read().reshape(M, N) == want).all()
+    gpu.begin()
+    for bad in ((100, K, N), (M, K + 64, N), (M, K, N + 64)):
+        with pytest.raises(h.H3Error):
+            gpu.linear_int8_bf16(out, qin, qs, tx, wq, wsc, *bad)
+    gpu.cancel()
+    gpu.free()
+
+
+def test_command_scope_and_errors():
+    gpu = h.Gpu()
+    assert gpu.backend_name() == "cuda-b200-q8"
+    x = gpu.tensor_from_bf16(np.zeros(64, np.uint16))
+    w = gpu.tensor_from_bf16(np.zeros(64 * 64, np.uint16))
+    out = gpu.tensor_new_bf16(64)
+    with pytest.raises(h.H3Error, match="requires h3_gpu_begin"):
+        gpu.linear_bf16(out, x, w, None, 1, 64, 64)
+    gpu.begin()
+    with pytest.raises(h.H3Error, match="already active"):
+        gpu.begin()
+    gpu.linear_bf16(out, x, w, None, 1, 64, 64)
+    gpu.submit()
+    other = h.Gpu()
+    foreign = other.tensor_new_bf16(64)
+    gpu.begin()
+    with pytest.raises(h.H3Error, match="another context"):
+        gpu.linear_bf16(foreign, x, w, None, 1, 64, 64)
+    with pytest.raises(h.H3Error):
+        gpu.linear_bf16(out, x, w, None, 0, 64, 64)
+    gpu.cancel()
+    gpu.begin()          # the context is reusable after cancel
+    gpu.submit()
+    other.free()
+    gpu.free()
+
+
+def test_nonfinite_activation_reported_at_submit(oracle):
+    """tests/quant_native.c:64-74: a non-finite input fails at submit, cancel recovers."""
+    M, N, K = 128, 128, 128
+    x, wq, ws = operands(70, M, N, K, 0)
+    gpu = h.Gpu()
+    gpu.quant_configure(2)
+    w = gpu.q8_from_host(wq, ws, 0)
+    bad = x.copy()
+    bad[5, 7] = 0x7F80
+    tx, out = gpu.tensor_from_bf16(bad), gpu.tensor_new_bf16(M * N)
+    gpu.begin()
+    gpu.linear_fused_bf16(out, tx, w, None, None, None, M, K, N, 0)
+    with pytest.raises(h.H3Error, match="non-finite"):
+        gpu.submit()
+    gpu.cancel()
+    tx.write(x)
+    gpu.begin()
+    gpu.linear_fused_bf16(out, tx, w, None, None, None, M, K, N, 0)
+    gpu.submit()
+    xq, xs = oracle.quantize_rows(x)
+    assert (out.read().reshape(M, N) == oracle.linear(oracle.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, x_scales=xs)).all()
+    gpu.free()
+
+
+def test_allocation_budget_fault_injection(monkeypatch):
+    """Host-side fault injection as in the reference (H3_CUDA_TEST_MEMORY_BUDGET,
+    src/weights/residency.c:31-32): allocations beyond the budget fail cleanly and
+    the planner answers 'streamed' or 'insufficient' without touching the device."""
+    monkeypatch.setenv("H3_CUDA_TEST_MEMORY_BUDGET", str(1 << 20))
+    gpu = h.Gpu()
+    small = gpu.tensor_new_bf16(1024)
+    with pytest.raises(h.H3Error, match="out of memory"):
+        gpu.tensor_new_bf16(1 << 20)
+    lib = h.library()
+    assert lib.h3_gpu_plan_weights(gpu.handle, 1 << 10, 1 << 10) == 0
+    assert lib.h3_gpu_plan_weights(gpu.handle, 1 << 30, 1 << 10) == 1
+    assert lib.h3_gpu_plan_weights(gpu.handle, 1 << 10, 1 << 30) == -1
+    small.free()
+    gpu.free()
+
+
+def test_launch_counter_moves(gpu):
+    before = h.library().h3q8_kernel_launches()
+    x, wq, ws = operands(80, 128, 128, 128, 0)
+    raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, kernel=h.KERNEL_TCGEN05)
+    assert h.library().h3q8_kernel_launches() == before + 1

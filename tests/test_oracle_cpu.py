@@ -1,0 +1,166 @@
+"""CPU checks that pin the oracle (oracle/h3q8_oracle.c) before it is trusted:
+the reference's golden vectors, the reference's own packer compiled as-is, and
+the committed fixtures.  Mirrors the host half of h3cli's tests/metal_q8.c."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def test_bf16_round_to_nearest_even(oracle):
+    # src/metal/shaders.metal:15-19
+    cases = {1.0: 0x3F80, 1.00390625: 0x3F80, 1.01171875: 0x3F82, -2.5: 0xC020, 0.0: 0, 3.3895313892515355e38: 0x7F7F}
+    for value, bits in cases.items():
+        assert oracle.lib().h3o_f32_to_bf16(value) == bits
+    x = np.random.default_rng(0).standard_normal(4096).astype(np.float32)
+    bits = oracle.f32_to_bf16(x)
+    assert all(oracle.lib().h3o_f32_to_bf16(float(v)) == b for v, b in zip(x[:256], bits[:256]))
+    assert (oracle.f32_to_bf16(oracle.bf16_to_f32(bits)) == bits).all()
+
+
+def test_packer_known_answers(oracle):
+    # tests/metal_q8.c:21-34
+    values = np.zeros((1, 65), np.float32)
+    values[0, :8] = [127, -127, .5, 1.5, 2.5, -.5, -1.5, -2.5]
+    src = oracle.f32_to_bf16(values).reshape(1, 65)
+    q, s = oracle.q8_pack_rows(src, 64)
+    assert q[0, :8].tolist() == [127, -127, 0, 2, 2, 0, -2, -2]
+    assert (s == 1.0).all() and q[0, 64] == 0
+    assert oracle.q8_layout(1, 65, 64) == (68, 76)
+    assert oracle.q8_layout(0, 65, 64) is None
+    assert oracle.q8_layout(0xFFFFFFFF, 0xFFFFFFFF, 64) is None
+    assert oracle.q8_layout(1, 0xFFFFFFFF - 31, 64) is None
+    for bad in (0x7FC0, 0x7F80):  # NaN, Inf
+        src[0, 64] = bad
+        assert oracle.q8_pack_rows(src, 64) is None
+    src[0, 64] = 1  # subnormal accepted, scale stays finite and normal
+    q, s = oracle.q8_pack_rows(src, 64)
+    assert np.isfinite(s).all() and s[0, 1] >= np.finfo(np.float32).tiny
+
+
+def test_packer_matches_reference_build(oracle):
+    ref = oracle.reference_q8()
+    if ref is None:
+        pytest.skip("oracle/_ref was not built (no reference tree); the committed fixtures cover this")
+    rng = np.random.default_rng(5)
+    for rows, cols in [(1, 1), (3, 63), (17, 65), (67, 129), (33, 256), (8, 1000)]:
+        w = oracle.f32_to_bf16((rng.standard_normal((rows, cols)) * 0.125).astype(np.float32)).reshape(rows, cols)
+        w[0, 0] = 0
+        if cols > 64:
+            w[rows - 1, :64] = 0  # an all-zero group: scale 1
+        q, s = oracle.q8_pack_rows(w, 64)
+        q2 = np.empty_like(q)
+        s2 = np.empty_like(s)
+        assert ref.h3_q8_pack_rows(w.ctypes.data, q2.ctypes.data, s2.ctypes.data, rows, cols)
+        assert (q == q2).all() and (s.view(np.uint32) == s2.view(np.uint32)).all()
+        off, total = ctypes.c_size_t(), ctypes.c_size_t()
+        assert ref.h3_q8_layout(rows, cols, ctypes.byref(off), ctypes.byref(total))
+        assert oracle.q8_layout(rows, cols, 64) == (off.value, total.value)
+
+
+def test_packer_matches_committed_fixtures(oracle):
+    g = np.load(os.path.join(GOLDEN, "q8_pack.npz"))
+    q, s = oracle.q8_pack_rows(g["known_src"], 64)
+    assert (q == g["known_q"]).all() and (s == g["known_s"]).all()
+    for i in range(4):
+        q, s = oracle.q8_pack_rows(g[f"src{i}"], 64)
+        assert (q == g[f"q{i}"]).all()
+        assert (s.view(np.uint32) == g[f"s{i}"].view(np.uint32)).all()
+
+
+def test_group_parameter(oracle):
+    rng = np.random.default_rng(6)
+    w = oracle.f32_to_bf16(rng.standard_normal((9, 384)).astype(np.float32)).reshape(9, 384)
+    for group, groups in [(0, 1), (64, 6), (128, 3), (256, 2)]:
+        q, s = oracle.q8_pack_rows(w, group)
+        assert s.shape == (9, groups)
+        width = group or 384
+        wf = oracle.bf16_to_f32(w).reshape(9, 384)
+        for g in range(groups):
+            peak = np.abs(wf[:, g * width:(g + 1) * width]).max(axis=1)
+            assert np.array_equal(s[:, g], np.maximum(peak / np.float32(127.0), np.finfo(np.float32).tiny).astype(np.float32))
+        assert np.abs(q).max() <= 127
+        deq = oracle.bf16_to_f32(oracle.q8_dequant(q, s, group)).reshape(9, 384)
+        assert np.abs(deq - wf).max() <= s.max() * 0.51 + np.abs(wf).max() * 2 ** -8
+
+
+def test_row_quantiser(oracle):
+    # src/metal/shaders.metal:1391-1460
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((6, 130)).astype(np.float32)
+    x[1] = 0.0
+    x[2, 5] *= 20
+    xb = oracle.f32_to_bf16(x).reshape(6, 130)
+    q, s = oracle.quantize_rows(xb, dispatch_rows=8)
+    xf = oracle.bf16_to_f32(xb).reshape(6, 130)
+    peak = np.abs(xf).max(axis=1)
+    assert s[1] == np.float32(1.0) / np.float32(127.0) and (q[1] == 0).all()     # zero row
+    assert (s[6:] == 1.0).all() and (q[6:] == 0).all()                           # padding rows
+    live = [0, 2, 3, 4, 5]
+    assert np.array_equal(s[live], (peak[live] / np.float32(127.0)).astype(np.float32))
+    inverse = (np.float32(127.0) / peak[live]).astype(np.float32)
+    expect = np.clip(np.rint((xf[live] * inverse[:, None]).astype(np.float32)), -127, 127).astype(np.int8)
+    assert (q[live] == expect).all()
+    assert np.abs(q[live]).max(axis=1).tolist() == [127] * 5
+    # ties go to even: x = 2.5 * max/127 ... use exact powers of two
+    t = np.array([[127.0, 0.5, 1.5, 2.5, -0.5, -1.5, -2.5, 63.5]], np.float32)
+    q, s = oracle.quantize_rows(oracle.f32_to_bf16(t).reshape(1, 8))
+    assert s[0] == 1.0 and q[0].tolist() == [127, 0, 2, 2, 0, -2, -2, 64]
+
+
+def test_epilogue_operators(oracle):
+    lib = oracle.lib()
+    # src/cuda/cuda_kernels.cuh:883-893: saturation guards and the tanh branch
+    for v in (-40.0, -12.0, 12.0, 40.0, 0.0, 1.0, -1.0, 3.0):
+        b = int(oracle.f32_to_bf16(np.float32(v))[()] if np.ndim(oracle.f32_to_bf16(np.float32(v))) == 0 else oracle.f32_to_bf16(np.array([v], np.float32))[0])
+        got = oracle.bf16_to_f32(np.array([lib.h3o_gelu_tanh_bf16(b)], np.uint16))[0]
+        x = oracle.bf16_to_f32(np.array([b], np.uint16))[0].astype(np.float64)
+        want = 0.5 * x * (1 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+        assert abs(got - want) <= abs(want) * 2 ** -8 + 1e-30
+    # src/cuda/cuda_kernels.cuh:979-984
+    r, b, g = (int(oracle.f32_to_bf16(np.array([v], np.float32))[0]) for v in (0.75, -1.5, 1.125))
+    got = oracle.bf16_to_f32(np.array([lib.h3o_gate_residual_bf16(r, b, g)], np.uint16))[0]
+    assert got == oracle.bf16_to_f32(oracle.f32_to_bf16(np.array([0.75 + (-1.5 * 1.125)], np.float32)))[0]
+
+
+def test_linear_fixture_and_fast_path(oracle):
+    pack = np.load(os.path.join(GOLDEN, "q8_pack.npz"))
+    lin = np.load(os.path.join(GOLDEN, "linear.npz"))
+    for i in range(4):
+        out = oracle.linear(oracle.MODE_W8A16, lin[f"x{i}"], pack[f"q{i}"], pack[f"s{i}"], 64, bias=lin[f"bias{i}"])
+        assert (out == lin[f"out{i}"]).all()
+        fast = oracle.linear(oracle.MODE_W8A16, lin[f"x{i}"], pack[f"q{i}"], pack[f"s{i}"], 64, bias=lin[f"bias{i}"], fast=True)
+        a, e = oracle.bf16_to_f32(fast).astype(np.float64), oracle.bf16_to_f32(out).astype(np.float64)
+        assert np.sqrt(((a - e) ** 2).sum() / max((e ** 2).sum(), 1e-30)) < 2e-3
+
+
+def test_w8a8_fixture(oracle):
+    g = np.load(os.path.join(GOLDEN, "w8a8.npz"))
+    for i in range(3):
+        xq, xs = oracle.quantize_rows(g[f"x{i}"])
+        assert (xq == g[f"xq{i}"]).all() and (xs.view(np.uint32) == g[f"xs{i}"].view(np.uint32)).all()
+        for fast in (False, True):
+            out, acc = oracle.linear(oracle.MODE_W8A8, xq, g[f"wq{i}"], g[f"ws{i}"], 0, x_scales=xs, want_acc=True, fast=fast)
+            assert (acc == g[f"acc{i}"]).all() and (out == g[f"out{i}"]).all()
+        # epilogue order: (float(acc) * in_scale) * w_scale, src/metal/shaders.metal:2463-2464
+        want = (g[f"acc{i}"].astype(np.float32) * xs[:, None]).astype(np.float32) * g[f"ws{i}"][None, :]
+        assert (oracle.f32_to_bf16(want.astype(np.float32)).reshape(out.shape) == out).all()
+
+
+def test_w8a8_grouped_combine_order(oracle):
+    rng = np.random.default_rng(9)
+    xq = rng.integers(-127, 128, (7, 512)).astype(np.int8)
+    wq = rng.integers(-127, 128, (5, 512)).astype(np.int8)
+    xs = rng.uniform(0.01, 0.05, 7).astype(np.float32)
+    ws = rng.uniform(0.005, 0.02, (5, 4)).astype(np.float32)
+    out = oracle.linear(oracle.MODE_W8A8, xq, wq, ws, 128, x_scales=xs)
+    total = None
+    for gidx in range(4):  # src/metal/shaders.metal:2727-2735: first group assigns, later groups add, in order
+        acc = xq[:, gidx * 128:(gidx + 1) * 128].astype(np.int32) @ wq[:, gidx * 128:(gidx + 1) * 128].astype(np.int32).T
+        value = ((acc.astype(np.float32) * xs[:, None]).astype(np.float32) * ws[None, :, gidx]).astype(np.float32)
+        total = value if total is None else (total + value).astype(np.float32)
+    assert (oracle.f32_to_bf16(total).reshape(7, 5) == out).all()
+    assert (oracle.linear(oracle.MODE_W8A8, xq, wq, ws, 128, x_scales=xs, fast=True) == out).all()
