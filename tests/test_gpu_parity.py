@@ -111,18 +111,30 @@ def test_device_packer_and_dequant_bit_exact(gpu, oracle, rows, cols, group):
 
 
 def test_gelu_operator_all_bf16_inputs(gpu, oracle):
-    """Every finite bf16 input through h3_gpu_gelu_bf16 against the oracle's tanh-GELU."""
+    """Every finite bf16 input through h3_gpu_gelu_bf16 against the oracle's tanh-GELU
+    (src/cuda/cuda_kernels.cuh:883-893).
+
+    The device evaluates 0.5 v (1 + tanh u) as v / (1 + exp(-2u)).  Where tanh u is
+    within 2^-24 of -1 the reference's own fp32 expression 1 + tanhf(u) cancels to
+    noise of about 2^-25 |v| (it returns exactly 0 below u = -8.7), so outputs there
+    are compared on that absolute scale; everywhere else within one bf16 step."""
     bits = np.arange(65536, dtype=np.uint32).astype(np.uint16)
-    finite = np.isfinite(bf16_to_f32(bits))
+    v = bf16_to_f32(bits).astype(np.float64)
+    finite = np.isfinite(v)
     tin, tout = gpu.tensor_from_bf16(bits), gpu.tensor_new_bf16(65536)
     gpu.begin()
     gpu.gelu_bf16(tout, tin, 65536, 1)
     gpu.submit()
-    got = tout.read()
-    want = oracle.gelu_tanh_bf16(bits)
-    # device tanhf and libm tanhf may differ in the last fp32 bit: allow one bf16 step, rarely
-    step = np.abs(got[finite].astype(np.int32) - want[finite].astype(np.int32))
-    assert step.max() <= 1 and (step != 0).mean() < 2e-3
+    got_bits, want_bits = tout.read(), oracle.gelu_tanh_bf16(bits)
+    got, want = bf16_to_f32(got_bits).astype(np.float64), bf16_to_f32(want_bits).astype(np.float64)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(want), 1e-300))) - 7)
+    allowed = np.maximum(ulp, np.abs(v) * 2.0 ** -23)
+    error = np.abs(got - want)
+    assert (error[finite] <= allowed[finite]).all()
+    assert (got_bits[finite] != want_bits[finite]).mean() < 0.02
+    exact = np.abs(v) < 3.0          # away from the cancellation region the stored bits agree almost always
+    assert (got_bits[finite & exact] != want_bits[finite & exact]).mean() < 2e-3
     tin.free(), tout.free()
 
 
