@@ -142,6 +142,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="h3q8")
+    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS],
+                    help="profiling aid: run only this projection (with --rows) and print a short line")
+    ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -183,6 +186,9 @@ def main():
             view[r0 * cols:r1 * cols].copy_(block.to(torch.bfloat16).reshape(-1))
         torch.cuda.synchronize()
         return t
+
+    if args.case:
+        return run_case(args, gpu, lib, stream, device_bf16)
 
     # ---- operands (weights replicated on every rank: same seed) ----------------------------------
     weights, inputs, outputs, gates, residuals = {}, {}, {}, {}, {}
@@ -307,6 +313,32 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    gpu.free()
+
+
+def run_case(args, gpu, lib, stream, device_bf16):
+    """One projection at --rows rows: the small workload used under ncu."""
+    import torch
+    name, k, n, spec = next(layer for layer in LAYERS if layer[0] == args.case)
+    rows = args.rows
+    wgen = np.random.default_rng(42)
+    wq = wgen.integers(-127, 128, (n, k), dtype=np.int8)
+    ws = np.exp(wgen.normal(np.log(0.01), 0.3, (n, 1))).astype(np.float32)
+    weight = gpu.q8_from_host(wq, ws, 0)
+    x, out = device_bf16(rows, k, seed=1), gpu.tensor_new_bf16(rows * n)
+    residual = device_bf16(rows, n, seed=3) if "r" in spec else None
+    gate = device_bf16(1, n, 1.0, 0.1, seed=4) if "g" in spec else None
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gpu.begin()
+    for i in range(args.warmup + args.steps):
+        if i == args.warmup:
+            start.record(stream)
+        gpu.linear_fused_bf16(out, x, weight, None, gate, residual, rows, k, n, 1 if "a" in spec else 0)
+    stop.record(stream)
+    gpu.submit()
+    ms = start.elapsed_time(stop) / args.steps
+    print(json.dumps({"case": name, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * n / ms / 1e9,
+                      "launches": int(lib.h3q8_kernel_launches())}), flush=True)
     gpu.free()
 
 
