@@ -1,0 +1,74 @@
+"""The N > 1 host logic on CPU ranks (gloo, world size 2): the row-sharding plan,
+the "concatenation of shard outputs equals the whole" property that makes the
+multi-GPU path collective-free, and the max-over-ranks timing reduce that
+bench.py uses.  Each rank computes its shard with the CPU oracle (the checker
+stands in for the GPU here; the GPU-side version of the same property is in
+test_gpu_parity.py::test_config1_single_w8a16)."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from h3cli_b200 import sharding, synth  # noqa: E402
+
+
+def test_row_ranges_partition_and_align():
+    for rows in (1, 127, 128, 129, 4096, 32400, 219600):
+        for world in (1, 2, 3, 4, 8):
+            ranges = sharding.all_ranges(rows, world)
+            assert ranges[0][0] == 0 and ranges[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))
+            assert all(e >= b for b, e in ranges)
+            if rows >= 128 * world * 4:
+                assert all(b % 128 == 0 for b, _ in ranges)
+                sizes = [e - b for b, e in ranges]
+                assert max(sizes) - min(sizes) <= 256
+    with pytest.raises(ValueError):
+        sharding.row_range(10, 2, 2)
+
+
+def _worker(rank, world, port, result_queue):
+    import torch
+    import torch.distributed as dist
+    import oracle
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    M, N, K = 517, 48, 192
+    x = synth.activations(5, 1, M, K).reshape(M, K)         # every rank can regenerate any rows
+    wq, ws = synth.int8_weights(5, 2, N, K), synth.lognormal_scales(5, 3, N, 3)
+    begin, end = sharding.row_range(M, rank, world)
+    mine = synth.activations(5, 1, end - begin, K, row0=begin).reshape(end - begin, K)
+    assert (mine == x[begin:end]).all()                     # counter-based generator: shard == slice
+    part = oracle.linear(oracle.MODE_W8A16, mine, wq, ws, 64, activation=1)
+    padded = np.zeros((M, N), np.int32)
+    padded[begin:end] = part
+    gathered = torch.from_numpy(padded)
+    dist.all_reduce(gathered)                               # shards are disjoint: the sum is the concatenation
+    seconds = torch.tensor([0.5 + rank], dtype=torch.float64)
+    dist.all_reduce(seconds, op=dist.ReduceOp.MAX)          # job time = slowest rank
+    if rank == 0:
+        whole = oracle.linear(oracle.MODE_W8A16, x, wq, ws, 64, activation=1)
+        result_queue.put((bool((gathered.numpy() == whole.astype(np.int32)).all()), float(seconds.item())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_sharded_linear_equals_whole():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, queue)) for r in range(2)]
+    for p in procs:
+        p.start()
+    same, seconds = queue.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert same and seconds == 1.5
