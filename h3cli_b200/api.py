@@ -72,6 +72,7 @@ def library():
         "h3q8_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32, u32]),
         "h3q8_linear": (C.c_int, [C.POINTER(LinearDesc), vp]),
         "h3q8_linear_grouped": (C.c_int, [C.POINTER(LinearDesc), u32, vp]),
+        "h3q8_linear_w8a8_static": (C.c_int, [C.POINTER(LinearDesc), vp, vp]),
         "h3q8_quantize_rows": (C.c_int, [vp, vp, vp, u32, u32, u32, C.c_float, vp]),
         "h3q8_q8_pack_rows_device": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
         "h3q8_q8_dequant": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),

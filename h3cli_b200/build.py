@@ -39,7 +39,7 @@ def build(force=False, verbose=False):
     run(["gcc", "-O2", "-std=c11", "-fPIC", "-ffp-contract=off", "-I", include, "-c",
          os.path.join(CSRC, "q8_pack.c"), "-o", pack_o])
     objects = [pack_o]
-    for unit in ("h3q8_raw.cu", "h3_gpu.cu"):
+    for unit in ("h3q8_raw.cu", "h3_gpu.cu", "h3q8_static.cu"):
         obj = os.path.join(build_dir, unit.replace(".cu", ".o"))
         run([_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-I", include, "-I", CSRC, "-c",
              os.path.join(CSRC, unit), "-o", obj])

@@ -79,6 +79,24 @@ int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream);
  * every problem is enqueued back to back on the stream with no host sync. */
 int h3q8_linear_grouped(const h3q8_linear_desc *problems, uint32_t count, void *cuda_stream);
 
+/* W8A8 projection that allocates nothing (no counterpart in the reference).
+ * For callers that may not call cudaMalloc at all -- a render loop that has
+ * given all of HBM to its own pools, code running inside another library's
+ * callback, a process with a fixed, audited memory budget.  desc->input is the
+ * bf16 [M,K] activation matrix; it is quantised per token into a scratch array
+ * that is part of the library's device image, then multiplied by the int8
+ * weight with the usual fused epilogue.  Limits: rows <= H3Q8_STATIC_MAX_ROWS
+ * and rows * input_dim <= H3Q8_STATIC_MAX_ACTIVATION_BYTES (larger problems are
+ * refused), per-channel weight scales, input_dim % 16 == 0, output_dim % 8 == 0.
+ * Every GPU that loads the library holds that array until exit.  All calls on a
+ * device share it: calls that overlap on the GPU race.  The first call on a
+ * device looks up the array's address and configures the kernel; make it
+ * outside stream capture.  device_status may be NULL, or a zeroed device word
+ * that receives a code if a bounded wait inside the kernel runs out. */
+#define H3Q8_STATIC_MAX_ACTIVATION_BYTES (16u << 20)
+#define H3Q8_STATIC_MAX_ROWS 16384u
+int h3q8_linear_w8a8_static(const h3q8_linear_desc *desc, uint32_t *device_status, void *cuda_stream);
+
 /* Per-token dynamic int8 quantiser (src/metal/shaders.metal:1391-1460):
  * scale = max|x|/127 (1/127 for a zero row), q = clamp(rint(x * (127/max))).
  * Rows in [rows, dispatch_rows) are padding: zero bytes, scale 1. */
