@@ -128,10 +128,12 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def workload_config():
+def workload_config(mode="w8a16"):
     return {"workload": "DiT block linear stack (BASELINE config 2): M=32400 tokens per GPU, hidden 3072, FFN 12288, "
-                        "W8A16 int8 weights with per-channel fp32 scales; QKV, attn-out(+gate,+residual), "
-                        "FFN-up(GELU-tanh), FFN-down(+gate,+residual)",
+                        + ("W8A16 int8 weights with per-channel fp32 scales" if mode == "w8a16" else
+                           "W8A8: int8 weights with per-channel scales, activations quantised per token in a fused kernel")
+                        + "; QKV, attn-out(+gate,+residual), FFN-up(GELU-tanh), FFN-down(+gate,+residual)",
+            "mode": mode,
             "rows_per_gpu": M_TOKENS, "hidden": HIDDEN, "ffn": FFN, "l2": "inputs_exceed_l2 (>= 199 MB per operand vs 126 MB L2)",
             "parallelism": "token-row sharding, weights replicated, no collective"}
 
@@ -145,6 +147,8 @@ def main():
     ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS],
                     help="profiling aid: run only this projection (with --rows) and print a short line")
     ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
+    ap.add_argument("--mode", default="w8a16", choices=["w8a16", "w8a8"],
+                    help="w8a16 (default, BASELINE config 2) or the W8A8 variant: per-token int8 activations, int8 MMAs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
@@ -163,7 +167,7 @@ def main():
     from h3cli_b200 import api
 
     gpu = h.Gpu()
-    gpu.quant_configure(1)
+    gpu.quant_configure(2 if args.mode == "w8a8" else 1)
     gpu.set_w8a16_scratch_rows(int(os.environ.get("H3Q8_W8A16_SCRATCH_ROWS", "1024")))
     stream = torch.cuda.ExternalStream(gpu.stream, device=local)
     lib = h.library()
@@ -292,7 +296,7 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": job_seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": workload_config(),
+            "dtype": "bf16" if args.mode == "w8a16" else "int8", "data": "synthetic", "config": workload_config(args.mode),
             "dit_block_linear_ms": job_seconds / args.steps * 1e3,
             "tensor_peak_fraction_per_gpu": value / world / burst,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": M_TOKENS * HIDDEN * 2,
@@ -301,7 +305,8 @@ def main():
                             "-> h3_gpu_submit -> h3_gpu_tensor_read_bf16, pinned host buffers"},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16, 128x256> after q8_dequant_kernel",
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16, 128x256> after q8_dequant_kernel" if args.mode == "w8a16"
+                         else "gemm_tcgen05_kernel<int8, 128x256> after quantize_rows_kernel (peak is the bf16 figure; no int8 peak is recorded)",
                          "achieved": achieved, "peak": burst, "unit": UNIT, "frac": achieved / burst if achieved else None,
                          "peak_source": f"bf16_tflops (burst) of {which}", "frac_of_sustained": achieved / sustained if achieved and sustained else None,
                          "launches": int(gemm_launches), "avg_launch_ms": gemm_seconds / max(gemm_launches, 1) * 1e3,
@@ -337,7 +342,7 @@ def run_case(args, gpu, lib, stream, device_bf16):
     stop.record(stream)
     gpu.submit()
     ms = start.elapsed_time(stop) / args.steps
-    print(json.dumps({"case": name, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * n / ms / 1e9,
+    print(json.dumps({"case": name, "mode": args.mode, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * n / ms / 1e9,
                       "launches": int(lib.h3q8_kernel_launches())}), flush=True)
     gpu.free()
 
