@@ -28,16 +28,41 @@ struct EpilogueParams {
     uint32_t activation;
 };
 
+/* Branch-free so that the compiler can interleave many elements per thread. */
 __device__ __forceinline__ float gelu_tanh_f32(float v) {
-    float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
-    float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(v, cube));
-    if (inner <= -10.0f) return 0.0f;
-    if (inner >= 10.0f) return v;
+    const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
+    const float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(v, cube));
     /* 0.5 v (1 + tanh u) == v / (1 + exp(-2u)).  The exponential and the division
      * use the hardware approximations (relative error about 1e-6), far inside the
      * bf16 rounding that follows; against a correctly rounded tanhf the stored
      * bf16 differs by one step for a few outputs in ten thousand. */
-    return __fdividef(v, 1.0f + __expf(-2.0f * inner));
+    float r = __fdividef(v, 1.0f + __expf(-2.0f * inner));
+    r = inner <= -10.0f ? 0.0f : r;   /* the reference's saturation guards */
+    r = inner >= 10.0f ? v : r;
+    return r;
+}
+
+/* Round two fp32 values to bf16 (nearest even, one cvt.rn.bf16x2.f32) and keep them
+ * packed: low half = first value.  Equal to the reference's bit recipe for every
+ * finite input. */
+__device__ __forceinline__ uint32_t pack_bf16_pair(float lo, float hi) {
+    uint32_t packed;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+    return packed;
+}
+__device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t packed) { return __uint_as_float(packed & 0xffff0000u); }
+
+/* Two adjacent outputs at once.  lin*: fp32 linear results before bias; bias, gate,
+ * residual: packed bf16 pairs.  Returns the final packed bf16 pair. */
+__device__ __forceinline__ uint32_t epilogue_pair(float lin0, float lin1, uint32_t bias, bool has_bias, uint32_t activation,
+                                                  bool gated, uint32_t gate, uint32_t residual) {
+    if (has_bias) { lin0 = __fadd_rn(lin0, bf16_lo(bias)); lin1 = __fadd_rn(lin1, bf16_hi(bias)); }
+    uint32_t y = pack_bf16_pair(lin0, lin1);
+    if (activation == ACT_GELU_TANH) y = pack_bf16_pair(gelu_tanh_f32(bf16_lo(y)), gelu_tanh_f32(bf16_hi(y)));
+    if (gated) y = pack_bf16_pair(__fadd_rn(bf16_lo(residual), __fmul_rn(bf16_lo(y), bf16_lo(gate))),
+                                  __fadd_rn(bf16_hi(residual), __fmul_rn(bf16_hi(y), bf16_hi(gate))));
+    return y;
 }
 
 /* linear: fp32 linear result before bias.  Returns the final bf16 bits. */

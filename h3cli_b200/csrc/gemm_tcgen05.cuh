@@ -297,15 +297,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 *reinterpret_cast<uint4 *>(res) = *reinterpret_cast<const uint4 *>(p.ep.residual + (size_t)row * p.N + col);
                             uint32_t packed[4];
 #pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                uint32_t lo = epilogue_value(lin[2 * j], bf16_bits_to_f32(bias[j] & 0xffffu), p.ep.bias != nullptr,
-                                                             p.ep.activation, gated, bf16_bits_to_f32(gate[j] & 0xffffu),
-                                                             bf16_bits_to_f32(res[j] & 0xffffu));
-                                uint32_t hi = epilogue_value(lin[2 * j + 1], bf16_bits_to_f32(bias[j] >> 16), p.ep.bias != nullptr,
-                                                             p.ep.activation, gated, bf16_bits_to_f32(gate[j] >> 16),
-                                                             bf16_bits_to_f32(res[j] >> 16));
-                                packed[j] = lo | (hi << 16);
-                            }
+                            for (int j = 0; j < 4; j++)
+                                packed[j] = epilogue_pair(lin[2 * j], lin[2 * j + 1], bias[j], p.ep.bias != nullptr, p.ep.activation,
+                                                          gated, gate[j], res[j]);
                             *reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + col) = *reinterpret_cast<uint4 *>(packed);
                         }
                     }
