@@ -16,8 +16,8 @@
  * Accumulators are double-buffered in TMEM whenever 2*MT*BN <= 512 columns so
  * the epilogue of one tile overlaps the main loop of the next.
  *
- * No cluster launch and no TMA multicast: every CTA fetches its own tiles and
- * tiles that share weights are co-scheduled so they meet in L2.
+ * Every CTA fetches its own operand tiles; tiles that share weights are
+ * co-scheduled so they meet in L2.
  */
 #pragma once
 #include "epilogue.cuh"

@@ -1,0 +1,219 @@
+/* Two-CTA variant of the tcgen05 GEMM: a cluster of two CTAs (one SM each)
+ * computes a 256 x 256 output tile with `tcgen05.mma.cta_group::2`.
+ *
+ * Why: with one CTA per tile every 128 x 256 x 16 MMA reads 12 KB of operands
+ * from that SM's shared memory while TMA writes the same amount, and shared
+ * memory bandwidth (not the tensor pipe) sets the pace.  In a pair each CTA
+ * stages its own 128 rows of A and only HALF of the weight tile (128 of the 256
+ * output channels); the tensor cores of the two SMs exchange the B halves, so
+ * per-SM shared-memory traffic per flop drops by a third and the stage shrinks
+ * from 48 KB to 32 KB (6 stages instead of 4).
+ *
+ * Protocol (leader = CTA rank 0 of the pair):
+ *   - both CTAs run a TMA producer for their own tiles; completion bytes of both
+ *     are counted on the leader's `full` barrier (the loads carry `.cta_group::2`
+ *     and name the leader's barrier); each CTA has its own `empty` barriers
+ *   - only the leader issues MMAs; `tcgen05.commit` arrives on the `empty` /
+ *     `tfull` barriers of both CTAs at once
+ *   - both CTAs run the epilogue on their own 128 accumulator rows (their own
+ *     TMEM); epilogue warps of both arrive on the leader's `tempty` barrier
+ *   - TMEM is allocated and freed by the same warp of both CTAs; a cluster
+ *     barrier brackets the kernel so that neither CTA leaves while the other can
+ *     still touch its shared memory or TMEM
+ * Modes: MODE_BF16 and MODE_W8A8 (per-channel scales).  All waits are bounded
+ * as in the single-CTA kernel.
+ */
+#pragma once
+#include "gemm_tcgen05.cuh"
+
+namespace h3q8 {
+
+template <int MODE>
+struct PairConfig {
+    static constexpr int BM = 256, BN = 256;           /* per pair */
+    static constexpr int ROW_BYTES = 128;
+    static constexpr int BKE = MODE == MODE_W8A8 ? 128 : 64;
+    static constexpr int A_BYTES = 128 * ROW_BYTES;     /* this CTA's 128 rows of A         */
+    static constexpr int B_BYTES = 128 * ROW_BYTES;     /* this CTA's 128 output channels   */
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = 6;
+    static constexpr int ACC_COLS = BN, ACC_BUFFERS = 2;
+    static constexpr int EPILOGUE_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, WARPS = 10, THREADS = WARPS * 32;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    static constexpr uint32_t IDESC = MODE == MODE_W8A8 ? umma_idesc(2, 1, 256, BN) : umma_idesc(1, 1, 256, BN);
+    static_assert(MODE == MODE_BF16 || MODE == MODE_W8A8, "pair kernel: bf16 or int8 operands");
+};
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<MODE>::THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmParams p) {
+    using C = PairConfig<MODE>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *stages = smem;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stages + C::STAGES * C::STAGE_BYTES);
+    uint64_t *full = bars, *empty = full + C::STAGES;
+    uint64_t *tfull = empty + C::STAGES, *tempty = tfull + C::ACC_BUFFERS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + C::ACC_BUFFERS);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();               /* 0 = leader */
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const uint32_t num_kb = (p.K + C::BKE - 1) / C::BKE;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 2 * C::EPILOGUE_WARPS); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == C::PRODUCER_WARP && lane == 0) { tma_prefetch_descriptor(&map_a); tma_prefetch_descriptor(&map_b); }
+    if (warp == C::MMA_WARP) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();           /* both CTAs' barriers exist before anything crosses the pair */
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    uint32_t failure = STATUS_OK;
+
+    if (warp == C::PRODUCER_WARP) {
+        if (lane == 0) {
+            PipeState st;
+            for (uint32_t tile = pair; tile < p.tiles && !failure; tile += pairs) {
+                uint32_t mb, nb;
+                tile_coordinates(p, tile, mb, nb);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!wait_or_abort(&empty[st.index], st.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
+                    uint8_t *stage = stages + st.index * C::STAGE_BYTES;
+                    /* the leader arms its barrier for the bytes of both CTAs */
+                    if (rank == 0) mbar_arrive_expect_tx(&full[st.index], 2 * C::STAGE_BYTES);
+                    const uint32_t leader_full = map_to_cta(smem_u32(&full[st.index]), 0);
+                    tma_load_2d_pair(stage, &map_a, leader_full, (int32_t)(kb * C::BKE), (int32_t)(mb * C::BM + rank * 128));
+                    tma_load_2d_pair(stage + C::A_BYTES, &map_b, leader_full, (int32_t)(kb * C::BKE), (int32_t)(nb * C::BN + rank * 128));
+                    st.advance(C::STAGES);
+                }
+            }
+        }
+    } else if (warp == C::MMA_WARP) {
+        if (lane == 0 && rank == 0) {
+            PipeState st, acc;
+            for (uint32_t tile = pair; tile < p.tiles && !failure; tile += pairs) {
+                if (!wait_or_abort(&tempty[acc.index], acc.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                tc_fence_after_sync();
+                const uint32_t d = tmem_base + acc.index * C::ACC_COLS;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!wait_or_abort(&full[st.index], st.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                    tc_fence_after_sync();
+                    uint8_t *stage = stages + st.index * C::STAGE_BYTES;
+                    const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(stage));
+                    const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(stage + C::A_BYTES));
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; k4++) {
+                        if (MODE == MODE_W8A8) umma_i8_pair(d, a_desc + 2 * k4, b_desc + 2 * k4, C::IDESC, kb | k4);
+                        else umma_bf16_pair(d, a_desc + 2 * k4, b_desc + 2 * k4, C::IDESC, kb | k4);
+                    }
+                    umma_commit_pair(&empty[st.index], 3);   /* frees the stage in both CTAs */
+                    st.advance(C::STAGES);
+                }
+                if (failure) break;
+                umma_commit_pair(&tfull[acc.index], 3);
+                acc.advance(C::ACC_BUFFERS);
+            }
+        }
+    } else {
+        /* epilogue: this CTA's 128 rows, TMEM lane quadrant warp % 4, column half warp / 4 */
+        constexpr int HALF_CHUNKS = C::BN / 64;
+        const uint32_t quadrant = warp & 3, half = warp >> 2;
+        const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
+        PipeState acc;
+        for (uint32_t tile = pair; tile < p.tiles && !failure; tile += pairs) {
+            uint32_t mb, nb;
+            tile_coordinates(p, tile, mb, nb);
+            const uint32_t n0 = nb * C::BN;
+            bool ready = wait_or_abort(&tfull[acc.index], acc.phase, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_EPILOGUE; break; }
+            tc_fence_after_sync();
+            const uint32_t row = mb * C::BM + rank * 128 + quadrant * 32 + lane;
+            const bool row_ok = row < p.M;
+            float a_scale = 1.0f;
+            if (MODE == MODE_W8A8) a_scale = row_ok ? p.a_scales[row] : 0.0f;
+#pragma unroll 1
+            for (int hc = 0; hc < HALF_CHUNKS; hc++) {
+                const int c = half * HALF_CHUNKS + hc;
+                uint32_t v[32];
+                tmem_load_32x32(tmem_base + ((quadrant * 32u) << 16) + acc.index * C::ACC_COLS + c * 32, v);
+                tmem_load_wait();
+                const uint32_t col0 = n0 + c * 32;
+                if (!row_ok) continue;
+                if (MODE == MODE_W8A8 && p.acc_dump) {
+#pragma unroll
+                    for (int j8 = 0; j8 < 4; j8++)
+                        if (col0 + j8 * 8 < p.N) {
+                            int4 *dst = reinterpret_cast<int4 *>(p.acc_dump + (size_t)row * p.N + col0 + j8 * 8);
+                            dst[0] = make_int4(v[j8 * 8 + 0], v[j8 * 8 + 1], v[j8 * 8 + 2], v[j8 * 8 + 3]);
+                            dst[1] = make_int4(v[j8 * 8 + 4], v[j8 * 8 + 5], v[j8 * 8 + 6], v[j8 * 8 + 7]);
+                        }
+                }
+#pragma unroll
+                for (int j8 = 0; j8 < 4; j8++) {
+                    const uint32_t col = col0 + j8 * 8;
+                    if (col >= p.N) continue;
+                    float lin[8];
+                    if (MODE == MODE_W8A8) {
+                        float4 s0 = *reinterpret_cast<const float4 *>(p.w_scales + col);
+                        float4 s1 = *reinterpret_cast<const float4 *>(p.w_scales + col + 4);
+                        const float ws[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            lin[j] = __fmul_rn(__fmul_rn((float)(int32_t)v[j8 * 8 + j], a_scale), ws[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; j++) lin[j] = __uint_as_float(v[j8 * 8 + j]);
+                    }
+                    uint32_t bias[4] = {0, 0, 0, 0}, gate[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+                    uint32_t res[4] = {0, 0, 0, 0};
+                    if (p.ep.bias) *reinterpret_cast<uint4 *>(bias) = *reinterpret_cast<const uint4 *>(p.ep.bias + col);
+                    if (p.ep.gate) *reinterpret_cast<uint4 *>(gate) = *reinterpret_cast<const uint4 *>(p.ep.gate + col);
+                    if (p.ep.residual)
+                        *reinterpret_cast<uint4 *>(res) = *reinterpret_cast<const uint4 *>(p.ep.residual + (size_t)row * p.N + col);
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        packed[j] = epilogue_pair(lin[2 * j], lin[2 * j + 1], bias[j], p.ep.bias != nullptr, p.ep.activation,
+                                                  gated, gate[j], res[j]);
+                    *reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + col) = *reinterpret_cast<uint4 *>(packed);
+                }
+            }
+            /* this warp is done with the accumulator: tell the leader's MMA issuer */
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(&tempty[acc.index]);
+                else mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc.index]), 0));
+            }
+            acc.advance(C::ACC_BUFFERS);
+        }
+    }
+
+    if (failure) {
+        *abort_flag = 1;
+        atomicCAS(p.status, 0u, failure | (blockIdx.x << 8));
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        long long start = clock64();
+        while (clock64() - start < 2000000ll) { }
+        __syncthreads();
+    }
+    cluster_sync();           /* the peer may still be read by the leader's MMAs until here */
+    if (warp == C::MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+} /* namespace h3q8 */

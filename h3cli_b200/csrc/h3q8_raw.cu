@@ -122,6 +122,45 @@ static int launch_tcgen05(const h3q8_linear_desc &d, GemmParams p, DeviceState *
     return cuda_ok(cudaGetLastError(), "tcgen05 linear launch");
 }
 
+/* Two-CTA clusters: the grid is twice the number of clusters that can be resident at once. */
+template <int MODE>
+static int launch_pair(const h3q8_linear_desc &d, GemmParams p, DeviceState *dev, cudaStream_t stream) {
+    using C = PairConfig<MODE>;
+    CUtensorMap map_a, map_b;
+    const uint32_t bytes = MODE == MODE_W8A8 ? 1 : 2;
+    if (!make_map(&map_a, d.input, bytes, d.rows, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    if (!make_map(&map_b, d.weight, bytes, d.output_dim, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    p.m_blocks = (d.rows + C::BM - 1) / C::BM;
+    p.n_blocks = (d.output_dim + C::BN - 1) / C::BN;
+    p.tiles = p.m_blocks * p.n_blocks;
+    p.band = p.m_blocks < 8 ? p.m_blocks : 8;
+    auto kernel = gemm_tcgen05_pair_kernel<MODE>;
+    static int clusters[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (!clusters[device]) {
+        if (!cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES),
+                     "shared memory opt-in")) return 0;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(dev->sms & ~1u);
+        config.blockDim = dim3(C::THREADS);
+        config.dynamicSmemBytes = C::SMEM_BYTES;
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = 2; attribute.val.clusterDim.y = 1; attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        int active = 0;
+        if (!cuda_ok(cudaOccupancyMaxActiveClusters(&active, kernel, &config), "cluster occupancy query")) return 0;
+        if (active < 1) return fail("the device cannot co-schedule a two-CTA cluster of the pair kernel");
+        clusters[device] = active < dev->sms / 2 ? active : dev->sms / 2;
+    }
+    const uint32_t pairs = p.tiles < (uint32_t)clusters[device] ? p.tiles : (uint32_t)clusters[device];
+    kernel<<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(map_a, map_b, p);
+    count_launch(1);
+    return cuda_ok(cudaGetLastError(), "tcgen05 pair linear launch");
+}
+
 template <int MODE>
 static int launch_plain(const h3q8_linear_desc &d, const GemmParams &p, cudaStream_t stream) {
     dim3 grid((d.output_dim + 63) / 64, (d.rows + 63) / 64);
@@ -137,6 +176,10 @@ static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t 
     if (grouped8) {
         if (MODE == MODE_W8A8) return launch_tcgen05<MODE_W8A8, 128, 1, true>(d, p, dev, stream);
         return fail("grouped W8A8 reached a non-W8A8 launch");
+    }
+    if (kernel == H3Q8_KERNEL_TCGEN05_PAIR) {
+        if constexpr (MODE == MODE_W8A16) return fail("the two-CTA kernel takes bf16 or int8 operands, not main-loop dequantisation");
+        else return launch_pair<MODE>(d, p, dev, stream);
     }
     if (kernel == H3Q8_KERNEL_TCGEN05_M256) return launch_tcgen05<MODE, 256, 2, false>(d, p, dev, stream);
     if (kernel == H3Q8_KERNEL_TCGEN05_N128) return launch_tcgen05<MODE, 128, 1, false>(d, p, dev, stream);
@@ -176,10 +219,15 @@ static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
     if (d.mode == H3Q8_MODE_W8A16 && d.weight_group && d.weight_group % 64) tma_ok = false;
     if (d.mode == H3Q8_MODE_W8A8 && d.weight_group && d.weight_group % 128) tma_ok = false;
     uint32_t kernel = d.kernel;
-    if (kernel > H3Q8_KERNEL_TCGEN05_N128) return fail("linear: unknown kernel selector %u", kernel);
+    if (kernel > H3Q8_KERNEL_TCGEN05_PAIR) return fail("linear: unknown kernel selector %u", kernel);
     if (kernel == H3Q8_KERNEL_AUTO) {
         const bool tiny = (uint64_t)d.rows * d.input_dim * d.output_dim <= (1u << 22);
-        kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128 : H3Q8_KERNEL_TCGEN05;
+        /* two-CTA tiles need both CTAs to have rows; main-loop dequantisation and grouped W8A8 stay single-CTA */
+        const bool pair_ok = d.rows > 128 && (d.mode == H3Q8_MODE_BF16 || (d.mode == H3Q8_MODE_W8A8 && !d.weight_group));
+        kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128
+               : pair_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_TCGEN05;
+    } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && d.weight_group))) {
+        return fail("linear: the two-CTA kernel takes bf16 or per-channel int8 operands");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {
         return fail("linear %ux%ux%u: shape or alignment not supported by the tcgen05 kernel "
                     "(K %% %u, N %% 8, 16-byte aligned operands, scale group %% 64/128)",

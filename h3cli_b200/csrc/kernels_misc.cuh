@@ -11,7 +11,7 @@
  */
 #pragma once
 #include <float.h>
-#include "gemm_tcgen05.cuh"
+#include "gemm_tcgen05_pair.cuh"
 
 namespace h3q8 {
 

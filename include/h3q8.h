@@ -46,7 +46,9 @@ enum { /* kernel selection; AUTO picks by shape */
     H3Q8_KERNEL_PLAIN = 1,     /* CUDA-core kernel, any shape                       */
     H3Q8_KERNEL_TCGEN05 = 2,   /* tcgen05/TMA kernel, 128 x 256 tiles               */
     H3Q8_KERNEL_TCGEN05_M256 = 3, /* tcgen05/TMA kernel, 256 x 256 tiles            */
-    H3Q8_KERNEL_TCGEN05_N128 = 4  /* tcgen05/TMA kernel, 128 x 128 tiles            */
+    H3Q8_KERNEL_TCGEN05_N128 = 4, /* tcgen05/TMA kernel, 128 x 128 tiles            */
+    H3Q8_KERNEL_TCGEN05_PAIR = 5  /* two-CTA tcgen05 kernel, 256 x 256 tiles per CTA
+                                     pair (BF16 and W8A8 per-channel modes)         */
 };
 
 /* out[M,N] = epilogue(input[M,K] . weight[N,K]^T), everything row-major.

@@ -19,6 +19,7 @@ from parity import bf16_to_f32, check_bf16, rel_l2
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 TC_KERNELS = [h.KERNEL_TCGEN05, h.KERNEL_TCGEN05_M256, h.KERNEL_TCGEN05_N128]
+PAIR = [h.KERNEL_TCGEN05_PAIR]   # two-CTA kernel: bf16 and per-channel int8 operands only
 GUARD = 64
 
 
@@ -235,13 +236,14 @@ def exact_pattern(M, N, K):
     return synth.to_bf16(x.astype(np.float32)).reshape(M, K), wq, ws
 
 
-@pytest.mark.parametrize("rows", [1, 3, 17, 129])
-@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS)
+@pytest.mark.parametrize("rows", [1, 3, 17, 129, 300])
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS + PAIR)
 def test_exact_patterns_bit_exact(gpu, oracle, rows, kernel):
     N, K = 256, 512
     x, wq, ws = exact_pattern(rows, N, K)
     want = oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0)
-    assert (raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, kernel=kernel) == want).all()
+    if kernel not in PAIR:
+        assert (raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, kernel=kernel) == want).all()
     wb = oracle.q8_dequant(wq, ws, 0)
     assert (raw_linear(gpu, h.MODE_BF16, x, wb, kernel=kernel) == want).all()
     xq, xs = oracle.quantize_rows(x)
@@ -272,7 +274,7 @@ def test_w8a16_parity(gpu, oracle, M, N, K, group, spec, kernel):
     check_bf16(got, want)
 
 
-@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS)
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS + PAIR)
 @pytest.mark.parametrize("M,N,K", SHAPES)
 def test_bf16_parity(gpu, oracle, M, N, K, kernel):
     x, wq, ws = operands(22, M, N, K, 64)
@@ -282,7 +284,7 @@ def test_bf16_parity(gpu, oracle, M, N, K, kernel):
     check_bf16(raw_linear(gpu, h.MODE_BF16, x, wb, bias=bias, gate=gate, residual=res, kernel=kernel), want)
 
 
-@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS)
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS + PAIR)
 @pytest.mark.parametrize("M,N,K", [(1, 8, 16), (40, 24, 128), (130, 128, 256), (300, 520, 512), (257, 264, 1040), (64, 3072, 3072)])
 @pytest.mark.parametrize("spec", ["", "ba", "gr"])
 def test_w8a8_int32_exact_and_epilogue(gpu, oracle, M, N, K, spec, kernel):
