@@ -147,6 +147,11 @@ def main():
     ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS],
                     help="profiling aid: run only this projection (with --rows) and print a short line")
     ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
+    ap.add_argument("--workload", default="block", choices=["block", "stream"],
+                    help="block: one DiT block stack, weights resident (default, BASELINE config 2); stream: the large render "
+                         "(config 5): M=219,600 rows sharded over the GPUs, --layers layers of group-128 weights streamed "
+                         "from pinned host memory through two device slots")
+    ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--mode", default="w8a16", choices=["w8a16", "w8a8"],
                     help="w8a16 (default, BASELINE config 2) or the W8A8 variant: per-token int8 activations, int8 MMAs")
     args = ap.parse_args()
@@ -193,6 +198,8 @@ def main():
 
     if args.case:
         return run_case(args, gpu, lib, stream, device_bf16)
+    if args.workload == "stream":
+        return run_stream(args, gpu, lib, stream, device_bf16, rank, world, local)
 
     # ---- operands (weights replicated on every rank: same seed) ----------------------------------
     weights, inputs, outputs, gates, residuals = {}, {}, {}, {}, {}
@@ -316,6 +323,85 @@ def main():
                 "sample": "1024-row slab of each of the 4 GEMM shapes (0.232 TFLOP), blocked fp32 OpenMP restatement"},
         }
         print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    gpu.free()
+
+
+def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
+    """BASELINE config 5: 48 layers x 4 projections at M = 219,600 (rows sharded over the ranks, strong scaling),
+    W8A16 per-group-128 weights (116.8 MB per layer) streamed from pinned host memory, two device slots, the copy
+    of layer l+1 overlapping the compute of layer l."""
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    from h3cli_b200 import sharding, q8_blob
+    total_rows, group, unique = 219600, 128, 4
+    begin, end = sharding.row_range(total_rows, rank, world)
+    rows = end - begin
+    shapes = [(n, k) for _, k, n, _ in LAYERS]
+    sizes = [lib.h3q8_q8_blob_bytes(n, k, group, None) for n, k in shapes]
+    offsets = [sum(sizes[:i]) for i in range(len(sizes))]
+    slot_bytes = sum(sizes)
+    host = gpu.tensor_alloc(unique * slot_bytes, 2, 2)                    # int8, pinned host memory
+    pointer = lib.h3_gpu_tensor_contents(host.handle)
+    view = np.ctypeslib.as_array((ctypes.c_uint8 * (unique * slot_bytes)).from_address(pointer))
+    wgen = np.random.default_rng(42)
+    for u in range(unique):
+        for (n, k), off in zip(shapes, offsets):
+            wq = wgen.integers(-127, 128, (n, k), dtype=np.int8)
+            ws = np.exp(wgen.normal(np.log(0.01), 0.3, (n, k // group))).astype(np.float32)
+            blob = q8_blob(wq, ws, group)
+            view[u * slot_bytes + off:u * slot_bytes + off + blob.size] = blob
+    ring = gpu.weight_stream(slot_bytes, 2)
+    views = [[ring.view(slot, off, n, k, group) for (n, k), off in zip(shapes, offsets)] for slot in range(2)]
+    x, hidden, residual = device_bf16(rows, HIDDEN, seed=1), device_bf16(rows, FFN, seed=2), device_bf16(rows, HIDDEN, seed=3)
+    gate = device_bf16(1, HIDDEN, 1.0, 0.1, seed=4)
+    inputs = [x, x, x, hidden]
+    outputs = [gpu.tensor_new_bf16(rows * n) for n, _ in shapes]
+
+    def one_pass():
+        slot = ring.prefetch(pointer, slot_bytes)
+        for layer in range(args.layers):
+            upcoming = ring.prefetch(pointer + ((layer + 1) % unique) * slot_bytes, slot_bytes) if layer + 1 < args.layers else None
+            ring.acquire(slot)
+            for i, (name, k, n, spec) in enumerate(LAYERS):
+                gpu.linear_fused_bf16(outputs[i], inputs[i], views[slot][i], None, gate if "g" in spec else None,
+                                      residual if "r" in spec else None, rows, k, n, 1 if "a" in spec else 0)
+            ring.release(slot)
+            gpu.continue_()
+            slot = upcoming
+
+    gpu.begin()
+    one_pass()
+    gpu.submit()
+    before = gpu.stats()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    passes = max(1, args.steps // 10)
+    gpu.begin()
+    start.record(stream)
+    for _ in range(passes):
+        one_pass()
+    stop.record(stream)
+    gpu.submit()
+    seconds = torch.tensor([start.elapsed_time(stop) * 1e-3], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(seconds, op=dist.ReduceOp.MAX)
+    after = gpu.stats()
+    flop = sum(2.0 * total_rows * k * n for _, k, n, _ in LAYERS) * args.layers * passes
+    if rank == 0:
+        t = float(seconds.item())
+        print(json.dumps({
+            "metric": METRIC, "workload": "stream", "value": flop / t / 1e12, "unit": UNIT, "n_gpus": world, "passes": passes,
+            "layers": args.layers, "rows_total": total_rows, "rows_this_rank": rows, "scaling": "strong",
+            "ms_per_layer": t / passes / args.layers * 1e3, "seconds_per_pass": t / passes,
+            "streamed_bytes_per_layer": slot_bytes, "h2d_gbs_this_rank": (after.streamed_bytes - before.streamed_bytes) / t / 1e9,
+            "stream_stalls": int(after.stream_stalls - before.stream_stalls), "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "large render (BASELINE config 5): 48-layer DiT linear stack, M=219600, W8A16 group-128, "
+                                   "weights streamed per layer from pinned host memory, 2 device slots"}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
     gpu.free()

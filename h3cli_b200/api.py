@@ -112,6 +112,13 @@ def library():
         "h3q8_gpu_set_w8a16_scratch_rows": (C.c_int, [vp, u32]),
         "h3q8_gpu_set_profiling": (C.c_int, [vp, C.c_int]),
         "h3q8_gpu_q8_from_host": (vp, [vp, vp, vp, u32, u32, u32]),
+        "h3q8_gpu_weight_stream_create": (vp, [vp, sz, u32]),
+        "h3q8_gpu_weight_stream_prefetch": (C.c_int, [vp, vp, sz]),
+        "h3q8_gpu_weight_stream_acquire": (C.c_int, [vp, C.c_int]),
+        "h3q8_gpu_weight_stream_release": (C.c_int, [vp, C.c_int]),
+        "h3q8_gpu_weight_stream_view": (vp, [vp, C.c_int, sz, u32, u32, u32]),
+        "h3q8_gpu_weight_stream_free": (None, [vp]),
+        "h3q8_q8_blob_bytes": (sz, [u32, u32, u32, C.POINTER(sz)]),
         "h3_gpu_quantize_weight_int8": (C.c_int, [vp, vp, vp, vp, u32, u32]),
         "h3_gpu_linear_int8_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
         "h3_gpu_gelu_bf16": (C.c_int, [vp, vp, vp, u32, C.c_int]),
@@ -172,6 +179,49 @@ class Tensor:
 
 def _h(t):
     return None if t is None else t.handle
+
+
+def q8_blob(weights, scales, group):
+    """Packs int8 [N,K] + fp32 scales into the byte layout weight-stream views expect."""
+    weights = np.ascontiguousarray(weights, np.int8)
+    rows, columns = weights.shape
+    offset = C.c_size_t()
+    total = library().h3q8_q8_blob_bytes(rows, columns, group, C.byref(offset))
+    blob = np.zeros(total, np.uint8)
+    blob[:rows * columns] = weights.reshape(-1).view(np.uint8)
+    s = np.ascontiguousarray(scales, np.float32).reshape(-1).view(np.uint8)
+    blob[offset.value:offset.value + s.size] = s
+    return blob
+
+
+class WeightStream:
+    """h3q8_weight_stream: device slots fed from host memory on the copy stream."""
+
+    def __init__(self, gpu, slot_bytes, slots):
+        self.gpu = gpu
+        self.handle = library().h3q8_gpu_weight_stream_create(gpu.handle, slot_bytes, slots)
+        if not self.handle:
+            raise H3Error(gpu.error())
+
+    def prefetch(self, host_pointer, nbytes):
+        slot = library().h3q8_gpu_weight_stream_prefetch(self.handle, host_pointer, nbytes)
+        if slot < 0:
+            raise H3Error(self.gpu.error())
+        return slot
+
+    def acquire(self, slot):
+        return self.gpu._check(library().h3q8_gpu_weight_stream_acquire(self.handle, slot))
+
+    def release(self, slot):
+        return self.gpu._check(library().h3q8_gpu_weight_stream_release(self.handle, slot))
+
+    def view(self, slot, offset, rows, columns, group):
+        return Tensor(self.gpu, library().h3q8_gpu_weight_stream_view(self.handle, slot, offset, rows, columns, group))
+
+    def free(self):
+        if self.handle:
+            library().h3q8_gpu_weight_stream_free(self.handle)
+            self.handle = None
 
 
 class Gpu:
@@ -283,6 +333,10 @@ class Gpu:
         rows, columns = weights.shape
         return Tensor(self, library().h3q8_gpu_q8_from_host(self.handle, weights.ctypes.data, scales.ctypes.data,
                                                             rows, columns, group))
+
+    # packed-weight streaming ----------------------------------------------
+    def weight_stream(self, slot_bytes, slots=2):
+        return WeightStream(self, slot_bytes, slots)
 
     # operators ----------------------------------------------------------
     def linear_bf16(self, output, input, weight, bias, rows, input_dim, output_dim):

@@ -41,6 +41,7 @@ struct h3_gpu_tensor {
     int q8 = 0;
     uint32_t q8_n = 0, q8_k = 0, q8_group = 0;
     size_t q8_scale_offset = 0;
+    bool borrowed = false; /* a view into a weight-stream slot: the memory is not this tensor's */
 };
 struct h3_gpu_event { h3_gpu *owner = nullptr; cudaEvent_t value = nullptr; bool recorded = false; };
 
@@ -330,10 +331,11 @@ extern "C" void h3_gpu_tensor_free(h3_gpu_tensor *t) {
     { /* work in flight may still use it: cudaFree waits, host memory needs an explicit wait */
         std::lock_guard<std::mutex> lock(g->mutex);
         for (auto it = g->accessed.begin(); it != g->accessed.end();) it = *it == t ? g->accessed.erase(it) : it + 1;
-        if (t->storage == H3_GPU_HOST_PINNED) { cudaStreamSynchronize(g->compute); cudaStreamSynchronize(g->copy); cudaFreeHost(t->data); }
+        if (t->borrowed) { /* nothing to release */ }
+        else if (t->storage == H3_GPU_HOST_PINNED) { cudaStreamSynchronize(g->compute); cudaStreamSynchronize(g->copy); cudaFreeHost(t->data); }
         else { if (t->ready_recorded) cudaEventSynchronize(t->ready); cudaFree(t->data); }
-        g->stats.live_bytes -= t->bytes;
-        if (t->storage == H3_GPU_HOST_PINNED) g->stats.pinned_bytes -= t->bytes;
+        if (!t->borrowed) g->stats.live_bytes -= t->bytes;
+        if (!t->borrowed && t->storage == H3_GPU_HOST_PINNED) g->stats.pinned_bytes -= t->bytes;
     }
     if (t->ready) cudaEventDestroy(t->ready);
     if (t->released) cudaEventDestroy(t->released);
@@ -655,6 +657,124 @@ extern "C" h3_gpu_tensor *h3q8_gpu_q8_from_host(h3_gpu *g, const int8_t *weights
         !upload(t, t->q8_scale_offset, scales, (size_t)rows * groups * sizeof(float))) { h3_gpu_tensor_free(t); return nullptr; }
     g->stats.q8_weights++;
     g->stats.q8_storage_bytes += t->bytes;
+    return t;
+}
+
+/* ------------------------------------------------------ packed-weight streaming */
+struct h3q8_weight_stream {
+    h3_gpu *owner = nullptr;
+    size_t slot_bytes = 0;
+    uint32_t slots = 0, next = 0;
+    std::vector<void *> memory;
+    std::vector<cudaEvent_t> ready, released;
+    std::vector<bool> ready_recorded, released_recorded;
+};
+
+extern "C" size_t h3q8_q8_blob_bytes(uint32_t rows, uint32_t columns, uint32_t group, size_t *scale_offset) {
+    size_t offset, bytes;
+    if (!h3q8_q8_layout(rows, columns, group, &offset, &bytes)) return 0;
+    size_t aligned = (offset + 15) & ~(size_t)15;
+    if (scale_offset) *scale_offset = aligned;
+    return (aligned + (bytes - offset) + 255) & ~(size_t)255;
+}
+
+extern "C" h3q8_weight_stream *h3q8_gpu_weight_stream_create(h3_gpu *g, size_t slot_bytes, uint32_t slots) {
+    if (!selected(g)) return nullptr;
+    if (!slot_bytes || slots < 2 || slots > 8) { set_error(g, "weight stream: needs 2..8 slots of non-zero size"); return nullptr; }
+    if (g->allocation_budget && g->stats.live_bytes + slot_bytes * slots > g->allocation_budget) {
+        set_error(g, "CUDA allocation: out of memory (test budget) for %u weight-stream slots of %zu bytes", slots, slot_bytes);
+        return nullptr;
+    }
+    auto *s = new (std::nothrow) h3q8_weight_stream;
+    if (!s) return nullptr;
+    s->owner = g; s->slot_bytes = slot_bytes; s->slots = slots;
+    for (uint32_t i = 0; i < slots; i++) {
+        void *memory = nullptr;
+        cudaEvent_t a = nullptr, b = nullptr;
+        if (cudaMalloc(&memory, slot_bytes) != cudaSuccess || cudaEventCreateWithFlags(&a, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&b, cudaEventDisableTiming) != cudaSuccess) {
+            cudaGetLastError();
+            set_error(g, "weight stream: cannot allocate slot %u of %zu bytes", i, slot_bytes);
+            if (memory) cudaFree(memory);
+            h3q8_gpu_weight_stream_free(s);
+            return nullptr;
+        }
+        s->memory.push_back(memory); s->ready.push_back(a); s->released.push_back(b);
+        s->ready_recorded.push_back(false); s->released_recorded.push_back(false);
+        g->stats.live_bytes += slot_bytes;
+        g->stats.stream_slot_bytes += slot_bytes;
+    }
+    if (g->stats.live_bytes > g->stats.peak_live_bytes) g->stats.peak_live_bytes = g->stats.live_bytes;
+    return s;
+}
+
+extern "C" void h3q8_gpu_weight_stream_free(h3q8_weight_stream *s) {
+    if (!s) return;
+    h3_gpu *g = s->owner;
+    cudaSetDevice(g->device);
+    cudaStreamSynchronize(g->copy);
+    cudaStreamSynchronize(g->compute);
+    for (size_t i = 0; i < s->memory.size(); i++) {
+        cudaFree(s->memory[i]);
+        cudaEventDestroy(s->ready[i]);
+        cudaEventDestroy(s->released[i]);
+        g->stats.live_bytes -= s->slot_bytes;
+        g->stats.stream_slot_bytes -= s->slot_bytes;
+    }
+    delete s;
+}
+
+extern "C" int h3q8_gpu_weight_stream_prefetch(h3q8_weight_stream *s, const void *host_blob, size_t bytes) {
+    if (!s || !host_blob) return -1;
+    h3_gpu *g = s->owner;
+    if (!bytes || bytes > s->slot_bytes) { set_error(g, "weight stream: %zu bytes do not fit a %zu-byte slot", bytes, s->slot_bytes); return -1; }
+    std::lock_guard<std::mutex> lock(g->copy_mutex);
+    if (cudaSetDevice(g->device) != cudaSuccess) return -1;
+    const int slot = (int)s->next;
+    s->next = (s->next + 1) % s->slots;
+    /* the copy may not overwrite a slot the compute stream is still reading */
+    if (s->released_recorded[slot] && !checked(g, cudaStreamWaitEvent(g->copy, s->released[slot], 0), "weight stream wait")) return -1;
+    if (!checked(g, cudaMemcpyAsync(s->memory[slot], host_blob, bytes, cudaMemcpyHostToDevice, g->copy), "weight stream copy", bytes) ||
+        !checked(g, cudaEventRecord(s->ready[slot], g->copy), "weight stream ready event")) return -1;
+    s->ready_recorded[slot] = true;
+    g->stats.h2d_bytes += bytes;
+    g->stats.streamed_bytes += bytes;
+    return slot;
+}
+
+extern "C" int h3q8_gpu_weight_stream_acquire(h3q8_weight_stream *s, int slot) {
+    if (!s || slot < 0 || (uint32_t)slot >= s->slots) return 0;
+    h3_gpu *g = s->owner;
+    if (!selected(g)) return 0;
+    if (!s->ready_recorded[slot]) return set_error(g, "weight stream: slot %d was never filled", slot);
+    if (cudaEventQuery(s->ready[slot]) == cudaErrorNotReady) g->stats.stream_stalls++;
+    cudaGetLastError();
+    return checked(g, cudaStreamWaitEvent(g->compute, s->ready[slot], 0), "weight stream acquire");
+}
+
+extern "C" int h3q8_gpu_weight_stream_release(h3q8_weight_stream *s, int slot) {
+    if (!s || slot < 0 || (uint32_t)slot >= s->slots) return 0;
+    h3_gpu *g = s->owner;
+    if (!selected(g)) return 0;
+    if (!checked(g, cudaEventRecord(s->released[slot], g->compute), "weight stream release event")) return 0;
+    s->released_recorded[slot] = true;
+    return 1;
+}
+
+extern "C" h3_gpu_tensor *h3q8_gpu_weight_stream_view(h3q8_weight_stream *s, int slot, size_t offset, uint32_t rows,
+                                                      uint32_t columns, uint32_t group) {
+    if (!s || slot < 0 || (uint32_t)slot >= s->slots) return nullptr;
+    h3_gpu *g = s->owner;
+    size_t scale_offset = 0, bytes = h3q8_q8_blob_bytes(rows, columns, group, &scale_offset);
+    if (!bytes || (offset & 255) || offset > s->slot_bytes || bytes > s->slot_bytes - offset) {
+        set_error(g, "weight stream view: %ux%u at offset %zu does not fit the slot (offsets are multiples of 256)", rows, columns, offset);
+        return nullptr;
+    }
+    h3_gpu_tensor *t = new (std::nothrow) h3_gpu_tensor;
+    if (!t) return nullptr;
+    t->owner = g; t->data = (char *)s->memory[slot] + offset; t->elements = (size_t)rows * columns; t->bytes = bytes;
+    t->dtype = H3_GPU_I8; t->storage = H3_GPU_DEVICE_ONLY; t->borrowed = true;
+    t->q8 = 1; t->q8_n = rows; t->q8_k = columns; t->q8_group = group; t->q8_scale_offset = scale_offset;
     return t;
 }
 

@@ -228,6 +228,31 @@ int h3q8_gpu_set_profiling(h3_gpu *gpu, int enabled);
 /* Same descriptor built from int8 weights + scales already in host memory. */
 h3_gpu_tensor *h3q8_gpu_q8_from_host(h3_gpu *gpu, const int8_t *weights, const float *scales,
                                      uint32_t rows, uint32_t columns, uint32_t group);
+/* Packed-weight streaming: a ring of device slots fed from (pinned) host memory on
+ * the context's copy stream while the compute stream works on the other slot --
+ * the two-slot layer streaming of src/denoise/dit.c:724-843, 2759-2820 and
+ * src/cuda/gpu_cuda.cu:761-841, for already packed q8 layers (the reference's
+ * quantised path copies synchronously on the compute stream instead,
+ * src/cuda/cuda_quant.cuh:346-350).  Per layer:
+ *   slot = prefetch(host blob)      copy stream: wait slot 'released', copy, record 'ready'
+ *   acquire(slot)                   compute stream waits for 'ready' (counts a stall if the copy is still running)
+ *   ... linears on views of the slot ...
+ *   release(slot)                   compute stream records 'released'
+ * A view is a q8 weight tensor that borrows slot memory (free it like any tensor;
+ * the slot memory stays). */
+typedef struct h3q8_weight_stream h3q8_weight_stream;
+h3q8_weight_stream *h3q8_gpu_weight_stream_create(h3_gpu *gpu, size_t slot_bytes, uint32_t slots);
+int h3q8_gpu_weight_stream_prefetch(h3q8_weight_stream *stream, const void *host_blob, size_t bytes);
+int h3q8_gpu_weight_stream_acquire(h3q8_weight_stream *stream, int slot);
+int h3q8_gpu_weight_stream_release(h3q8_weight_stream *stream, int slot);
+h3_gpu_tensor *h3q8_gpu_weight_stream_view(h3q8_weight_stream *stream, int slot, size_t offset, uint32_t rows,
+                                           uint32_t columns, uint32_t group);
+void h3q8_gpu_weight_stream_free(h3q8_weight_stream *stream);
+/* Size of one packed q8 weight as the views expect it (int8 payload, padding to 16
+ * bytes, fp32 scales, padded to 256 bytes so that blobs can be concatenated), and
+ * the offset of its scale plane. */
+size_t h3q8_q8_blob_bytes(uint32_t rows, uint32_t columns, uint32_t group, size_t *scale_offset);
+
 /* W8A8 family -- src/gpu.h:523-537 */
 int h3_gpu_quantize_weight_int8(h3_gpu *gpu, h3_gpu_tensor *output, h3_gpu_tensor *scales,
                                 const h3_gpu_tensor *input, uint32_t rows, uint32_t columns);

@@ -463,6 +463,70 @@ def test_fused_equals_unfused_chain(gpu):
         t.free()
 
 
+# --------------------------------------------------------------------------- weight streaming
+def pinned_bytes(gpu, count):
+    import ctypes
+    host = gpu.tensor_alloc(count, 2, 2)   # int8, H3_GPU_HOST_PINNED
+    pointer = h.library().h3_gpu_tensor_contents(host.handle)
+    view = np.ctypeslib.as_array((ctypes.c_uint8 * count).from_address(pointer))
+    return host, pointer, view
+
+
+def test_weight_streaming_double_buffered(oracle):
+    """Config 5 in miniature: packed group-128 layers streamed from pinned host memory
+    through two device slots, one layer prefetched while the previous one computes
+    (slot handoffs as in the reference's tests/test_cuda_runtime.c)."""
+    M, K, N1, N2, group, layers = 300, 256, 512, 256, 128, 9
+    gpu = h.Gpu()
+    gpu.quant_configure(1)
+    x = synth.activations(30, 1, M, K).reshape(M, K)
+    weights, blobs = [], []
+    for layer in range(layers):
+        wq1, ws1 = synth.int8_weights(30 + layer, 2, N1, K), synth.lognormal_scales(30 + layer, 3, N1, K // group)
+        wq2, ws2 = synth.int8_weights(30 + layer, 4, N2, N1), synth.lognormal_scales(30 + layer, 5, N2, N1 // group)
+        first, second = h.q8_blob(wq1, ws1, group), h.q8_blob(wq2, ws2, group)
+        weights.append((wq1, ws1, wq2, ws2, first.size))
+        blobs.append(np.concatenate([first, second]))
+    slot_bytes = blobs[0].size
+    host, pointer, view = pinned_bytes(gpu, layers * slot_bytes)
+    for layer, blob in enumerate(blobs):
+        view[layer * slot_bytes:(layer + 1) * slot_bytes] = blob
+    stream = gpu.weight_stream(slot_bytes, 2)
+    with pytest.raises(h.H3Error):
+        stream.prefetch(pointer, slot_bytes + 1)
+    tx = gpu.tensor_from_bf16(x)
+    mids = [gpu.tensor_new_bf16(M * N1) for _ in range(layers)]
+    outs = [gpu.tensor_new_bf16(M * N2) for _ in range(layers)]
+    views = []
+    slot = stream.prefetch(pointer, slot_bytes)
+    gpu.begin()
+    for layer in range(layers):
+        upcoming = stream.prefetch(pointer + (layer + 1) * slot_bytes, slot_bytes) if layer + 1 < layers else None
+        stream.acquire(slot)
+        w1 = stream.view(slot, 0, N1, K, group)
+        w2 = stream.view(slot, weights[layer][4], N2, N1, group)
+        gpu.linear_fused_bf16(mids[layer], tx, w1, None, None, None, M, K, N1, h.ACT_GELU_TANH)
+        gpu.linear_fused_bf16(outs[layer], mids[layer], w2, None, None, None, M, N1, N2, 0)
+        stream.release(slot)
+        gpu.continue_()
+        views += [w1, w2]
+        slot = upcoming
+    gpu.submit()
+    for layer in range(layers):
+        wq1, ws1, wq2, ws2, _ = weights[layer]
+        mid = mids[layer].read().reshape(M, N1)
+        check_bf16(mid, oracle.linear(oracle.MODE_W8A16, x, wq1, ws1, group, activation=1))
+        check_bf16(outs[layer].read().reshape(M, N2), oracle.linear(oracle.MODE_W8A16, mid, wq2, ws2, group))
+    stats = gpu.stats()
+    assert stats.streamed_bytes == layers * slot_bytes and stats.stream_slot_bytes == 2 * slot_bytes
+    for t in views + mids + outs + [tx]:
+        t.free()
+    stream.free()
+    assert gpu.stats().stream_slot_bytes == 0
+    host.free()
+    gpu.free()
+
+
 # --------------------------------------------------------------------------- interface behaviour
 def test_int8_operator_family_like_the_reference(oracle):
     """h3_gpu_quantize_weight_int8 + h3_gpu_linear_int8_bf16 (src/metal/gpu.m:3174-3249):
