@@ -85,7 +85,7 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def oracle_slab(rows, steps, warmup):
+def oracle_slab(rows, steps, warmup, mode="w8a16"):
     """Times the CPU restatement (oracle fast path, all host threads) on `rows` rows of each GEMM shape."""
     import oracle
     oracle.build()
@@ -103,7 +103,11 @@ def oracle_slab(rows, steps, warmup):
     for i in range(warmup + steps):
         t0 = time.perf_counter()
         for x, wq, ws, gate, res, act in work:
-            oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0, gate=gate, residual=res, activation=act, fast=True)
+            if mode == "w8a8":
+                xq, xs = oracle.quantize_rows(x)
+                oracle.linear(oracle.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, x_scales=xs, gate=gate, residual=res, activation=act, fast=True)
+            else:
+                oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0, gate=gate, residual=res, activation=act, fast=True)
         if i >= warmup:
             times.append(time.perf_counter() - t0)
     seconds = float(np.mean(times))
@@ -114,12 +118,12 @@ def run_reference(args, rank):
     if rank != 0:
         return
     rows = 512
-    value, seconds, cores = oracle_slab(rows, args.steps, args.warmup)
+    value, seconds, cores = oracle_slab(rows, args.steps, args.warmup, args.mode)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(),
+        "config": workload_config(args.mode),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{rows}-row slab of each of the 4 GEMM shapes per step (the reference has no CPU linear; "
                                    "this is the CPU restatement of its shader arithmetic, blocked fp32 + OpenMP)"},
@@ -298,7 +302,7 @@ def main():
     if rank == 0:
         cpu_value, cpu_seconds, cores = (None, None, None)
         if world == 1:
-            cpu_value, cpu_seconds, cores = oracle_slab(1024, 2, 1)
+            cpu_value, cpu_seconds, cores = oracle_slab(1024, 2, 1, args.mode)
         clocks = sampler.summary()
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -375,6 +379,7 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
     gpu.begin()
     one_pass()
     gpu.submit()
+    gpu.set_profiling(True)
     before = gpu.stats()
     if world > 1:
         dist.barrier()
@@ -399,7 +404,8 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
             "layers": args.layers, "rows_total": total_rows, "rows_this_rank": rows, "scaling": "strong",
             "ms_per_layer": t / passes / args.layers * 1e3, "seconds_per_pass": t / passes,
             "streamed_bytes_per_layer": slot_bytes, "h2d_gbs_this_rank": (after.streamed_bytes - before.streamed_bytes) / t / 1e9,
-            "stream_stalls": int(after.stream_stalls - before.stream_stalls), "dtype": "bf16", "data": "synthetic",
+            "stream_stalls": int(after.stream_stalls - before.stream_stalls),
+            "slot_wait_ms_per_pass": (after.stream_wait_seconds - before.stream_wait_seconds) / passes * 1e3, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "large render (BASELINE config 5): 48-layer DiT linear stack, M=219600, W8A16 group-128, "
                                    "weights streamed per layer from pinned host memory, 2 device slots"}}), flush=True)
     if world > 1:

@@ -97,6 +97,10 @@ static void harvest_profile(h3_gpu *g) {
         float ms = 0;
         if (cudaEventElapsedTime(&ms, s.start, s.stop) == cudaSuccess) {
             if (s.category == 0) { g->stats.linear_seconds += ms * 1e-3; g->stats.linear_kernel_launches++; }
+            else if (s.category == 3) { /* slot wait: time the compute stream sat idle waiting for a weight copy */
+                g->stats.stream_wait_seconds += ms * 1e-3;
+                if (ms > 0.02f) g->stats.stream_stalls++;
+            }
             else { g->stats.quant_conversion_seconds += ms * 1e-3; g->stats.conversion_kernel_launches++; }
         }
         g->spare_events.push_back(s.start);
@@ -747,8 +751,9 @@ extern "C" int h3q8_gpu_weight_stream_acquire(h3q8_weight_stream *s, int slot) {
     h3_gpu *g = s->owner;
     if (!selected(g)) return 0;
     if (!s->ready_recorded[slot]) return set_error(g, "weight stream: slot %d was never filled", slot);
-    if (cudaEventQuery(s->ready[slot]) == cudaErrorNotReady) g->stats.stream_stalls++;
-    cudaGetLastError();
+    /* with profiling on, an event pair around the wait measures how long the compute
+     * stream really stalled for the copy (category 3, slot wait) */
+    ProfileScope timing(g, 3);
     return checked(g, cudaStreamWaitEvent(g->compute, s->ready[slot], 0), "weight stream acquire");
 }
 

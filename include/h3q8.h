@@ -235,7 +235,7 @@ h3_gpu_tensor *h3q8_gpu_q8_from_host(h3_gpu *gpu, const int8_t *weights, const f
  * quantised path copies synchronously on the compute stream instead,
  * src/cuda/cuda_quant.cuh:346-350).  Per layer:
  *   slot = prefetch(host blob)      copy stream: wait slot 'released', copy, record 'ready'
- *   acquire(slot)                   compute stream waits for 'ready' (counts a stall if the copy is still running)
+ *   acquire(slot)                   compute stream waits for 'ready' (with profiling on, waits over 20 us count as stalls)
  *   ... linears on views of the slot ...
  *   release(slot)                   compute stream records 'released'
  * A view is a q8 weight tensor that borrows slot memory (free it like any tensor;
