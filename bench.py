@@ -316,8 +316,8 @@ def main():
                             "-> h3_gpu_submit -> h3_gpu_tensor_read_bf16, pinned host buffers"},
             "gpu_launches": int(launches),
             "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel<bf16, 128x256> after q8_dequant_kernel" if args.mode == "w8a16"
-                         else "gemm_tcgen05_kernel<int8, 128x256> after quantize_rows_kernel (peak is the bf16 figure; no int8 peak is recorded)",
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel<bf16> (256x256 tile per CTA pair) after q8_dequant_kernel" if args.mode == "w8a16"
+                         else "gemm_tcgen05_pair_kernel<int8> after quantize_rows_kernel (peak is the bf16 figure; no int8 peak is recorded)",
                          "achieved": achieved, "peak": burst, "unit": UNIT, "frac": achieved / burst if achieved else None,
                          "peak_source": f"bf16_tflops (burst) of {which}", "frac_of_sustained": achieved / sustained if achieved and sustained else None,
                          "launches": int(gemm_launches), "avg_launch_ms": gemm_seconds / max(gemm_launches, 1) * 1e3,
