@@ -35,9 +35,9 @@ LAYERS = [("qkv", HIDDEN, 3 * HIDDEN, ""), ("attn_out", HIDDEN, HIDDEN, "gr"),
 FLOP_PER_STEP = sum(2.0 * M_TOKENS * k * n for _, k, n, _ in LAYERS)
 METRIC = "q8_dit_block_linear_tflops"
 UNIT = "TFLOP/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_tcgen05_kernel launch, from the ncu
-# capture summarised in profiles/ (null until a capture exists for the bench workload)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch of this workload (mean of QKV, attn-out, FFN-up,
+# FFN-down at M = 32,400), from the 1-pass ncu capture summarised in profiles/bench_default_dram_traffic.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2.484e9
 
 
 def measured_peak():
