@@ -45,6 +45,7 @@ struct GemmParams {
     int32_t *acc_dump;      /* optional int32 [M,N] raw accumulators (MODE_W8A8, ungrouped)  */
     uint32_t *status;       /* device error word, 0 = ok                                     */
     uint32_t m_blocks, n_blocks, tiles, band;
+    uint64_t l2_policy_a, l2_policy_b; /* TMA L2 eviction policies for activations / weights (two-CTA kernel) */
 };
 
 template <int MODE, int BN, int MT, bool GROUPED>

@@ -91,8 +91,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
                     /* the leader arms its barrier for the bytes of both CTAs */
                     if (rank == 0) mbar_arrive_expect_tx(&full[st.index], 2 * C::STAGE_BYTES);
                     const uint32_t leader_full = map_to_cta(smem_u32(&full[st.index]), 0);
-                    tma_load_2d_pair(stage, &map_a, leader_full, (int32_t)(kb * C::BKE), (int32_t)(mb * C::BM + rank * 128));
-                    tma_load_2d_pair(stage + C::A_BYTES, &map_b, leader_full, (int32_t)(kb * C::BKE), (int32_t)(nb * C::BN + rank * 128));
+                    tma_load_2d_pair(stage, &map_a, leader_full, (int32_t)(kb * C::BKE), (int32_t)(mb * C::BM + rank * 128), p.l2_policy_a);
+                    tma_load_2d_pair(stage + C::A_BYTES, &map_b, leader_full, (int32_t)(kb * C::BKE), (int32_t)(nb * C::BN + rank * 128), p.l2_policy_b);
                     st.advance(C::STAGES);
                 }
             }

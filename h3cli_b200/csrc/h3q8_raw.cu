@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 
 #include "h3q8.h"
@@ -134,6 +135,11 @@ static int launch_pair(const h3q8_linear_desc &d, GemmParams p, DeviceState *dev
     p.n_blocks = (d.output_dim + C::BN - 1) / C::BN;
     p.tiles = p.m_blocks * p.n_blocks;
     p.band = p.m_blocks < 8 ? p.m_blocks : 8;
+    p.l2_policy_a = L2_EVICT_NORMAL;
+    p.l2_policy_b = L2_EVICT_NORMAL;
+    /* experiment knobs (not part of the interface): H3Q8_BAND=rows-blocks per band, H3Q8_L2=1 keeps weights, streams activations */
+    if (const char *e = getenv("H3Q8_BAND")) { uint32_t v = (uint32_t)atoi(e); if (v) p.band = v < p.m_blocks ? v : p.m_blocks; }
+    if (const char *e = getenv("H3Q8_L2")) { if (atoi(e) == 1) { p.l2_policy_a = L2_EVICT_FIRST; p.l2_policy_b = L2_EVICT_LAST; } }
     auto kernel = gemm_tcgen05_pair_kernel<MODE>;
     static int clusters[64] = {};
     int device = 0;
