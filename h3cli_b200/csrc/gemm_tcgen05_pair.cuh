@@ -22,6 +22,12 @@
  *     still touch its shared memory or TMEM
  * Modes: MODE_BF16 and MODE_W8A8 (per-channel scales).  All waits are bounded
  * as in the single-CTA kernel.
+ *
+ * One launch can carry up to PAIR_MAX_PROBLEMS independent problems of different
+ * shapes (the video and audio streams of the DiT): the tile index space is the
+ * concatenation of the problems' tiles, each with its own tensor maps and
+ * parameters, and all of them flow through the same TMA / MMA / TMEM pipeline
+ * without draining it between problems.
  */
 #pragma once
 #include "gemm_tcgen05.cuh"
@@ -44,11 +50,29 @@ struct PairConfig {
     static_assert(MODE == MODE_BF16 || MODE == MODE_W8A8, "pair kernel: bf16 or int8 operands");
 };
 
+constexpr int PAIR_MAX_PROBLEMS = 4;
+struct alignas(64) PairArgs {
+    CUtensorMap map_a[PAIR_MAX_PROBLEMS];
+    CUtensorMap map_b[PAIR_MAX_PROBLEMS];
+    GemmParams p[PAIR_MAX_PROBLEMS];
+    uint32_t tile_start[PAIR_MAX_PROBLEMS + 1]; /* first global tile index of each problem; [count] = total */
+    uint32_t count;
+};
+/* problem that owns global tile `tile`, and the tile's index inside it */
+__device__ __forceinline__ uint32_t locate_problem(const PairArgs &args, uint32_t tile, uint32_t &local) {
+    uint32_t g = 0;
+#pragma unroll
+    for (int i = 1; i < PAIR_MAX_PROBLEMS; i++)
+        if (i < (int)args.count && tile >= args.tile_start[i]) g = i;
+    local = tile - args.tile_start[g];
+    return g;
+}
+
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<MODE>::THREADS, 1)
-gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                         const GemmParams p) {
+gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
     using C = PairConfig<MODE>;
+    const uint32_t total_tiles = args.tile_start[args.count];
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *stages = smem;
@@ -61,7 +85,6 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_cta_rank();               /* 0 = leader */
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
-    const uint32_t num_kb = (p.K + C::BKE - 1) / C::BKE;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -70,7 +93,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    if (warp == C::PRODUCER_WARP && lane == 0) { tma_prefetch_descriptor(&map_a); tma_prefetch_descriptor(&map_b); }
+    if (warp == C::PRODUCER_WARP && lane == 0)
+        for (uint32_t g = 0; g < args.count; g++) { tma_prefetch_descriptor(&args.map_a[g]); tma_prefetch_descriptor(&args.map_b[g]); }
     if (warp == C::MMA_WARP) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
     tc_fence_before_sync();
     __syncthreads();
@@ -82,9 +106,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     if (warp == C::PRODUCER_WARP) {
         if (lane == 0) {
             PipeState st;
-            for (uint32_t tile = pair; tile < p.tiles && !failure; tile += pairs) {
-                uint32_t mb, nb;
-                tile_coordinates(p, tile, mb, nb);
+            for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
+                uint32_t local, mb, nb;
+                const uint32_t g = locate_problem(args, tile, local);
+                const GemmParams &p = args.p[g];
+                const CUtensorMap &map_a = args.map_a[g], &map_b = args.map_b[g];
+                const uint32_t num_kb = (p.K + C::BKE - 1) / C::BKE;
+                tile_coordinates(p, local, mb, nb);
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!wait_or_abort(&empty[st.index], st.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
                     uint8_t *stage = stages + st.index * C::STAGE_BYTES;
@@ -100,7 +128,10 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     } else if (warp == C::MMA_WARP) {
         if (lane == 0 && rank == 0) {
             PipeState st, acc;
-            for (uint32_t tile = pair; tile < p.tiles && !failure; tile += pairs) {
+            for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
+                uint32_t local;
+                const uint32_t g = locate_problem(args, tile, local);
+                const uint32_t num_kb = (args.p[g].K + C::BKE - 1) / C::BKE;
                 if (!wait_or_abort(&tempty[acc.index], acc.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
                 tc_fence_after_sync();
                 const uint32_t d = tmem_base + acc.index * C::ACC_COLS;
@@ -127,11 +158,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
         /* epilogue: this CTA's 128 rows, TMEM lane quadrant warp % 4, column half warp / 4 */
         constexpr int HALF_CHUNKS = C::BN / 64;
         const uint32_t quadrant = warp & 3, half = warp >> 2;
-        const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
         PipeState acc;
-        for (uint32_t tile = pair; tile < p.tiles && !failure; tile += pairs) {
-            uint32_t mb, nb;
-            tile_coordinates(p, tile, mb, nb);
+        for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
+            uint32_t local, mb, nb;
+            const uint32_t g = locate_problem(args, tile, local);
+            const GemmParams &p = args.p[g];
+            const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
+            tile_coordinates(p, local, mb, nb);
             const uint32_t n0 = nb * C::BN;
             bool ready = wait_or_abort(&tfull[acc.index], acc.phase, abort_flag);
             if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_EPILOGUE; break; }
@@ -200,7 +233,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 
     if (failure) {
         *abort_flag = 1;
-        atomicCAS(p.status, 0u, failure | (blockIdx.x << 8));
+        atomicCAS(args.p[0].status, 0u, failure | (blockIdx.x << 8));
     }
     tc_fence_before_sync();
     __syncthreads();

@@ -784,70 +784,122 @@ extern "C" h3_gpu_tensor *h3q8_gpu_weight_stream_view(h3q8_weight_stream *s, int
 }
 
 /* ------------------------------------------------------------------ linears */
+static size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+/* Scratch a problem needs from the context arenas: [0] int8 activations, [1] their scales, [2] bf16 weight. */
+static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size_t need[3]) {
+    need[0] = need[1] = need[2] = 0;
+    if (!q.weight || !q.weight->q8) return;
+    if (g->quant_mode == 2) {
+        size_t padded = ((size_t)q.rows + 127u) & ~(size_t)127u;
+        need[0] = round256(padded * q.input_dim);
+        need[1] = round256(padded * sizeof(float));
+    } else if (g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows && q.input_dim % 16 == 0) {
+        need[2] = round256((size_t)q.output_dim * q.input_dim * 2);
+    }
+}
+
+/* The linear operators: validate every problem, run the conversion kernels each needs
+ * (per-token quantiser for W8A8, weight dequantiser for the W8A16 scratch policy), then
+ * hand all of them to the raw layer in one grouped call. */
+static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count) {
+    if (!launch_ready(g)) return 0;
+    if (!problems || !count || count > 16) return set_error(g, "linear: between 1 and 16 problems per call");
+    size_t total[3] = {0, 0, 0};
+    for (uint32_t i = 0; i < count; i++) {
+        const h3_gpu_linear_problem &q = problems[i];
+        const uint32_t rows = q.rows, k = q.input_dim, n = q.output_dim;
+        if (!rows || !k || !n) return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
+        if (!q.weight || q.weight->owner != g) return set_error(g, "linear %ux%ux%u: weight is missing or foreign", rows, n, k);
+        if (!require(g, q.input, H3_GPU_BF16, (size_t)rows * k, "linear input") ||
+            !require(g, q.output, H3_GPU_BF16, (size_t)rows * n, "linear output")) return 0;
+        if (q.bias && !require(g, q.bias, H3_GPU_BF16, n, "linear bias")) return 0;
+        if (q.gate && !require(g, q.gate, H3_GPU_BF16, n, "linear gate")) return 0;
+        if (q.residual && !require(g, q.residual, H3_GPU_BF16, (size_t)rows * n, "linear residual")) return 0;
+        if (q.output == q.input || q.output == q.weight) return set_error(g, "linear %ux%ux%u: output aliases an operand", rows, n, k);
+        if (q.activation < 0 || q.activation > H3Q8_ACT_GELU_TANH) return set_error(g, "linear: unknown activation %d", q.activation);
+        if (q.weight->q8) {
+            if (q.weight->q8_n != n || q.weight->q8_k != k)
+                return set_error(g, "linear %ux%ux%u: q8 weight is %ux%u", rows, n, k, q.weight->q8_n, q.weight->q8_k);
+        } else if (q.weight->dtype != H3_GPU_BF16 || q.weight->elements < (size_t)n * k) {
+            return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
+        }
+        size_t need[3];
+        linear_scratch(g, q, need);
+        for (int a = 0; a < 3; a++) total[a] += need[a];
+    }
+    for (int a = 0; a < 3; a++)
+        if (total[a] && !arena(g, a, total[a])) return 0;
+
+    h3q8_linear_desc descs[16];
+    size_t offset[3] = {0, 0, 0};
+    unsigned dispatches = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        const h3_gpu_linear_problem &q = problems[i];
+        const h3_gpu_tensor *w = q.weight;
+        h3q8_linear_desc &d = descs[i];
+        d = h3q8_linear_desc{};
+        d.rows = q.rows; d.input_dim = q.input_dim; d.output_dim = q.output_dim;
+        d.bias = q.bias ? (const uint16_t *)pointer(q.bias) : nullptr;
+        d.gate = q.gate ? (const uint16_t *)pointer(q.gate) : nullptr;
+        d.residual = q.residual ? (const uint16_t *)pointer(q.residual) : nullptr;
+        d.activation = (uint32_t)q.activation;
+        d.output = (uint16_t *)pointer(q.output);
+        d.input = pointer(q.input);
+        d.weight = pointer(w);
+        size_t need[3];
+        linear_scratch(g, q, need);
+        if (w->q8) {
+            d.weight_scales = (const float *)((const char *)w->data + w->q8_scale_offset);
+            d.weight_group = w->q8_group;
+            if (need[0]) { /* W8A8: per-token quantise into context scratch, then the int8 GEMM */
+                const uint32_t padded = (q.rows + 127u) & ~127u;
+                int8_t *xq = (int8_t *)g->arena[0] + offset[0];
+                float *xs = (float *)((char *)g->arena[1] + offset[1]);
+                {
+                    ProfileScope timing(g, 7);
+                    quantize_rows_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)d.input, xq, xs, q.rows, q.input_dim, 1.0f, g->flags + 1);
+                }
+                count_launch(1);
+                dispatches++;
+                d.mode = H3Q8_MODE_W8A8;
+                d.input = xq;
+                d.input_scales = xs;
+            } else if (need[2]) {
+                /* policy 0 of the reference: dequantise once, then a bf16 GEMM (src/metal/q8_host.inc:75-88) */
+                uint16_t *wb = (uint16_t *)((char *)g->arena[2] + offset[2]);
+                ProfileScope timing(g, 7);
+                if (!h3q8_q8_dequant((const int8_t *)d.weight, d.weight_scales, wb, q.output_dim, q.input_dim, d.weight_group, g->compute)) {
+                    g->accessed.clear();
+                    return set_error(g, "%s", h3q8_last_error());
+                }
+                dispatches++;
+                d.mode = H3Q8_MODE_BF16;
+                d.weight = wb;
+                d.weight_scales = nullptr;
+                d.weight_group = 0;
+            } else d.mode = H3Q8_MODE_W8A16;
+            g->stats.q8_dispatches++;
+            g->stats.quant_projection_dispatches++;
+        } else d.mode = H3Q8_MODE_BF16;
+        for (int a = 0; a < 3; a++) offset[a] += need[a];
+    }
+    const uint64_t before = h3q8_kernel_launches();
+    {
+        ProfileScope timing(g, 0);
+        int ok = count == 1 ? h3q8_linear(&descs[0], g->compute) : h3q8_linear_grouped(descs, count, g->compute);
+        if (!ok) { g->accessed.clear(); return set_error(g, "%s", h3q8_last_error()); }
+    }
+    dispatches += (unsigned)(h3q8_kernel_launches() - before);
+    g->stats.linear_dispatches += count;
+    return launch_status(g, "linear", dispatches);
+}
+
 static int linear_dispatch(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *in, const h3_gpu_tensor *w,
                            const h3_gpu_tensor *bias, const h3_gpu_tensor *gate, const h3_gpu_tensor *residual,
                            uint32_t rows, uint32_t k, uint32_t n, int activation) {
-    if (!launch_ready(g)) return 0;
-    if (!rows || !k || !n) return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
-    if (!w || w->owner != g) return set_error(g, "linear %ux%ux%u: weight is missing or foreign", rows, n, k);
-    if (!require(g, in, H3_GPU_BF16, (size_t)rows * k, "linear input") ||
-        !require(g, out, H3_GPU_BF16, (size_t)rows * n, "linear output")) return 0;
-    if (bias && !require(g, bias, H3_GPU_BF16, n, "linear bias")) return 0;
-    if (gate && !require(g, gate, H3_GPU_BF16, n, "linear gate")) return 0;
-    if (residual && !require(g, residual, H3_GPU_BF16, (size_t)rows * n, "linear residual")) return 0;
-    if (out == in || out == w) return set_error(g, "linear %ux%ux%u: output aliases an operand", rows, n, k);
-    if (activation < 0 || activation > H3Q8_ACT_GELU_TANH) return set_error(g, "linear: unknown activation %d", activation);
-    h3q8_linear_desc d = {};
-    d.rows = rows; d.input_dim = k; d.output_dim = n;
-    d.bias = bias ? (const uint16_t *)pointer(bias) : nullptr;
-    d.gate = gate ? (const uint16_t *)pointer(gate) : nullptr;
-    d.residual = residual ? (const uint16_t *)pointer(residual) : nullptr;
-    d.activation = (uint32_t)activation;
-    d.output = (uint16_t *)pointer(out);
-    d.input = pointer(in);
-    d.weight = pointer(w);
-    unsigned dispatches = 1;
-    if (w->q8) {
-        if (w->q8_n != n || w->q8_k != k) return set_error(g, "linear %ux%ux%u: q8 weight is %ux%u", rows, n, k, w->q8_n, w->q8_k);
-        d.weight_scales = (const float *)((const char *)w->data + w->q8_scale_offset);
-        d.weight_group = w->q8_group;
-        if (g->quant_mode == 2) { /* W8A8: per-token quantise into context scratch, then the int8 GEMM */
-            uint32_t padded = (rows + 127u) & ~127u;
-            if (!arena(g, 0, (size_t)padded * k) || !arena(g, 1, (size_t)padded * sizeof(float))) return 0;
-            {
-                ProfileScope timing(g, 7);
-                quantize_rows_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)d.input, (int8_t *)g->arena[0], (float *)g->arena[1],
-                                                                     rows, k, 1.0f, g->flags + 1);
-            }
-            count_launch(1);
-            dispatches++;
-            d.mode = H3Q8_MODE_W8A8;
-            d.input = g->arena[0];
-            d.input_scales = (const float *)g->arena[1];
-        } else if (g->w8a16_scratch_rows && rows >= (uint32_t)g->w8a16_scratch_rows && k % 16 == 0) {
-            /* policy 0 of the reference: dequantise once, then a bf16 GEMM (src/metal/q8_host.inc:75-88) */
-            if (!arena(g, 2, (size_t)n * k * 2)) return 0;
-            ProfileScope timing(g, 7);
-            if (!h3q8_q8_dequant((const int8_t *)d.weight, d.weight_scales, (uint16_t *)g->arena[2], n, k, d.weight_group, g->compute))
-                return set_error(g, "%s", h3q8_last_error());
-            dispatches++;
-            d.mode = H3Q8_MODE_BF16;
-            d.weight = g->arena[2];
-            d.weight_scales = nullptr;
-            d.weight_group = 0;
-        } else d.mode = H3Q8_MODE_W8A16;
-        g->stats.q8_dispatches++;
-        g->stats.quant_projection_dispatches++;
-    } else {
-        if (w->dtype != H3_GPU_BF16 || w->elements < (size_t)n * k) return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
-        d.mode = H3Q8_MODE_BF16;
-    }
-    {
-        ProfileScope timing(g, 0);
-        if (!h3q8_linear(&d, g->compute)) { g->accessed.clear(); return set_error(g, "%s", h3q8_last_error()); }
-    }
-    g->stats.linear_dispatches++;
-    return launch_status(g, "linear", dispatches);
+    h3_gpu_linear_problem q = {out, in, w, bias, gate, residual, rows, k, n, activation};
+    return linear_dispatch_many(g, &q, 1);
 }
 
 extern "C" int h3_gpu_linear_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *in, const h3_gpu_tensor *w,
@@ -859,14 +911,11 @@ extern "C" int h3_gpu_linear_fused_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_
                                         uint32_t rows, uint32_t k, uint32_t n, int activation) {
     return linear_dispatch(g, out, in, w, bias, gate, residual, rows, k, n, activation);
 }
+/* Several projections of different shapes in one call: with bf16 or W8A8 operands (and
+ * the W8A16 scratch policy) all of them run in ONE GEMM launch on the two-CTA kernel. */
 extern "C" int h3_gpu_linear_grouped_bf16(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count) {
-    if (!g || !problems || !count) return set_error(g, "grouped linear: no problems");
-    for (uint32_t i = 0; i < count; i++) {
-        const h3_gpu_linear_problem &p = problems[i];
-        if (!linear_dispatch(g, p.output, p.input, p.weight, p.bias, p.gate, p.residual, p.rows, p.input_dim, p.output_dim, p.activation))
-            return 0;
-    }
-    return 1;
+    if (!g) return 0;
+    return linear_dispatch_many(g, problems, count);
 }
 
 extern "C" int h3_gpu_quantize_weight_int8(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_tensor *scales, const h3_gpu_tensor *in,

@@ -124,22 +124,35 @@ static int launch_tcgen05(const h3q8_linear_desc &d, GemmParams p, DeviceState *
 }
 
 /* Two-CTA clusters: the grid is twice the number of clusters that can be resident at once. */
+/* `count` problems (1..PAIR_MAX_PROBLEMS) of one operand mode in ONE launch. */
 template <int MODE>
-static int launch_pair(const h3q8_linear_desc &d, GemmParams p, DeviceState *dev, cudaStream_t stream) {
+static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, uint32_t count, DeviceState *dev, cudaStream_t stream) {
     using C = PairConfig<MODE>;
-    CUtensorMap map_a, map_b;
+    static_assert(sizeof(PairArgs) <= 4000, "kernel parameter block too large");
+    PairArgs args;
+    memset(&args, 0, sizeof args);
+    args.count = count;
     const uint32_t bytes = MODE == MODE_W8A8 ? 1 : 2;
-    if (!make_map(&map_a, d.input, bytes, d.rows, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
-    if (!make_map(&map_b, d.weight, bytes, d.output_dim, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
-    p.m_blocks = (d.rows + C::BM - 1) / C::BM;
-    p.n_blocks = (d.output_dim + C::BN - 1) / C::BN;
-    p.tiles = p.m_blocks * p.n_blocks;
-    p.band = p.m_blocks < 8 ? p.m_blocks : 8;
-    p.l2_policy_a = L2_EVICT_NORMAL;
-    p.l2_policy_b = L2_EVICT_NORMAL;
-    /* experiment knobs (not part of the interface): H3Q8_BAND=rows-blocks per band, H3Q8_L2=1 keeps weights, streams activations */
-    if (const char *e = getenv("H3Q8_BAND")) { uint32_t v = (uint32_t)atoi(e); if (v) p.band = v < p.m_blocks ? v : p.m_blocks; }
-    if (const char *e = getenv("H3Q8_L2")) { if (atoi(e) == 1) { p.l2_policy_a = L2_EVICT_FIRST; p.l2_policy_b = L2_EVICT_LAST; } }
+    uint32_t tiles = 0;
+    for (uint32_t i = 0; i < count; i++) {
+        const h3q8_linear_desc &d = descs[i];
+        GemmParams &p = args.p[i];
+        p = params[i];
+        if (!make_map(&args.map_a[i], d.input, bytes, d.rows, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+        if (!make_map(&args.map_b[i], d.weight, bytes, d.output_dim, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+        p.m_blocks = (d.rows + C::BM - 1) / C::BM;
+        p.n_blocks = (d.output_dim + C::BN - 1) / C::BN;
+        p.tiles = p.m_blocks * p.n_blocks;
+        /* measured: bands of 16 row blocks are best while a 256-row block of X is small (K*bytes <= 8 KB per row),
+         * 8 beyond that (FFN-down); L2 eviction hints (activations first, weights last) lost 3-5 % everywhere */
+        const uint32_t band = (uint64_t)d.input_dim * bytes <= 8192 ? 16 : 8;
+        p.band = p.m_blocks < band ? p.m_blocks : band;
+        p.l2_policy_a = L2_EVICT_NORMAL;
+        p.l2_policy_b = L2_EVICT_NORMAL;
+        args.tile_start[i] = tiles;
+        tiles += p.tiles;
+    }
+    args.tile_start[count] = tiles;
     auto kernel = gemm_tcgen05_pair_kernel<MODE>;
     static int clusters[64] = {};
     int device = 0;
@@ -161,8 +174,8 @@ static int launch_pair(const h3q8_linear_desc &d, GemmParams p, DeviceState *dev
         if (active < 1) return fail("the device cannot co-schedule a two-CTA cluster of the pair kernel");
         clusters[device] = active < dev->sms / 2 ? active : dev->sms / 2;
     }
-    const uint32_t pairs = p.tiles < (uint32_t)clusters[device] ? p.tiles : (uint32_t)clusters[device];
-    kernel<<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(map_a, map_b, p);
+    const uint32_t pairs = tiles < (uint32_t)clusters[device] ? tiles : (uint32_t)clusters[device];
+    kernel<<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(args);
     count_launch(1);
     return cuda_ok(cudaGetLastError(), "tcgen05 pair linear launch");
 }
@@ -185,14 +198,15 @@ static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t 
     }
     if (kernel == H3Q8_KERNEL_TCGEN05_PAIR) {
         if constexpr (MODE == MODE_W8A16) return fail("the two-CTA kernel takes bf16 or int8 operands, not main-loop dequantisation");
-        else return launch_pair<MODE>(d, p, dev, stream);
+        else return launch_pair<MODE>(&d, &p, 1, dev, stream);
     }
     if (kernel == H3Q8_KERNEL_TCGEN05_M256) return launch_tcgen05<MODE, 256, 2, false>(d, p, dev, stream);
     if (kernel == H3Q8_KERNEL_TCGEN05_N128) return launch_tcgen05<MODE, 128, 1, false>(d, p, dev, stream);
     return launch_tcgen05<MODE, 256, 1, false>(d, p, dev, stream);
 }
 
-static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
+/* Validation, kernel parameters and kernel choice for one problem. */
+static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kernel, DeviceState *&dev) {
     if (!d.rows || !d.input_dim || !d.output_dim) return fail("linear %ux%ux%u: empty dimension", d.rows, d.output_dim, d.input_dim);
     if (!d.input || !d.weight || !d.output) return fail("linear %ux%ux%u: null operand", d.rows, d.output_dim, d.input_dim);
     if (d.mode > H3Q8_MODE_W8A8) return fail("linear: unknown mode %u", d.mode);
@@ -203,11 +217,11 @@ static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
         return fail("linear: the int32 dump exists only for W8A8 with per-channel weight scales");
     if ((uint64_t)d.output_dim * d.input_dim > UINT32_MAX - 31u) return fail("linear: weight exceeds 32-bit indexing");
     if (static_cast<const void *>(d.output) == d.input) return fail("linear: output aliases the input");
-    DeviceState *dev = device_state();
+    dev = device_state();
     if (!dev) return 0;
 
     const uint32_t width = d.weight_group ? d.weight_group : d.input_dim;
-    GemmParams p = {};
+    p = GemmParams{};
     p.M = d.rows; p.N = d.output_dim; p.K = d.input_dim;
     p.scale_group = d.mode == H3Q8_MODE_BF16 ? 0 : d.weight_group;
     p.scale_groups = d.mode == H3Q8_MODE_BF16 ? 1 : (d.input_dim + width - 1) / width;
@@ -224,7 +238,7 @@ static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
                   (d.mode != H3Q8_MODE_W8A8 || aligned16(d.weight_scales));
     if (d.mode == H3Q8_MODE_W8A16 && d.weight_group && d.weight_group % 64) tma_ok = false;
     if (d.mode == H3Q8_MODE_W8A8 && d.weight_group && d.weight_group % 128) tma_ok = false;
-    uint32_t kernel = d.kernel;
+    kernel = d.kernel;
     if (kernel > H3Q8_KERNEL_TCGEN05_PAIR) return fail("linear: unknown kernel selector %u", kernel);
     if (kernel == H3Q8_KERNEL_AUTO) {
         const bool tiny = (uint64_t)d.rows * d.input_dim * d.output_dim <= (1u << 22);
@@ -241,6 +255,10 @@ static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
     }
     if (kernel == H3Q8_KERNEL_PLAIN && d.mode == H3Q8_MODE_W8A8 && d.weight_group % 16)
         return fail("linear: W8A8 weight scale group must be a multiple of 16");
+    return 1;
+}
+
+static int launch_planned(const h3q8_linear_desc &d, const GemmParams &p, uint32_t kernel, DeviceState *dev, cudaStream_t stream) {
     switch (d.mode) {
     case H3Q8_MODE_BF16: return launch_mode<MODE_BF16>(d, p, kernel, dev, stream);
     case H3Q8_MODE_W8A16: return launch_mode<MODE_W8A16>(d, p, kernel, dev, stream);
@@ -252,6 +270,13 @@ static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
 
 using namespace h3q8;
 
+static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
+    GemmParams p;
+    uint32_t kernel;
+    DeviceState *dev;
+    return plan_linear(d, p, kernel, dev) && launch_planned(d, p, kernel, dev, stream);
+}
+
 extern "C" int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream) {
     if (!desc) return fail("linear: null descriptor");
     return linear_one(*desc, (cudaStream_t)cuda_stream);
@@ -259,8 +284,24 @@ extern "C" int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream) {
 
 extern "C" int h3q8_linear_grouped(const h3q8_linear_desc *problems, uint32_t count, void *cuda_stream) {
     if (!problems || !count) return fail("grouped linear: no problems");
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    /* One launch when every problem runs on the two-CTA kernel in the same operand mode;
+     * otherwise the problems are enqueued back to back. */
+    if (count <= PAIR_MAX_PROBLEMS) {
+        GemmParams params[PAIR_MAX_PROBLEMS];
+        DeviceState *dev = nullptr;
+        bool together = true;
+        for (uint32_t i = 0; i < count; i++) {
+            uint32_t kernel;
+            if (!plan_linear(problems[i], params[i], kernel, dev)) return 0;
+            together = together && kernel == H3Q8_KERNEL_TCGEN05_PAIR && problems[i].mode == problems[0].mode;
+        }
+        if (together && count > 1)
+            return problems[0].mode == H3Q8_MODE_BF16 ? launch_pair<MODE_BF16>(problems, params, count, dev, stream)
+                                                       : launch_pair<MODE_W8A8>(problems, params, count, dev, stream);
+    }
     for (uint32_t i = 0; i < count; i++)
-        if (!linear_one(problems[i], (cudaStream_t)cuda_stream)) return 0;
+        if (!linear_one(problems[i], stream)) return 0;
     return 1;
 }
 
