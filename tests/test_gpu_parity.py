@@ -422,10 +422,15 @@ def test_config2_block_stack(oracle):
         gpu.free()
 
 
-def test_config4_grouped_call(gpu, oracle):
-    """Video (K=N=3072) and audio (K=N=1536) problems with separate weight sets in
-    one grouped call (row counts scaled down; the two shapes are what matters)."""
+@pytest.mark.parametrize("quant_mode", [1, 2])
+def test_config4_grouped_call(oracle, quant_mode):
+    """Video (K=N=3072) and audio (K=N=1536) problems with separate weight sets in ONE
+    GEMM launch (row counts scaled down; the two shapes are what matters): after the
+    per-problem conversion kernels exactly one more kernel is launched."""
     specs = [(2 * 1296, 3072, 3072), (2 * 1152, 1536, 1536)]
+    gpu = h.Gpu()
+    gpu.quant_configure(quant_mode)
+    gpu.set_w8a16_scratch_rows(1)
     problems, wants = [], []
     for i, (M, N, K) in enumerate(specs):
         x, wq, ws = operands(40 + i, M, N, K, 0)
@@ -433,14 +438,55 @@ def test_config4_grouped_call(gpu, oracle):
         tx, out = gpu.tensor_from_bf16(x), gpu.tensor_new_bf16(M * N)
         problems.append(dict(output=out, input=tx, weight=w, rows=M, input_dim=K, output_dim=N))
         rows = sample_rows(M, 16, i)
-        wants.append((rows, oracle.linear(oracle.MODE_W8A16, x[rows], wq, ws, 0), M, N))
+        if quant_mode == 1:
+            wants.append((rows, oracle.linear(oracle.MODE_W8A16, x[rows], wq, ws, 0), M, N))
+        else:
+            xq, xs = oracle.quantize_rows(x[rows])
+            wants.append((rows, oracle.linear(oracle.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, x_scales=xs), M, N))
+    before = h.library().h3q8_kernel_launches()
     gpu.begin()
     gpu.linear_grouped_bf16(problems)
     gpu.submit()
+    assert h.library().h3q8_kernel_launches() - before == 3      # two conversion kernels + ONE GEMM launch
     for p, (rows, want, M, N) in zip(problems, wants):
-        check_bf16(p["output"].read().reshape(M, N)[rows], want)
+        got = p["output"].read().reshape(M, N)[rows]
+        if quant_mode == 2:
+            assert (got == want).all()
+        else:
+            check_bf16(got, want)
         for key in ("output", "input", "weight"):
             p[key].free()
+    gpu.free()
+
+
+def test_grouped_launch_equals_separate_launches(gpu, oracle):
+    """Four bf16 problems of different shapes (ragged rows, N and K tails) through
+    h3q8_linear_grouped: one launch, and the same bits as four separate launches."""
+    import ctypes
+    shapes = [(300, 520, 512), (129, 264, 1040), (1000, 256, 64), (257, 3072, 128)]
+    lib = h.library()
+    descs, keep, separate = (h.LinearDesc * len(shapes))(), [], []
+    for i, (M, N, K) in enumerate(shapes):
+        x, wq, ws = operands(45 + i, M, N, K, 64)
+        wb = oracle.q8_dequant(wq, ws, 64)
+        bias, gate, res, act = epilogue_operands(45 + i, M, N, "bgra" if i % 2 else "b")
+        separate.append(raw_linear(gpu, h.MODE_BF16, x, wb, bias=bias, gate=gate, residual=res, activation=act,
+                                   kernel=h.KERNEL_TCGEN05_PAIR))
+        t = upload(gpu, input=x, weight=wb, bias=bias, gate=gate, residual=res)
+        t["output"] = gpu.tensor_new_bf16(M * N)
+        keep.append(t)
+        d = descs[i]
+        d.mode, d.rows, d.input_dim, d.output_dim, d.activation, d.kernel = h.MODE_BF16, M, K, N, act, h.KERNEL_TCGEN05_PAIR
+        for name, tensor in t.items():
+            setattr(d, name, tensor.device_pointer)
+    before = lib.h3q8_kernel_launches()
+    assert lib.h3q8_linear_grouped(descs, len(shapes), gpu.stream), lib.h3q8_last_error()
+    assert gpu.raw_status() == 0
+    assert lib.h3q8_kernel_launches() - before == 1
+    for (M, N, K), t, want in zip(shapes, keep, separate):
+        assert (t["output"].read().reshape(M, N) == want).all()
+        for tensor in t.values():
+            tensor.free()
 
 
 def test_fused_equals_unfused_chain(gpu):
