@@ -268,32 +268,45 @@ def main():
     # ---- e2e: the same four operators, host buffers in, host buffer out ------------------------------
     # Chain as a DiT block calls them: x -> qkv; x -> attn_out (+gate, residual x) -> ffn_up (GELU) ->
     # ffn_down (+gate, residual h1).  Per step the block input crosses PCIe in and the block output out.
+    # The rows are cut into E2E_CHUNKS slices with their own tensors, so that the upload of slice c+1 and the
+    # download of slice c-1 (copy stream, h3q8_gpu_tensor_upload_async / _download_async) overlap the GEMMs of slice c.
+    from h3cli_b200 import sharding
     host_x = torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory()
     host_y = torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory()
     lib.h3_gpu_tensor_read_bf16(x.handle, host_x.data_ptr(), M_TOKENS * HIDDEN)
-    h1 = gpu.tensor_new_bf16(M_TOKENS * HIDDEN)
+    for t in list(outputs.values()) + [hidden, residual]:
+        t.free()                                      # the resident-run tensors are no longer needed
+    E2E_CHUNKS = 4
+    slices = []
+    for begin, end in sharding.all_ranges(M_TOKENS, E2E_CHUNKS):
+        rows = end - begin
+        slices.append(dict(rows=rows, offset=begin * HIDDEN * 2, x=gpu.tensor_new_bf16(rows * HIDDEN),
+                           qkv=gpu.tensor_new_bf16(rows * 3 * HIDDEN), h1=gpu.tensor_new_bf16(rows * HIDDEN),
+                           up=gpu.tensor_new_bf16(rows * FFN), y=gpu.tensor_new_bf16(rows * HIDDEN)))
 
     def step_e2e():
-        lib.h3_gpu_tensor_write_bf16(x.handle, host_x.data_ptr(), M_TOKENS * HIDDEN)
+        for c in slices:
+            c["x"].upload_async(host_x.data_ptr() + c["offset"], c["rows"] * HIDDEN * 2)
         gpu.begin()
-        gpu.linear_fused_bf16(outputs["qkv"], x, weights["qkv"], None, None, None, M_TOKENS, HIDDEN, 3 * HIDDEN, 0)
-        gpu.linear_fused_bf16(h1, x, weights["attn_out"], None, gate, x, M_TOKENS, HIDDEN, HIDDEN, 0)
-        gpu.linear_fused_bf16(outputs["ffn_up"], h1, weights["ffn_up"], None, None, None, M_TOKENS, HIDDEN, FFN, 1)
-        gpu.linear_fused_bf16(outputs["ffn_down"], outputs["ffn_up"], weights["ffn_down"], None, gate, h1, M_TOKENS, FFN, HIDDEN, 0)
+        for c in slices:
+            rows = c["rows"]
+            gpu.linear_fused_bf16(c["qkv"], c["x"], weights["qkv"], None, None, None, rows, HIDDEN, 3 * HIDDEN, 0)
+            gpu.linear_fused_bf16(c["h1"], c["x"], weights["attn_out"], None, gate, c["x"], rows, HIDDEN, HIDDEN, 0)
+            gpu.linear_fused_bf16(c["up"], c["h1"], weights["ffn_up"], None, None, None, rows, HIDDEN, FFN, 1)
+            gpu.linear_fused_bf16(c["y"], c["up"], weights["ffn_down"], None, gate, c["h1"], rows, FFN, HIDDEN, 0)
+            gpu.continue_()
+            c["y"].download_async(host_y.data_ptr() + c["offset"], rows * HIDDEN * 2)
         gpu.submit()
-        lib.h3_gpu_tensor_read_bf16(outputs["ffn_down"].handle, host_y.data_ptr(), M_TOKENS * HIDDEN)
+        gpu.synchronize()                             # the block output is in host memory when the step ends
 
     for _ in range(3):
         step_e2e()
     barrier()
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record(stream)
     wall = time.perf_counter()
     for _ in range(args.steps):
         step_e2e()
-    e_stop.record(stream)
+    e_seconds = time.perf_counter() - wall
     barrier()
-    e_seconds = max(e_start.elapsed_time(e_stop) * 1e-3, time.perf_counter() - wall if world == 1 else 0.0)
     t = torch.tensor([e_seconds], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -312,8 +325,10 @@ def main():
             "tensor_peak_fraction_per_gpu": value / world / burst,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": M_TOKENS * HIDDEN * 2,
                     "d2h_bytes_per_step": M_TOKENS * HIDDEN * 2,
-                    "path": "h3_gpu_tensor_write_bf16 -> 4 x h3_gpu_linear_fused_bf16 (chained as the DiT block calls them) "
-                            "-> h3_gpu_submit -> h3_gpu_tensor_read_bf16, pinned host buffers"},
+                    "ms_per_step": float(t.item()) / args.steps * 1e3,
+                    "path": "pinned host x -> h3q8_gpu_tensor_upload_async -> 4 x h3_gpu_linear_fused_bf16 per row slice (chained as "
+                            "the DiT block calls them, 4 row slices so copies overlap compute) -> h3q8_gpu_tensor_download_async -> "
+                            "pinned host y; h3_gpu_submit + h3_gpu_synchronize end the step; host wall clock, max over ranks"},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel<bf16> (256x256 tile per CTA pair) after q8_dequant_kernel" if args.mode == "w8a16"

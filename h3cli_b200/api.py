@@ -30,6 +30,7 @@ class LinearDesc(C.Structure):
         ("input", C.c_void_p), ("weight", C.c_void_p), ("weight_scales", C.c_void_p), ("weight_group", C.c_uint32),
         ("input_scales", C.c_void_p), ("bias", C.c_void_p), ("gate", C.c_void_p), ("residual", C.c_void_p),
         ("activation", C.c_uint32), ("output", C.c_void_p), ("accumulators", C.c_void_p), ("kernel", C.c_uint32),
+        ("input_group", C.c_uint32),
     ]
 
 
@@ -74,6 +75,7 @@ def library():
         "h3q8_linear_grouped": (C.c_int, [C.POINTER(LinearDesc), u32, vp]),
         "h3q8_linear_w8a8_static": (C.c_int, [C.POINTER(LinearDesc), vp, vp]),
         "h3q8_quantize_rows": (C.c_int, [vp, vp, vp, u32, u32, u32, C.c_float, vp]),
+        "h3q8_quantize_rows_grouped": (C.c_int, [vp, vp, vp, u32, u32, u32, u32, vp]),
         "h3q8_q8_pack_rows_device": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
         "h3q8_q8_dequant": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
         "h3q8_device_status": (u32, [vp]),
@@ -111,6 +113,8 @@ def library():
         "h3q8_gpu_tensor_device_pointer": (vp, [vp]), "h3q8_gpu_compute_stream": (vp, [vp]),
         "h3q8_gpu_set_w8a16_scratch_rows": (C.c_int, [vp, u32]),
         "h3q8_gpu_set_profiling": (C.c_int, [vp, C.c_int]),
+        "h3q8_gpu_tensor_upload_async": (C.c_int, [vp, vp, sz]),
+        "h3q8_gpu_tensor_download_async": (C.c_int, [vp, vp, sz]),
         "h3q8_gpu_q8_from_host": (vp, [vp, vp, vp, u32, u32, u32]),
         "h3q8_gpu_weight_stream_create": (vp, [vp, sz, u32]),
         "h3q8_gpu_weight_stream_prefetch": (C.c_int, [vp, vp, sz]),
@@ -170,6 +174,12 @@ class Tensor:
         values = np.ascontiguousarray(values)
         fn = {F32: "write_f32", BF16: "write_bf16", I8: "write_i8"}[self.dtype]
         self.gpu._check(getattr(library(), "h3_gpu_tensor_" + fn)(self.handle, values.ctypes.data, values.size))
+
+    def upload_async(self, host_pointer, nbytes):
+        self.gpu._check(library().h3q8_gpu_tensor_upload_async(self.handle, host_pointer, nbytes))
+
+    def download_async(self, host_pointer, nbytes):
+        self.gpu._check(library().h3q8_gpu_tensor_download_async(self.handle, host_pointer, nbytes))
 
     def free(self):
         if self.handle:

@@ -36,8 +36,9 @@ enum : uint32_t {
 
 struct GemmParams {
     uint32_t M, N, K;
-    uint32_t scale_group;   /* K elements per weight scale; 0 = one scale per output channel */
-    uint32_t scale_groups;  /* scales per weight row                                         */
+    uint32_t scale_group;   /* K elements per scale group (weights and/or activations); 0 = none */
+    uint32_t scale_groups;  /* scales per weight row (1 = per output channel)                    */
+    uint32_t a_scale_groups;/* scales per activation row (1 = per token), MODE_W8A8              */
     const float *w_scales;  /* [N, scale_groups] (MODE_W8A16, MODE_W8A8)                     */
     const float *a_scales;  /* [M] per-token scales (MODE_W8A8)                              */
     EpilogueParams ep;
@@ -243,7 +244,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     const uint32_t row = mb * C::BM + mt * 128 + quadrant * 32 + lane;
                     const bool row_ok = row < p.M;
                     float a_scale = 1.0f;
-                    if (MODE == MODE_W8A8) a_scale = row_ok ? p.a_scales[row] : 0.0f;
+                    if (MODE == MODE_W8A8)
+                        a_scale = !row_ok ? 0.0f : !GROUPED || p.a_scale_groups == 1 ? p.a_scales[(size_t)row * p.a_scale_groups]
+                                                 : p.a_scales[(size_t)row * p.a_scale_groups + chunk];
 #pragma unroll(GROUPED ? HALF_CHUNKS : 1)
                     for (int hc = 0; hc < HALF_CHUNKS; hc++) {
                         const int c = half * HALF_CHUNKS + hc;
@@ -255,7 +258,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                             for (int j = 0; j < 32; j++) {
                                 uint32_t col = col0 + j;
-                                float ws = col < p.N ? p.w_scales[(size_t)col * p.scale_groups + chunk] : 0.0f;
+                                float ws = col < p.N ? p.w_scales[(size_t)col * p.scale_groups + (p.scale_groups == 1 ? 0 : chunk)] : 0.0f;
                                 float value = __fmul_rn(__fmul_rn((float)(int32_t)v[j], a_scale), ws);
                                 totals[hc * 32 + j] = chunk ? __fadd_rn(totals[hc * 32 + j], value) : value;
                             }

@@ -413,6 +413,33 @@ extern "C" int h3_gpu_tensor_write_bf16_range(h3_gpu_tensor *t, size_t offset, c
     return upload(t, offset * 2, values, elements * 2);
 }
 
+extern "C" int h3q8_gpu_tensor_upload_async(h3_gpu_tensor *t, const void *host, size_t bytes) {
+    if (!t || !host) return 0;
+    h3_gpu *g = t->owner;
+    if (bytes > t->bytes) return set_error(g, "tensor write out of range");
+    std::lock_guard<std::mutex> lock(g->copy_mutex);
+    if (!selected(g)) return 0;
+    if (t->release_recorded) cudaStreamWaitEvent(g->copy, t->released, 0);
+    if (!checked(g, cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, g->copy), "asynchronous host to device copy", bytes) ||
+        !checked(g, cudaEventRecord(t->ready, g->copy), "tensor ready event")) return 0;
+    t->ready_recorded = true;
+    g->stats.h2d_bytes += bytes;
+    return 1;
+}
+extern "C" int h3q8_gpu_tensor_download_async(h3_gpu_tensor *t, void *host, size_t bytes) {
+    if (!t || !host) return 0;
+    h3_gpu *g = t->owner;
+    if (bytes > t->bytes) return set_error(g, "tensor read out of range");
+    std::lock_guard<std::mutex> lock(g->copy_mutex);
+    if (!selected(g)) return 0;
+    if (t->release_recorded) cudaStreamWaitEvent(g->copy, t->released, 0);
+    if (!checked(g, cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, g->copy), "asynchronous device to host copy", bytes) ||
+        !checked(g, cudaEventRecord(t->ready, g->copy), "tensor ready event")) return 0;
+    t->ready_recorded = true; /* the next operator that writes the tensor waits for this copy */
+    g->stats.d2h_bytes += bytes;
+    return 1;
+}
+
 extern "C" h3_gpu_event *h3_gpu_event_new(h3_gpu *g) {
     if (!selected(g)) return nullptr;
     h3_gpu_event *e = new (std::nothrow) h3_gpu_event;

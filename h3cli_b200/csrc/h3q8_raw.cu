@@ -190,7 +190,7 @@ static int launch_plain(const h3q8_linear_desc &d, const GemmParams &p, cudaStre
 
 template <int MODE>
 static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t kernel, DeviceState *dev, cudaStream_t stream) {
-    const bool grouped8 = MODE == MODE_W8A8 && d.weight_group != 0;
+    const bool grouped8 = MODE == MODE_W8A8 && p.scale_group != 0;
     if (kernel == H3Q8_KERNEL_PLAIN) return launch_plain<MODE>(d, p, stream);
     if (grouped8) {
         if (MODE == MODE_W8A8) return launch_tcgen05<MODE_W8A8, 128, 1, true>(d, p, dev, stream);
@@ -221,10 +221,16 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     if (!dev) return 0;
 
     const uint32_t width = d.weight_group ? d.weight_group : d.input_dim;
+    if (d.input_group && d.mode != H3Q8_MODE_W8A8) return fail("linear: input_group applies to W8A8 only");
+    if (d.input_group && d.weight_group && d.input_group != d.weight_group)
+        return fail("linear: activation and weight scale groups must have the same width");
+    if (d.input_group && d.input_dim % d.input_group) return fail("linear: input_dim must be a multiple of input_group");
+    if (d.accumulators && d.input_group) return fail("linear: the int32 dump exists only for ungrouped W8A8");
     p = GemmParams{};
     p.M = d.rows; p.N = d.output_dim; p.K = d.input_dim;
-    p.scale_group = d.mode == H3Q8_MODE_BF16 ? 0 : d.weight_group;
-    p.scale_groups = d.mode == H3Q8_MODE_BF16 ? 1 : (d.input_dim + width - 1) / width;
+    p.scale_group = d.mode == H3Q8_MODE_BF16 ? 0 : d.weight_group ? d.weight_group : d.input_group;
+    p.scale_groups = d.mode == H3Q8_MODE_BF16 || !d.weight_group ? 1 : (d.input_dim + width - 1) / width;
+    p.a_scale_groups = d.input_group ? d.input_dim / d.input_group : 1;
     p.w_scales = d.weight_scales; p.a_scales = d.input_scales;
     p.ep.bias = d.bias; p.ep.gate = d.gate; p.ep.residual = d.residual; p.ep.activation = d.activation;
     p.out = d.output; p.acc_dump = d.accumulators; p.status = dev->status;
@@ -237,23 +243,23 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
                   (!d.residual || aligned16(d.residual)) && (!d.accumulators || aligned16(d.accumulators)) &&
                   (d.mode != H3Q8_MODE_W8A8 || aligned16(d.weight_scales));
     if (d.mode == H3Q8_MODE_W8A16 && d.weight_group && d.weight_group % 64) tma_ok = false;
-    if (d.mode == H3Q8_MODE_W8A8 && d.weight_group && d.weight_group % 128) tma_ok = false;
+    if (d.mode == H3Q8_MODE_W8A8 && p.scale_group && p.scale_group % 128) tma_ok = false;
     kernel = d.kernel;
     if (kernel > H3Q8_KERNEL_TCGEN05_PAIR) return fail("linear: unknown kernel selector %u", kernel);
     if (kernel == H3Q8_KERNEL_AUTO) {
         const bool tiny = (uint64_t)d.rows * d.input_dim * d.output_dim <= (1u << 22);
         /* two-CTA tiles need both CTAs to have rows; main-loop dequantisation and grouped W8A8 stay single-CTA */
-        const bool pair_ok = d.rows > 128 && (d.mode == H3Q8_MODE_BF16 || (d.mode == H3Q8_MODE_W8A8 && !d.weight_group));
+        const bool pair_ok = d.rows > 128 && (d.mode == H3Q8_MODE_BF16 || (d.mode == H3Q8_MODE_W8A8 && !p.scale_group));
         kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128
                : pair_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_TCGEN05;
-    } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && d.weight_group))) {
+    } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && p.scale_group))) {
         return fail("linear: the two-CTA kernel takes bf16 or per-channel int8 operands");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {
         return fail("linear %ux%ux%u: shape or alignment not supported by the tcgen05 kernel "
                     "(K %% %u, N %% 8, 16-byte aligned operands, scale group %% 64/128)",
                     d.rows, d.output_dim, d.input_dim, k_multiple);
     }
-    if (kernel == H3Q8_KERNEL_PLAIN && d.mode == H3Q8_MODE_W8A8 && d.weight_group % 16)
+    if (kernel == H3Q8_KERNEL_PLAIN && d.mode == H3Q8_MODE_W8A8 && p.scale_group % 16)
         return fail("linear: W8A8 weight scale group must be a multiple of 16");
     return 1;
 }
@@ -315,6 +321,15 @@ extern "C" int h3q8_quantize_rows(const uint16_t *input, int8_t *output, float *
     quantize_rows_kernel<<<dispatch_rows, 256, 0, (cudaStream_t)cuda_stream>>>(input, output, scales, rows, columns, clip, nullptr);
     count_launch(1);
     return cuda_ok(cudaGetLastError(), "quantize rows launch");
+}
+
+extern "C" int h3q8_quantize_rows_grouped(const uint16_t *input, int8_t *output, float *scales, uint32_t rows,
+                                          uint32_t dispatch_rows, uint32_t columns, uint32_t group, void *cuda_stream) {
+    if (!group || columns % group) return fail("quantize rows: columns must be a multiple of the group width");
+    const uint64_t groups = columns / group;
+    if (dispatch_rows * groups > UINT32_MAX) return fail("quantize rows: too many row groups");
+    /* every (row, group) is an independent row of `group` columns of the same contiguous matrix */
+    return h3q8_quantize_rows(input, output, scales, (uint32_t)(rows * groups), (uint32_t)(dispatch_rows * groups), group, 1.0f, cuda_stream);
 }
 
 extern "C" int h3q8_q8_pack_rows_device(const uint16_t *source, int8_t *weights, float *scales, uint32_t rows,

@@ -132,7 +132,7 @@ extern "C" int h3q8_linear_w8a8_static(const h3q8_linear_desc *desc, uint32_t *d
     if (!d.rows || !d.input_dim || !d.output_dim || !d.input || !d.weight || !d.weight_scales || !d.output)
         return fail("static W8A8: missing operand or empty dimension");
     if (d.input_scales) return fail("static W8A8: input is bf16 here; leave input_scales NULL (the scales live in the static scratch)");
-    if (d.weight_group || d.accumulators) return fail("static W8A8: per-channel weight scales only, no accumulator dump");
+    if (d.weight_group || d.input_group || d.accumulators) return fail("static W8A8: per-channel weight scales only, no accumulator dump");
     if (d.activation > H3Q8_ACT_GELU_TANH) return fail("static W8A8: unknown activation %u", d.activation);
     if (d.rows > MAX_ROWS || (uint64_t)d.rows * d.input_dim > ACTIVATION_BYTES)
         return fail("static W8A8: %u x %u activations exceed the built-in scratch (rows <= %u and rows * input_dim <= %zu bytes); "
@@ -163,7 +163,7 @@ extern "C" int h3q8_linear_w8a8_static(const h3q8_linear_desc *desc, uint32_t *d
         return fail("static W8A8: cuTensorMapEncodeTiled failed");
     GemmParams p = {};
     p.M = d.rows; p.N = d.output_dim; p.K = d.input_dim;
-    p.scale_group = 0; p.scale_groups = 1;
+    p.scale_group = 0; p.scale_groups = 1; p.a_scale_groups = 1;
     p.w_scales = d.weight_scales; p.a_scales = scales;
     p.ep.bias = d.bias; p.ep.gate = d.gate; p.ep.residual = d.residual; p.ep.activation = d.activation;
     p.out = d.output; p.acc_dump = nullptr; p.status = status;

@@ -220,7 +220,8 @@ __global__ void __launch_bounds__(256) linear_plain_kernel(const void *__restric
                 for (int j = 0; j < 4; j++) {
                     const uint32_t r = row0 + ty * 4 + i, c = col0 + tx * 4 + j;
                     if (r < p.M && c < p.N) {
-                        float value = __fmul_rn(__fmul_rn((float)acc[i][j], p.a_scales[r]), p.w_scales[(size_t)c * p.scale_groups + g]);
+                        float value = __fmul_rn(__fmul_rn((float)acc[i][j], p.a_scales[(size_t)r * p.a_scale_groups + (p.a_scale_groups == 1 ? 0 : g)]),
+                                                p.w_scales[(size_t)c * p.scale_groups + (p.scale_groups == 1 ? 0 : g)]);
                         totals[i][j] = g ? __fadd_rn(totals[i][j], value) : value;
                     }
                     acc[i][j] = 0;

@@ -74,6 +74,9 @@ typedef struct {
     uint16_t *output;         /* bf16 [M,N]                                                */
     int32_t *accumulators;    /* optional int32 [M,N] dump (W8A8, per-channel scales)      */
     uint32_t kernel;          /* H3Q8_KERNEL_*                                             */
+    uint32_t input_group;     /* W8A8: K elements per activation scale, input_scales is then
+                                 [M, K/input_group] (the reference's per-1024 FC2 scales,
+                                 src/metal/shaders.metal:2663-2742); 0 = one scale per token   */
 } h3q8_linear_desc;
 int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream);
 
@@ -104,6 +107,11 @@ int h3q8_linear_w8a8_static(const h3q8_linear_desc *desc, uint32_t *device_statu
  * Rows in [rows, dispatch_rows) are padding: zero bytes, scale 1. */
 int h3q8_quantize_rows(const uint16_t *input, int8_t *output, float *scales, uint32_t rows,
                        uint32_t dispatch_rows, uint32_t columns, float clip, void *cuda_stream);
+/* Per-token, per-K-group variant (src/metal/shaders.metal:1552-1598): the same recipe
+ * applied to every `group` consecutive columns of a row; scales are [dispatch_rows,
+ * columns/group].  columns must be a multiple of group. */
+int h3q8_quantize_rows_grouped(const uint16_t *input, int8_t *output, float *scales, uint32_t rows,
+                               uint32_t dispatch_rows, uint32_t columns, uint32_t group, void *cuda_stream);
 /* Device version of h3q8_q8_pack_rows (bf16 [N,K] -> int8 [N,K] + scales). */
 int h3q8_q8_pack_rows_device(const uint16_t *source, int8_t *weights, float *scales, uint32_t rows,
                              uint32_t columns, uint32_t group, void *cuda_stream);
@@ -219,6 +227,14 @@ int h3q8_gpu_set_group(h3_gpu *gpu, uint32_t group);
  * tensors with the raw h3q8_* entry points. */
 void *h3q8_gpu_tensor_device_pointer(const h3_gpu_tensor *tensor);
 void *h3q8_gpu_compute_stream(h3_gpu *gpu);
+/* Asynchronous host <-> tensor copies on the context's copy stream, ordered against the
+ * compute stream by the tensor's own events (the mechanism of the reference's streamed
+ * tensors, src/cuda/gpu_cuda.cu:223-251): an upload waits until compute has released the
+ * tensor and marks it ready, operators wait for ready; a download waits until the last
+ * operator that touched the tensor is done, and later operators wait for the download.
+ * Host memory should be pinned.  h3_gpu_synchronize() waits for both streams. */
+int h3q8_gpu_tensor_upload_async(h3_gpu_tensor *tensor, const void *host, size_t bytes);
+int h3q8_gpu_tensor_download_async(h3_gpu_tensor *tensor, void *host, size_t bytes);
 /* Rows at or above which a W8A16 linear first dequantises the weight into
  * context scratch and runs the bf16 GEMM (the reference's policy 0,
  * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop. */

@@ -34,7 +34,7 @@ class _Args(ctypes.Structure):
         ("bias", ctypes.c_void_p), ("gate", ctypes.c_void_p), ("residual", ctypes.c_void_p),
         ("activation", ctypes.c_uint32),
         ("output", ctypes.c_void_p), ("accumulators", ctypes.c_void_p),
-        ("fast", ctypes.c_int),
+        ("fast", ctypes.c_int), ("input_group", ctypes.c_uint32),
     ]
 
 
@@ -135,8 +135,17 @@ def gelu_tanh_bf16(b):
     return np.array([f(int(v)) for v in np.asarray(b, np.uint16).ravel()], np.uint16).reshape(np.shape(b))
 
 
+def quantize_rows_grouped(x_bf16, group, dispatch_rows=None):
+    """src/metal/shaders.metal:1552-1598: the row recipe on every `group` columns; scales [rows, K/group]."""
+    rows, cols = x_bf16.shape
+    dispatch_rows = dispatch_rows or rows
+    groups = cols // group
+    q, s = quantize_rows(np.ascontiguousarray(x_bf16).reshape(rows * groups, group), dispatch_rows * groups)
+    return q.reshape(dispatch_rows, cols), s.reshape(dispatch_rows, groups)
+
+
 def linear(mode, x, w, w_scales=None, group=0, x_scales=None, bias=None, gate=None,
-           residual=None, activation=ACT_NONE, fast=False, want_acc=False):
+           residual=None, activation=ACT_NONE, fast=False, want_acc=False, input_group=0):
     """out[M,N] (bf16 bits) = epilogue(x . w^T); see h3o_linear_args."""
     M, K = x.shape
     N = w.shape[0]
@@ -145,7 +154,7 @@ def linear(mode, x, w, w_scales=None, group=0, x_scales=None, bias=None, gate=No
     out = np.empty((M, N), np.uint16)
     acc = np.empty((M, N), np.int32) if want_acc else None
     a = _Args(mode, M, K, N, _ptr(keep[0]), _ptr(keep[1]), _ptr(keep[2]), group, _ptr(keep[3]),
-              _ptr(keep[4]), _ptr(keep[5]), _ptr(keep[6]), activation, _ptr(out), _ptr(acc), int(fast))
+              _ptr(keep[4]), _ptr(keep[5]), _ptr(keep[6]), activation, _ptr(out), _ptr(acc), int(fast), input_group)
     if not lib().h3o_linear(ctypes.byref(a)):
         raise ValueError("oracle rejected the arguments")
     return (out, acc) if want_acc else out

@@ -183,8 +183,10 @@ static int validate(const h3o_linear_args *a) {
  * fp32 products of bf16 activations and bf16-rounded dequantised weights). */
 static void linear_spec(const h3o_linear_args *a) {
     uint32_t M = a->rows, K = a->input_dim, N = a->output_dim;
-    uint32_t width = group_width(K, a->weight_group);
+    uint32_t chunk = a->weight_group ? a->weight_group : a->input_group;
+    uint32_t width = group_width(K, a->mode == H3O_MODE_W8A8 ? chunk : a->weight_group);
     uint32_t groups = (uint32_t)(((uint64_t)K + width - 1) / width);
+    uint32_t wgroups = a->weight_group ? groups : 1, agroups = a->input_group ? groups : 1;
 #pragma omp parallel for schedule(dynamic, 4)
     for (uint32_t r = 0; r < M; r++) {
         for (uint32_t n = 0; n < N; n++) {
@@ -192,7 +194,7 @@ static void linear_spec(const h3o_linear_args *a) {
             if (a->mode == H3O_MODE_W8A8) {
                 const int8_t *x = (const int8_t *)a->input + (size_t)r * K;
                 const int8_t *w = (const int8_t *)a->weight + (size_t)n * K;
-                if (!a->weight_group) { /* shaders.metal:2455-2465 */
+                if (!chunk) { /* shaders.metal:2455-2465 */
                     int32_t acc = 0;
                     for (uint32_t k = 0; k < K; k++) acc += (int32_t)x[k] * (int32_t)w[k];
                     if (a->accumulators) a->accumulators[(size_t)r * N + n] = acc;
@@ -204,8 +206,8 @@ static void linear_spec(const h3o_linear_args *a) {
                         uint32_t last = (g + 1) * width < K ? (g + 1) * width : K;
                         for (uint32_t k = g * width; k < last; k++)
                             acc += (int32_t)x[k] * (int32_t)w[k];
-                        float value = (float)acc * a->input_scales[r] *
-                                      a->weight_scales[(size_t)n * groups + g];
+                        float value = (float)acc * a->input_scales[(size_t)r * agroups + (agroups == 1 ? 0 : g)] *
+                                      a->weight_scales[(size_t)n * wgroups + (wgroups == 1 ? 0 : g)];
                         linear = g ? linear + value : value;
                     }
                 }
@@ -265,10 +267,12 @@ static void micro_i32(const int16_t *x, size_t xs, const int16_t *wt, uint32_t k
 
 static void linear_fast(const h3o_linear_args *a) {
     uint32_t M = a->rows, K = a->input_dim, N = a->output_dim;
-    uint32_t width = group_width(K, a->weight_group);
-    uint32_t groups = (uint32_t)(((uint64_t)K + width - 1) / width);
     int integer = a->mode == H3O_MODE_W8A8;
-    uint32_t kslab = integer && a->weight_group ? width : KB;
+    uint32_t chunk = a->weight_group ? a->weight_group : a->input_group;
+    uint32_t width = group_width(K, integer ? chunk : a->weight_group);
+    uint32_t groups = (uint32_t)(((uint64_t)K + width - 1) / width);
+    uint32_t wgroups = a->weight_group ? groups : 1, agroups = a->input_group ? groups : 1;
+    uint32_t kslab = integer && chunk ? width : KB;
     uint32_t ntiles = (N + NB - 1) / NB;
     /* Activations widened once: fp32 (bf16 is exact in fp32) or int16. */
     size_t xelements = (size_t)M * K;
@@ -333,10 +337,10 @@ static void linear_fast(const h3o_linear_args *a) {
                                     acc[i][j] += (int32_t)xi[(size_t)(r0 + i) * K + k0 + k] * wti[(size_t)k * NB + j];
                         for (uint32_t i = 0; i < rw; i++)
                             for (uint32_t j = 0; j < nw; j++) {
-                                if (!a->weight_group) itotal[r0 + i][j] += acc[i][j];
+                                if (!chunk) itotal[r0 + i][j] += acc[i][j];
                                 else {
-                                    float value = (float)acc[i][j] * a->input_scales[r0 + i] *
-                                        a->weight_scales[(size_t)(n0 + j) * groups + g];
+                                    float value = (float)acc[i][j] * a->input_scales[(size_t)(r0 + i) * agroups + (agroups == 1 ? 0 : g)] *
+                                        a->weight_scales[(size_t)(n0 + j) * wgroups + (wgroups == 1 ? 0 : g)];
                                     total[r0 + i][j] = g ? total[r0 + i][j] + value : value;
                                 }
                             }
@@ -346,7 +350,7 @@ static void linear_fast(const h3o_linear_args *a) {
             for (uint32_t r = 0; r < M; r++)
                 for (uint32_t j = 0; j < nw; j++) {
                     float linear = total[r][j];
-                    if (integer && !a->weight_group) {
+                    if (integer && !chunk) {
                         if (a->accumulators) a->accumulators[(size_t)r * N + n0 + j] = itotal[r][j];
                         linear = (float)itotal[r][j] * a->input_scales[r] * a->weight_scales[n0 + j];
                     }

@@ -76,6 +76,8 @@ typedef struct {
     uint16_t *output;
     int32_t *accumulators; /* optional [M,N] int32 dump, W8A8 per-channel only */
     int fast;              /* 0: scalar spec (FP64 dot); 1: blocked fp32 OpenMP */
+    uint32_t input_group;  /* W8A8: K elements per activation scale (input_scales [M, K/group]);
+                              0 = per token.  src/metal/shaders.metal:2663-2742 (per-1024 FC2 scales) */
 } h3o_linear_args;
 int h3o_linear(const h3o_linear_args *args);
 

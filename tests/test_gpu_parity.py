@@ -316,6 +316,28 @@ def test_w8a8_group128_weight_scales(gpu, oracle, M, N, K, kernel):
     assert (got == want).all()
 
 
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN, h.KERNEL_AUTO])
+@pytest.mark.parametrize("M,N,K,group", [(40, 24, 2048, 1024), (300, 520, 2048, 1024), (130, 128, 512, 128), (64, 5376, 14336, 1024)])
+def test_w8a8_activation_group_scales(gpu, oracle, M, N, K, group, kernel):
+    """The reference's FC2 recipe: per-row, per-1024-K-group activation scales, per-channel
+    weight scales, group sums combined in fp32 (src/metal/shaders.metal:1552-1598, 2663-2742)."""
+    x, wq, ws = operands(26, M, N, K, 0, outliers=True)
+    want_q, want_s = oracle.quantize_rows_grouped(x, group)
+    tx, q, sc = gpu.tensor_from_bf16(x), gpu.tensor_new_i8(M * K), gpu.tensor_new_f32(M * (K // group))
+    lib = h.library()
+    assert lib.h3q8_quantize_rows_grouped(tx.device_pointer, q.device_pointer, sc.device_pointer, M, M, K, group, gpu.stream)
+    gpu.synchronize()
+    assert (q.read().reshape(M, K) == want_q).all() and (sc.read().reshape(M, -1).view(np.uint32) == want_s.view(np.uint32)).all()
+    want = oracle.linear(oracle.MODE_W8A8, want_q, wq, ws[:, 0].copy(), 0, x_scales=want_s, input_group=group, fast=True)
+    tw, tws, out = gpu.tensor_from_i8(wq), gpu.tensor_from_f32(ws[:, 0].copy()), gpu.tensor_new_bf16(M * N)
+    gpu.raw_linear(mode=h.MODE_W8A8, rows=M, input_dim=K, output_dim=N, input=q, input_scales=sc, input_group=group,
+                   weight=tw, weight_scales=tws, output=out, kernel=kernel)
+    assert gpu.raw_status() == 0
+    assert (out.read().reshape(M, N) == want).all()
+    for t in (tx, q, sc, tw, tws, out):
+        t.free()
+
+
 def test_fixture_w8a8(gpu):
     g = np.load(os.path.join(GOLDEN, "w8a8.npz"))
     for i in range(3):

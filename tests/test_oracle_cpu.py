@@ -164,3 +164,27 @@ def test_w8a8_grouped_combine_order(oracle):
         total = value if total is None else (total + value).astype(np.float32)
     assert (oracle.f32_to_bf16(total).reshape(7, 5) == out).all()
     assert (oracle.linear(oracle.MODE_W8A8, xq, wq, ws, 128, x_scales=xs, fast=True) == out).all()
+
+
+def test_w8a8_activation_group_scales(oracle):
+    """Per-row, per-1024-K-group activation scales of the reference's FC2 path
+    (quantiser src/metal/shaders.metal:1552-1598, GEMM :2663-2742)."""
+    rng = np.random.default_rng(10)
+    x = oracle.f32_to_bf16(rng.standard_normal((5, 2048)).astype(np.float32)).reshape(5, 2048)
+    x[3, :1024] = 0
+    xq, xs = oracle.quantize_rows_grouped(x, 1024, dispatch_rows=6)
+    assert xs.shape == (6, 2) and (xs[5] == 1.0).all() and (xq[5] == 0).all()
+    assert xs[3, 0] == np.float32(1.0) / np.float32(127.0) and (xq[3, :1024] == 0).all()
+    for g in range(2):
+        q, s = oracle.quantize_rows(np.ascontiguousarray(x[:, g * 1024:(g + 1) * 1024]))
+        assert (q == xq[:5, g * 1024:(g + 1) * 1024]).all() and (s == xs[:5, g]).all()
+    wq = rng.integers(-127, 128, (7, 2048)).astype(np.int8)
+    ws = rng.uniform(0.005, 0.02, 7).astype(np.float32)
+    out = oracle.linear(oracle.MODE_W8A8, xq[:5], wq, ws, 0, x_scales=xs[:5], input_group=1024)
+    total = None
+    for g in range(2):
+        acc = xq[:5, g * 1024:(g + 1) * 1024].astype(np.int32) @ wq[:, g * 1024:(g + 1) * 1024].astype(np.int32).T
+        value = ((acc.astype(np.float32) * xs[:5, g:g + 1]).astype(np.float32) * ws[None, :]).astype(np.float32)
+        total = value if total is None else (total + value).astype(np.float32)
+    assert (oracle.f32_to_bf16(total).reshape(5, 7) == out).all()
+    assert (oracle.linear(oracle.MODE_W8A8, xq[:5], wq, ws, 0, x_scales=xs[:5], input_group=1024, fast=True) == out).all()
