@@ -29,6 +29,10 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 M_TOKENS, HIDDEN, FFN = 32400, 3072, 12288
+# The real MiniMax-H3 DiT projections (src/denoise/dit.c:31-46, 2424-2494): hidden 5376, heads 56 x 128, FFN 14336
+# SwiGLU, no bias, group-64 scales.  "s" = fc1 + SwiGLU (weight rows [gate | up]).  Measured with --case real_*.
+REAL_LAYERS = [("real_qkv", 5376, 21504, ""), ("real_attn_out", 7168, 5376, "gr"), ("real_fc1", 5376, 14336, "s"),
+               ("real_fc2", 14336, 5376, "gr")]
 # name, K, N, epilogue
 LAYERS = [("qkv", HIDDEN, 3 * HIDDEN, ""), ("attn_out", HIDDEN, HIDDEN, "gr"),
           ("ffn_up", HIDDEN, FFN, "a"), ("ffn_down", FFN, HIDDEN, "gr")]
@@ -148,7 +152,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="h3q8")
-    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS],
+    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS],
                     help="profiling aid: run only this projection (with --rows) and print a short line")
     ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
     ap.add_argument("--workload", default="block", choices=["block", "stream"],
@@ -431,12 +435,15 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
 def run_case(args, gpu, lib, stream, device_bf16):
     """One projection at --rows rows: the small workload used under ncu."""
     import torch
-    name, k, n, spec = next(layer for layer in LAYERS if layer[0] == args.case)
+    name, k, n, spec = next(layer for layer in LAYERS + REAL_LAYERS if layer[0] == args.case)
     rows = args.rows
+    real = name.startswith("real_")
+    wrows = 2 * n if "s" in spec else n
+    group = 64 if real and args.mode == "w8a16" else 0
     wgen = np.random.default_rng(42)
-    wq = wgen.integers(-127, 128, (n, k), dtype=np.int8)
-    ws = np.exp(wgen.normal(np.log(0.01), 0.3, (n, 1))).astype(np.float32)
-    weight = gpu.q8_from_host(wq, ws, 0)
+    wq = wgen.integers(-127, 128, (wrows, k), dtype=np.int8)
+    ws = np.exp(wgen.normal(np.log(0.002 if "s" in spec else 0.01), 0.3, (wrows, k // group if group else 1))).astype(np.float32)
+    weight = gpu.q8_from_host(wq, ws, group)
     x, out = device_bf16(rows, k, seed=1), gpu.tensor_new_bf16(rows * n)
     residual = device_bf16(rows, n, seed=3) if "r" in spec else None
     gate = device_bf16(1, n, 1.0, 0.1, seed=4) if "g" in spec else None
@@ -445,11 +452,11 @@ def run_case(args, gpu, lib, stream, device_bf16):
     for i in range(args.warmup + args.steps):
         if i == args.warmup:
             start.record(stream)
-        gpu.linear_fused_bf16(out, x, weight, None, gate, residual, rows, k, n, 1 if "a" in spec else 0)
+        gpu.linear_fused_bf16(out, x, weight, None, gate, residual, rows, k, n, 2 if "s" in spec else 1 if "a" in spec else 0)
     stop.record(stream)
     gpu.submit()
     ms = start.elapsed_time(stop) / args.steps
-    print(json.dumps({"case": name, "mode": args.mode, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * n / ms / 1e9,
+    print(json.dumps({"case": name, "mode": args.mode, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * wrows / ms / 1e9,
                       "launches": int(lib.h3q8_kernel_launches())}), flush=True)
     gpu.free()
 

@@ -10,7 +10,7 @@ import os
 import numpy as np
 
 MODE_BF16, MODE_W8A16, MODE_W8A8 = 0, 1, 2
-ACT_NONE, ACT_GELU_TANH = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_SWIGLU = 0, 1, 2
 KERNEL_AUTO, KERNEL_PLAIN, KERNEL_TCGEN05, KERNEL_TCGEN05_M256, KERNEL_TCGEN05_N128, KERNEL_TCGEN05_PAIR = 0, 1, 2, 3, 4, 5
 F32, BF16, I8, U32, F16 = 0, 1, 2, 3, 4
 HOST_VISIBLE, DEVICE_ONLY, HOST_PINNED = 0, 1, 2
@@ -128,6 +128,7 @@ def library():
         "h3_gpu_gelu_bf16": (C.c_int, [vp, vp, vp, u32, C.c_int]),
         "h3_gpu_gate_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]),
         "h3_gpu_add_bf16": (C.c_int, [vp, vp, vp, vp, u32]),
+        "h3_gpu_swiglu_bf16": (C.c_int, [vp, vp, vp, u32, u32]),
         "h3_gpu_linear_fused_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
         "h3_gpu_linear_grouped_bf16": (C.c_int, [vp, C.POINTER(Problem), u32]),
     }
@@ -379,6 +380,9 @@ class Gpu:
     def gate_bf16(self, output, residual, branch, modulation, row_map, rows, width, slots, gate_slot):
         return self._check(library().h3_gpu_gate_bf16(self.handle, _h(output), _h(residual), _h(branch), _h(modulation),
                                                       _h(row_map), rows, width, slots, gate_slot))
+
+    def swiglu_bf16(self, output, fused, rows, width):
+        return self._check(library().h3_gpu_swiglu_bf16(self.handle, _h(output), _h(fused), rows, width))
 
     def add_bf16(self, output, left, right, elements):
         return self._check(library().h3_gpu_add_bf16(self.handle, _h(output), _h(left), _h(right), elements))

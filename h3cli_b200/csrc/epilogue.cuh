@@ -18,7 +18,7 @@
 
 namespace h3q8 {
 
-enum : uint32_t { ACT_NONE = 0, ACT_GELU_TANH = 1 };
+enum : uint32_t { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SWIGLU = 2 };
 
 /* Device view of the optional epilogue operands (all may be null). */
 struct EpilogueParams {
@@ -63,6 +63,17 @@ __device__ __forceinline__ uint32_t epilogue_pair(float lin0, float lin1, uint32
     if (gated) y = pack_bf16_pair(__fadd_rn(bf16_lo(residual), __fmul_rn(bf16_lo(y), bf16_lo(gate))),
                                   __fadd_rn(bf16_hi(residual), __fmul_rn(bf16_hi(y), bf16_hi(gate))));
     return y;
+}
+
+/* SwiGLU of the fc1 projection whose weight rows are [gate (N) | up (N)]:
+ *   out = bf16( gate_b / (1 + exp(-gate_b)) * up ),  gate_b = bf16(gate linear result)
+ * up stays fp32 on the int8 path (src/metal/shaders.metal:2269-2314) and is the bf16
+ * linear output on the bf16 / W8A16 path, where the reference runs h3_swiglu_bf16 on the
+ * stored [M, 2N] tensor (src/cuda/cuda_kernels.cuh:1047-1059). */
+__device__ __forceinline__ float swiglu_f32(float gate_linear, float up_linear, bool round_up) {
+    const float gate = bf16_lo(pack_bf16_pair(gate_linear, 0.0f));
+    const float up = round_up ? bf16_lo(pack_bf16_pair(up_linear, 0.0f)) : up_linear;
+    return __fmul_rn(__fdividef(gate, 1.0f + __expf(-gate)), up);
 }
 
 /* linear: fp32 linear result before bias.  Returns the final bf16 bits. */

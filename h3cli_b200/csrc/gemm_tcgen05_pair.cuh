@@ -120,7 +120,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
                     if (rank == 0) mbar_arrive_expect_tx(&full[st.index], 2 * C::STAGE_BYTES);
                     const uint32_t leader_full = map_to_cta(smem_u32(&full[st.index]), 0);
                     tma_load_2d_pair(stage, &map_a, leader_full, (int32_t)(kb * C::BKE), (int32_t)(mb * C::BM + rank * 128), p.l2_policy_a);
-                    tma_load_2d_pair(stage + C::A_BYTES, &map_b, leader_full, (int32_t)(kb * C::BKE), (int32_t)(nb * C::BN + rank * 128), p.l2_policy_b);
+                    /* SwiGLU: the leader stages 128 gate rows, its peer the matching 128 up rows (weight rows N + n) */
+                    const uint32_t b_row = p.ep.activation == ACT_SWIGLU ? nb * 128 + rank * p.N : nb * C::BN + rank * 128;
+                    tma_load_2d_pair(stage + C::A_BYTES, &map_b, leader_full, (int32_t)(kb * C::BKE), (int32_t)b_row, p.l2_policy_b);
                     st.advance(C::STAGES);
                 }
             }
@@ -165,7 +167,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
             const GemmParams &p = args.p[g];
             const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
             tile_coordinates(p, local, mb, nb);
-            const uint32_t n0 = nb * C::BN;
+            const bool swiglu = p.ep.activation == ACT_SWIGLU;
+            const uint32_t n0 = swiglu ? nb * 128 : nb * C::BN;
             bool ready = wait_or_abort(&tfull[acc.index], acc.phase, abort_flag);
             if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_EPILOGUE; break; }
             tc_fence_after_sync();
@@ -173,6 +176,55 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
             const bool row_ok = row < p.M;
             float a_scale = 1.0f;
             if (MODE == MODE_W8A8) a_scale = row_ok ? p.a_scales[row] : 0.0f;
+            if (swiglu) {
+                /* accumulator columns 0..127 hold the gate, 128..255 the up projection of the same 128 outputs */
+#pragma unroll 1
+                for (int hc = 0; hc < 2; hc++) {
+                    const int c = half * 2 + hc;
+                    uint32_t vg[32], vu[32];
+                    const uint32_t taddr = tmem_base + ((quadrant * 32u) << 16) + acc.index * C::ACC_COLS + c * 32;
+                    tmem_load_32x32(taddr, vg);
+                    tmem_load_32x32(taddr + 128, vu);
+                    tmem_load_wait();
+                    if (!row_ok) continue;
+#pragma unroll
+                    for (int j8 = 0; j8 < 4; j8++) {
+                        const uint32_t col = n0 + c * 32 + j8 * 8;
+                        if (col >= p.N) continue;
+                        float gl[8], ul[8];
+                        if (MODE == MODE_W8A8) {
+                            float4 g0 = *reinterpret_cast<const float4 *>(p.w_scales + col), g1 = *reinterpret_cast<const float4 *>(p.w_scales + col + 4);
+                            float4 u0 = *reinterpret_cast<const float4 *>(p.w_scales + p.N + col), u1 = *reinterpret_cast<const float4 *>(p.w_scales + p.N + col + 4);
+                            const float wg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                            const float wu[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+                            for (int j = 0; j < 8; j++) {
+                                gl[j] = __fmul_rn(__fmul_rn((float)(int32_t)vg[j8 * 8 + j], a_scale), wg[j]);
+                                ul[j] = __fmul_rn(__fmul_rn((float)(int32_t)vu[j8 * 8 + j], a_scale), wu[j]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) { gl[j] = __uint_as_float(vg[j8 * 8 + j]); ul[j] = __uint_as_float(vu[j8 * 8 + j]); }
+                        }
+                        if (p.ep.bias) {
+                            uint32_t bg[4], bu[4];
+                            *reinterpret_cast<uint4 *>(bg) = *reinterpret_cast<const uint4 *>(p.ep.bias + col);
+                            *reinterpret_cast<uint4 *>(bu) = *reinterpret_cast<const uint4 *>(p.ep.bias + p.N + col);
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                gl[2 * j] = __fadd_rn(gl[2 * j], bf16_lo(bg[j])); gl[2 * j + 1] = __fadd_rn(gl[2 * j + 1], bf16_hi(bg[j]));
+                                ul[2 * j] = __fadd_rn(ul[2 * j], bf16_lo(bu[j])); ul[2 * j + 1] = __fadd_rn(ul[2 * j + 1], bf16_hi(bu[j]));
+                            }
+                        }
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            packed[j] = pack_bf16_pair(swiglu_f32(gl[2 * j], ul[2 * j], MODE != MODE_W8A8),
+                                                       swiglu_f32(gl[2 * j + 1], ul[2 * j + 1], MODE != MODE_W8A8));
+                        *reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + col) = *reinterpret_cast<uint4 *>(packed);
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int hc = 0; hc < HALF_CHUNKS; hc++) {
                 const int c = half * HALF_CHUNKS + hc;

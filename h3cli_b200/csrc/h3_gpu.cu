@@ -821,8 +821,10 @@ static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size
         size_t padded = ((size_t)q.rows + 127u) & ~(size_t)127u;
         need[0] = round256(padded * q.input_dim);
         need[1] = round256(padded * sizeof(float));
-    } else if (g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows && q.input_dim % 16 == 0) {
-        need[2] = round256((size_t)q.output_dim * q.input_dim * 2);
+    } else if (q.input_dim % 16 == 0 && (q.activation == H3Q8_ACT_SWIGLU ||
+               (g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows))) {
+        /* SwiGLU always takes this route: its fused kernel wants bf16 or int8 operands */
+        need[2] = round256((size_t)q.output_dim * (q.activation == H3Q8_ACT_SWIGLU ? 2 : 1) * q.input_dim * 2);
     }
 }
 
@@ -840,15 +842,16 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
         if (!q.weight || q.weight->owner != g) return set_error(g, "linear %ux%ux%u: weight is missing or foreign", rows, n, k);
         if (!require(g, q.input, H3_GPU_BF16, (size_t)rows * k, "linear input") ||
             !require(g, q.output, H3_GPU_BF16, (size_t)rows * n, "linear output")) return 0;
-        if (q.bias && !require(g, q.bias, H3_GPU_BF16, n, "linear bias")) return 0;
+        const uint32_t wrows = q.activation == H3Q8_ACT_SWIGLU ? 2 * n : n; /* SwiGLU weight: [gate n | up n] rows */
+        if (q.bias && !require(g, q.bias, H3_GPU_BF16, wrows, "linear bias")) return 0;
         if (q.gate && !require(g, q.gate, H3_GPU_BF16, n, "linear gate")) return 0;
         if (q.residual && !require(g, q.residual, H3_GPU_BF16, (size_t)rows * n, "linear residual")) return 0;
         if (q.output == q.input || q.output == q.weight) return set_error(g, "linear %ux%ux%u: output aliases an operand", rows, n, k);
-        if (q.activation < 0 || q.activation > H3Q8_ACT_GELU_TANH) return set_error(g, "linear: unknown activation %d", q.activation);
+        if (q.activation < 0 || q.activation > H3Q8_ACT_SWIGLU) return set_error(g, "linear: unknown activation %d", q.activation);
         if (q.weight->q8) {
-            if (q.weight->q8_n != n || q.weight->q8_k != k)
+            if (q.weight->q8_n != wrows || q.weight->q8_k != k)
                 return set_error(g, "linear %ux%ux%u: q8 weight is %ux%u", rows, n, k, q.weight->q8_n, q.weight->q8_k);
-        } else if (q.weight->dtype != H3_GPU_BF16 || q.weight->elements < (size_t)n * k) {
+        } else if (q.weight->dtype != H3_GPU_BF16 || q.weight->elements < (size_t)wrows * k) {
             return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
         }
         size_t need[3];
@@ -896,7 +899,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
                 /* policy 0 of the reference: dequantise once, then a bf16 GEMM (src/metal/q8_host.inc:75-88) */
                 uint16_t *wb = (uint16_t *)((char *)g->arena[2] + offset[2]);
                 ProfileScope timing(g, 7);
-                if (!h3q8_q8_dequant((const int8_t *)d.weight, d.weight_scales, wb, q.output_dim, q.input_dim, d.weight_group, g->compute)) {
+                if (!h3q8_q8_dequant((const int8_t *)d.weight, d.weight_scales, wb, w->q8_n, q.input_dim, d.weight_group, g->compute)) {
                     g->accessed.clear();
                     return set_error(g, "%s", h3q8_last_error());
                 }
@@ -1022,6 +1025,21 @@ extern "C" int h3_gpu_gate_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tens
         row_map ? (const uint32_t *)pointer(row_map) : nullptr, (uint16_t *)pointer(out), rows, width, slots, gate_slot);
     count_launch(1);
     return launch_status(g, "gate", 1);
+}
+/* src/gpu.h:714-716, src/cuda/cuda_kernels.cuh:1047-1059: fused row = [gate width | up width] */
+static __global__ void swiglu_kernel(const uint16_t *fused, uint16_t *out, uint32_t rows, uint32_t width) {
+    uint32_t c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c >= width || r >= rows) return;
+    size_t base = (size_t)r * width * 2;
+    out[(size_t)r * width + c] = (uint16_t)f32_to_bf16_bits(swiglu_f32(bf16_bits_to_f32(fused[base + c]), bf16_bits_to_f32(fused[base + width + c]), true));
+}
+extern "C" int h3_gpu_swiglu_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *fused, uint32_t rows, uint32_t width) {
+    if (!launch_ready(g)) return 0;
+    if (!rows || !width || rows > 65535 || !require(g, fused, H3_GPU_BF16, (size_t)rows * width * 2, "swiglu input") ||
+        !require(g, out, H3_GPU_BF16, (size_t)rows * width, "swiglu output")) return set_error(g, "swiglu: invalid arguments");
+    swiglu_kernel<<<dim3((width + 255) / 256, rows), 256, 0, g->compute>>>((const uint16_t *)pointer(fused), (uint16_t *)pointer(out), rows, width);
+    count_launch(1);
+    return launch_status(g, "swiglu", 1);
 }
 extern "C" int h3_gpu_add_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *a, const h3_gpu_tensor *b, uint32_t elements) {
     if (!launch_ready(g)) return 0;

@@ -139,9 +139,11 @@ static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, 
         GemmParams &p = args.p[i];
         p = params[i];
         if (!make_map(&args.map_a[i], d.input, bytes, d.rows, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
-        if (!make_map(&args.map_b[i], d.weight, bytes, d.output_dim, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+        const bool swiglu = d.activation == H3Q8_ACT_SWIGLU; /* weight rows [gate N | up N], 128 outputs per tile */
+        if (!make_map(&args.map_b[i], d.weight, bytes, (uint64_t)d.output_dim * (swiglu ? 2 : 1), d.input_dim, C::BKE, 128,
+                      CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
         p.m_blocks = (d.rows + C::BM - 1) / C::BM;
-        p.n_blocks = (d.output_dim + C::BN - 1) / C::BN;
+        p.n_blocks = swiglu ? (d.output_dim + 127) / 128 : (d.output_dim + C::BN - 1) / C::BN;
         p.tiles = p.m_blocks * p.n_blocks;
         /* measured: bands of 16 row blocks are best while a 256-row block of X is small (K*bytes <= 8 KB per row),
          * 8 beyond that (FFN-down); L2 eviction hints (activations first, weights last) lost 3-5 % everywhere */
@@ -210,12 +212,16 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     if (!d.rows || !d.input_dim || !d.output_dim) return fail("linear %ux%ux%u: empty dimension", d.rows, d.output_dim, d.input_dim);
     if (!d.input || !d.weight || !d.output) return fail("linear %ux%ux%u: null operand", d.rows, d.output_dim, d.input_dim);
     if (d.mode > H3Q8_MODE_W8A8) return fail("linear: unknown mode %u", d.mode);
-    if (d.activation > H3Q8_ACT_GELU_TANH) return fail("linear: unknown activation %u", d.activation);
+    if (d.activation > H3Q8_ACT_SWIGLU) return fail("linear: unknown activation %u", d.activation);
+    const bool swiglu = d.activation == H3Q8_ACT_SWIGLU;
+    if (swiglu && (d.gate || d.residual || d.weight_group || d.input_group || d.accumulators))
+        return fail("linear: SwiGLU takes per-channel scales and no gate, residual or accumulator dump");
+    if (swiglu && d.output_dim % 8) return fail("linear: SwiGLU needs output_dim %% 8 == 0");
     if (d.mode != H3Q8_MODE_BF16 && !d.weight_scales) return fail("linear: int8 weights need weight_scales");
     if (d.mode == H3Q8_MODE_W8A8 && !d.input_scales) return fail("linear: W8A8 needs per-token input_scales");
     if (d.accumulators && (d.mode != H3Q8_MODE_W8A8 || d.weight_group))
         return fail("linear: the int32 dump exists only for W8A8 with per-channel weight scales");
-    if ((uint64_t)d.output_dim * d.input_dim > UINT32_MAX - 31u) return fail("linear: weight exceeds 32-bit indexing");
+    if ((uint64_t)d.output_dim * (swiglu ? 2u : 1u) * d.input_dim > UINT32_MAX - 31u) return fail("linear: weight exceeds 32-bit indexing");
     if (static_cast<const void *>(d.output) == d.input) return fail("linear: output aliases the input");
     dev = device_state();
     if (!dev) return 0;
@@ -252,6 +258,10 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
         const bool pair_ok = d.rows > 128 && (d.mode == H3Q8_MODE_BF16 || (d.mode == H3Q8_MODE_W8A8 && !p.scale_group));
         kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128
                : pair_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_TCGEN05;
+        /* SwiGLU runs on the two-CTA kernel (gate rows in one CTA, up rows in its peer) or on the plain kernel */
+        if (swiglu) kernel = tma_ok && d.mode != H3Q8_MODE_W8A16 ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_PLAIN;
+    } else if (swiglu && kernel != H3Q8_KERNEL_PLAIN && kernel != H3Q8_KERNEL_TCGEN05_PAIR) {
+        return fail("linear: SwiGLU is available on the two-CTA and the plain kernel");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && p.scale_group))) {
         return fail("linear: the two-CTA kernel takes bf16 or per-channel int8 operands");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {

@@ -163,38 +163,42 @@ __global__ void __launch_bounds__(256) linear_plain_kernel(const void *__restric
     using acc_t = typename std::conditional<MODE == MODE_W8A8, int32_t, float>::type;
     __shared__ acc_t xs[16][65];
     __shared__ acc_t ws[16][65];
+    __shared__ acc_t ws2[16][65]; /* SwiGLU: the up-projection rows N + c of the same output columns */
+    const bool swiglu = p.ep.activation == ACT_SWIGLU;
     const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const uint32_t row0 = blockIdx.y * 64, col0 = blockIdx.x * 64;
     const uint32_t width = p.scale_group ? p.scale_group : p.K;
     const bool grouped8 = MODE == MODE_W8A8 && p.scale_group != 0;
-    acc_t acc[4][4];
+    acc_t acc[4][4], acc2[4][4];
     float totals[4][4];
 #pragma unroll
     for (int i = 0; i < 4; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) { acc[i][j] = 0; totals[i][j] = 0.0f; }
+        for (int j = 0; j < 4; j++) { acc[i][j] = 0; acc2[i][j] = 0; totals[i][j] = 0.0f; }
+    auto weight_value = [&](uint32_t wrow, uint32_t gk) -> acc_t {
+        if (MODE == MODE_BF16) return (acc_t)bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(win)[(size_t)wrow * p.K + gk]);
+        const int qv = reinterpret_cast<const int8_t *>(win)[(size_t)wrow * p.K + gk];
+        if (MODE == MODE_W8A8) return (acc_t)qv;
+        return (acc_t)bf16_bits_to_f32(f32_to_bf16_bits(__fmul_rn((float)qv, p.w_scales[(size_t)wrow * p.scale_groups + gk / width])));
+    };
     for (uint32_t k0 = 0; k0 < p.K; k0 += 16) {
         for (uint32_t e = threadIdx.x; e < 64 * 16; e += 256) {
             const uint32_t r = e >> 4, k = e & 15;
             const uint32_t gr = row0 + r, gc = col0 + r, gk = k0 + k;
-            acc_t xv = 0, wv = 0;
+            acc_t xv = 0, wv = 0, wv2 = 0;
             if (gk < p.K) {
                 if (gr < p.M) {
                     if (MODE == MODE_W8A8) xv = (acc_t)reinterpret_cast<const int8_t *>(xin)[(size_t)gr * p.K + gk];
                     else xv = (acc_t)bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(xin)[(size_t)gr * p.K + gk]);
                 }
                 if (gc < p.N) {
-                    if (MODE == MODE_BF16) wv = (acc_t)bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(win)[(size_t)gc * p.K + gk]);
-                    else {
-                        const int qv = reinterpret_cast<const int8_t *>(win)[(size_t)gc * p.K + gk];
-                        if (MODE == MODE_W8A8) wv = (acc_t)qv;
-                        else wv = (acc_t)bf16_bits_to_f32(f32_to_bf16_bits(
-                                 __fmul_rn((float)qv, p.w_scales[(size_t)gc * p.scale_groups + gk / width])));
-                    }
+                    wv = weight_value(gc, gk);
+                    if (swiglu) wv2 = weight_value(p.N + gc, gk);
                 }
             }
             xs[k][r] = xv;
             ws[k][r] = wv;
+            ws2[k][r] = wv2;
         }
         __syncthreads();
 #pragma unroll
@@ -209,6 +213,17 @@ __global__ void __launch_bounds__(256) linear_plain_kernel(const void *__restric
                     if (MODE == MODE_W8A8) acc[i][j] += a[i] * b[j];
                     else acc[i][j] = (acc_t)fmaf((float)a[i], (float)b[j], (float)acc[i][j]);
                 }
+            if (swiglu) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) b[i] = ws2[k][tx * 4 + i];
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) {
+                        if (MODE == MODE_W8A8) acc2[i][j] += a[i] * b[j];
+                        else acc2[i][j] = (acc_t)fmaf((float)a[i], (float)b[j], (float)acc2[i][j]);
+                    }
+            }
         }
         __syncthreads();
         /* grouped W8A8: close the K-group -- scale its exact int32 sum and add in fp32 */
@@ -243,6 +258,12 @@ __global__ void __launch_bounds__(256) linear_plain_kernel(const void *__restric
                     linear = __fmul_rn(__fmul_rn((float)acc[i][j], p.a_scales[r]), p.w_scales[c]);
                 }
             } else linear = (float)acc[i][j];
+            if (swiglu) { /* ungrouped scales only */
+                float up = MODE == MODE_W8A8 ? __fmul_rn(__fmul_rn((float)acc2[i][j], p.a_scales[r]), p.w_scales[p.N + c]) : (float)acc2[i][j];
+                if (p.ep.bias) { linear = __fadd_rn(linear, bf16_bits_to_f32(p.ep.bias[c])); up = __fadd_rn(up, bf16_bits_to_f32(p.ep.bias[p.N + c])); }
+                p.out[(size_t)r * p.N + c] = (uint16_t)f32_to_bf16_bits(swiglu_f32(linear, up, MODE != MODE_W8A8));
+                continue;
+            }
             const uint32_t y = epilogue_value(linear, p.ep.bias ? bf16_bits_to_f32(p.ep.bias[c]) : 0.0f, p.ep.bias != nullptr,
                                               p.ep.activation, gated, p.ep.gate ? bf16_bits_to_f32(p.ep.gate[c]) : 1.0f,
                                               p.ep.residual ? bf16_bits_to_f32(p.ep.residual[(size_t)r * p.N + c]) : 0.0f);

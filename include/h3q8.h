@@ -40,7 +40,11 @@ int h3q8_q8_pack_rows(const uint16_t *source, int8_t *weights, float *scales,
  * Layer 2: raw entry points (device pointers, caller-owned memory)
  * ===================================================================== */
 enum { H3Q8_MODE_BF16 = 0, H3Q8_MODE_W8A16 = 1, H3Q8_MODE_W8A8 = 2 };
-enum { H3Q8_ACT_NONE = 0, H3Q8_ACT_GELU_TANH = 1 };
+enum { H3Q8_ACT_NONE = 0, H3Q8_ACT_GELU_TANH = 1,
+       /* fc1 + SwiGLU of the real model: weight is [2*output_dim, K] = [gate rows | up rows],
+        * out = bf16(silu(bf16(gate)) * up)  (src/metal/shaders.metal:2209-2317,
+        * src/cuda/cuda_kernels.cuh:1047-1059); bias, if given, is [2*output_dim] */
+       H3Q8_ACT_SWIGLU = 2 };
 enum { /* kernel selection; AUTO picks by shape */
     H3Q8_KERNEL_AUTO = 0,
     H3Q8_KERNEL_PLAIN = 1,     /* CUDA-core kernel, any shape                       */
@@ -282,6 +286,7 @@ int h3_gpu_gelu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *in
 int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
                      const h3_gpu_tensor *branch, const h3_gpu_tensor *modulation,
                      const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width, uint32_t slots, uint32_t gate_slot);
+int h3_gpu_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *fused, uint32_t rows, uint32_t width); /* src/gpu.h:714-716 */
 int h3_gpu_add_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *left,
                     const h3_gpu_tensor *right, uint32_t elements);
 
@@ -290,7 +295,8 @@ int h3_gpu_add_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *lef
  * (h3_gpu_adaln_linear_bf16 :600-611, h3_gpu_gate_adaln_bf16 :618-629).
  * weight may be bf16 or carry a q8 descriptor; with W8A8 configured the
  * activations are quantised per token into context-owned scratch first.
- * bias, gate, residual may be NULL.  activation: H3Q8_ACT_*. */
+ * bias, gate, residual may be NULL.  activation: H3Q8_ACT_*; with H3Q8_ACT_SWIGLU the weight (and bias)
+ * have 2 * output_dim rows, gate rows first (the fc1 of src/denoise/dit.c:2489-2491 in one call). */
 int h3_gpu_linear_fused_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input,
                              const h3_gpu_tensor *weight, const h3_gpu_tensor *bias,
                              const h3_gpu_tensor *gate, const h3_gpu_tensor *residual,

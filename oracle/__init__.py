@@ -16,7 +16,7 @@ _LIB = os.path.join(_HERE, "_build", "libh3q8_oracle.so")
 _REF = os.path.join(_HERE, "_ref", "libh3q8_ref.so")
 
 MODE_BF16, MODE_W8A16, MODE_W8A8 = 0, 1, 2
-ACT_NONE, ACT_GELU_TANH = 0, 1
+ACT_NONE, ACT_GELU_TANH, ACT_SWIGLU = 0, 1, 2
 
 
 def build():
@@ -148,7 +148,7 @@ def linear(mode, x, w, w_scales=None, group=0, x_scales=None, bias=None, gate=No
            residual=None, activation=ACT_NONE, fast=False, want_acc=False, input_group=0):
     """out[M,N] (bf16 bits) = epilogue(x . w^T); see h3o_linear_args."""
     M, K = x.shape
-    N = w.shape[0]
+    N = w.shape[0] // 2 if activation == ACT_SWIGLU else w.shape[0]
     keep = [np.ascontiguousarray(a) if a is not None else None
             for a in (x, w, w_scales, x_scales, bias, gate, residual)]
     out = np.empty((M, N), np.uint16)

@@ -157,8 +157,11 @@ uint16_t h3o_gate_residual_bf16(uint16_t residual, uint16_t branch, uint16_t gat
 
 /* Everything after the linear result: bf16 round, then the reference's
  * separate bf16->bf16 operators in their call order. */
+static float *capture; /* when set, receives the fp32 linear result (+bias) of every output */
+
 static uint16_t finish(const h3o_linear_args *a, float linear, uint32_t r, uint32_t n) {
     if (a->bias) linear = linear + h3o_bf16_to_f32(a->bias[n]); /* shaders.metal:855 */
+    if (capture) capture[(size_t)r * a->output_dim + n] = linear;
     uint16_t y = h3o_f32_to_bf16(linear);
     if (a->activation == H3O_ACT_GELU_TANH) y = h3o_gelu_tanh_bf16(y);
     if (a->residual || a->gate) {
@@ -175,7 +178,7 @@ static int validate(const h3o_linear_args *a) {
     if (a->mode > H3O_MODE_W8A8) return 0;
     if (a->mode != H3O_MODE_BF16 && !a->weight_scales) return 0;
     if (a->mode == H3O_MODE_W8A8 && !a->input_scales) return 0;
-    if (a->activation > H3O_ACT_GELU_TANH) return 0;
+    if (a->activation > H3O_ACT_SWIGLU) return 0;
     return 1;
 }
 
@@ -362,8 +365,36 @@ static void linear_fast(const h3o_linear_args *a) {
     free(xf); free(xi);
 }
 
+/* fc1 + SwiGLU: one linear over the [gate | up] rows, then the gated product. */
+static int linear_swiglu(const h3o_linear_args *args) {
+    uint32_t M = args->rows, N = args->output_dim;
+    if (args->gate || args->residual || args->weight_group || args->input_group) return 0;
+    h3o_linear_args wide = *args;
+    wide.output_dim = 2 * N;
+    wide.activation = H3O_ACT_NONE;
+    wide.accumulators = NULL;
+    wide.output = malloc((size_t)M * 2 * N * sizeof(uint16_t));
+    float *raw = malloc((size_t)M * 2 * N * sizeof(float));
+    if (!wide.output || !raw) { free(wide.output); free(raw); return 0; }
+    capture = raw;
+    if (wide.fast) linear_fast(&wide); else linear_spec(&wide);
+    capture = NULL;
+    for (uint32_t r = 0; r < M; r++)
+        for (uint32_t n = 0; n < N; n++) {
+            float gate = h3o_bf16_to_f32(wide.output[(size_t)r * 2 * N + n]);
+            float up = args->mode == H3O_MODE_W8A8 ? raw[(size_t)r * 2 * N + N + n]
+                                                   : h3o_bf16_to_f32(wide.output[(size_t)r * 2 * N + N + n]);
+            float value = gate / (1.0f + expf(-gate)) * up;
+            args->output[(size_t)r * N + n] = h3o_f32_to_bf16(value);
+        }
+    free(wide.output);
+    free(raw);
+    return 1;
+}
+
 int h3o_linear(const h3o_linear_args *args) {
     if (!validate(args)) return 0;
+    if (args->activation == H3O_ACT_SWIGLU) return linear_swiglu(args);
     if (args->fast) linear_fast(args);
     else linear_spec(args);
     return 1;

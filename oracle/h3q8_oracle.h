@@ -48,7 +48,11 @@ uint16_t h3o_gelu_tanh_bf16(uint16_t value);
 /* src/cuda/cuda_kernels.cuh:973-986: bf16(float(res) + float(branch)*float(gate)) */
 uint16_t h3o_gate_residual_bf16(uint16_t residual, uint16_t branch, uint16_t gate);
 
-enum { H3O_ACT_NONE = 0, H3O_ACT_GELU_TANH = 1 };
+/* H3O_ACT_SWIGLU: weight (and bias) have 2*output_dim rows, gate rows first;
+ * out = bf16(silu(bf16(gate)) * up), up kept in fp32 on the int8 path
+ * (src/metal/shaders.metal:2269-2314) and rounded to bf16 on the bf16 / W8A16 path
+ * (linear output stored as bf16, then src/cuda/cuda_kernels.cuh:1047-1059). */
+enum { H3O_ACT_NONE = 0, H3O_ACT_GELU_TANH = 1, H3O_ACT_SWIGLU = 2 };
 enum { H3O_MODE_BF16 = 0, H3O_MODE_W8A16 = 1, H3O_MODE_W8A8 = 2 };
 
 /* One fused linear: out = epilogue(input x weight^T).  Mirrors the argument

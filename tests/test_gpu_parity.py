@@ -338,6 +338,66 @@ def test_w8a8_activation_group_scales(gpu, oracle, M, N, K, group, kernel):
         t.free()
 
 
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN, h.KERNEL_AUTO])
+@pytest.mark.parametrize("M,N,K", [(40, 24, 128), (300, 520, 512), (257, 1000, 320), (129, 14336 // 8, 5376 // 4)])
+@pytest.mark.parametrize("mode", ["bf16", "w8a16", "w8a8"])
+def test_swiglu_projection(gpu, oracle, mode, M, N, K, kernel):
+    """fc1 + SwiGLU in one kernel: weight [gate N | up N] rows, out = bf16(silu(bf16(gate)) * up)
+    (src/metal/shaders.metal:2209-2317 for int8, linear + src/cuda/cuda_kernels.cuh:1047-1059 otherwise)."""
+    x, wq, ws = operands(27, M, 2 * N, K, 0)
+    ws = (ws * np.float32(0.2)).astype(np.float32)       # keep silu(gate) * up in a sane range
+    bias = synth.bf16_normal(27, 4, 1, 2 * N, 0, 0.02)[0]
+    if mode == "w8a8":
+        xq, xs = oracle.quantize_rows(x)
+        want = oracle.linear(oracle.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, x_scales=xs, bias=bias, activation=2, fast=True)
+        got = raw_swiglu(gpu, h.MODE_W8A8, xq, wq, ws[:, 0].copy(), xs, bias, M, N, K, kernel)
+    elif mode == "w8a16":
+        want = oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0, bias=bias, activation=2)
+        got = raw_swiglu(gpu, h.MODE_W8A16, x, wq, ws, None, bias, M, N, K, kernel)
+    else:
+        wb = oracle.q8_dequant(wq, ws, 0)
+        want = oracle.linear(oracle.MODE_BF16, x, wb, bias=bias, activation=2)
+        got = raw_swiglu(gpu, h.MODE_BF16, x, wb, None, None, bias, M, N, K, kernel)
+    check_bf16(got, want)
+
+
+def raw_swiglu(gpu, mode, x, w, ws, xs, bias, M, N, K, kernel):
+    t = upload(gpu, input=x, weight=w, weight_scales=ws, input_scales=xs, bias=bias)
+    out = gpu.tensor_from_bf16(np.full(M * N + GUARD, 0x3F80, np.uint16))
+    gpu.raw_linear(mode=mode, rows=M, input_dim=K, output_dim=N, activation=h.ACT_SWIGLU, kernel=kernel, output=out, **t)
+    assert gpu.raw_status() == 0
+    got = out.read()
+    assert (got[M * N:] == 0x3F80).all()
+    for tensor in list(t.values()) + [out]:
+        tensor.free()
+    return got[:M * N].reshape(M, N)
+
+
+@pytest.mark.parametrize("quant_mode", [0, 1])
+def test_swiglu_fused_equals_unfused_chain(oracle, quant_mode):
+    """h3_gpu_linear_bf16 over the [gate | up] weight followed by h3_gpu_swiglu_bf16 (what
+    src/denoise/dit.c:2489-2491 does) gives the same bits as the fused projection."""
+    M, N, K = 300, 512, 256
+    x, wq, ws = operands(28, M, 2 * N, K, 64)
+    ws = (ws * np.float32(0.2)).astype(np.float32)
+    gpu = h.Gpu()
+    if quant_mode:
+        gpu.quant_configure(1)
+        gpu.set_w8a16_scratch_rows(1)
+        w = gpu.q8_from_host(wq, ws, 64)
+    else:
+        w = gpu.tensor_from_bf16(oracle.q8_dequant(wq, ws, 64))
+    tx, wide, chain, fused = gpu.tensor_from_bf16(x), gpu.tensor_new_bf16(M * 2 * N), gpu.tensor_new_bf16(M * N), gpu.tensor_new_bf16(M * N)
+    gpu.begin()
+    gpu.linear_bf16(wide, tx, w, None, M, K, 2 * N)
+    gpu.swiglu_bf16(chain, wide, M, N)
+    gpu.linear_fused_bf16(fused, tx, w, None, None, None, M, K, N, h.ACT_SWIGLU)
+    gpu.submit()
+    assert (chain.read() == fused.read()).all()
+    check_bf16(fused.read().reshape(M, N), oracle.linear(oracle.MODE_W8A16, x, wq, ws, 64, activation=2))
+    gpu.free()
+
+
 def test_fixture_w8a8(gpu):
     g = np.load(os.path.join(GOLDEN, "w8a8.npz"))
     for i in range(3):
