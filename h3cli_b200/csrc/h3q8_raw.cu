@@ -214,8 +214,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     if (d.mode > H3Q8_MODE_W8A8) return fail("linear: unknown mode %u", d.mode);
     if (d.activation > H3Q8_ACT_SWIGLU) return fail("linear: unknown activation %u", d.activation);
     const bool swiglu = d.activation == H3Q8_ACT_SWIGLU;
-    if (swiglu && (d.gate || d.residual || d.weight_group || d.input_group || d.accumulators))
-        return fail("linear: SwiGLU takes per-channel scales and no gate, residual or accumulator dump");
+    if (swiglu && (d.gate || d.residual || d.input_group || d.accumulators || (d.mode == H3Q8_MODE_W8A8 && d.weight_group)))
+        return fail("linear: SwiGLU takes no gate, residual or accumulator dump, and per-channel scales on the int8 path");
     if (swiglu && d.output_dim % 8) return fail("linear: SwiGLU needs output_dim %% 8 == 0");
     if (d.mode != H3Q8_MODE_BF16 && !d.weight_scales) return fail("linear: int8 weights need weight_scales");
     if (d.mode == H3Q8_MODE_W8A8 && !d.input_scales) return fail("linear: W8A8 needs per-token input_scales");

@@ -368,7 +368,8 @@ static void linear_fast(const h3o_linear_args *a) {
 /* fc1 + SwiGLU: one linear over the [gate | up] rows, then the gated product. */
 static int linear_swiglu(const h3o_linear_args *args) {
     uint32_t M = args->rows, N = args->output_dim;
-    if (args->gate || args->residual || args->weight_group || args->input_group) return 0;
+    if (args->gate || args->residual || args->input_group) return 0;
+    if (args->mode == H3O_MODE_W8A8 && args->weight_group) return 0; /* int8 SwiGLU: per-channel scales only */
     h3o_linear_args wide = *args;
     wide.output_dim = 2 * N;
     wide.activation = H3O_ACT_NONE;
