@@ -181,7 +181,6 @@ def main():
 
     gpu = h.Gpu()
     gpu.quant_configure(2 if args.mode == "w8a8" else 1)
-    gpu.set_w8a16_scratch_rows(int(os.environ.get("H3Q8_W8A16_SCRATCH_ROWS", "1024")))
     stream = torch.cuda.ExternalStream(gpu.stream, device=local)
     lib = h.library()
 

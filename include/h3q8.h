@@ -241,7 +241,8 @@ int h3q8_gpu_tensor_upload_async(h3_gpu_tensor *tensor, const void *host, size_t
 int h3q8_gpu_tensor_download_async(h3_gpu_tensor *tensor, void *host, size_t bytes);
 /* Rows at or above which a W8A16 linear first dequantises the weight into
  * context scratch and runs the bf16 GEMM (the reference's policy 0,
- * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop. */
+ * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop.  Default 1
+ * (every call), or H3Q8_W8A16_SCRATCH_ROWS from the environment. */
 int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *gpu, uint32_t rows);
 /* Per-kernel CUDA-event timing into h3_gpu_stats (on when H3_PROFILE is set). */
 int h3q8_gpu_set_profiling(h3_gpu *gpu, int enabled);
