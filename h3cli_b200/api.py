@@ -125,6 +125,8 @@ def library():
         "h3q8_q8_blob_bytes": (sz, [u32, u32, u32, C.POINTER(sz)]),
         "h3_gpu_quantize_weight_int8": (C.c_int, [vp, vp, vp, vp, u32, u32]),
         "h3_gpu_linear_int8_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
+        "h3_gpu_gate_adaln_quantize_int8": (C.c_int, [vp] * 10 + [u32] * 7 + [C.c_float]),
+        "h3_gpu_linear_fused_int8_bf16": (C.c_int, [vp, vp, vp, vp, u32, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
         "h3_gpu_gelu_bf16": (C.c_int, [vp, vp, vp, u32, C.c_int]),
         "h3_gpu_gate_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]),
         "h3_gpu_add_bf16": (C.c_int, [vp, vp, vp, vp, u32]),
@@ -373,6 +375,20 @@ class Gpu:
         return self._check(library().h3_gpu_linear_int8_bf16(self.handle, _h(output), _h(quantized_input), _h(input_scales),
                                                              _h(input), _h(weight), _h(weight_scales), rows, input_dim,
                                                              output_dim, use_slower_uncached_int8_scales))
+
+    def gate_adaln_quantize_int8(self, gated_residual, quantized_output, quantized_scales, residual, branch, norm_weight,
+                                 gate_modulation, norm_modulation, row_map, rows, padded_rows, width, slots, gate_slot,
+                                 shift_slot, scale_slot, epsilon):
+        return self._check(library().h3_gpu_gate_adaln_quantize_int8(
+            self.handle, _h(gated_residual), _h(quantized_output), _h(quantized_scales), _h(residual), _h(branch),
+            _h(norm_weight), _h(gate_modulation), _h(norm_modulation), _h(row_map), rows, padded_rows, width, slots,
+            gate_slot, shift_slot, scale_slot, epsilon))
+
+    def linear_fused_int8_bf16(self, output, quantized_input, input_scales, input_group, weight, bias, gate, residual,
+                               rows, input_dim, output_dim, activation):
+        return self._check(library().h3_gpu_linear_fused_int8_bf16(
+            self.handle, _h(output), _h(quantized_input), _h(input_scales), input_group, _h(weight), _h(bias), _h(gate),
+            _h(residual), rows, input_dim, output_dim, activation))
 
     def gelu_bf16(self, output, input, elements, approximate=1):
         return self._check(library().h3_gpu_gelu_bf16(self.handle, _h(output), _h(input), elements, approximate))

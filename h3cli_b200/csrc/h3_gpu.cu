@@ -987,6 +987,68 @@ extern "C" int h3_gpu_linear_int8_bf16(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_ten
     return launch_status(g, "int8 linear", 2);
 }
 
+/* src/gpu.h:630-642, src/metal/gpu.m:3837-3900: gate + residual, RMS/AdaLN and the per-row int8
+ * quantiser in one pass; the output feeds h3_gpu_linear_fused_int8_bf16 without another
+ * look at the bf16 activations. */
+extern "C" int h3_gpu_gate_adaln_quantize_int8(h3_gpu *g, h3_gpu_tensor *gated_residual, h3_gpu_tensor *quantized_output,
+                                               h3_gpu_tensor *quantized_scales, const h3_gpu_tensor *residual,
+                                               const h3_gpu_tensor *branch, const h3_gpu_tensor *norm_weight,
+                                               const h3_gpu_tensor *gate_modulation, const h3_gpu_tensor *norm_modulation,
+                                               const h3_gpu_tensor *row_map, uint32_t rows, uint32_t padded_rows, uint32_t width,
+                                               uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot,
+                                               float epsilon) {
+    if (!launch_ready(g)) return 0;
+    const size_t n = (size_t)rows * width;
+    if (!rows || padded_rows < rows || !width || width > 24576 || !slots || gate_slot >= slots || shift_slot >= slots || scale_slot >= slots)
+        return set_error(g, "gate/AdaLN/quantize: invalid shape or slot");
+    if (!require(g, residual, H3_GPU_BF16, n, "gate residual") || !require(g, branch, H3_GPU_BF16, n, "gate branch") ||
+        !require(g, gated_residual, H3_GPU_BF16, n, "gated residual") || !require(g, norm_weight, H3_GPU_BF16, width, "AdaLN norm weight") ||
+        !require(g, gate_modulation, H3_GPU_BF16, (size_t)slots * width, "gate modulation") ||
+        !require(g, norm_modulation, H3_GPU_BF16, (size_t)slots * width, "AdaLN modulation") ||
+        !require(g, quantized_output, H3_GPU_I8, (size_t)padded_rows * width, "int8 quantized output") ||
+        !require(g, quantized_scales, H3_GPU_F32, padded_rows, "int8 quantization scales") ||
+        (row_map && !require(g, row_map, H3_GPU_U32, rows, "row map"))) return 0;
+    gate_adaln_quantize_kernel<<<padded_rows, 256, width * sizeof(uint16_t), g->compute>>>(
+        (const uint16_t *)pointer(residual), (const uint16_t *)pointer(branch), (const uint16_t *)pointer(gate_modulation),
+        row_map ? (const uint32_t *)pointer(row_map) : nullptr, (const uint16_t *)pointer(norm_weight),
+        (const uint16_t *)pointer(norm_modulation), (uint16_t *)pointer(gated_residual), (int8_t *)pointer(quantized_output),
+        (float *)pointer(quantized_scales), rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);
+    count_launch(1);
+    return launch_status(g, "gate/AdaLN/quantize", 1);
+}
+
+/* The fused projection on activations that are already int8 (from the call above or from
+ * h3q8_quantize_rows): weight is a q8 descriptor with per-channel scales, or per-K-group
+ * activation scales when input_group != 0 (input_scales is then [rows, K/input_group]). */
+extern "C" int h3_gpu_linear_fused_int8_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *quantized_input,
+                                             const h3_gpu_tensor *input_scales, uint32_t input_group, const h3_gpu_tensor *w,
+                                             const h3_gpu_tensor *bias, const h3_gpu_tensor *gate, const h3_gpu_tensor *residual,
+                                             uint32_t rows, uint32_t k, uint32_t n, int activation) {
+    if (!launch_ready(g)) return 0;
+    if (!rows || !k || !n || activation < 0 || activation > H3Q8_ACT_SWIGLU) return set_error(g, "int8 linear %ux%ux%u: invalid arguments", rows, n, k);
+    const uint32_t wrows = activation == H3Q8_ACT_SWIGLU ? 2 * n : n;
+    if (!w || w->owner != g || !w->q8 || w->q8_n != wrows || w->q8_k != k) return set_error(g, "int8 linear %ux%ux%u: needs a matching q8 weight", rows, n, k);
+    if (input_group && k % input_group) return set_error(g, "int8 linear: K must be a multiple of the activation scale group");
+    if (!require(g, quantized_input, H3_GPU_I8, (size_t)rows * k, "int8 linear input") ||
+        !require(g, input_scales, H3_GPU_F32, (size_t)rows * (input_group ? k / input_group : 1), "int8 linear input scales") ||
+        !require(g, out, H3_GPU_BF16, (size_t)rows * n, "int8 linear output") ||
+        (bias && !require(g, bias, H3_GPU_BF16, wrows, "linear bias")) || (gate && !require(g, gate, H3_GPU_BF16, n, "linear gate")) ||
+        (residual && !require(g, residual, H3_GPU_BF16, (size_t)rows * n, "linear residual"))) return 0;
+    h3q8_linear_desc d = {};
+    d.mode = H3Q8_MODE_W8A8; d.rows = rows; d.input_dim = k; d.output_dim = n; d.activation = (uint32_t)activation;
+    d.input = pointer(quantized_input); d.input_scales = (const float *)pointer(input_scales); d.input_group = input_group;
+    d.weight = pointer(w); d.weight_scales = (const float *)((const char *)w->data + w->q8_scale_offset); d.weight_group = w->q8_group;
+    d.bias = bias ? (const uint16_t *)pointer(bias) : nullptr; d.gate = gate ? (const uint16_t *)pointer(gate) : nullptr;
+    d.residual = residual ? (const uint16_t *)pointer(residual) : nullptr; d.output = (uint16_t *)pointer(out);
+    {
+        ProfileScope timing(g, 0);
+        if (!h3q8_linear(&d, g->compute)) { g->accessed.clear(); return set_error(g, "%s", h3q8_last_error()); }
+    }
+    g->stats.linear_dispatches++;
+    g->stats.q8_dispatches++;
+    return launch_status(g, "int8 linear", 1);
+}
+
 /* ------------------------------------------- unfused epilogue operators */
 static __global__ void gelu_kernel(const uint16_t *in, uint16_t *out, uint32_t count) {
     uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;

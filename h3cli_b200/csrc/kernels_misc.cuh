@@ -102,6 +102,72 @@ static __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_
     }
 }
 
+/* Producer-side fusion of the activation quantiser (src/metal/shaders.metal:3390-3473,
+ * src/gpu.h:630-642): per row
+ *   gated = bf16(residual + branch * gate[class, gate_slot])          -> gated_residual (may alias residual)
+ *   inv   = rsqrt(mean(gated^2) + epsilon)                             (fp32, fma accumulation, 256-way tree)
+ *   v     = bf16(gated * inv * norm_weight * (1 + scale[class]) + shift[class])
+ *   q     = per-row int8 of v (scale = max|v|/127)                    -> quantized, quantized_scales
+ * so the W8A8 GEMM that follows reads int8 directly and the bf16 activation is never
+ * re-read.  One 256-thread CTA per row; the row lives in shared memory between passes.
+ * Rows in [rows, padded_rows) are written as zeros with scale 1.  HBM-bound:
+ * 2*2*W read, 2*W + W + 4 written per row. */
+static __global__ void __launch_bounds__(256) gate_adaln_quantize_kernel(
+    const uint16_t *residual, const uint16_t *__restrict__ branch, const uint16_t *__restrict__ gate_modulation,
+    const uint32_t *__restrict__ row_map, const uint16_t *__restrict__ norm_weight, const uint16_t *__restrict__ norm_modulation,
+    uint16_t *gated_residual, int8_t *__restrict__ quantized, float *__restrict__ quantized_scales, uint32_t rows, uint32_t width,
+    uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    extern __shared__ uint16_t row_values[];
+    __shared__ float reductions[256];
+    __shared__ float max_scratch[8];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const size_t row_base = (size_t)row * width;
+    if (row >= rows) {
+        for (uint32_t c = tid; c < width; c += 256) quantized[row_base + c] = 0;
+        if (tid == 0) quantized_scales[row] = 1.0f;
+        return;
+    }
+    const size_t base = (size_t)(row_map ? row_map[row] : 0) * slots * width;
+    float local_sum = 0.0f;
+    for (uint32_t c = tid; c < width; c += 256) {
+        const float gate = bf16_bits_to_f32(gate_modulation[base + (size_t)gate_slot * width + c]);
+        const uint32_t gated = f32_to_bf16_bits(__fadd_rn(bf16_bits_to_f32(residual[row_base + c]),
+                                                          __fmul_rn(bf16_bits_to_f32(branch[row_base + c]), gate)));
+        gated_residual[row_base + c] = (uint16_t)gated;
+        row_values[c] = (uint16_t)gated;
+        const float v = bf16_bits_to_f32(gated);
+        local_sum = fmaf(v, v, local_sum);
+    }
+    reductions[tid] = local_sum;
+    __syncthreads();
+    for (uint32_t stride = 128; stride >= 32; stride >>= 1) {
+        if (tid < stride) reductions[tid] += reductions[tid + stride];
+        __syncthreads();
+    }
+    if (tid < 32) {
+        float sum = reductions[tid];
+#pragma unroll
+        for (int stride = 16; stride; stride >>= 1) sum += __shfl_down_sync(0xffffffffu, sum, stride);
+        if (tid == 0) reductions[0] = rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)width), epsilon));
+    }
+    __syncthreads();
+    const float inverse = reductions[0];
+    float local_max = 0.0f;
+    for (uint32_t c = tid; c < width; c += 256) {
+        const float normalized = __fmul_rn(__fmul_rn(bf16_bits_to_f32(row_values[c]), inverse), bf16_bits_to_f32(norm_weight[c]));
+        const float shift = bf16_bits_to_f32(norm_modulation[base + (size_t)shift_slot * width + c]);
+        const float scale = bf16_bits_to_f32(norm_modulation[base + (size_t)scale_slot * width + c]);
+        const uint32_t v = f32_to_bf16_bits(__fadd_rn(__fmul_rn(normalized, __fadd_rn(1.0f, scale)), shift));
+        row_values[c] = (uint16_t)v;
+        local_max = fmaxf(local_max, fabsf(bf16_bits_to_f32(v)));
+    }
+    const float peak = block_max_256(local_max, max_scratch);
+    const float out_scale = peak > 0.0f ? __fdiv_rn(peak, 127.0f) : __fdiv_rn(1.0f, 127.0f);
+    const float q_scale = peak > 0.0f ? __fdiv_rn(127.0f, peak) : 127.0f;
+    if (tid == 0) quantized_scales[row] = out_scale;
+    for (uint32_t c = tid; c < width; c += 256) quantized[row_base + c] = (int8_t)quantize_one(bf16_bits_to_f32(row_values[c]), q_scale);
+}
+
 /* Weight-only Q8 group packer on the device: one warp per (row, K-group).
  * scale = max==0 ? 1 : max(max/127, FLT_MIN); q = round-half-even(w/scale). */
 static __global__ void __launch_bounds__(256) q8_pack_rows_kernel(const uint16_t *__restrict__ src, int8_t *__restrict__ q,

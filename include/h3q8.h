@@ -282,6 +282,23 @@ int h3_gpu_linear_int8_bf16(h3_gpu *gpu, h3_gpu_tensor *output, h3_gpu_tensor *q
                             const h3_gpu_tensor *weight, const h3_gpu_tensor *weight_scales,
                             uint32_t rows, uint32_t input_dim, uint32_t output_dim,
                             int use_slower_uncached_int8_scales);
+/* src/gpu.h:630-642: gate*branch + residual, RMS norm, AdaLN modulation and per-row int8
+ * quantisation of the result in one row pass (the producer-side fusion of the activation
+ * quantiser; src/metal/shaders.metal:3390-3587).  gated_residual may alias residual. */
+int h3_gpu_gate_adaln_quantize_int8(h3_gpu *gpu, h3_gpu_tensor *gated_residual, h3_gpu_tensor *quantized_output,
+                                    h3_gpu_tensor *quantized_scales, const h3_gpu_tensor *residual,
+                                    const h3_gpu_tensor *branch, const h3_gpu_tensor *norm_weight,
+                                    const h3_gpu_tensor *gate_modulation, const h3_gpu_tensor *norm_modulation,
+                                    const h3_gpu_tensor *row_map, uint32_t rows, uint32_t padded_rows, uint32_t width,
+                                    uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot,
+                                    float epsilon);
+/* Fused projection on activations that are already int8 (the `input_is_quantized` route of
+ * h3_gpu_mlp_int8_bf16, src/gpu.h:547-563).  weight: q8 descriptor.  input_group: 0 = one
+ * scale per row, else K elements per activation scale (the per-1024 FC2 recipe). */
+int h3_gpu_linear_fused_int8_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *quantized_input,
+                                  const h3_gpu_tensor *input_scales, uint32_t input_group, const h3_gpu_tensor *weight,
+                                  const h3_gpu_tensor *bias, const h3_gpu_tensor *gate, const h3_gpu_tensor *residual,
+                                  uint32_t rows, uint32_t input_dim, uint32_t output_dim, int activation);
 /* Unfused epilogue operators kept for comparison -- src/gpu.h:575-577, 612-617, 750-752 */
 int h3_gpu_gelu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input, uint32_t elements, int approximate);
 int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,

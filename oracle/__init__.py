@@ -130,6 +130,22 @@ def quantize_rows(x_bf16, dispatch_rows=None, clip=1.0):
     return q, s
 
 
+def gate_adaln_quantize(residual, branch, gate_modulation, norm_weight, norm_modulation, row_map, padded_rows,
+                        slots, gate_slot, shift_slot, scale_slot, epsilon):
+    """Returns (gated_residual bf16 [M,W], normalized bf16 [M,W], int8 [padded,W], scales [padded])."""
+    rows, width = residual.shape
+    f = lib().h3o_gate_adaln_quantize
+    f.argtypes = [ctypes.c_void_p] * 10 + [ctypes.c_uint32] * 7 + [ctypes.c_float]
+    f.restype = None
+    keep = [np.ascontiguousarray(a) if a is not None else None
+            for a in (residual, branch, gate_modulation, row_map, norm_weight, norm_modulation)]
+    gated, normalized = np.empty((rows, width), np.uint16), np.empty((rows, width), np.uint16)
+    q, s = np.empty((padded_rows, width), np.int8), np.empty(padded_rows, np.float32)
+    f(*[_ptr(a) for a in keep], _ptr(gated), _ptr(normalized), _ptr(q), _ptr(s), rows, padded_rows, width, slots,
+      gate_slot, shift_slot, scale_slot, epsilon)
+    return gated, normalized, q, s
+
+
 def gelu_tanh_bf16(b):
     f = lib().h3o_gelu_tanh_bf16
     return np.array([f(int(v)) for v in np.asarray(b, np.uint16).ravel()], np.uint16).reshape(np.shape(b))

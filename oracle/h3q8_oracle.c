@@ -155,6 +155,52 @@ uint16_t h3o_gate_residual_bf16(uint16_t residual, uint16_t branch, uint16_t gat
     return h3o_f32_to_bf16(value);
 }
 
+/* src/metal/shaders.metal:3390-3473 */
+void h3o_gate_adaln_quantize(const uint16_t *residual, const uint16_t *branch, const uint16_t *gate_modulation,
+                             const uint32_t *row_map, const uint16_t *norm_weight, const uint16_t *norm_modulation,
+                             uint16_t *gated_residual, uint16_t *normalized_out, int8_t *quantized, float *quantized_scales,
+                             uint32_t rows, uint32_t padded_rows, uint32_t width, uint32_t slots, uint32_t gate_slot,
+                             uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    for (uint32_t row = 0; row < padded_rows; row++) {
+        size_t row_base = (size_t)row * width;
+        if (row >= rows) { /* :3405-3411 */
+            memset(quantized + row_base, 0, width);
+            quantized_scales[row] = 1.0f;
+            continue;
+        }
+        size_t base = (size_t)(row_map ? row_map[row] : 0) * slots * width;
+        float lanes[256];
+        for (int t = 0; t < 256; t++) lanes[t] = 0.0f;
+        for (uint32_t c = 0; c < width; c++) { /* :3419-3430, lane = c % 256 walks its columns in order */
+            float gate = h3o_bf16_to_f32(gate_modulation[base + (size_t)gate_slot * width + c]);
+            float product = h3o_bf16_to_f32(branch[row_base + c]) * gate;
+            uint16_t gated = h3o_f32_to_bf16(h3o_bf16_to_f32(residual[row_base + c]) + product);
+            gated_residual[row_base + c] = gated;
+            float v = h3o_bf16_to_f32(gated);
+            lanes[c % 256] = fmaf(v, v, lanes[c % 256]);
+        }
+        for (int stride = 128; stride >= 1; stride >>= 1) /* :3433-3444 */
+            for (int t = 0; t < stride; t++) lanes[t] += lanes[t + stride];
+        float inverse = 1.0f / sqrtf(lanes[0] / (float)width + epsilon);
+        float peak = 0.0f;
+        for (uint32_t c = 0; c < width; c++) { /* :3450-3461 */
+            float normalized = h3o_bf16_to_f32(gated_residual[row_base + c]) * inverse * h3o_bf16_to_f32(norm_weight[c]);
+            float shift = h3o_bf16_to_f32(norm_modulation[base + (size_t)shift_slot * width + c]);
+            float scale = h3o_bf16_to_f32(norm_modulation[base + (size_t)scale_slot * width + c]);
+            uint16_t v = h3o_f32_to_bf16(normalized * (1.0f + scale) + shift);
+            normalized_out[row_base + c] = v;
+            peak = fmaxf(peak, fabsf(h3o_bf16_to_f32(v)));
+        }
+        float out_scale = peak > 0.0f ? peak / 127.0f : 1.0f / 127.0f;
+        float q_scale = peak > 0.0f ? 127.0f / peak : 127.0f;
+        quantized_scales[row] = out_scale;
+        for (uint32_t c = 0; c < width; c++) {
+            int v = (int)rintf(h3o_bf16_to_f32(normalized_out[row_base + c]) * q_scale);
+            quantized[row_base + c] = (int8_t)(v < -127 ? -127 : v > 127 ? 127 : v);
+        }
+    }
+}
+
 /* Everything after the linear result: bf16 round, then the reference's
  * separate bf16->bf16 operators in their call order. */
 static float *capture; /* when set, receives the fp32 linear result (+bias) of every output */

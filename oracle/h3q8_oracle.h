@@ -85,6 +85,16 @@ typedef struct {
 } h3o_linear_args;
 int h3o_linear(const h3o_linear_args *args);
 
+/* src/metal/shaders.metal:3390-3473 (h3_gate_adaln_quantize_int8_scalar): gate + residual,
+ * RMS norm with the shader's 256-lane strided fma accumulation and tree reduction, AdaLN
+ * modulation, per-row int8.  rsqrt is 1/sqrtf here (the GPU's is an approximation), so the
+ * int8 bytes are compared within one step.  row_map may be NULL (class 0). */
+void h3o_gate_adaln_quantize(const uint16_t *residual, const uint16_t *branch, const uint16_t *gate_modulation,
+                             const uint32_t *row_map, const uint16_t *norm_weight, const uint16_t *norm_modulation,
+                             uint16_t *gated_residual, uint16_t *normalized, int8_t *quantized, float *quantized_scales,
+                             uint32_t rows, uint32_t padded_rows, uint32_t width, uint32_t slots, uint32_t gate_slot,
+                             uint32_t shift_slot, uint32_t scale_slot, float epsilon);
+
 int h3o_threads(void);
 #ifdef __cplusplus
 }

@@ -591,6 +591,48 @@ def test_fused_equals_unfused_chain(gpu):
         t.free()
 
 
+# --------------------------------------------------------------------------- producer-side quantiser fusion
+@pytest.mark.parametrize("rows,width", [(5, 256), (130, 5376), (300, 3072)])
+def test_gate_adaln_quantize_feeds_the_int8_gemm(oracle, rows, width):
+    """h3_gpu_gate_adaln_quantize_int8 (src/gpu.h:630-642, src/metal/shaders.metal:3390-3473) and the int8
+    projection that consumes its output without re-reading bf16 activations.  gated_residual is bit-exact;
+    the normalised row passes through rsqrt (approximate on the GPU), so int8 bytes may differ by one step."""
+    slots, padded = 6, (rows + 127) // 128 * 128
+    rng = np.random.default_rng(rows)
+    bf = lambda a: synth.to_bf16(a.astype(np.float32)).reshape(a.shape)
+    res, branch = bf(rng.standard_normal((rows, width))), bf(rng.standard_normal((rows, width)))
+    mod = bf(rng.standard_normal((2, slots, width)) * 0.1)
+    norm_w = bf(1 + 0.1 * rng.standard_normal(width))
+    row_map = (np.arange(rows) % 2).astype(np.uint32)
+    want_g, want_n, want_q, want_s = oracle.gate_adaln_quantize(res, branch, mod, norm_w, mod, row_map, padded, slots, 2, 3, 4, 1e-5)
+    gpu = h.Gpu()
+    t_res, t_br, t_mod, t_nw = (gpu.tensor_from_bf16(a) for a in (res, branch, mod, norm_w))
+    t_map = gpu.tensor_from_u32(row_map)
+    q, sc = gpu.tensor_new_i8(padded * width), gpu.tensor_new_f32(padded)
+    gpu.begin()
+    gpu.gate_adaln_quantize_int8(t_res, q, sc, t_res, t_br, t_nw, t_mod, t_mod, t_map, rows, padded, width, slots, 2, 3, 4, 1e-5)
+    gpu.submit()
+    assert (t_res.read().reshape(rows, width) == want_g).all()          # in place, bit-exact
+    got_q, got_s = q.read().reshape(padded, width).astype(np.int32), sc.read()
+    assert np.abs(got_q - want_q.astype(np.int32)).max() <= 1 and (got_q != want_q).mean() < 0.02
+    assert np.allclose(got_s, want_s, rtol=1e-2) and (got_s[rows:] == 1.0).all() and (got_q[rows:] == 0).all()
+    # the int8 projection on exactly these bytes/scales is then bit-exact against the oracle
+    N = 256
+    wq, ws = synth.int8_weights(7, 2, N, width), synth.lognormal_scales(7, 3, N, 1)
+    w = gpu.q8_from_host(wq, ws, 0)
+    out = gpu.tensor_new_bf16(rows * N)
+    gpu.begin()
+    gpu.linear_fused_int8_bf16(out, q, sc, 0, w, None, None, None, rows, width, N, h.ACT_GELU_TANH)
+    gpu.submit()
+    want = oracle.linear(oracle.MODE_W8A8, got_q[:rows].astype(np.int8), wq, ws[:, 0].copy(), 0, x_scales=got_s[:rows], activation=1, fast=True)
+    check_bf16(out.read().reshape(rows, N), want)
+    with pytest.raises(h.H3Error):
+        gpu.begin()
+        gpu.gate_adaln_quantize_int8(t_res, q, sc, t_res, t_br, t_nw, t_mod, t_mod, t_map, rows, padded, width, slots, 9, 3, 4, 1e-5)
+    gpu.cancel()
+    gpu.free()
+
+
 # --------------------------------------------------------------------------- weight streaming
 def pinned_bytes(gpu, count):
     import ctypes
