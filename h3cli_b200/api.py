@@ -30,7 +30,7 @@ class LinearDesc(C.Structure):
         ("input", C.c_void_p), ("weight", C.c_void_p), ("weight_scales", C.c_void_p), ("weight_group", C.c_uint32),
         ("input_scales", C.c_void_p), ("bias", C.c_void_p), ("gate", C.c_void_p), ("residual", C.c_void_p),
         ("activation", C.c_uint32), ("output", C.c_void_p), ("accumulators", C.c_void_p), ("kernel", C.c_uint32),
-        ("input_group", C.c_uint32),
+        ("input_group", C.c_uint32), ("rope", C.c_void_p),
     ]
 
 
@@ -131,6 +131,8 @@ def library():
         "h3_gpu_gate_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]),
         "h3_gpu_add_bf16": (C.c_int, [vp, vp, vp, vp, u32]),
         "h3_gpu_swiglu_bf16": (C.c_int, [vp, vp, vp, u32, u32]),
+        "h3_gpu_grouped_qkv_rope_bf16": (C.c_int, [vp] * 9 + [u32] * 4 + [C.c_float]),
+        "h3_gpu_grouped_qkv_linear_rope_bf16": (C.c_int, [vp] * 11 + [u32] * 5 + [C.c_float]),
         "h3_gpu_linear_fused_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
         "h3_gpu_linear_grouped_bf16": (C.c_int, [vp, C.POINTER(Problem), u32]),
     }
@@ -396,6 +398,18 @@ class Gpu:
     def gate_bf16(self, output, residual, branch, modulation, row_map, rows, width, slots, gate_slot):
         return self._check(library().h3_gpu_gate_bf16(self.handle, _h(output), _h(residual), _h(branch), _h(modulation),
                                                       _h(row_map), rows, width, slots, gate_slot))
+
+    def grouped_qkv_rope_bf16(self, query, key, value, qkv, q_norm, k_norm, rope_cos, rope_sin, sequence, heads, head_dim,
+                              rope_half, epsilon):
+        return self._check(library().h3_gpu_grouped_qkv_rope_bf16(
+            self.handle, _h(query), _h(key), _h(value), _h(qkv), _h(q_norm), _h(k_norm), _h(rope_cos), _h(rope_sin),
+            sequence, heads, head_dim, rope_half, epsilon))
+
+    def grouped_qkv_linear_rope_bf16(self, query, key, value, qkv, input, weight, q_norm, k_norm, rope_cos, rope_sin, rows,
+                                     input_dim, heads, head_dim, rope_half, epsilon):
+        return self._check(library().h3_gpu_grouped_qkv_linear_rope_bf16(
+            self.handle, _h(query), _h(key), _h(value), _h(qkv), _h(input), _h(weight), _h(q_norm), _h(k_norm),
+            _h(rope_cos), _h(rope_sin), rows, input_dim, heads, head_dim, rope_half, epsilon))
 
     def swiglu_bf16(self, output, fused, rows, width):
         return self._check(library().h3_gpu_swiglu_bf16(self.handle, _h(output), _h(fused), rows, width))

@@ -18,7 +18,19 @@
 
 namespace h3q8 {
 
-enum : uint32_t { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SWIGLU = 2 };
+enum : uint32_t { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_SWIGLU = 2, ACT_QKV_ROPE = 3 };
+
+/* QKV epilogue of the DiT block (src/cuda/cuda_kernels.cuh:988-1045, grouped layout
+ * src/gpu.h:652-653): output columns are [head, q/k/v, 128]; q and k get a per-head RMS
+ * norm with a learned weight and rotary embedding on the first 2*rope_half dimensions,
+ * v is copied; all three are stored as [row, head, 128]. */
+struct RopeParams {
+    const uint16_t *q_norm, *k_norm;   /* bf16 [128]                 */
+    const uint16_t *cos, *sin;         /* bf16 [rows, rope_half]     */
+    uint16_t *query, *key, *value;     /* bf16 [rows, heads, 128]    */
+    uint32_t heads, rope_half;         /* rope_half: 48 or 64        */
+    float epsilon;
+};
 
 /* Device view of the optional epilogue operands (all may be null). */
 struct EpilogueParams {
@@ -26,6 +38,7 @@ struct EpilogueParams {
     const uint16_t *gate;      /* bf16 [N]   */
     const uint16_t *residual;  /* bf16 [M,N] */
     uint32_t activation;
+    RopeParams rope;           /* used when activation == ACT_QKV_ROPE */
 };
 
 /* Branch-free so that the compiler can interleave many elements per thread. */
@@ -85,6 +98,50 @@ __device__ __forceinline__ uint32_t epilogue_value(float linear, float bias, boo
     if (activation == ACT_GELU_TANH) y = f32_to_bf16_bits(gelu_tanh_f32(bf16_bits_to_f32(y)));
     if (gated) y = f32_to_bf16_bits(__fadd_rn(residual, __fmul_rn(bf16_bits_to_f32(y), gate)));
     return y;
+}
+
+/* One (row, head, q-or-k) stream held by one thread: xp = its 128 linear outputs, already
+ * rounded to bf16 and packed in pairs; sum = sum of their squares accumulated in dimension
+ * order with fmaf, as the reference's loop does.  Writes the 128 normalised, rotated values. */
+template <int ROPE_HALF>
+__device__ __forceinline__ void qkv_rope_store(const uint32_t (&xp)[64], float sum, const uint16_t *__restrict__ norm_weight,
+                                               const uint16_t *__restrict__ cos_row, const uint16_t *__restrict__ sin_row,
+                                               float epsilon, uint16_t *__restrict__ dst) {
+    static_assert(ROPE_HALF % 8 == 0 && 2 * ROPE_HALF <= 128, "rotary half must be a multiple of 8 within the head");
+    const float inverse = rsqrtf(__fadd_rn(__fdiv_rn(sum, 128.0f), epsilon));
+    /* eight dimensions at a time; the rotary partner of a group of eight is another aligned group of eight */
+#pragma unroll
+    for (int g = 0; g < 16; g++) {
+        const int d0 = g * 8;
+        const bool rotary = d0 < 2 * ROPE_HALF, low = d0 < ROPE_HALF;
+        const int p0 = low ? d0 + ROPE_HALF : d0 - ROPE_HALF;        /* partner group (unused when !rotary) */
+        const int f0 = low ? d0 : d0 - ROPE_HALF;                     /* cos/sin index of the group          */
+        uint32_t w[4], wp[4] = {0, 0, 0, 0}, c[4] = {0, 0, 0, 0}, sn[4] = {0, 0, 0, 0}, out[4];
+        *reinterpret_cast<uint4 *>(w) = reinterpret_cast<const uint4 *>(norm_weight)[g];
+        if (rotary) {
+            *reinterpret_cast<uint4 *>(wp) = reinterpret_cast<const uint4 *>(norm_weight)[p0 / 8];
+            *reinterpret_cast<uint4 *>(c) = reinterpret_cast<const uint4 *>(cos_row)[f0 / 8];
+            *reinterpret_cast<uint4 *>(sn) = reinterpret_cast<const uint4 *>(sin_row)[f0 / 8];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float v0 = __fmul_rn(__fmul_rn(bf16_lo(xp[d0 / 2 + j]), inverse), bf16_lo(w[j]));
+            float v1 = __fmul_rn(__fmul_rn(bf16_hi(xp[d0 / 2 + j]), inverse), bf16_hi(w[j]));
+            if (rotary) {
+                const float o0 = __fmul_rn(__fmul_rn(bf16_lo(xp[p0 / 2 + j]), inverse), bf16_lo(wp[j]));
+                const float o1 = __fmul_rn(__fmul_rn(bf16_hi(xp[p0 / 2 + j]), inverse), bf16_hi(wp[j]));
+                if (low) {
+                    v0 = __fsub_rn(__fmul_rn(v0, bf16_lo(c[j])), __fmul_rn(o0, bf16_lo(sn[j])));
+                    v1 = __fsub_rn(__fmul_rn(v1, bf16_hi(c[j])), __fmul_rn(o1, bf16_hi(sn[j])));
+                } else {
+                    v0 = __fadd_rn(__fmul_rn(v0, bf16_lo(c[j])), __fmul_rn(o0, bf16_lo(sn[j])));
+                    v1 = __fadd_rn(__fmul_rn(v1, bf16_hi(c[j])), __fmul_rn(o1, bf16_hi(sn[j])));
+                }
+            }
+            out[j] = pack_bf16_pair(v0, v1);
+        }
+        reinterpret_cast<uint4 *>(dst)[g] = *reinterpret_cast<uint4 *>(out);
+    }
 }
 
 } /* namespace h3q8 */

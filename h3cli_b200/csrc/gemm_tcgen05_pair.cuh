@@ -68,7 +68,9 @@ __device__ __forceinline__ uint32_t locate_problem(const PairArgs &args, uint32_
     return g;
 }
 
-template <int MODE>
+/* ROPE selects the QKV norm + rotary epilogue (its own instantiation: it keeps a whole
+ * 128-wide head row in registers, which the other epilogues should not pay for). */
+template <int MODE, bool ROPE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<MODE>::THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
     using C = PairConfig<MODE>;
@@ -176,7 +178,53 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
             const bool row_ok = row < p.M;
             float a_scale = 1.0f;
             if (MODE == MODE_W8A8) a_scale = row_ok ? p.a_scales[row] : 0.0f;
-            if (swiglu) {
+            if (ROPE) {
+                /* each 128-column group is one (head, q|k|v) stream; this warp owns the group `half` of the tile and
+                 * every thread keeps its row's 128 bf16 values in registers between the norm and the rotation */
+                const uint32_t block = nb * 2 + half;
+                if (block * 128 < p.N) {
+                    const uint32_t head = block / 3, which = block - head * 3;
+                    uint32_t xp[64];
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        uint32_t v[32];
+                        tmem_load_32x32(tmem_base + ((quadrant * 32u) << 16) + acc.index * C::ACC_COLS + half * 128 + c * 32, v);
+                        tmem_load_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            float l0, l1;
+                            if (MODE == MODE_W8A8) {
+                                const float2 ws = *reinterpret_cast<const float2 *>(p.w_scales + block * 128 + c * 32 + 2 * j);
+                                l0 = __fmul_rn(__fmul_rn((float)(int32_t)v[2 * j], a_scale), ws.x);
+                                l1 = __fmul_rn(__fmul_rn((float)(int32_t)v[2 * j + 1], a_scale), ws.y);
+                            } else { l0 = __uint_as_float(v[2 * j]); l1 = __uint_as_float(v[2 * j + 1]); }
+                            const uint32_t packed = pack_bf16_pair(l0, l1);
+                            xp[c * 16 + j] = packed;
+                            sum = fmaf(bf16_lo(packed), bf16_lo(packed), sum);
+                            sum = fmaf(bf16_hi(packed), bf16_hi(packed), sum);
+                        }
+                    }
+                    if (row_ok) {
+                        if (p.out) {
+#pragma unroll
+                            for (int i = 0; i < 16; i++)
+                                reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + block * 128)[i] = *reinterpret_cast<uint4 *>(&xp[4 * i]);
+                        }
+                        const RopeParams &rp = p.ep.rope;
+                        uint16_t *dst = (which == 0 ? rp.query : which == 1 ? rp.key : rp.value) + ((size_t)row * rp.heads + head) * 128;
+                        if (which == 2) {
+#pragma unroll
+                            for (int i = 0; i < 16; i++) reinterpret_cast<uint4 *>(dst)[i] = *reinterpret_cast<uint4 *>(&xp[4 * i]);
+                        } else {
+                            const uint16_t *norm = which == 0 ? rp.q_norm : rp.k_norm;
+                            const uint16_t *cos_row = rp.cos + (size_t)row * rp.rope_half, *sin_row = rp.sin + (size_t)row * rp.rope_half;
+                            if (rp.rope_half == 48) qkv_rope_store<48>(xp, sum, norm, cos_row, sin_row, rp.epsilon, dst);
+                            else qkv_rope_store<64>(xp, sum, norm, cos_row, sin_row, rp.epsilon, dst);
+                        }
+                    }
+                }
+            } else if (!ROPE && swiglu) {
                 /* accumulator columns 0..127 hold the gate, 128..255 the up projection of the same 128 outputs */
 #pragma unroll 1
                 for (int hc = 0; hc < 2; hc++) {
@@ -224,7 +272,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
                         *reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + col) = *reinterpret_cast<uint4 *>(packed);
                     }
                 }
-            } else
+            } else if (!ROPE)
 #pragma unroll 1
             for (int hc = 0; hc < HALF_CHUNKS; hc++) {
                 const int c = half * HALF_CHUNKS + hc;

@@ -833,7 +833,7 @@ static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size
 /* The linear operators: validate every problem, run the conversion kernels each needs
  * (per-token quantiser for W8A8, weight dequantiser for the W8A16 scratch policy), then
  * hand all of them to the raw layer in one grouped call. */
-static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count) {
+static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count, const h3q8_rope_desc *rope = nullptr) {
     if (!launch_ready(g)) return 0;
     if (!problems || !count || count > 16) return set_error(g, "linear: between 1 and 16 problems per call");
     size_t total[3] = {0, 0, 0};
@@ -843,7 +843,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
         if (!rows || !k || !n) return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
         if (!q.weight || q.weight->owner != g) return set_error(g, "linear %ux%ux%u: weight is missing or foreign", rows, n, k);
         if (!require(g, q.input, H3_GPU_BF16, (size_t)rows * k, "linear input") ||
-            !require(g, q.output, H3_GPU_BF16, (size_t)rows * n, "linear output")) return 0;
+            ((q.output || !rope) && !require(g, q.output, H3_GPU_BF16, (size_t)rows * n, "linear output"))) return 0;
         const uint32_t wrows = q.activation == H3Q8_ACT_SWIGLU ? 2 * n : n; /* SwiGLU weight: [gate n | up n] rows */
         if (q.bias && !require(g, q.bias, H3_GPU_BF16, wrows, "linear bias")) return 0;
         if (q.gate && !require(g, q.gate, H3_GPU_BF16, n, "linear gate")) return 0;
@@ -876,7 +876,8 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
         d.gate = q.gate ? (const uint16_t *)pointer(q.gate) : nullptr;
         d.residual = q.residual ? (const uint16_t *)pointer(q.residual) : nullptr;
         d.activation = (uint32_t)q.activation;
-        d.output = (uint16_t *)pointer(q.output);
+        d.output = q.output ? (uint16_t *)pointer(q.output) : nullptr;
+        d.rope = rope;
         d.input = pointer(q.input);
         d.weight = pointer(w);
         size_t need[3];
@@ -1090,6 +1091,90 @@ extern "C" int h3_gpu_gate_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tens
     count_launch(1);
     return launch_status(g, "gate", 1);
 }
+/* src/cuda/cuda_kernels.cuh:988-1045 with grouped = 1: one thread per (row, head, dimension);
+ * every thread accumulates the head's squares in dimension order like the reference. */
+static __global__ void __launch_bounds__(128) grouped_qkv_rope_kernel(const uint16_t *__restrict__ qkv, const uint16_t *__restrict__ q_weight,
+                                                                     const uint16_t *__restrict__ k_weight, const uint16_t *__restrict__ rope_cos,
+                                                                     const uint16_t *__restrict__ rope_sin, uint16_t *query, uint16_t *key,
+                                                                     uint16_t *value, uint32_t heads, uint32_t head_dim, uint32_t rope_half,
+                                                                     float epsilon) {
+    const uint32_t row = blockIdx.y, head = blockIdx.x;
+    const size_t q_base = ((size_t)row * heads + head) * head_dim * 3, k_base = q_base + head_dim, v_base = k_base + head_dim;
+    float q_sum = 0.0f, k_sum = 0.0f;
+    for (uint32_t d = 0; d < head_dim; d++) {
+        const float q = bf16_bits_to_f32(qkv[q_base + d]), k = bf16_bits_to_f32(qkv[k_base + d]);
+        q_sum = fmaf(q, q, q_sum);
+        k_sum = fmaf(k, k, k_sum);
+    }
+    const float q_inverse = rsqrtf(__fadd_rn(__fdiv_rn(q_sum, (float)head_dim), epsilon));
+    const float k_inverse = rsqrtf(__fadd_rn(__fdiv_rn(k_sum, (float)head_dim), epsilon));
+    for (uint32_t d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float q0 = __fmul_rn(__fmul_rn(bf16_bits_to_f32(qkv[q_base + d]), q_inverse), bf16_bits_to_f32(q_weight[d]));
+        float k0 = __fmul_rn(__fmul_rn(bf16_bits_to_f32(qkv[k_base + d]), k_inverse), bf16_bits_to_f32(k_weight[d]));
+        if (d < 2 * rope_half) {
+            const bool low = d < rope_half;
+            const uint32_t pair = low ? d + rope_half : d - rope_half, first = low ? d : pair;
+            const float q1 = __fmul_rn(__fmul_rn(bf16_bits_to_f32(qkv[q_base + pair]), q_inverse), bf16_bits_to_f32(q_weight[pair]));
+            const float k1 = __fmul_rn(__fmul_rn(bf16_bits_to_f32(qkv[k_base + pair]), k_inverse), bf16_bits_to_f32(k_weight[pair]));
+            const float c = bf16_bits_to_f32(rope_cos[(size_t)row * rope_half + first]), s = bf16_bits_to_f32(rope_sin[(size_t)row * rope_half + first]);
+            q0 = low ? __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, s)) : __fadd_rn(__fmul_rn(q0, c), __fmul_rn(q1, s));
+            k0 = low ? __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, s)) : __fadd_rn(__fmul_rn(k0, c), __fmul_rn(k1, s));
+        }
+        const size_t o = ((size_t)row * heads + head) * head_dim + d;
+        query[o] = (uint16_t)f32_to_bf16_bits(q0);
+        key[o] = (uint16_t)f32_to_bf16_bits(k0);
+        value[o] = qkv[v_base + d];
+    }
+}
+static int rope_operands(h3_gpu *g, const h3_gpu_tensor *q, const h3_gpu_tensor *k, const h3_gpu_tensor *v, const h3_gpu_tensor *qw,
+                         const h3_gpu_tensor *kw, const h3_gpu_tensor *c, const h3_gpu_tensor *s, uint32_t rows, uint32_t heads,
+                         uint32_t dim, uint32_t half) {
+    const size_t count = (size_t)rows * heads * dim;
+    if (!rows || !heads || !dim || half * 2 > dim || rows > 65535u * 64u) return set_error(g, "QKV norm/RoPE: invalid shape");
+    return require(g, q, H3_GPU_BF16, count, "Q") && require(g, k, H3_GPU_BF16, count, "K") && require(g, v, H3_GPU_BF16, count, "V") &&
+           require(g, qw, H3_GPU_BF16, dim, "Q norm") && require(g, kw, H3_GPU_BF16, dim, "K norm") &&
+           require(g, c, H3_GPU_BF16, (size_t)rows * half, "RoPE cos") && require(g, s, H3_GPU_BF16, (size_t)rows * half, "RoPE sin");
+}
+extern "C" int h3_gpu_grouped_qkv_rope_bf16(h3_gpu *g, h3_gpu_tensor *q, h3_gpu_tensor *k, h3_gpu_tensor *v, const h3_gpu_tensor *qkv,
+                                            const h3_gpu_tensor *qw, const h3_gpu_tensor *kw, const h3_gpu_tensor *c, const h3_gpu_tensor *s,
+                                            uint32_t rows, uint32_t heads, uint32_t dim, uint32_t half, float epsilon) {
+    if (!launch_ready(g)) return 0;
+    if (!rope_operands(g, q, k, v, qw, kw, c, s, rows, heads, dim, half) ||
+        !require(g, qkv, H3_GPU_BF16, (size_t)rows * heads * dim * 3, "QKV")) return 0;
+    if (rows > 65535) return set_error(g, "QKV norm/RoPE: at most 65535 rows per call");
+    grouped_qkv_rope_kernel<<<dim3(heads, rows), 128, 0, g->compute>>>(
+        (const uint16_t *)pointer(qkv), (const uint16_t *)pointer(qw), (const uint16_t *)pointer(kw), (const uint16_t *)pointer(c),
+        (const uint16_t *)pointer(s), (uint16_t *)pointer(q), (uint16_t *)pointer(k), (uint16_t *)pointer(v), heads, dim, half, epsilon);
+    count_launch(1);
+    return launch_status(g, "QKV norm/RoPE", 1);
+}
+extern "C" int h3_gpu_grouped_qkv_linear_rope_bf16(h3_gpu *g, h3_gpu_tensor *q, h3_gpu_tensor *k, h3_gpu_tensor *v, h3_gpu_tensor *qkv,
+                                                   const h3_gpu_tensor *input, const h3_gpu_tensor *w, const h3_gpu_tensor *qw,
+                                                   const h3_gpu_tensor *kw, const h3_gpu_tensor *c, const h3_gpu_tensor *s, uint32_t rows,
+                                                   uint32_t width, uint32_t heads, uint32_t dim, uint32_t half, float epsilon) {
+    if (!launch_ready(g)) return 0;
+    if (!rope_operands(g, q, k, v, qw, kw, c, s, rows, heads, dim, half)) return 0;
+    const uint32_t n = heads * dim * 3;
+    /* one kernel when the epilogue can hold a head row: head_dim 128, rotary half 48 or 64, operands the two-CTA kernel takes */
+    const bool grouped_scales = w && w->q8 && g->quant_mode == 2 && w->q8_group;
+    const bool fusable = dim == 128 && (half == 48 || half == 64) && width % 16 == 0 && rows > 0 && !grouped_scales &&
+                         (!w || !w->q8 || g->quant_mode == 2 || g->w8a16_scratch_rows);
+    if (fusable) {
+        h3q8_rope_desc rope = {(const uint16_t *)pointer(qw), (const uint16_t *)pointer(kw), (const uint16_t *)pointer(c),
+                               (const uint16_t *)pointer(s), (uint16_t *)pointer(q), (uint16_t *)pointer(k), (uint16_t *)pointer(v),
+                               heads, dim, half, epsilon};
+        h3_gpu_linear_problem problem = {qkv, input, w, nullptr, nullptr, nullptr, rows, width, n, H3Q8_ACT_NONE};
+        const int saved = g->w8a16_scratch_rows;
+        if (w && w->q8 && g->quant_mode != 2) g->w8a16_scratch_rows = 1; /* the fused epilogue wants bf16 operands */
+        int ok = linear_dispatch_many(g, &problem, 1, &rope);
+        g->w8a16_scratch_rows = saved;
+        return ok;
+    }
+    if (!qkv) return set_error(g, "QKV projection: this shape needs the qkv tensor for the unfused route");
+    return h3_gpu_linear_bf16(g, qkv, input, w, nullptr, rows, width, n) &&
+           h3_gpu_grouped_qkv_rope_bf16(g, q, k, v, qkv, qw, kw, c, s, rows, heads, dim, half, epsilon);
+}
+
 /* src/gpu.h:714-716, src/cuda/cuda_kernels.cuh:1047-1059: fused row = [gate width | up width] */
 static __global__ void swiglu_kernel(const uint16_t *fused, uint16_t *out, uint32_t rows, uint32_t width) {
     uint32_t c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;

@@ -125,7 +125,7 @@ static int launch_tcgen05(const h3q8_linear_desc &d, GemmParams p, DeviceState *
 
 /* Two-CTA clusters: the grid is twice the number of clusters that can be resident at once. */
 /* `count` problems (1..PAIR_MAX_PROBLEMS) of one operand mode in ONE launch. */
-template <int MODE>
+template <int MODE, bool ROPE = false>
 static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, uint32_t count, DeviceState *dev, cudaStream_t stream) {
     using C = PairConfig<MODE>;
     static_assert(sizeof(PairArgs) <= 4000, "kernel parameter block too large");
@@ -155,7 +155,7 @@ static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, 
         tiles += p.tiles;
     }
     args.tile_start[count] = tiles;
-    auto kernel = gemm_tcgen05_pair_kernel<MODE>;
+    auto kernel = gemm_tcgen05_pair_kernel<MODE, ROPE>;
     static int clusters[64] = {};
     int device = 0;
     cudaGetDevice(&device);
@@ -200,7 +200,7 @@ static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t 
     }
     if (kernel == H3Q8_KERNEL_TCGEN05_PAIR) {
         if constexpr (MODE == MODE_W8A16) return fail("the two-CTA kernel takes bf16 or int8 operands, not main-loop dequantisation");
-        else return launch_pair<MODE>(&d, &p, 1, dev, stream);
+        else return d.rope ? launch_pair<MODE, true>(&d, &p, 1, dev, stream) : launch_pair<MODE>(&d, &p, 1, dev, stream);
     }
     if (kernel == H3Q8_KERNEL_TCGEN05_M256) return launch_tcgen05<MODE, 256, 2, false>(d, p, dev, stream);
     if (kernel == H3Q8_KERNEL_TCGEN05_N128) return launch_tcgen05<MODE, 128, 1, false>(d, p, dev, stream);
@@ -210,7 +210,16 @@ static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t 
 /* Validation, kernel parameters and kernel choice for one problem. */
 static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kernel, DeviceState *&dev) {
     if (!d.rows || !d.input_dim || !d.output_dim) return fail("linear %ux%ux%u: empty dimension", d.rows, d.output_dim, d.input_dim);
-    if (!d.input || !d.weight || !d.output) return fail("linear %ux%ux%u: null operand", d.rows, d.output_dim, d.input_dim);
+    if (!d.input || !d.weight || (!d.output && !d.rope)) return fail("linear %ux%ux%u: null operand", d.rows, d.output_dim, d.input_dim);
+    if (d.rope) {
+        const h3q8_rope_desc &r = *d.rope;
+        if (d.activation || d.bias || d.gate || d.residual || d.accumulators || d.weight_group || d.input_group || d.mode == H3Q8_MODE_W8A16)
+            return fail("linear: the QKV rotary epilogue takes bf16 or per-channel W8A8 operands and no other epilogue term");
+        if (r.head_dim != 128 || (r.rope_half != 48 && r.rope_half != 64) || !r.heads || d.output_dim != r.heads * 3 * 128)
+            return fail("linear: fused QKV rotary epilogue needs head_dim 128, rope_half 48 or 64 and output_dim = heads * 384");
+        if (!r.q_norm || !r.k_norm || !r.rope_cos || !r.rope_sin || !r.query || !r.key || !r.value)
+            return fail("linear: QKV rotary epilogue operand missing");
+    }
     if (d.mode > H3Q8_MODE_W8A8) return fail("linear: unknown mode %u", d.mode);
     if (d.activation > H3Q8_ACT_SWIGLU) return fail("linear: unknown activation %u", d.activation);
     const bool swiglu = d.activation == H3Q8_ACT_SWIGLU;
@@ -240,12 +249,17 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     p.w_scales = d.weight_scales; p.a_scales = d.input_scales;
     p.ep.bias = d.bias; p.ep.gate = d.gate; p.ep.residual = d.residual; p.ep.activation = d.activation;
     p.out = d.output; p.acc_dump = d.accumulators; p.status = dev->status;
+    if (d.rope) {
+        const h3q8_rope_desc &r = *d.rope;
+        p.ep.activation = ACT_QKV_ROPE;
+        p.ep.rope = RopeParams{r.q_norm, r.k_norm, r.rope_cos, r.rope_sin, r.query, r.key, r.value, r.heads, r.rope_half, r.epsilon};
+    }
 
     /* What the TMA path needs: 16-byte aligned bases and row pitches, output rows
      * that take 16-byte stores, scale groups that align with the k-blocks. */
     const uint32_t k_multiple = d.mode == H3Q8_MODE_BF16 ? 8 : 16;
     bool tma_ok = d.input_dim % k_multiple == 0 && d.output_dim % 8 == 0 && aligned16(d.input) && aligned16(d.weight) &&
-                  aligned16(d.output) && (!d.bias || aligned16(d.bias)) && (!d.gate || aligned16(d.gate)) &&
+                  (!d.output || aligned16(d.output)) && (!d.bias || aligned16(d.bias)) && (!d.gate || aligned16(d.gate)) &&
                   (!d.residual || aligned16(d.residual)) && (!d.accumulators || aligned16(d.accumulators)) &&
                   (d.mode != H3Q8_MODE_W8A8 || aligned16(d.weight_scales));
     if (d.mode == H3Q8_MODE_W8A16 && d.weight_group && d.weight_group % 64) tma_ok = false;
@@ -260,7 +274,17 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
                : pair_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_TCGEN05;
         /* SwiGLU runs on the two-CTA kernel (gate rows in one CTA, up rows in its peer) or on the plain kernel */
         if (swiglu) kernel = tma_ok && d.mode != H3Q8_MODE_W8A16 ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_PLAIN;
-    } else if (swiglu && kernel != H3Q8_KERNEL_PLAIN && kernel != H3Q8_KERNEL_TCGEN05_PAIR) {
+        if (d.rope) kernel = H3Q8_KERNEL_TCGEN05_PAIR;
+    }
+    if (d.rope) {
+        const h3q8_rope_desc &r = *d.rope;
+        if (kernel != H3Q8_KERNEL_TCGEN05_PAIR || !tma_ok || !aligned16(r.q_norm) || !aligned16(r.k_norm) || !aligned16(r.rope_cos) ||
+            !aligned16(r.rope_sin) || !aligned16(r.query) || !aligned16(r.key) || !aligned16(r.value))
+            return fail("linear: the fused QKV rotary epilogue runs on the two-CTA kernel with 16-byte aligned operands");
+        return 1;
+    }
+    /* an explicitly requested kernel must be able to take the problem */
+    if (swiglu && kernel != H3Q8_KERNEL_PLAIN && kernel != H3Q8_KERNEL_TCGEN05_PAIR) {
         return fail("linear: SwiGLU is available on the two-CTA and the plain kernel");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && p.scale_group))) {
         return fail("linear: the two-CTA kernel takes bf16 or per-channel int8 operands");
@@ -310,7 +334,7 @@ extern "C" int h3q8_linear_grouped(const h3q8_linear_desc *problems, uint32_t co
         for (uint32_t i = 0; i < count; i++) {
             uint32_t kernel;
             if (!plan_linear(problems[i], params[i], kernel, dev)) return 0;
-            together = together && kernel == H3Q8_KERNEL_TCGEN05_PAIR && problems[i].mode == problems[0].mode;
+            together = together && kernel == H3Q8_KERNEL_TCGEN05_PAIR && problems[i].mode == problems[0].mode && !problems[i].rope;
         }
         if (together && count > 1)
             return problems[0].mode == H3Q8_MODE_BF16 ? launch_pair<MODE_BF16>(problems, params, count, dev, stream)

@@ -55,6 +55,19 @@ enum { /* kernel selection; AUTO picks by shape */
                                      pair (BF16 and W8A8 per-channel modes)         */
 };
 
+/* QKV epilogue (src/cuda/cuda_kernels.cuh:988-1045 with the grouped column layout of
+ * src/gpu.h:652-653): weight rows / output columns are [head, q|k|v, head_dim]; q and k get
+ * the per-head RMS norm (weight q_norm / k_norm) and rotary embedding on dimensions
+ * [0, 2*rope_half), v is copied; all are stored as [row, head, head_dim].  Fused form:
+ * head_dim 128, rope_half 48 or 64, BF16 or W8A8 per-channel operands. */
+typedef struct {
+    const uint16_t *q_norm, *k_norm;     /* bf16 [head_dim]            */
+    const uint16_t *rope_cos, *rope_sin; /* bf16 [rows, rope_half]     */
+    uint16_t *query, *key, *value;       /* bf16 [rows, heads, head_dim] */
+    uint32_t heads, head_dim, rope_half;
+    float epsilon;
+} h3q8_rope_desc;
+
 /* out[M,N] = epilogue(input[M,K] . weight[N,K]^T), everything row-major.
  * Replaces the body of gemm()/quant_gemm() (src/cuda/gpu_cuda.cu:927-1005,
  * src/cuda/cuda_quant.cuh:339-398) and the Metal kernels h3_linear_q8_bf16 /
@@ -81,6 +94,8 @@ typedef struct {
     uint32_t input_group;     /* W8A8: K elements per activation scale, input_scales is then
                                  [M, K/input_group] (the reference's per-1024 FC2 scales,
                                  src/metal/shaders.metal:2663-2742); 0 = one scale per token   */
+    const h3q8_rope_desc *rope; /* optional QKV norm + rotary epilogue; output may then be NULL
+                                 (when given it also receives the plain bf16 projection)       */
 } h3q8_linear_desc;
 int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream);
 
@@ -304,6 +319,19 @@ int h3_gpu_gelu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *in
 int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
                      const h3_gpu_tensor *branch, const h3_gpu_tensor *modulation,
                      const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width, uint32_t slots, uint32_t gate_slot);
+/* src/gpu.h:652-664 and 665-683: norm + RoPE on a stored grouped QKV tensor, and the projection
+ * fused with it (one kernel when head_dim is 128 and rope_half 48 or 64; qkv may be NULL then,
+ * otherwise the projection is stored there first and the separate kernel follows). */
+int h3_gpu_grouped_qkv_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key, h3_gpu_tensor *value,
+                                 const h3_gpu_tensor *qkv, const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+                                 const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin, uint32_t sequence,
+                                 uint32_t heads, uint32_t head_dim, uint32_t rope_half, float epsilon);
+int h3_gpu_grouped_qkv_linear_rope_bf16(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key, h3_gpu_tensor *value,
+                                        h3_gpu_tensor *qkv, const h3_gpu_tensor *input, const h3_gpu_tensor *weight,
+                                        const h3_gpu_tensor *q_norm, const h3_gpu_tensor *k_norm,
+                                        const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin, uint32_t rows,
+                                        uint32_t input_dim, uint32_t heads, uint32_t head_dim, uint32_t rope_half,
+                                        float epsilon);
 int h3_gpu_swiglu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *fused, uint32_t rows, uint32_t width); /* src/gpu.h:714-716 */
 int h3_gpu_add_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *left,
                     const h3_gpu_tensor *right, uint32_t elements);

@@ -146,6 +146,17 @@ def gate_adaln_quantize(residual, branch, gate_modulation, norm_weight, norm_mod
     return gated, normalized, q, s
 
 
+def grouped_qkv_rope(qkv, q_weight, k_weight, rope_cos, rope_sin, heads, head_dim, rope_half, epsilon):
+    rows = qkv.shape[0]
+    f = lib().h3o_grouped_qkv_rope
+    f.argtypes = [ctypes.c_void_p] * 8 + [ctypes.c_uint32] * 4 + [ctypes.c_float]
+    f.restype = None
+    keep = [np.ascontiguousarray(a) for a in (qkv, q_weight, k_weight, rope_cos, rope_sin)]
+    out = [np.empty((rows, heads, head_dim), np.uint16) for _ in range(3)]
+    f(*[_ptr(a) for a in keep], *[_ptr(a) for a in out], rows, heads, head_dim, rope_half, epsilon)
+    return out
+
+
 def gelu_tanh_bf16(b):
     f = lib().h3o_gelu_tanh_bf16
     return np.array([f(int(v)) for v in np.asarray(b, np.uint16).ravel()], np.uint16).reshape(np.shape(b))

@@ -201,6 +201,43 @@ void h3o_gate_adaln_quantize(const uint16_t *residual, const uint16_t *branch, c
     }
 }
 
+/* src/cuda/cuda_kernels.cuh:988-1045 */
+void h3o_grouped_qkv_rope(const uint16_t *qkv, const uint16_t *q_weight, const uint16_t *k_weight, const uint16_t *rope_cos,
+                          const uint16_t *rope_sin, uint16_t *query, uint16_t *key, uint16_t *value, uint32_t sequence,
+                          uint32_t heads, uint32_t head_dim, uint32_t rope_half, float epsilon) {
+#pragma omp parallel for schedule(static)
+    for (uint32_t row = 0; row < sequence; row++)
+        for (uint32_t head = 0; head < heads; head++) {
+            size_t q_base = ((size_t)row * heads + head) * head_dim * 3, k_base = q_base + head_dim, v_base = k_base + head_dim;
+            float q_sum = 0.0f, k_sum = 0.0f;
+            for (uint32_t d = 0; d < head_dim; d++) {
+                float q = h3o_bf16_to_f32(qkv[q_base + d]), k = h3o_bf16_to_f32(qkv[k_base + d]);
+                q_sum = fmaf(q, q, q_sum);
+                k_sum = fmaf(k, k, k_sum);
+            }
+            float qi = 1.0f / sqrtf(q_sum / (float)head_dim + epsilon), ki = 1.0f / sqrtf(k_sum / (float)head_dim + epsilon);
+            for (uint32_t d = 0; d < head_dim; d++) {
+                float q0 = h3o_bf16_to_f32(qkv[q_base + d]) * qi * h3o_bf16_to_f32(q_weight[d]);
+                float k0 = h3o_bf16_to_f32(qkv[k_base + d]) * ki * h3o_bf16_to_f32(k_weight[d]);
+                if (d < 2 * rope_half) {
+                    int low = d < rope_half;
+                    uint32_t pair = low ? d + rope_half : d - rope_half, first = low ? d : pair;
+                    float q1 = h3o_bf16_to_f32(qkv[q_base + pair]) * qi * h3o_bf16_to_f32(q_weight[pair]);
+                    float k1 = h3o_bf16_to_f32(qkv[k_base + pair]) * ki * h3o_bf16_to_f32(k_weight[pair]);
+                    float c = h3o_bf16_to_f32(rope_cos[(size_t)row * rope_half + first]);
+                    float s = h3o_bf16_to_f32(rope_sin[(size_t)row * rope_half + first]);
+                    float qa = q0 * c, qb = q1 * s, ka = k0 * c, kb = k1 * s;
+                    q0 = low ? qa - qb : qa + qb;
+                    k0 = low ? ka - kb : ka + kb;
+                }
+                size_t o = ((size_t)row * heads + head) * head_dim + d;
+                query[o] = h3o_f32_to_bf16(q0);
+                key[o] = h3o_f32_to_bf16(k0);
+                value[o] = qkv[v_base + d];
+            }
+        }
+}
+
 /* Everything after the linear result: bf16 round, then the reference's
  * separate bf16->bf16 operators in their call order. */
 static float *capture; /* when set, receives the fp32 linear result (+bias) of every output */

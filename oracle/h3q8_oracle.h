@@ -95,6 +95,13 @@ void h3o_gate_adaln_quantize(const uint16_t *residual, const uint16_t *branch, c
                              uint32_t rows, uint32_t padded_rows, uint32_t width, uint32_t slots, uint32_t gate_slot,
                              uint32_t shift_slot, uint32_t scale_slot, float epsilon);
 
+/* src/cuda/cuda_kernels.cuh:988-1045 with grouped = 1 (columns [head, q|k|v, head_dim]):
+ * per-head RMS norm of q and k (fmaf accumulation in dimension order), learned weight, rotary
+ * embedding on dimensions [0, 2*rope_half); outputs [row, head, head_dim]. */
+void h3o_grouped_qkv_rope(const uint16_t *qkv, const uint16_t *q_weight, const uint16_t *k_weight, const uint16_t *rope_cos,
+                          const uint16_t *rope_sin, uint16_t *query, uint16_t *key, uint16_t *value, uint32_t sequence,
+                          uint32_t heads, uint32_t head_dim, uint32_t rope_half, float epsilon);
+
 int h3o_threads(void);
 #ifdef __cplusplus
 }

@@ -633,6 +633,54 @@ def test_gate_adaln_quantize_feeds_the_int8_gemm(oracle, rows, width):
     gpu.free()
 
 
+@pytest.mark.parametrize("quant_mode", [0, 1, 2])
+@pytest.mark.parametrize("rows,heads,width,half", [(300, 4, 512, 48), (129, 3, 256, 64), (1000, 7, 384, 48)])
+def test_qkv_projection_with_norm_and_rope(oracle, quant_mode, rows, heads, width, half):
+    """h3_gpu_grouped_qkv_linear_rope_bf16 (src/gpu.h:665-683): the QKV projection with per-head RMS
+    norm + rotary embedding in its epilogue, grouped [head, q|k|v, 128] columns, head-major outputs.
+    Checked bit for bit against the two-call route (projection stored, then h3_gpu_grouped_qkv_rope_bf16,
+    formulas of src/cuda/cuda_kernels.cuh:988-1045) and within tolerance against the CPU oracle."""
+    dim, n = 128, heads * 3 * 128
+    rng = np.random.default_rng(rows)
+    bf = lambda a: synth.to_bf16(a.astype(np.float32)).reshape(a.shape)
+    x, wq, ws = operands(33, rows, n, width, 0)
+    q_norm, k_norm = bf(1 + 0.1 * rng.standard_normal(dim)), bf(1 + 0.1 * rng.standard_normal(dim))
+    angle = rng.uniform(0, 6.28, (rows, half))
+    cos, sin = bf(np.cos(angle)), bf(np.sin(angle))
+    gpu = h.Gpu()
+    if quant_mode:
+        gpu.quant_configure(quant_mode)
+        w = gpu.q8_from_host(wq, ws, 0)
+    else:
+        w = gpu.tensor_from_bf16(oracle.q8_dequant(wq, ws, 0))
+    tx, tqn, tkn, tc, ts = (gpu.tensor_from_bf16(a) for a in (x, q_norm, k_norm, cos, sin))
+    fused = [gpu.tensor_new_bf16(rows * heads * dim) for _ in range(3)]
+    chain = [gpu.tensor_new_bf16(rows * heads * dim) for _ in range(3)]
+    qkv_fused, qkv_chain = gpu.tensor_new_bf16(rows * n), gpu.tensor_new_bf16(rows * n)
+    before = h.library().h3q8_kernel_launches()
+    gpu.begin()
+    gpu.grouped_qkv_linear_rope_bf16(*fused, qkv_fused, tx, w, tqn, tkn, tc, ts, rows, width, heads, dim, half, 1e-5)
+    gpu.submit()
+    assert h.library().h3q8_kernel_launches() - before == (2 if quant_mode else 1)   # (conversion +) ONE fused kernel
+    gpu.begin()
+    gpu.linear_fused_bf16(qkv_chain, tx, w, None, None, None, rows, width, n, 0)
+    gpu.grouped_qkv_rope_bf16(*chain, qkv_chain, tqn, tkn, tc, ts, rows, heads, dim, half, 1e-5)
+    gpu.submit()
+    stored = qkv_fused.read()
+    assert (stored == qkv_chain.read()).all()
+    for a, b in zip(fused, chain):
+        assert (a.read() == b.read()).all()
+    want = oracle.grouped_qkv_rope(stored.reshape(rows, n), q_norm, k_norm, cos, sin, heads, dim, half, 1e-5)
+    for a, e in zip(fused, want):
+        check_bf16(a.read(), e.ravel())
+    # without a qkv tensor the fused route still works; shapes it cannot fuse need one
+    gpu.begin()
+    gpu.grouped_qkv_linear_rope_bf16(*chain, None, tx, w, tqn, tkn, tc, ts, rows, width, heads, dim, half, 1e-5)
+    gpu.submit()
+    assert (chain[0].read() == fused[0].read()).all()
+    gpu.free()
+
+
 # --------------------------------------------------------------------------- weight streaming
 def pinned_bytes(gpu, count):
     import ctypes
