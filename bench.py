@@ -31,7 +31,7 @@ sys.path.insert(0, ROOT)
 M_TOKENS, HIDDEN, FFN = 32400, 3072, 12288
 # The real MiniMax-H3 DiT projections (src/denoise/dit.c:31-46, 2424-2494): hidden 5376, heads 56 x 128, FFN 14336
 # SwiGLU, no bias, group-64 scales.  "s" = fc1 + SwiGLU (weight rows [gate | up]).  Measured with --case real_*.
-REAL_LAYERS = [("real_qkv", 5376, 21504, ""), ("real_attn_out", 7168, 5376, "gr"), ("real_fc1", 5376, 14336, "s"),
+REAL_LAYERS = [("real_qkv", 5376, 21504, ""), ("real_qkv_rope", 5376, 21504, "q"), ("real_attn_out", 7168, 5376, "gr"), ("real_fc1", 5376, 14336, "s"),
                ("real_fc2", 14336, 5376, "gr")]
 # name, K, N, epilogue
 LAYERS = [("qkv", HIDDEN, 3 * HIDDEN, ""), ("attn_out", HIDDEN, HIDDEN, "gr"),
@@ -447,10 +447,18 @@ def run_case(args, gpu, lib, stream, device_bf16):
     residual = device_bf16(rows, n, seed=3) if "r" in spec else None
     gate = device_bf16(1, n, 1.0, 0.1, seed=4) if "g" in spec else None
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if "q" in spec:   # QKV projection with per-head RMS norm + RoPE in the epilogue: 56 heads x 128, rotary half 48
+        heads, half = n // 384, 48
+        q, kk, v = (gpu.tensor_new_bf16(rows * heads * 128) for _ in range(3))
+        qn, kn = device_bf16(1, 128, 1.0, 0.1, seed=5), device_bf16(1, 128, 1.0, 0.1, seed=6)
+        cos, sin = device_bf16(rows, half, 0.0, 0.7, seed=7), device_bf16(rows, half, 0.0, 0.7, seed=8)
     gpu.begin()
     for i in range(args.warmup + args.steps):
         if i == args.warmup:
             start.record(stream)
+        if "q" in spec:
+            gpu.grouped_qkv_linear_rope_bf16(q, kk, v, None, x, weight, qn, kn, cos, sin, rows, k, heads, 128, half, 1e-5)
+            continue
         gpu.linear_fused_bf16(out, x, weight, None, gate, residual, rows, k, n, 2 if "s" in spec else 1 if "a" in spec else 0)
     stop.record(stream)
     gpu.submit()
