@@ -71,6 +71,13 @@ def library():
         "h3_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32]),
         "h3q8_q8_layout": (C.c_int, [u32, u32, u32, C.POINTER(sz), C.POINTER(sz)]),
         "h3q8_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32, u32]),
+        "h3q8_cache_open": (vp, [C.c_char_p, C.c_char_p, u64, u32, u32, u32, C.c_char_p, sz]),
+        "h3q8_cache_read": (C.c_int, [vp, vp, C.c_char_p, sz]),
+        "h3q8_cache_write": (C.c_int, [vp, vp, C.c_char_p, sz]),
+        "h3q8_cache_unchanged": (C.c_int, [vp, C.c_char_p, sz]),
+        "h3q8_cache_payload_bytes": (sz, [vp]),
+        "h3q8_cache_artifact": (C.c_char_p, [vp]),
+        "h3q8_cache_close": (None, [vp]),
         "h3q8_linear": (C.c_int, [C.POINTER(LinearDesc), vp]),
         "h3q8_linear_grouped": (C.c_int, [C.POINTER(LinearDesc), u32, vp]),
         "h3q8_linear_w8a8_static": (C.c_int, [C.POINTER(LinearDesc), vp, vp]),

@@ -20,6 +20,7 @@
 #include <new>
 #include <sys/stat.h>
 #include <unistd.h>
+#include <string>
 #include <vector>
 
 #include "h3q8.h"
@@ -61,6 +62,7 @@ struct h3_gpu {
     void *bounce[2] = {nullptr, nullptr};
     cudaEvent_t bounce_free[2] = {nullptr, nullptr};
     bool bounce_used[2] = {false, false};
+    std::string quant_cache;    /* directory of packed-weight artifacts; empty = no cache */
     uint64_t allocation_budget = 0; /* H3_CUDA_TEST_MEMORY_BUDGET: fail allocations beyond this many live bytes */
     std::mutex mutex, copy_mutex;
     std::vector<h3_gpu_tensor *> accessed;
@@ -585,11 +587,24 @@ extern "C" int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *g, uint32_t rows) {
     g->w8a16_scratch_rows = (int)rows;
     return 1;
 }
-extern "C" int h3_gpu_quant_configure(h3_gpu *g, int mode, const char *, uint64_t weights, uint64_t activations, int force_stream) {
+static int make_directories(const std::string &path) {
+    for (size_t i = 1; i <= path.size(); i++)
+        if (i == path.size() || path[i] == '/') {
+            std::string part = path.substr(0, i);
+            if (mkdir(part.c_str(), 0755) && errno != EEXIST) return 0;
+        }
+    struct stat st;
+    return !stat(path.c_str(), &st) && S_ISDIR(st.st_mode);
+}
+extern "C" int h3_gpu_quant_configure(h3_gpu *g, int mode, const char *cache, uint64_t weights, uint64_t activations, int force_stream) {
     if (!g) return 0;
     if (mode < 0 || mode > 2) return set_error(g, "quantisation mode must be 0 (off), 1 (W8A16) or 2 (W8A8)");
     if (!mode) return 1;
     if (g->quant_mode) return set_error(g, "quantized GPU context already configured");
+    if (cache && *cache) { /* src/cuda/cuda_quant.cpp:137-139: the cache directory is created at configure time */
+        if (!make_directories(cache)) return set_error(g, "cannot create quantization cache %s: %s", cache, strerror(errno));
+        g->quant_cache = cache;
+    }
     if (weights || activations) {
         int plan = h3_gpu_plan_weights(g, weights / 2, activations);
         if (plan < 0) return 0;
@@ -675,8 +690,39 @@ extern "C" h3_gpu_tensor *h3_gpu_quant_load(h3_gpu *g, const char *path, uint64_
         set_error(g, "quantized weight shape must be nonzero and a multiple of 128"); /* src/cuda/cuda_quant.cuh:293-295 */
         return nullptr;
     }
-    h3_gpu_tensor *t = q8_load_file(g, path, offset, rows, columns, g->group);
-    if (t) g->stats.quant_cache_misses++;
+    if (g->quant_cache.empty()) {
+        h3_gpu_tensor *t = q8_load_file(g, path, offset, rows, columns, g->group);
+        if (t) g->stats.quant_cache_misses++;
+        return t;
+    }
+    /* src/cuda/cuda_quant.cuh:292-333: artifact hit -> upload the packed bytes; miss -> pack on the
+     * device, read the blob back, publish it; the source is re-checked before either is accepted */
+    h3q8_cache *entry = h3q8_cache_open(g->quant_cache.c_str(), path, offset, rows, columns, g->group, g->error, sizeof g->error);
+    if (!entry) return nullptr;
+    const size_t bytes = h3q8_cache_payload_bytes(entry);
+    std::vector<unsigned char> payload;
+    try { payload.resize(bytes); } catch (const std::bad_alloc &) {
+        h3q8_cache_close(entry);
+        set_error(g, "host allocation failed for %zu-byte packed weight", bytes);
+        return nullptr;
+    }
+    int status = h3q8_cache_read(entry, payload.data(), g->error, sizeof g->error);
+    h3_gpu_tensor *t = nullptr;
+    if (status == 1) {
+        t = q8_blob(g, rows, columns, g->group);
+        if (t && !upload(t, 0, payload.data(), t->bytes < bytes ? t->bytes : bytes)) { h3_gpu_tensor_free(t); t = nullptr; }
+        if (t) { g->stats.quant_cache_hits++; g->stats.q8_weights++; g->stats.q8_storage_bytes += t->bytes; }
+    } else if (status == 0) {
+        t = q8_load_file(g, path, offset, rows, columns, g->group);
+        if (t) {
+            memset(payload.data(), 0, bytes);
+            if (!download(t, payload.data(), t->bytes < bytes ? t->bytes : bytes) ||
+                !h3q8_cache_write(entry, payload.data(), g->error, sizeof g->error)) { h3_gpu_tensor_free(t); t = nullptr; }
+            else g->stats.quant_cache_misses++;
+        }
+    }
+    if (t && !h3q8_cache_unchanged(entry, g->error, sizeof g->error)) { h3_gpu_tensor_free(t); t = nullptr; }
+    h3q8_cache_close(entry);
     return t;
 }
 extern "C" h3_gpu_tensor *h3q8_gpu_q8_from_host(h3_gpu *g, const int8_t *weights, const float *scales,

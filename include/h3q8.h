@@ -36,6 +36,21 @@ int h3q8_q8_layout(uint32_t rows, uint32_t columns, uint32_t group, size_t *scal
 int h3q8_q8_pack_rows(const uint16_t *source, int8_t *weights, float *scales,
                       uint32_t rows, uint32_t columns, uint32_t group);
 
+/* On-disk cache of packed q8 weights (host only), after src/weights/quant_cache.h:14-41:
+ * artifacts are keyed by source path + file identity + offset + shape + group + recipe
+ * (no weight bytes are hashed), writers hold a per-artifact flock from open to close,
+ * publishing is tmp + fsync + rename, a malformed artifact is an error and never a miss.
+ * read: 1 hit, 0 absent, -1 invalid; payload buffers have h3q8_cache_payload_bytes(). */
+typedef struct h3q8_cache h3q8_cache;
+h3q8_cache *h3q8_cache_open(const char *directory, const char *source, uint64_t offset, uint32_t rows, uint32_t columns,
+                            uint32_t group, char *error, size_t size);
+int h3q8_cache_read(h3q8_cache *cache, void *payload, char *error, size_t size);
+int h3q8_cache_write(h3q8_cache *cache, const void *payload, char *error, size_t size);
+int h3q8_cache_unchanged(const h3q8_cache *cache, char *error, size_t size);
+size_t h3q8_cache_payload_bytes(const h3q8_cache *cache);
+const char *h3q8_cache_artifact(const h3q8_cache *cache);
+void h3q8_cache_close(h3q8_cache *cache);
+
 /* =====================================================================
  * Layer 2: raw entry points (device pointers, caller-owned memory)
  * ===================================================================== */

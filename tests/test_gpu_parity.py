@@ -681,6 +681,40 @@ def test_qkv_projection_with_norm_and_rope(oracle, quant_mode, rows, heads, widt
     gpu.free()
 
 
+def test_quant_load_uses_the_artifact_cache(oracle, tmp_path):
+    """h3_gpu_quant_configure(cache) + h3_gpu_quant_load (src/cuda/cuda_quant.cuh:292-333): the first load
+    packs on the device and publishes an artifact, the second one is a cache hit with identical bytes."""
+    rows, cols, group = 256, 384, 128
+    w = synth.bf16_normal(90, 2, rows, cols, 0, 0.05).reshape(rows, cols)
+    source = tmp_path / "weights.bf16"
+    source.write_bytes(b"\0" * 64 + w.tobytes())
+    want_q, want_s = oracle.q8_pack_rows(w, group)
+    blobs = []
+    for attempt in range(2):
+        gpu = h.Gpu()
+        gpu.set_group(group)
+        gpu.quant_configure(1, cache=str(tmp_path / "cache" / "nested"))
+        t = gpu.quant_load(str(source), 64, rows, cols)
+        stats = gpu.stats()
+        assert (stats.quant_cache_misses, stats.quant_cache_hits) == ((1, 0) if attempt == 0 else (0, 1))
+        offset = (rows * cols + 15) & ~15
+        blob = t.read(offset + want_s.size * 4, dtype=2)
+        assert (blob[:rows * cols].reshape(rows, cols) == want_q).all()
+        assert (blob[offset:].view(np.float32).view(np.uint32) == want_s.ravel().view(np.uint32)).all()
+        blobs.append(blob)
+        x = synth.activations(91, 1, 130, cols).reshape(130, cols)
+        tx, out = gpu.tensor_from_bf16(x), gpu.tensor_new_bf16(130 * rows)
+        gpu.begin()
+        gpu.linear_bf16(out, tx, t, None, 130, cols, rows)
+        gpu.submit()
+        check_bf16(out.read().reshape(130, rows), oracle.linear(oracle.MODE_W8A16, x, want_q, want_s, group))
+        with pytest.raises(h.H3Error):
+            gpu.quant_load(str(source), 64, rows + 1, cols)        # shapes must be multiples of 128
+        gpu.free()
+    assert (blobs[0] == blobs[1]).all()
+    assert len([f for f in os.listdir(tmp_path / "cache" / "nested") if f.endswith(".h3q8")]) == 1
+
+
 # --------------------------------------------------------------------------- weight streaming
 def pinned_bytes(gpu, count):
     import ctypes
