@@ -47,7 +47,21 @@ class Stats(C.Structure):
                                            "native_scratch_bytes", "native_scratch_allocations",
                                            "native_scratch_reuses")] +
                 [("linear_seconds", C.c_double), ("linear_kernel_launches", C.c_uint64),
-                 ("conversion_kernel_launches", C.c_uint64)])
+                 ("conversion_kernel_launches", C.c_uint64)] +
+                [(n, C.c_uint64) for n in ("resident_weight_bytes", "resident_blocks", "active_weight_blocks",
+                                           "resident_block_mask")])
+
+
+class WeightOptions(C.Structure):
+    """h3_weight_options"""
+    _fields_ = [("mode", C.c_int), ("max_resident", C.c_int), ("capacity_limit", C.c_uint64), ("allocation_limit", C.c_uint64)]
+
+
+class WeightPlan(C.Structure):
+    """h3_weight_plan"""
+    _fields_ = [("options", WeightOptions)] + [(n, C.c_uint64) for n in (
+        "active_mask", "resident_mask", "free_bytes", "live_bytes", "reserve_bytes", "future_bytes", "block_bytes",
+        "resident_bytes", "slot_bytes")] + [("active_count", C.c_uint), ("resident_count", C.c_uint), ("effective_mode", C.c_int)]
 
 
 class Problem(C.Structure):
@@ -71,6 +85,14 @@ def library():
         "h3_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32]),
         "h3q8_q8_layout": (C.c_int, [u32, u32, u32, C.POINTER(sz), C.POINTER(sz)]),
         "h3q8_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32, u32]),
+        "h3_gpu_plan_bf16_weights": (C.c_int, [vp, u64, u64, u64, C.c_int, C.c_int, C.POINTER(WeightPlan)]),
+        "h3_gpu_weight_plan_compatible": (C.c_int, [vp, C.c_int]),
+        "h3_gpu_should_retry_streaming": (C.c_int, [vp]),
+        "h3_weight_mode_name": (C.c_char_p, [C.c_int]),
+        "h3_weight_options_read": (C.c_int, [C.POINTER(WeightOptions), C.c_int, C.c_char_p, sz]),
+        "h3_weight_options_equal": (C.c_int, [C.POINTER(WeightOptions), C.POINTER(WeightOptions)]),
+        "h3_weight_plan_build": (C.c_int, [C.POINTER(WeightPlan), WeightOptions, u64, u64, u64, u64, u64, u64, C.c_char_p, sz]),
+        "h3_weight_retry_cap": (C.c_int, [C.c_uint]),
         "h3q8_cache_open": (vp, [C.c_char_p, C.c_char_p, u64, u32, u32, u32, C.c_char_p, sz]),
         "h3q8_cache_read": (C.c_int, [vp, vp, C.c_char_p, sz]),
         "h3q8_cache_write": (C.c_int, [vp, vp, C.c_char_p, sz]),
@@ -270,6 +292,13 @@ class Gpu:
 
     def cancel(self):
         library().h3_gpu_cancel(self.handle)
+
+    def plan_bf16_weights(self, active_mask, block_bytes, future_bytes=0, force_stream=0, retry_cap=-1):
+        """h3_gpu_plan_bf16_weights: returns the accepted h3_weight_plan or raises."""
+        plan = WeightPlan()
+        self._check(library().h3_gpu_plan_bf16_weights(self.handle, active_mask, block_bytes, future_bytes, force_stream,
+                                                       retry_cap, C.byref(plan)))
+        return plan
 
     def stats(self):
         s = Stats()

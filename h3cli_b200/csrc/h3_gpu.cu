@@ -64,6 +64,9 @@ struct h3_gpu {
     bool bounce_used[2] = {false, false};
     std::string quant_cache;    /* directory of packed-weight artifacts; empty = no cache */
     uint64_t allocation_budget = 0; /* H3_CUDA_TEST_MEMORY_BUDGET: fail allocations beyond this many live bytes */
+    h3_weight_options weight_options = {H3_WEIGHTS_AUTO, -1, 0, 0};
+    h3_weight_plan weight_plan = {};
+    bool allocation_failed = false; /* an allocation ran out of memory: an automatic plan may retry with fewer resident blocks */
     std::mutex mutex, copy_mutex;
     std::vector<h3_gpu_tensor *> accessed;
     /* profiling: event pairs per kernel, category 0 = GEMM, 7 = conversion */
@@ -204,8 +207,11 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
     h3_gpu *g = new (std::nothrow) h3_gpu;
     if (!g) return refuse("out of host memory");
     g->device = device;
-    const char *budget = getenv("H3_CUDA_TEST_MEMORY_BUDGET"); /* src/weights/residency.c:31-32 */
-    if (budget && *budget) g->allocation_budget = strtoull(budget, nullptr, 10);
+    {   /* src/cuda/gpu_cuda.cu:305: residency options are read once, when the context is made */
+        char why[160] = {0};
+        if (!h3_weight_options_read(&g->weight_options, 0, why, sizeof why)) { delete g; return refuse(why); }
+        g->allocation_budget = g->weight_options.allocation_limit;
+    }
     g->profiling = getenv("H3_PROFILE") != nullptr;
     const char *policy = getenv("H3Q8_W8A16_SCRATCH_ROWS");
     /* measured on B200 (N, K in 3072..12288, M from 16 to 32400): dequantise-then-GEMM is faster than main-loop
@@ -309,6 +315,7 @@ extern "C" h3_gpu_tensor *h3_gpu_tensor_alloc(h3_gpu *g, size_t elements, h3_gpu
     if (g->allocation_budget && g->stats.live_bytes + bytes > g->allocation_budget) {
         set_error(g, "CUDA allocation: out of memory (test budget %llu, live %llu, requested %zu)",
                   (unsigned long long)g->allocation_budget, (unsigned long long)g->stats.live_bytes, bytes);
+        g->allocation_failed = true;
         return nullptr;
     }
     h3_gpu_tensor *t = new (std::nothrow) h3_gpu_tensor;
@@ -566,6 +573,50 @@ extern "C" int h3_gpu_plan_weights(h3_gpu *g, uint64_t weights, uint64_t activat
     return -1;
 }
 extern "C" int h3_gpu_release_weight_cache(h3_gpu *g) { return g != nullptr; }
+
+/* src/cuda/gpu_cuda.cu:559-578: plan which blocks stay resident from the device's free memory,
+ * the context's live bytes and a reserve of max(1 GiB, 10 % of the device). */
+extern "C" int h3_gpu_plan_bf16_weights(h3_gpu *g, uint64_t active_mask, uint64_t block_bytes, uint64_t future_bytes,
+                                        int force_stream, int retry_cap, h3_weight_plan *plan) {
+    if (!selected(g) || !plan) return 0;
+    size_t available = 0, total = 0;
+    if (!checked(g, cudaMemGetInfo(&available, &total), "weight planner")) return 0;
+    h3_weight_options options = g->weight_options;
+    if (force_stream && options.mode == H3_WEIGHTS_RESIDENT)
+        return set_error(g, "--ssd-streaming conflicts with CUDA resident weight mode");
+    if (force_stream) options.mode = H3_WEIGHTS_STREAM;
+    if (retry_cap >= 0 && (options.max_resident < 0 || retry_cap < options.max_resident)) options.max_resident = retry_cap;
+    uint64_t reserve = total / 10 > (1ull << 30) ? total / 10 : (1ull << 30);
+    char why[256] = {0};
+    if (!h3_weight_plan_build(plan, options, active_mask, block_bytes, available, g->stats.live_bytes, future_bytes, reserve,
+                              why, sizeof why))
+        return set_error(g, "%s", why);
+    g->weight_plan = *plan;
+    g->allocation_failed = false;
+    g->stats.resident_weight_bytes = plan->resident_bytes;
+    g->stats.stream_slot_bytes = plan->slot_bytes;
+    g->stats.resident_blocks = plan->resident_count;
+    g->stats.active_weight_blocks = plan->active_count;
+    g->stats.resident_block_mask = plan->resident_mask;
+    return 1;
+}
+extern "C" int h3_gpu_should_retry_streaming(const h3_gpu *g) {
+    return g && g->allocation_failed && g->weight_options.mode == H3_WEIGHTS_AUTO;
+}
+/* src/cuda/gpu_cuda.cu:579-594: may a context made under earlier options be kept for this request? */
+extern "C" int h3_gpu_weight_plan_compatible(h3_gpu *g, int force_stream) {
+    if (!g) return 0;
+    h3_weight_options requested, old = g->weight_options;
+    char why[160];
+    if (!h3_weight_options_read(&requested, force_stream, why, sizeof why)) return 0;
+    if (force_stream) { requested.mode = H3_WEIGHTS_STREAM; old.mode = H3_WEIGHTS_STREAM; }
+    if (!h3_weight_options_equal(&requested, &old)) return 0;
+    if (old.mode == H3_WEIGHTS_AUTO && g->weight_plan.active_count && g->weight_plan.resident_count < g->weight_plan.active_count)
+        return 0; /* a constrained automatic plan reconsiders capacity on every request */
+    size_t free_bytes = 0, total = 0;
+    return selected(g) && cudaMemGetInfo(&free_bytes, &total) == cudaSuccess &&
+           free_bytes >= (total / 10 > (1ull << 30) ? total / 10 : (1ull << 30));
+}
 
 /* -------------------------------------------------------- quantised weights */
 extern "C" int h3q8_gpu_set_group(h3_gpu *g, uint32_t group) {

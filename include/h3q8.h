@@ -36,6 +36,30 @@ int h3q8_q8_layout(uint32_t rows, uint32_t columns, uint32_t group, size_t *scal
 int h3q8_q8_pack_rows(const uint16_t *source, int8_t *weights, float *scales,
                       uint32_t rows, uint32_t columns, uint32_t group);
 
+/* Weight residency planning (host only) -- src/weights/residency.h:7-33.  The plan says which of
+ * the (at most 50) active blocks stay resident and whether two streaming slots are needed. */
+enum { H3_WEIGHTS_AUTO, H3_WEIGHTS_RESIDENT, H3_WEIGHTS_STREAM };
+typedef struct {
+    int mode;
+    int max_resident;          /* -1 = uncapped; test-only, never increases capacity */
+    uint64_t capacity_limit;   /* test-only total capacity; 0 = uncapped             */
+    uint64_t allocation_limit; /* allocation fault injection, not a planner input    */
+} h3_weight_options;
+typedef struct {
+    h3_weight_options options;
+    uint64_t active_mask, resident_mask;
+    uint64_t free_bytes, live_bytes, reserve_bytes, future_bytes;
+    uint64_t block_bytes, resident_bytes, slot_bytes;
+    unsigned active_count, resident_count;
+    int effective_mode;        /* auto here means partially resident */
+} h3_weight_plan;
+const char *h3_weight_mode_name(int mode);
+int h3_weight_options_read(h3_weight_options *out, int force_stream, char *error, size_t size);
+int h3_weight_options_equal(const h3_weight_options *a, const h3_weight_options *b);
+int h3_weight_plan_build(h3_weight_plan *out, h3_weight_options options, uint64_t active_mask, uint64_t block_bytes,
+                         uint64_t available, uint64_t live, uint64_t future, uint64_t reserve, char *error, size_t size);
+int h3_weight_retry_cap(unsigned count);
+
 /* On-disk cache of packed q8 weights (host only), after src/weights/quant_cache.h:14-41:
  * artifacts are keyed by source path + file identity + offset + shape + group + recipe
  * (no weight bytes are hashed), writers hold a per-artifact flock from open to close,
@@ -188,6 +212,8 @@ typedef struct {
      * the quantise / dequantise kernels, harvested at submit while profiling is on. */
     double linear_seconds;
     uint64_t linear_kernel_launches, conversion_kernel_launches;
+    /* last accepted residency plan (src/gpu.h:99-142, same names) */
+    uint64_t resident_weight_bytes, resident_blocks, active_weight_blocks, resident_block_mask;
 } h3_gpu_stats;
 
 /* Context -- src/gpu.h:144-145, 180-182, 203, 207, 267-268 */
@@ -239,6 +265,12 @@ int h3_gpu_tensor_stream_file_bf16(h3_gpu_tensor *tensor, const char *path, uint
                                    size_t elements, char *error, size_t error_size);
 /* Planning -- src/gpu.h:34-36, 48-50: 0 resident, 1 streamed, -1 insufficient. */
 int h3_gpu_plan_weights(h3_gpu *gpu, uint64_t weights, uint64_t activations);
+/* src/gpu.h:38-40, 205: per-block residency plan from the device's free memory (reserve = max(1 GiB,
+ * 10 % of the device)); retry_cap >= 0 lowers the resident-block ceiling after an out-of-memory retry. */
+int h3_gpu_plan_bf16_weights(h3_gpu *gpu, uint64_t active_mask, uint64_t block_bytes, uint64_t future_bytes,
+                             int force_stream, int retry_cap, h3_weight_plan *plan);
+int h3_gpu_weight_plan_compatible(h3_gpu *gpu, int force_stream);
+int h3_gpu_should_retry_streaming(const h3_gpu *gpu);
 int h3_gpu_release_weight_cache(h3_gpu *gpu);
 
 /* Linear -- src/gpu.h:501-505.  A weight that carries a q8 descriptor (made by

@@ -715,6 +715,39 @@ def test_quant_load_uses_the_artifact_cache(oracle, tmp_path):
     assert len([f for f in os.listdir(tmp_path / "cache" / "nested") if f.endswith(".h3q8")]) == 1
 
 
+def test_residency_plan_on_the_device(monkeypatch):
+    """h3_gpu_plan_bf16_weights (src/cuda/gpu_cuda.cu:559-578): free memory and reserve come from the device;
+    the test-only block ceiling and capacity turn the same request into partial and streamed plans."""
+    block, mask = 64 << 20, (1 << 48) - 1
+    gpu = h.Gpu()
+    plan = gpu.plan_bf16_weights(mask, block, future_bytes=1 << 30)
+    stats = gpu.stats()
+    assert plan.effective_mode == 1 and plan.resident_count == 48 and plan.slot_bytes == 0
+    assert (stats.resident_blocks, stats.active_weight_blocks, stats.resident_block_mask) == (48, 48, mask)
+    assert stats.resident_weight_bytes == 48 * block and plan.reserve_bytes >= 1 << 30
+    partial = gpu.plan_bf16_weights(mask, block, retry_cap=5)
+    assert partial.effective_mode == 0 and partial.resident_mask == 0x1F and partial.slot_bytes == 2 * block
+    streamed = gpu.plan_bf16_weights(mask, block, force_stream=1)
+    assert streamed.effective_mode == 2 and streamed.resident_count == 0 and gpu.stats().stream_slot_bytes == 2 * block
+    assert not h.library().h3_gpu_should_retry_streaming(gpu.handle)
+    with pytest.raises(h.H3Error, match="two-slot streaming"):
+        gpu.plan_bf16_weights(mask, 1 << 40)
+    assert h.library().h3_gpu_weight_plan_compatible(gpu.handle, 0) == 0   # last accepted plan was constrained
+    gpu.free()
+    monkeypatch.setenv("H3_TEST_CUDA_RESIDENT_BLOCKS", "3")
+    monkeypatch.setenv("H3_TEST_CUDA_CAPACITY_BYTES", str(40 * block))
+    gpu = h.Gpu()
+    plan = gpu.plan_bf16_weights(mask, block)
+    assert plan.resident_count == 3 and plan.free_bytes <= 40 * block and plan.options.max_resident == 3
+    assert h.library().h3_gpu_weight_plan_compatible(gpu.handle, 0) == 0
+    monkeypatch.setenv("H3_TEST_CUDA_RESIDENT_BLOCKS", "4")
+    assert h.library().h3_gpu_weight_plan_compatible(gpu.handle, 0) == 0   # options differ from the context's
+    gpu.free()
+    monkeypatch.setenv("H3_CUDA_WEIGHT_MODE", "bogus")
+    with pytest.raises(h.H3Error, match="auto, resident, or stream"):
+        h.Gpu()
+
+
 # --------------------------------------------------------------------------- weight streaming
 def pinned_bytes(gpu, count):
     import ctypes
