@@ -144,6 +144,7 @@ def library():
         "h3q8_gpu_set_profiling": (C.c_int, [vp, C.c_int]),
         "h3q8_gpu_tensor_upload_async": (C.c_int, [vp, vp, sz]),
         "h3q8_gpu_tensor_download_async": (C.c_int, [vp, vp, sz]),
+        "h3q8_gpu_tensor_wait": (C.c_int, [vp]),
         "h3q8_gpu_q8_from_host": (vp, [vp, vp, vp, u32, u32, u32]),
         "h3q8_gpu_weight_stream_create": (vp, [vp, sz, u32]),
         "h3q8_gpu_weight_stream_prefetch": (C.c_int, [vp, vp, sz]),
@@ -214,6 +215,9 @@ class Tensor:
 
     def download_async(self, host_pointer, nbytes):
         self.gpu._check(library().h3q8_gpu_tensor_download_async(self.handle, host_pointer, nbytes))
+
+    def wait(self):
+        self.gpu._check(library().h3q8_gpu_tensor_wait(self.handle))
 
     def free(self):
         if self.handle:

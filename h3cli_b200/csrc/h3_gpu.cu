@@ -48,7 +48,8 @@ struct h3_gpu_event { h3_gpu *owner = nullptr; cudaEvent_t value = nullptr; bool
 
 struct h3_gpu {
     int device = 0;
-    cudaStream_t compute = nullptr, copy = nullptr;
+    cudaStream_t compute = nullptr, copy = nullptr; /* copy: host to device and weight streaming */
+    cudaStream_t copy_out = nullptr;                /* device to host, so that both PCIe directions run at once */
     bool active = false, deferred_error = false;
     char error[1024] = {0};
     h3_gpu_stats stats = {};
@@ -220,6 +221,7 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
     bool ok = cudaSetDevice(device) == cudaSuccess &&
               cudaStreamCreateWithFlags(&g->compute, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&g->copy, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&g->copy_out, cudaStreamNonBlocking) == cudaSuccess &&
               cudaMalloc(&g->flags, 2 * sizeof(uint32_t)) == cudaSuccess &&
               cudaMemset(g->flags, 0, 2 * sizeof(uint32_t)) == cudaSuccess;
     if (!ok) {
@@ -236,6 +238,7 @@ extern "C" void h3_gpu_cancel(h3_gpu *g) {
     cudaSetDevice(g->device);
     cudaStreamSynchronize(g->compute);
     cudaStreamSynchronize(g->copy);
+    cudaStreamSynchronize(g->copy_out);
     cudaGetLastError();
     if (g->flags) cudaMemset(g->flags, 0, 2 * sizeof(uint32_t));
     g->accessed.clear();
@@ -256,6 +259,7 @@ extern "C" void h3_gpu_free(h3_gpu *g) {
     if (g->flags) cudaFree(g->flags);
     if (g->compute) cudaStreamDestroy(g->compute);
     if (g->copy) cudaStreamDestroy(g->copy);
+    if (g->copy_out) cudaStreamDestroy(g->copy_out);
     delete g;
 }
 
@@ -304,7 +308,8 @@ extern "C" int h3_gpu_submit(h3_gpu *g) {
 extern "C" int h3_gpu_synchronize(h3_gpu *g) {
     if (!selected(g)) return 0;
     return checked(g, cudaStreamSynchronize(g->compute), "synchronize") &&
-           checked(g, cudaStreamSynchronize(g->copy), "synchronize copy stream");
+           checked(g, cudaStreamSynchronize(g->copy), "synchronize copy stream") &&
+           checked(g, cudaStreamSynchronize(g->copy_out), "synchronize download stream");
 }
 
 /* ------------------------------------------------------------------ tensors */
@@ -347,7 +352,7 @@ extern "C" void h3_gpu_tensor_free(h3_gpu_tensor *t) {
         std::lock_guard<std::mutex> lock(g->mutex);
         for (auto it = g->accessed.begin(); it != g->accessed.end();) it = *it == t ? g->accessed.erase(it) : it + 1;
         if (t->borrowed) { /* nothing to release */ }
-        else if (t->storage == H3_GPU_HOST_PINNED) { cudaStreamSynchronize(g->compute); cudaStreamSynchronize(g->copy); cudaFreeHost(t->data); }
+        else if (t->storage == H3_GPU_HOST_PINNED) { cudaStreamSynchronize(g->compute); cudaStreamSynchronize(g->copy); cudaStreamSynchronize(g->copy_out); cudaFreeHost(t->data); }
         else { if (t->ready_recorded) cudaEventSynchronize(t->ready); cudaFree(t->data); }
         if (!t->borrowed) g->stats.live_bytes -= t->bytes;
         if (!t->borrowed && t->storage == H3_GPU_HOST_PINNED) g->stats.pinned_bytes -= t->bytes;
@@ -361,6 +366,7 @@ extern "C" void *h3_gpu_tensor_contents(h3_gpu_tensor *t) {
     cudaSetDevice(t->owner->device);
     cudaStreamSynchronize(t->owner->compute);
     cudaStreamSynchronize(t->owner->copy);
+    cudaStreamSynchronize(t->owner->copy_out);
     return t->data;
 }
 extern "C" size_t h3_gpu_tensor_elements(const h3_gpu_tensor *t) { return t ? t->elements : 0; }
@@ -431,6 +437,7 @@ extern "C" int h3q8_gpu_tensor_upload_async(h3_gpu_tensor *t, const void *host, 
     std::lock_guard<std::mutex> lock(g->copy_mutex);
     if (!selected(g)) return 0;
     if (t->release_recorded) cudaStreamWaitEvent(g->copy, t->released, 0);
+    if (t->ready_recorded) cudaStreamWaitEvent(g->copy, t->ready, 0); /* an earlier download of this tensor */
     if (!checked(g, cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, g->copy), "asynchronous host to device copy", bytes) ||
         !checked(g, cudaEventRecord(t->ready, g->copy), "tensor ready event")) return 0;
     t->ready_recorded = true;
@@ -443,12 +450,21 @@ extern "C" int h3q8_gpu_tensor_download_async(h3_gpu_tensor *t, void *host, size
     if (bytes > t->bytes) return set_error(g, "tensor read out of range");
     std::lock_guard<std::mutex> lock(g->copy_mutex);
     if (!selected(g)) return 0;
-    if (t->release_recorded) cudaStreamWaitEvent(g->copy, t->released, 0);
-    if (!checked(g, cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, g->copy), "asynchronous device to host copy", bytes) ||
-        !checked(g, cudaEventRecord(t->ready, g->copy), "tensor ready event")) return 0;
+    if (t->release_recorded) cudaStreamWaitEvent(g->copy_out, t->released, 0);
+    if (t->ready_recorded) cudaStreamWaitEvent(g->copy_out, t->ready, 0); /* an earlier upload of this tensor */
+    if (!checked(g, cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, g->copy_out), "asynchronous device to host copy", bytes) ||
+        !checked(g, cudaEventRecord(t->ready, g->copy_out), "tensor ready event")) return 0;
     t->ready_recorded = true; /* the next operator that writes the tensor waits for this copy */
     g->stats.d2h_bytes += bytes;
     return 1;
+}
+/* Host-side wait for the tensor's last asynchronous copy only: nothing else is drained, so later
+ * uploads and operators already queued keep running. */
+extern "C" int h3q8_gpu_tensor_wait(h3_gpu_tensor *t) {
+    if (!t) return 0;
+    h3_gpu *g = t->owner;
+    if (!selected(g)) return 0;
+    return !t->ready_recorded || checked(g, cudaEventSynchronize(t->ready), "tensor copy wait");
 }
 
 extern "C" h3_gpu_event *h3_gpu_event_new(h3_gpu *g) {

@@ -293,13 +293,15 @@ int h3q8_gpu_set_group(h3_gpu *gpu, uint32_t group);
  * tensors with the raw h3q8_* entry points. */
 void *h3q8_gpu_tensor_device_pointer(const h3_gpu_tensor *tensor);
 void *h3q8_gpu_compute_stream(h3_gpu *gpu);
-/* Asynchronous host <-> tensor copies on the context's copy stream, ordered against the
+/* Asynchronous host <-> tensor copies on the context's two copy streams (uploads and downloads
+ * have one each, so both PCIe directions run at once), ordered against the
  * compute stream by the tensor's own events (the mechanism of the reference's streamed
  * tensors, src/cuda/gpu_cuda.cu:223-251): an upload waits until compute has released the
  * tensor and marks it ready, operators wait for ready; a download waits until the last
  * operator that touched the tensor is done, and later operators wait for the download.
- * Host memory should be pinned.  h3_gpu_synchronize() waits for both streams. */
+ * Host memory should be pinned.  h3_gpu_synchronize() waits for all three streams. */
 int h3q8_gpu_tensor_upload_async(h3_gpu_tensor *tensor, const void *host, size_t bytes);
+int h3q8_gpu_tensor_wait(h3_gpu_tensor *tensor); /* host waits for the tensor's last asynchronous copy only */
 int h3q8_gpu_tensor_download_async(h3_gpu_tensor *tensor, void *host, size_t bytes);
 /* Rows at or above which a W8A16 linear first dequantises the weight into
  * context scratch and runs the bf16 GEMM (the reference's policy 0,

@@ -734,11 +734,17 @@ def test_residency_plan_on_the_device(monkeypatch):
         gpu.plan_bf16_weights(mask, 1 << 40)
     assert h.library().h3_gpu_weight_plan_compatible(gpu.handle, 0) == 0   # last accepted plan was constrained
     gpu.free()
+    capacity = plan.reserve_bytes + 40 * block   # the visible capacity has to cover the reserve first
     monkeypatch.setenv("H3_TEST_CUDA_RESIDENT_BLOCKS", "3")
-    monkeypatch.setenv("H3_TEST_CUDA_CAPACITY_BYTES", str(40 * block))
+    monkeypatch.setenv("H3_TEST_CUDA_CAPACITY_BYTES", str(capacity))
     gpu = h.Gpu()
     plan = gpu.plan_bf16_weights(mask, block)
-    assert plan.resident_count == 3 and plan.free_bytes <= 40 * block and plan.options.max_resident == 3
+    assert plan.resident_count == 3 and plan.free_bytes <= capacity and plan.options.max_resident == 3
+    monkeypatch.setenv("H3_TEST_CUDA_RESIDENT_BLOCKS", "50")
+    roomy = h.Gpu()
+    assert roomy.plan_bf16_weights(mask, block).resident_count in (37, 38)   # 40 blocks of budget minus two slots (minus live bytes)
+    roomy.free()
+    monkeypatch.setenv("H3_TEST_CUDA_RESIDENT_BLOCKS", "3")
     assert h.library().h3_gpu_weight_plan_compatible(gpu.handle, 0) == 0
     monkeypatch.setenv("H3_TEST_CUDA_RESIDENT_BLOCKS", "4")
     assert h.library().h3_gpu_weight_plan_compatible(gpu.handle, 0) == 0   # options differ from the context's
