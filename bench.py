@@ -160,6 +160,8 @@ def main():
                          "(config 5): M=219,600 rows sharded over the GPUs, --layers layers of group-128 weights streamed "
                          "from pinned host memory through two device slots")
     ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--e2e-depth", type=int, default=4, help="end-to-end steps in flight (buffer sets)")
+    ap.add_argument("--e2e-slices", type=int, default=1, help="row slices per end-to-end step (copy/compute overlap inside a step)")
     ap.add_argument("--mode", default="w8a16", choices=["w8a16", "w8a8"],
                     help="w8a16 (default, BASELINE config 2) or the W8A8 variant: per-token int8 activations, int8 MMAs")
     args = ap.parse_args()
@@ -279,13 +281,14 @@ def main():
     lib.h3_gpu_tensor_read_bf16(x.handle, host_x.data_ptr(), M_TOKENS * HIDDEN)
     for t in list(outputs.values()) + [hidden, residual]:
         t.free()                                      # the resident-run tensors are no longer needed
-    # Two sets of slice tensors and two host output buffers: step i+1 is enqueued (its uploads start at once on
-    # the upload stream) before the host waits for step i's output, so a stream of independent batches keeps
-    # the upload stream, the compute stream and the download stream busy at the same time.
-    E2E_CHUNKS = 4
-    host_out = [host_y, torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory()]
+    # DEPTH sets of slice tensors and host output buffers: steps i+1 .. i+DEPTH-1 are enqueued (their uploads start
+    # at once on the upload stream) before the host waits for step i's output, so a stream of independent batches
+    # keeps the upload stream, the compute stream and the download stream busy at the same time.
+    E2E_CHUNKS = args.e2e_slices
+    DEPTH = max(1, args.e2e_depth)
+    host_out = [host_y] + [torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory() for _ in range(DEPTH - 1)]
     sets = []
-    for _ in range(2):
+    for _ in range(DEPTH):
         slices = []
         for begin, end in sharding.all_ranges(M_TOKENS, E2E_CHUNKS):
             rows = end - begin
@@ -295,7 +298,7 @@ def main():
         sets.append(slices)
 
     def enqueue_e2e(index):
-        slices, out = sets[index % 2], host_out[index % 2]
+        slices, out = sets[index % DEPTH], host_out[index % DEPTH]
         for c in slices:
             c["x"].upload_async(host_x.data_ptr() + c["offset"], c["rows"] * HIDDEN * 2)
         for c in slices:
@@ -308,11 +311,11 @@ def main():
             c["y"].download_async(out.data_ptr() + c["offset"], rows * HIDDEN * 2)
 
     def finish_e2e(index):
-        for c in sets[index % 2]:
+        for c in sets[index % DEPTH]:
             c["y"].wait()                             # this step's block output is in host memory
 
     def run_e2e(steps, depth):
-        """depth 1: each step ends before the next is enqueued; depth 2: one step in flight behind the current one."""
+        """depth 1: each step ends before the next is enqueued; depth d: d-1 steps in flight behind the current one."""
         begin = time.perf_counter()
         gpu.begin()                                   # one command scope; h3_gpu_continue commits each slice
         for i in range(steps):
@@ -336,7 +339,7 @@ def main():
         return float(t.item())
 
     e_serial = timed_e2e(1)
-    e_seconds = timed_e2e(2)
+    e_seconds = timed_e2e(DEPTH)
     e2e_value = world * FLOP_PER_STEP * args.steps / e_seconds / 1e12
 
     if rank == 0:
@@ -355,10 +358,10 @@ def main():
                     "ms_per_step": e_seconds / args.steps * 1e3,
                     "ms_per_step_one_at_a_time": e_serial / args.steps * 1e3,
                     "path": "pinned host x -> h3q8_gpu_tensor_upload_async -> 4 x h3_gpu_linear_fused_bf16 per row slice (chained as "
-                            "the DiT block calls them, 4 row slices so copies overlap compute) -> h3q8_gpu_tensor_download_async -> "
-                            "pinned host y -> h3q8_gpu_tensor_wait; steps are independent batches, double buffered: step i+1 is "
-                            "enqueued before the host waits for step i's output (ms_per_step_one_at_a_time: no step in flight "
-                            "behind the current one); host wall clock over all steps, max over ranks"},
+                            "the DiT block calls them, " + str(E2E_CHUNKS) + " row slices so copies overlap compute) -> h3q8_gpu_tensor_download_async -> "
+                            "pinned host y -> h3q8_gpu_tensor_wait; steps are independent batches with " + str(DEPTH) + " buffer sets: "
+                            "later steps are enqueued before the host waits for step i's output (ms_per_step_one_at_a_time: no "
+                            "step in flight behind the current one); host wall clock over all steps, max over ranks"},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel<bf16> (256x256 tile per CTA pair) after q8_dequant_kernel" if args.mode == "w8a16"
