@@ -8,6 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libh3q8.so")
+PREPARE = os.path.join(HERE, "h3q8_prepare")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-pthread"]
 
@@ -49,6 +50,9 @@ def build(force=False, verbose=False):
              os.path.join(CSRC, unit), "-o", obj])
         objects.append(obj)
     run([_nvcc(), "-shared", "-o", LIB, *objects, "-lm"])
+    # the artifact preparation tool links the library it sits beside
+    run(["gcc", "-O2", "-std=c11", "-I", include, os.path.join(CSRC, "q8_prepare.c"), "-o", PREPARE, "-L", HERE, "-lh3q8",
+         "-Wl,-rpath,$ORIGIN"])
     return LIB
 
 

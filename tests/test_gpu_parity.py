@@ -715,6 +715,37 @@ def test_quant_load_uses_the_artifact_cache(oracle, tmp_path):
     assert len([f for f in os.listdir(tmp_path / "cache" / "nested") if f.endswith(".h3q8")]) == 1
 
 
+def test_prepare_tool_builds_every_artifact(oracle, tmp_path):
+    """h3q8_prepare (the job of src/weights/quant_prepare.c): walks a safetensors directory, publishes one
+    artifact per DiT projection, and a second run finds all of them; a context then loads from the cache."""
+    import subprocess
+    from h3cli_b200 import build
+    from safetensors_fixture import write_directory
+    model, cache = tmp_path / "transformer", tmp_path / "cache"
+    model.mkdir()
+    written = write_directory(model)
+    first = subprocess.run([build.PREPARE, "w8a16", str(model), str(cache), "64"], capture_output=True, text=True)
+    assert first.returncode == 0, first.stderr
+    assert "8 weights, 8 prepared, 0 already cached" in first.stderr
+    assert len([f for f in os.listdir(cache) if f.endswith(".h3q8")]) == 8
+    second = subprocess.run([build.PREPARE, "w8a16", str(model), str(cache), "64"], capture_output=True, text=True)
+    assert second.returncode == 0 and "8 weights, 0 prepared, 8 already cached" in second.stderr
+    gpu = h.Gpu()
+    gpu.set_group(64)
+    gpu.quant_configure(1, cache=str(cache))
+    for name, (path, offset, w) in sorted(written.items())[:3]:
+        rows, cols = w.shape
+        t = gpu.quant_load(path, offset, rows, cols)
+        want_q, want_s = oracle.q8_pack_rows(w, 64)
+        blob = t.read(((rows * cols + 15) & ~15) + want_s.size * 4, dtype=2)
+        assert (blob[:rows * cols].reshape(rows, cols) == want_q).all()
+        assert (blob[(rows * cols + 15) & ~15:].view(np.float32).view(np.uint32) == want_s.ravel().view(np.uint32)).all()
+    assert gpu.stats().quant_cache_hits == 3 and gpu.stats().quant_cache_misses == 0
+    gpu.free()
+    other = subprocess.run([build.PREPARE, "w8a16", str(model), str(cache), "128"], capture_output=True, text=True)
+    assert other.returncode == 0 and "8 prepared" in other.stderr      # another scale group is another artifact
+
+
 def test_residency_plan_on_the_device(monkeypatch):
     """h3_gpu_plan_bf16_weights (src/cuda/gpu_cuda.cu:559-578): free memory and reserve come from the device;
     the test-only block ceiling and capacity turn the same request into partial and streamed plans."""
