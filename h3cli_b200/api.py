@@ -49,7 +49,8 @@ class Stats(C.Structure):
                 [("linear_seconds", C.c_double), ("linear_kernel_launches", C.c_uint64),
                  ("conversion_kernel_launches", C.c_uint64)] +
                 [(n, C.c_uint64) for n in ("resident_weight_bytes", "resident_blocks", "active_weight_blocks",
-                                           "resident_block_mask")])
+                                           "resident_block_mask")] +
+                [("h2d_seconds", C.c_double), ("d2h_seconds", C.c_double)])
 
 
 class WeightOptions(C.Structure):
@@ -85,6 +86,8 @@ def library():
         "h3_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32]),
         "h3q8_q8_layout": (C.c_int, [u32, u32, u32, C.POINTER(sz), C.POINTER(sz)]),
         "h3q8_q8_pack_rows": (C.c_int, [vp, vp, vp, u32, u32, u32]),
+        "h3_gpu_profile_set_label": (None, [vp, C.c_char_p]),
+        "h3_gpu_profile_mark": (None, [vp, C.c_char_p]),
         "h3_gpu_plan_bf16_weights": (C.c_int, [vp, u64, u64, u64, C.c_int, C.c_int, C.POINTER(WeightPlan)]),
         "h3_gpu_weight_plan_compatible": (C.c_int, [vp, C.c_int]),
         "h3_gpu_should_retry_streaming": (C.c_int, [vp]),

@@ -75,12 +75,18 @@ struct h3_gpu {
     struct Span { cudaEvent_t start, stop; int category; };
     std::vector<Span> spans;
     std::vector<cudaEvent_t> spare_events;
+    std::mutex span_mutex;      /* copies may be issued from another thread than the operators */
+    std::string label = "DiT";  /* names the context in profile reports */
+    double created = 0;
 };
 
-/* Brackets kernel launches on the compute stream with an event pair while
- * profiling; the pairs are read back after the next synchronising submit. */
+/* Brackets work on one stream (the compute stream unless another is named) with an event
+ * pair while profiling; finished pairs are read back after the next synchronising submit.
+ * Categories as in src/cuda/gpu_cuda.cu:231-273: 0 GEMM, 3 slot wait, 4 host to device,
+ * 5 device to host, 7 quantisation conversion.  No fence or cross-stream dependency is added. */
 struct ProfileScope {
     h3_gpu *g;
+    cudaStream_t stream;
     h3_gpu::Span span{};
     bool live = false;
     static cudaEvent_t event(h3_gpu *g) {
@@ -89,30 +95,40 @@ struct ProfileScope {
         else cudaEventCreate(&e);
         return e;
     }
-    ProfileScope(h3_gpu *gpu, int category) : g(gpu) {
+    ProfileScope(h3_gpu *gpu, int category, cudaStream_t target = nullptr) : g(gpu), stream(target ? target : gpu->compute) {
         if (!g->profiling) return;
-        span.start = event(g); span.stop = event(g); span.category = category;
-        live = span.start && span.stop && cudaEventRecord(span.start, g->compute) == cudaSuccess;
+        {
+            std::lock_guard<std::mutex> lock(g->span_mutex);
+            span.start = event(g); span.stop = event(g); span.category = category;
+        }
+        live = span.start && span.stop && cudaEventRecord(span.start, stream) == cudaSuccess;
     }
     ~ProfileScope() {
-        if (live && cudaEventRecord(span.stop, g->compute) == cudaSuccess) g->spans.push_back(span);
+        if (!live || cudaEventRecord(span.stop, stream) != cudaSuccess) return;
+        std::lock_guard<std::mutex> lock(g->span_mutex);
+        g->spans.push_back(span);
     }
 };
 static void harvest_profile(h3_gpu *g) {
+    std::lock_guard<std::mutex> lock(g->span_mutex);
+    std::vector<h3_gpu::Span> pending;
     for (auto &s : g->spans) {
         float ms = 0;
+        if (cudaEventQuery(s.stop) == cudaErrorNotReady) { pending.push_back(s); continue; } /* a copy still in flight */
         if (cudaEventElapsedTime(&ms, s.start, s.stop) == cudaSuccess) {
             if (s.category == 0) { g->stats.linear_seconds += ms * 1e-3; g->stats.linear_kernel_launches++; }
             else if (s.category == 3) { /* slot wait: time the compute stream sat idle waiting for a weight copy */
                 g->stats.stream_wait_seconds += ms * 1e-3;
                 if (ms > 0.02f) g->stats.stream_stalls++;
             }
+            else if (s.category == 4) g->stats.h2d_seconds += ms * 1e-3;
+            else if (s.category == 5) g->stats.d2h_seconds += ms * 1e-3;
             else { g->stats.quant_conversion_seconds += ms * 1e-3; g->stats.conversion_kernel_launches++; }
         }
         g->spare_events.push_back(s.start);
         g->spare_events.push_back(s.stop);
     }
-    g->spans.clear();
+    g->spans.swap(pending);
 }
 
 static const size_t BOUNCE_BYTES = 16u << 20; /* src/cuda/gpu_cuda.cu:79-82 */
@@ -208,6 +224,7 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
     h3_gpu *g = new (std::nothrow) h3_gpu;
     if (!g) return refuse("out of host memory");
     g->device = device;
+    g->created = now_seconds();
     {   /* src/cuda/gpu_cuda.cu:305: residency options are read once, when the context is made */
         char why[160] = {0};
         if (!h3_weight_options_read(&g->weight_options, 0, why, sizeof why)) { delete g; return refuse(why); }
@@ -250,6 +267,7 @@ extern "C" void h3_gpu_cancel(h3_gpu *g) {
 extern "C" void h3_gpu_free(h3_gpu *g) {
     if (!g) return;
     h3_gpu_cancel(g);
+    for (auto &s : g->spans) { cudaEventDestroy(s.start); cudaEventDestroy(s.stop); }
     for (cudaEvent_t e : g->spare_events) cudaEventDestroy(e);
     for (int i = 0; i < 3; i++) if (g->arena[i]) cudaFree(g->arena[i]);
     for (int i = 0; i < 2; i++) {
@@ -261,6 +279,35 @@ extern "C" void h3_gpu_free(h3_gpu *g) {
     if (g->copy) cudaStreamDestroy(g->copy);
     if (g->copy_out) cudaStreamDestroy(g->copy_out);
     delete g;
+}
+
+/* src/cuda/gpu_cuda.cu:497-524: the H3_PROFILE report, limited to the lines this path feeds --
+ * weight placement, quantisation, transfers and the GEMM / conversion event categories. */
+extern "C" void h3_gpu_profile_set_label(h3_gpu *g, const char *label) {
+    if (g && label) g->label = label;
+}
+extern "C" void h3_gpu_profile_mark(h3_gpu *g, const char *phase) {
+    if (!g || !getenv("H3_PROFILE")) return;
+    if (!phase) phase = "";
+    const h3_gpu_stats &s = g->stats;
+    const double gib = 1073741824.;
+    if (s.active_weight_blocks)
+        fprintf(stderr, "h3cli: weight placement %s: resident=%llu/%llu resident_bytes=%llu slot_bytes=%llu pinned_bytes=%llu uploaded_bytes=%llu\n",
+                phase, (unsigned long long)s.resident_blocks, (unsigned long long)s.active_weight_blocks,
+                (unsigned long long)s.resident_weight_bytes, (unsigned long long)s.stream_slot_bytes,
+                (unsigned long long)s.pinned_bytes, (unsigned long long)s.streamed_bytes);
+    if (g->quant_mode)
+        fprintf(stderr, "h3cli: quant profile %s / %s: mode=%s group=%u native_calls=%llu cache_hits=%llu prepared=%llu conversion=%.6fs (%llu kernels)\n",
+                g->label.c_str(), phase, g->quant_mode == 2 ? "w8a8" : "w8a16", g->group,
+                (unsigned long long)s.quant_projection_dispatches, (unsigned long long)s.quant_cache_hits,
+                (unsigned long long)s.quant_cache_misses, s.quant_conversion_seconds, (unsigned long long)s.conversion_kernel_launches);
+    fprintf(stderr, "h3cli: CUDA profile %s / %s: wall %.3fs peak %.3f GiB, GEMM %llu, H2D %.3f GiB D2H %.3f GiB stream %.3f GiB wait %.3fs\n",
+            g->label.c_str(), phase, now_seconds() - g->created, s.peak_live_bytes / gib, (unsigned long long)s.linear_dispatches,
+            s.h2d_bytes / gib, s.d2h_bytes / gib, s.streamed_bytes / gib, s.stream_wait_seconds);
+    fprintf(stderr, "h3cli: CUDA category seconds: GEMM %.6f (%llu kernels) conversion %.6f; stream stalls %llu / %.6fs\n", s.linear_seconds,
+            (unsigned long long)s.linear_kernel_launches, s.quant_conversion_seconds, (unsigned long long)s.stream_stalls, s.stream_wait_seconds);
+    fprintf(stderr, "h3cli: CUDA transfer events: H2D %.6fs (%.3f GiB/s), D2H %.6fs (%.3f GiB/s)\n", s.h2d_seconds,
+            s.h2d_seconds > 0 ? s.h2d_bytes / gib / s.h2d_seconds : 0.0, s.d2h_seconds, s.d2h_seconds > 0 ? s.d2h_bytes / gib / s.d2h_seconds : 0.0);
 }
 
 extern "C" const char *h3_gpu_error(const h3_gpu *g) { return g ? g->error : "no GPU context"; }
@@ -438,6 +485,7 @@ extern "C" int h3q8_gpu_tensor_upload_async(h3_gpu_tensor *t, const void *host, 
     if (!selected(g)) return 0;
     if (t->release_recorded) cudaStreamWaitEvent(g->copy, t->released, 0);
     if (t->ready_recorded) cudaStreamWaitEvent(g->copy, t->ready, 0); /* an earlier download of this tensor */
+    ProfileScope timing(g, 4, g->copy);
     if (!checked(g, cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, g->copy), "asynchronous host to device copy", bytes) ||
         !checked(g, cudaEventRecord(t->ready, g->copy), "tensor ready event")) return 0;
     t->ready_recorded = true;
@@ -452,6 +500,7 @@ extern "C" int h3q8_gpu_tensor_download_async(h3_gpu_tensor *t, void *host, size
     if (!selected(g)) return 0;
     if (t->release_recorded) cudaStreamWaitEvent(g->copy_out, t->released, 0);
     if (t->ready_recorded) cudaStreamWaitEvent(g->copy_out, t->ready, 0); /* an earlier upload of this tensor */
+    ProfileScope timing(g, 5, g->copy_out);
     if (!checked(g, cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, g->copy_out), "asynchronous device to host copy", bytes) ||
         !checked(g, cudaEventRecord(t->ready, g->copy_out), "tensor ready event")) return 0;
     t->ready_recorded = true; /* the next operator that writes the tensor waits for this copy */
@@ -880,6 +929,7 @@ extern "C" int h3q8_gpu_weight_stream_prefetch(h3q8_weight_stream *s, const void
     s->next = (s->next + 1) % s->slots;
     /* the copy may not overwrite a slot the compute stream is still reading */
     if (s->released_recorded[slot] && !checked(g, cudaStreamWaitEvent(g->copy, s->released[slot], 0), "weight stream wait")) return -1;
+    ProfileScope timing(g, 4, g->copy);
     if (!checked(g, cudaMemcpyAsync(s->memory[slot], host_blob, bytes, cudaMemcpyHostToDevice, g->copy), "weight stream copy", bytes) ||
         !checked(g, cudaEventRecord(s->ready[slot], g->copy), "weight stream ready event")) return -1;
     s->ready_recorded[slot] = true;

@@ -214,6 +214,8 @@ typedef struct {
     uint64_t linear_kernel_launches, conversion_kernel_launches;
     /* last accepted residency plan (src/gpu.h:99-142, same names) */
     uint64_t resident_weight_bytes, resident_blocks, active_weight_blocks, resident_block_mask;
+    /* H3_PROFILE categories 4 and 5: event time of the asynchronous copies (uploads, weight streaming; downloads) */
+    double h2d_seconds, d2h_seconds;
 } h3_gpu_stats;
 
 /* Context -- src/gpu.h:144-145, 180-182, 203, 207, 267-268 */
@@ -221,6 +223,10 @@ h3_gpu *h3_gpu_create(const char *shader_source_path, char *error, size_t error_
 void h3_gpu_free(h3_gpu *gpu);
 void h3_gpu_cancel(h3_gpu *gpu);
 const char *h3_gpu_error(const h3_gpu *gpu);
+/* src/gpu.h:271-272: with H3_PROFILE set, prints the report lines this path feeds (weight placement,
+ * quantisation, transfers, GEMM and conversion event seconds) to stderr; silent otherwise. */
+void h3_gpu_profile_set_label(h3_gpu *gpu, const char *label);
+void h3_gpu_profile_mark(h3_gpu *gpu, const char *phase);
 int h3_gpu_get_stats(const h3_gpu *gpu, h3_gpu_stats *stats);
 const char *h3_gpu_backend_name(const h3_gpu *gpu);
 int h3_gpu_has_int8_mlp(const h3_gpu *gpu);

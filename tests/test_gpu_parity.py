@@ -746,6 +746,53 @@ def test_prepare_tool_builds_every_artifact(oracle, tmp_path):
     assert other.returncode == 0 and "8 prepared" in other.stderr      # another scale group is another artifact
 
 
+def test_profile_report_lines(oracle, monkeypatch, capfd):
+    """H3_PROFILE: h3_gpu_profile_mark prints the placement / quant / transfer / category lines
+    (src/cuda/gpu_cuda.cu:497-524), fed by the event categories 0, 4, 5 and 7; silent without the variable."""
+    rows, cols, n = 512, 256, 384
+    x = synth.activations(77, 1, rows, cols).reshape(rows, cols)
+    w = synth.bf16_normal(78, 2, n, cols, 0, 0.05).reshape(n, cols)
+    wq, ws = oracle.q8_pack_rows(w, 0)
+
+    def run():
+        gpu = h.Gpu()
+        gpu.quant_configure(1)
+        h.library().h3_gpu_profile_set_label(gpu.handle, b"unit")
+        weight = gpu.q8_from_host(wq, ws, 0)
+        tx, out = gpu.tensor_new_bf16(rows * cols), gpu.tensor_new_bf16(rows * n)
+        host = np.ascontiguousarray(x)
+        back = np.zeros(rows * n, dtype=np.uint16)
+        tx.upload_async(host.ctypes.data, host.nbytes)
+        gpu.begin()
+        gpu.linear_bf16(out, tx, weight, None, rows, cols, n)
+        gpu.continue_()
+        out.download_async(back.ctypes.data, back.nbytes)
+        out.wait()
+        gpu.submit()
+        gpu.synchronize()
+        gpu.plan_bf16_weights(0xFF, 1 << 20)
+        gpu.begin()
+        gpu.submit()                                   # harvests the copy events that finished after the first submit
+        h.library().h3_gpu_profile_mark(gpu.handle, b"after block")
+        stats = gpu.stats()
+        check_bf16(back.reshape(rows, n), oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0))
+        gpu.free()
+        return stats
+
+    monkeypatch.delenv("H3_PROFILE", raising=False)
+    capfd.readouterr()
+    quiet = run()
+    assert capfd.readouterr().err == "" and quiet.linear_seconds == 0
+    monkeypatch.setenv("H3_PROFILE", "1")
+    stats = run()
+    err = capfd.readouterr().err
+    assert "h3cli: weight placement after block: resident=8/8" in err
+    assert "h3cli: quant profile unit / after block: mode=w8a16" in err
+    assert "h3cli: CUDA profile unit / after block: wall" in err and "GEMM 1," in err
+    assert "h3cli: CUDA category seconds: GEMM 0.0" in err and "h3cli: CUDA transfer events: H2D" in err
+    assert stats.linear_seconds > 0 and stats.h2d_seconds > 0 and stats.d2h_seconds > 0 and stats.quant_conversion_seconds > 0
+
+
 def test_residency_plan_on_the_device(monkeypatch):
     """h3_gpu_plan_bf16_weights (src/cuda/gpu_cuda.cu:559-578): free memory and reserve come from the device;
     the test-only block ceiling and capacity turn the same request into partial and streamed plans."""
