@@ -160,6 +160,7 @@ def main():
                          "(config 5): M=219,600 rows sharded over the GPUs, --layers layers of group-128 weights streamed "
                          "from pinned host memory through two device slots")
     ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--group", type=int, default=-1, help="weight scale group for --case (default: 64 for real W8A16 shapes, else per channel)")
     ap.add_argument("--e2e-depth", type=int, default=4, help="end-to-end steps in flight (buffer sets)")
     ap.add_argument("--e2e-slices", type=int, default=1, help="row slices per end-to-end step (copy/compute overlap inside a step)")
     ap.add_argument("--mode", default="w8a16", choices=["w8a16", "w8a8"],
@@ -468,7 +469,7 @@ def run_case(args, gpu, lib, stream, device_bf16):
     rows = args.rows
     real = name.startswith("real_")
     wrows = 2 * n if "s" in spec else n
-    group = 64 if real and args.mode == "w8a16" else 0
+    group = args.group if args.group >= 0 else 64 if real and args.mode == "w8a16" else 0
     wgen = np.random.default_rng(42)
     wq = wgen.integers(-127, 128, (wrows, k), dtype=np.int8)
     ws = np.exp(wgen.normal(np.log(0.002 if "s" in spec else 0.01), 0.3, (wrows, k // group if group else 1))).astype(np.float32)
@@ -493,7 +494,7 @@ def run_case(args, gpu, lib, stream, device_bf16):
     stop.record(stream)
     gpu.submit()
     ms = start.elapsed_time(stop) / args.steps
-    print(json.dumps({"case": name, "mode": args.mode, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * wrows / ms / 1e9,
+    print(json.dumps({"case": name, "mode": args.mode, "group": group, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * wrows / ms / 1e9,
                       "launches": int(lib.h3q8_kernel_launches())}), flush=True)
     gpu.free()
 

@@ -182,6 +182,29 @@ static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, 
     return cuda_ok(cudaGetLastError(), "tcgen05 pair linear launch");
 }
 
+/* W8A8 with per-K-group scales on the two-CTA kernel (one problem per launch). */
+template <bool MAGIC>
+static int launch_pair_grouped(const h3q8_linear_desc &d, const GemmParams &params, DeviceState *dev, cudaStream_t stream) {
+    constexpr uint32_t BM = 256, BN = 128, BKE = 128; /* PairGroupedConfig: 256 x 128 tile, each CTA stages 64 weight rows */
+    PairArgs args;
+    memset(&args, 0, sizeof args);
+    args.count = 1;
+    GemmParams &p = args.p[0];
+    p = params;
+    if (!make_map(&args.map_a[0], d.input, 1, d.rows, d.input_dim, BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    if (!make_map(&args.map_b[0], d.weight, 1, d.output_dim, d.input_dim, BKE, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    p.m_blocks = (d.rows + BM - 1) / BM;
+    p.n_blocks = (d.output_dim + BN - 1) / BN;
+    p.tiles = p.m_blocks * p.n_blocks;
+    const uint32_t band = d.input_dim <= 8192 ? 16 : 8;
+    p.band = p.m_blocks < band ? p.m_blocks : band;
+    p.l2_policy_a = L2_EVICT_NORMAL;
+    p.l2_policy_b = L2_EVICT_NORMAL;
+    args.tile_start[0] = 0;
+    args.tile_start[1] = p.tiles;
+    return launch_pair_grouped_kernel(args, MAGIC, dev->sms, stream);
+}
+
 template <int MODE>
 static int launch_plain(const h3q8_linear_desc &d, const GemmParams &p, cudaStream_t stream) {
     dim3 grid((d.output_dim + 63) / 64, (d.rows + 63) / 64);
@@ -195,8 +218,10 @@ static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t 
     const bool grouped8 = MODE == MODE_W8A8 && p.scale_group != 0;
     if (kernel == H3Q8_KERNEL_PLAIN) return launch_plain<MODE>(d, p, stream);
     if (grouped8) {
-        if (MODE == MODE_W8A8) return launch_tcgen05<MODE_W8A8, 128, 1, true>(d, p, dev, stream);
-        return fail("grouped W8A8 reached a non-W8A8 launch");
+        if (MODE != MODE_W8A8) return fail("grouped W8A8 reached a non-W8A8 launch");
+        if (kernel == H3Q8_KERNEL_TCGEN05_PAIR)
+            return p.scale_group <= 256 ? launch_pair_grouped<true>(d, p, dev, stream) : launch_pair_grouped<false>(d, p, dev, stream);
+        return launch_tcgen05<MODE_W8A8, 128, 1, true>(d, p, dev, stream);
     }
     if (kernel == H3Q8_KERNEL_TCGEN05_PAIR) {
         if constexpr (MODE == MODE_W8A16) return fail("the two-CTA kernel takes bf16 or int8 operands, not main-loop dequantisation");
@@ -264,12 +289,15 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
                   (d.mode != H3Q8_MODE_W8A8 || aligned16(d.weight_scales));
     if (d.mode == H3Q8_MODE_W8A16 && d.weight_group && d.weight_group % 64) tma_ok = false;
     if (d.mode == H3Q8_MODE_W8A8 && p.scale_group && p.scale_group % 128) tma_ok = false;
+    /* the grouped two-CTA kernel hands whole scale groups to the epilogue: groups of whole k-blocks that tile K */
+    const bool grouped_pair_ok = d.mode == H3Q8_MODE_W8A8 && p.scale_group && p.scale_group % 128 == 0 &&
+                                 d.input_dim % p.scale_group == 0 && !swiglu && !d.rope;
     kernel = d.kernel;
     if (kernel > H3Q8_KERNEL_TCGEN05_PAIR) return fail("linear: unknown kernel selector %u", kernel);
     if (kernel == H3Q8_KERNEL_AUTO) {
         const bool tiny = (uint64_t)d.rows * d.input_dim * d.output_dim <= (1u << 22);
-        /* two-CTA tiles need both CTAs to have rows; main-loop dequantisation and grouped W8A8 stay single-CTA */
-        const bool pair_ok = d.rows > 128 && (d.mode == H3Q8_MODE_BF16 || (d.mode == H3Q8_MODE_W8A8 && !p.scale_group));
+        /* two-CTA tiles need both CTAs to have rows; main-loop dequantisation stays single-CTA */
+        const bool pair_ok = d.rows > 128 && (d.mode == H3Q8_MODE_BF16 || (d.mode == H3Q8_MODE_W8A8 && (!p.scale_group || grouped_pair_ok)));
         kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128
                : pair_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_TCGEN05;
         /* SwiGLU runs on the two-CTA kernel (gate rows in one CTA, up rows in its peer) or on the plain kernel */
@@ -286,8 +314,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     /* an explicitly requested kernel must be able to take the problem */
     if (swiglu && kernel != H3Q8_KERNEL_PLAIN && kernel != H3Q8_KERNEL_TCGEN05_PAIR) {
         return fail("linear: SwiGLU is available on the two-CTA and the plain kernel");
-    } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && p.scale_group))) {
-        return fail("linear: the two-CTA kernel takes bf16 or per-channel int8 operands");
+    } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && p.scale_group && !grouped_pair_ok))) {
+        return fail("linear: the two-CTA kernel takes bf16 or int8 operands (scale groups: multiples of 128 that divide K)");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {
         return fail("linear %ux%ux%u: shape or alignment not supported by the tcgen05 kernel "
                     "(K %% %u, N %% 8, 16-byte aligned operands, scale group %% 64/128)",
@@ -334,7 +362,8 @@ extern "C" int h3q8_linear_grouped(const h3q8_linear_desc *problems, uint32_t co
         for (uint32_t i = 0; i < count; i++) {
             uint32_t kernel;
             if (!plan_linear(problems[i], params[i], kernel, dev)) return 0;
-            together = together && kernel == H3Q8_KERNEL_TCGEN05_PAIR && problems[i].mode == problems[0].mode && !problems[i].rope;
+            together = together && kernel == H3Q8_KERNEL_TCGEN05_PAIR && problems[i].mode == problems[0].mode && !problems[i].rope &&
+                       !(problems[i].mode == H3Q8_MODE_W8A8 && params[i].scale_group);
         }
         if (together && count > 1)
             return problems[0].mode == H3Q8_MODE_BF16 ? launch_pair<MODE_BF16>(problems, params, count, dev, stream)

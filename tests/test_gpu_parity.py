@@ -302,7 +302,7 @@ def test_w8a8_int32_exact_and_epilogue(gpu, oracle, M, N, K, spec, kernel):
         assert (got == want).all()      # identical accumulators and identical fp32 epilogue: identical bits
 
 
-@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN, h.KERNEL_TCGEN05])
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN, h.KERNEL_TCGEN05, h.KERNEL_TCGEN05_PAIR])
 @pytest.mark.parametrize("M,N,K", [(40, 24, 256), (130, 128, 256), (300, 520, 512), (64, 3072, 3072)])
 def test_w8a8_group128_weight_scales(gpu, oracle, M, N, K, kernel):
     """Config 3(b): per-group-128 weight scales.  No reference implementation
@@ -314,6 +314,37 @@ def test_w8a8_group128_weight_scales(gpu, oracle, M, N, K, kernel):
     want = oracle.linear(oracle.MODE_W8A8, xq, wq, ws, 128, x_scales=xs, bias=bias, fast=True)
     got = raw_linear(gpu, h.MODE_W8A8, xq, wq, ws, 128, xs=xs, bias=bias, kernel=kernel)
     assert (got == want).all()
+
+
+@pytest.mark.parametrize("spec", ["", "bgr", "ba"])
+@pytest.mark.parametrize("M,N,K,group,both", [(1000, 776, 1024, 128, False), (513, 256, 3072, 256, True), (700, 1032, 2048, 512, False),
+                                              (2100, 3072, 1536, 128, True)])
+def test_w8a8_grouped_two_cta_kernel(gpu, oracle, M, N, K, group, both, spec):
+    """Per-K-group weight scales (and, with `both`, per-group activation scales of the same width) on the
+    two-CTA kernel: group sums leave TMEM per group and are combined in fp32 registers, bit-equal to the
+    oracle's ascending-group sum; groups <= 256 take the exact bias-trick conversion, wider ones cvt."""
+    x, wq, ws = operands(31, M, N, K, group, outliers=True)
+    bias, gate, res, act = epilogue_operands(31, M, N, spec)
+    if both:
+        xq, xs = oracle.quantize_rows_grouped(x, group)
+    else:
+        xq, xs = oracle.quantize_rows(x)
+    want = oracle.linear(oracle.MODE_W8A8, xq, wq, ws, group, x_scales=xs, bias=bias, gate=gate, residual=res, activation=act,
+                         input_group=group if both else 0, fast=True)
+    t = upload(gpu, input=xq, weight=wq, weight_scales=ws, input_scales=np.ascontiguousarray(xs), bias=bias, gate=gate, residual=res)
+    out = gpu.tensor_from_bf16(np.full(M * N + GUARD, 0x3F80, np.uint16))
+    launches = h.library().h3q8_kernel_launches()
+    gpu.raw_linear(mode=h.MODE_W8A8, rows=M, input_dim=K, output_dim=N, weight_group=group, input_group=group if both else 0,
+                   activation=act, kernel=h.KERNEL_AUTO, output=out, **t)
+    assert gpu.raw_status() == 0 and h.library().h3q8_kernel_launches() - launches == 1
+    got = out.read()
+    assert (got[M * N:] == 0x3F80).all(), "wrote past the end of the output"
+    if act:
+        check_bf16(got[:M * N].reshape(M, N), want)
+    else:
+        assert (got[:M * N].reshape(M, N) == want).all()
+    for tensor in list(t.values()) + [out]:
+        tensor.free()
 
 
 @pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN, h.KERNEL_AUTO])
