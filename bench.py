@@ -152,7 +152,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="h3q8")
-    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS],
+    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS] + ["helpers"],
                     help="profiling aid: run only this projection (with --rows) and print a short line")
     ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
     ap.add_argument("--workload", default="block", choices=["block", "stream"],
@@ -206,6 +206,8 @@ def main():
         torch.cuda.synchronize()
         return t
 
+    if args.case == "helpers":
+        return run_helpers(args, gpu, lib, stream, device_bf16)
     if args.case:
         return run_case(args, gpu, lib, stream, device_bf16)
     if args.workload == "stream":
@@ -459,6 +461,57 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
                                    "weights streamed per layer from pinned host memory, 2 device slots"}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    gpu.free()
+
+
+def run_helpers(args, gpu, lib, stream, device_bf16):
+    """The memory-bound kernels beside the GEMM, each timed alone with CUDA events against the measured copy
+    bandwidth: algorithmic bytes (what must cross HBM once) / time.  Operands exceed L2 (126 MB)."""
+    import torch
+    rows, hidden, ffn = args.rows, HIDDEN, FFN
+    burst, _, which = measured_peak()
+    try:
+        hbm = float(json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")))["hbm_gbs"])
+        source = "measured"
+    except (OSError, KeyError, ValueError):
+        hbm, source = 6650.0, "fallback"
+    x = device_bf16(rows, ffn, seed=1)                       # [rows, 12288] bf16 = 796 MB at 32 400 rows
+    branch, residual = device_bf16(rows, hidden, seed=2), device_bf16(rows, hidden, seed=3)
+    q, sc = gpu.tensor_new_i8(rows * ffn), gpu.tensor_new_f32(rows * (ffn // 1024))
+    wbf = device_bf16(ffn, ffn, 0.0, 0.02, seed=4)           # [12288, 12288] bf16 weight = 302 MB
+    wq, ws = gpu.tensor_new_i8(ffn * ffn), gpu.tensor_new_f32(ffn * (ffn // 128))
+    wout = gpu.tensor_new_bf16(ffn * ffn)
+    norm_w, mod = device_bf16(1, hidden, 1.0, 0.1, seed=5), device_bf16(1, 3 * hidden, 0.0, 0.1, seed=6)
+    gated, q3, s3 = gpu.tensor_new_bf16(rows * hidden), gpu.tensor_new_i8(rows * hidden), gpu.tensor_new_f32(rows)
+    p = lambda t: t.device_pointer
+    cases = [
+        ("quantize_rows_kernel [M,3072]", lambda: lib.h3q8_quantize_rows(p(branch), p(q3), p(s3), rows, rows, hidden, 1.0, gpu.stream),
+         rows * hidden * 3 + rows * 4),
+        ("quantize_rows_kernel [M,12288]", lambda: lib.h3q8_quantize_rows(p(x), p(q), p(sc), rows, rows, ffn, 1.0, gpu.stream),
+         rows * ffn * 3 + rows * 4),
+        ("quantize_rows_kernel grouped 1024 [M,12288]", lambda: lib.h3q8_quantize_rows_grouped(p(x), p(q), p(sc), rows, rows, ffn, 1024, gpu.stream),
+         rows * ffn * 3 + rows * (ffn // 1024) * 4),
+        ("q8_pack_rows_kernel [12288,12288] group 128", lambda: lib.h3q8_q8_pack_rows_device(p(wbf), p(wq), p(ws), ffn, ffn, 128, gpu.stream),
+         ffn * ffn * 3 + ffn * (ffn // 128) * 4),
+        ("q8_dequant_kernel [12288,12288] group 128", lambda: lib.h3q8_q8_dequant(p(wq), p(ws), p(wout), ffn, ffn, 128, gpu.stream),
+         ffn * ffn * 3 + ffn * (ffn // 128) * 4),
+        ("gate_adaln_quantize_kernel [M,3072]", lambda: gpu.gate_adaln_quantize_int8(gated, q3, s3, residual, branch, norm_w, mod, mod, None, rows, rows,
+                                                                                  hidden, 3, 0, 1, 2, 1e-6),
+         rows * hidden * (2 + 2 + 2 + 1) + rows * 4),
+    ]
+    out = []
+    for name, call, nbytes in cases:
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        gpu.begin()
+        for i in range(args.warmup + args.steps):
+            if i == args.warmup:
+                start.record(stream)
+            assert call()
+        stop.record(stream)
+        gpu.submit()
+        ms = start.elapsed_time(stop) / args.steps
+        out.append({"kernel": name, "ms": ms, "algorithmic_bytes": nbytes, "gbs": nbytes / ms / 1e6, "frac_of_hbm_peak": nbytes / ms / 1e6 / hbm})
+    print(json.dumps({"case": "helpers", "rows": rows, "hbm_peak_gbs": hbm, "peak_source": source, "kernels": out}), flush=True)
     gpu.free()
 
 

@@ -1054,7 +1054,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
                 float *xs = (float *)((char *)g->arena[1] + offset[1]);
                 {
                     ProfileScope timing(g, 7);
-                    quantize_rows_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)d.input, xq, xs, q.rows, q.input_dim, 1.0f, g->flags + 1);
+                    launch_quantize_rows((const uint16_t *)d.input, xq, xs, q.rows, padded, q.input_dim, 1.0f, g->flags + 1, g->compute);
                 }
                 count_launch(1);
                 dispatches++;
@@ -1120,8 +1120,8 @@ extern "C" int h3_gpu_quantize_weight_int8(h3_gpu *g, h3_gpu_tensor *out, h3_gpu
     if (!rows || !columns || !require(g, in, H3_GPU_BF16, (size_t)rows * columns, "BF16 weight to quantize") ||
         !require(g, out, H3_GPU_I8, (size_t)rows * columns, "int8 quantized output") ||
         !require(g, scales, H3_GPU_F32, rows, "int8 quantization scales")) return 0;
-    quantize_rows_kernel<<<rows, 256, 0, g->compute>>>((const uint16_t *)pointer(in), (int8_t *)pointer(out), (float *)pointer(scales),
-                                                       rows, columns, 1.0f, g->flags + 1);
+    launch_quantize_rows((const uint16_t *)pointer(in), (int8_t *)pointer(out), (float *)pointer(scales), rows, rows, columns, 1.0f,
+                         g->flags + 1, g->compute);
     count_launch(1);
     return launch_status(g, "weight quantiser", 1);
 }
@@ -1138,8 +1138,8 @@ extern "C" int h3_gpu_linear_int8_bf16(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_ten
         !require(g, out, H3_GPU_BF16, (size_t)rows * n, "int8 linear output") || !require(g, in, H3_GPU_BF16, (size_t)rows * k, "int8 linear input") ||
         !require(g, qin, H3_GPU_I8, (size_t)padded * k, "int8 quantized output") ||
         !require(g, in_scales, H3_GPU_F32, padded, "int8 quantization scales")) return 0;
-    quantize_rows_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)pointer(in), (int8_t *)pointer(qin), (float *)pointer(in_scales),
-                                                         rows, k, 1.0f, g->flags + 1);
+    launch_quantize_rows((const uint16_t *)pointer(in), (int8_t *)pointer(qin), (float *)pointer(in_scales), rows, padded, k, 1.0f,
+                         g->flags + 1, g->compute);
     count_launch(1);
     h3q8_linear_desc d = {};
     d.mode = H3Q8_MODE_W8A8; d.rows = rows; d.input_dim = k; d.output_dim = n;
@@ -1172,11 +1172,27 @@ extern "C" int h3_gpu_gate_adaln_quantize_int8(h3_gpu *g, h3_gpu_tensor *gated_r
         !require(g, quantized_output, H3_GPU_I8, (size_t)padded_rows * width, "int8 quantized output") ||
         !require(g, quantized_scales, H3_GPU_F32, padded_rows, "int8 quantization scales") ||
         (row_map && !require(g, row_map, H3_GPU_U32, rows, "row map"))) return 0;
-    gate_adaln_quantize_kernel<<<padded_rows, 256, width * sizeof(uint16_t), g->compute>>>(
-        (const uint16_t *)pointer(residual), (const uint16_t *)pointer(branch), (const uint16_t *)pointer(gate_modulation),
-        row_map ? (const uint32_t *)pointer(row_map) : nullptr, (const uint16_t *)pointer(norm_weight),
-        (const uint16_t *)pointer(norm_modulation), (uint16_t *)pointer(gated_residual), (int8_t *)pointer(quantized_output),
-        (float *)pointer(quantized_scales), rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);
+    const uint16_t *res_p = (const uint16_t *)pointer(residual), *branch_p = (const uint16_t *)pointer(branch);
+    const uint16_t *gate_p = (const uint16_t *)pointer(gate_modulation), *norm_p = (const uint16_t *)pointer(norm_weight);
+    const uint16_t *mod_p = (const uint16_t *)pointer(norm_modulation);
+    const uint32_t *map_p = row_map ? (const uint32_t *)pointer(row_map) : nullptr;
+    uint16_t *gated_p = (uint16_t *)pointer(gated_residual);
+    int8_t *q_p = (int8_t *)pointer(quantized_output);
+    float *s_p = (float *)pointer(quantized_scales);
+    const uintptr_t alignment = (uintptr_t)res_p | (uintptr_t)branch_p | (uintptr_t)gate_p | (uintptr_t)norm_p | (uintptr_t)mod_p |
+                                (uintptr_t)gated_p | (uintptr_t)q_p;
+    /* rows of at most 6144 elements on 16-byte aligned operands: one warp per row, the row stays in registers */
+    if (width % 8 == 0 && width <= 6144 && (alignment & 15u) == 0) {
+        const unsigned grid = (padded_rows + 3) / 4;
+        if (width <= 3072)
+            gate_adaln_quantize_warp_kernel<12><<<grid, 128, 0, g->compute>>>(res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows,
+                                                                            padded_rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);
+        else
+            gate_adaln_quantize_warp_kernel<24><<<grid, 128, 0, g->compute>>>(res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows,
+                                                                            padded_rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);
+    } else
+        gate_adaln_quantize_kernel<<<padded_rows, 256, width * sizeof(uint16_t), g->compute>>>(
+            res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);
     count_launch(1);
     return launch_status(g, "gate/AdaLN/quantize", 1);
 }

@@ -381,9 +381,9 @@ extern "C" int h3q8_quantize_rows(const uint16_t *input, int8_t *output, float *
     if (!(clip > 0.0f) || clip > 1.0f) return fail("quantize rows: clip must be in (0, 1]");
     uint32_t *status = device_status_word();
     if (!status) return 0;
-    quantize_rows_kernel<<<dispatch_rows, 256, 0, (cudaStream_t)cuda_stream>>>(input, output, scales, rows, columns, clip, nullptr);
+    cudaError_t e = launch_quantize_rows(input, output, scales, rows, dispatch_rows, columns, clip, nullptr, (cudaStream_t)cuda_stream);
     count_launch(1);
-    return cuda_ok(cudaGetLastError(), "quantize rows launch");
+    return cuda_ok(e, "quantize rows launch");
 }
 
 extern "C" int h3q8_quantize_rows_grouped(const uint16_t *input, int8_t *output, float *scales, uint32_t rows,

@@ -102,6 +102,77 @@ static __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_
     }
 }
 
+/* The same quantiser with one WARP per segment (a row, or one K-group of a row) of at most
+ * ITERS * 256 elements: every lane keeps its 16-byte vectors in registers between the maximum
+ * and the rounding pass, nothing goes through shared memory and no CTA-wide barrier is
+ * needed, so short segments (a 1024-wide group is 2 KB) keep many loads in flight.
+ * Segment s covers in[s * segment ..); segments >= live are padding (zeros, scale 1). */
+template <int ITERS>
+static __global__ void __launch_bounds__(256) quantize_segments_warp_kernel(const uint16_t *__restrict__ in, int8_t *__restrict__ out,
+                                                                     float *__restrict__ scales, uint64_t live, uint64_t total,
+                                                                     uint32_t segment, float clip, uint32_t *nonfinite) {
+    const uint64_t s = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (s >= total) return;
+    const uint32_t lane = threadIdx.x & 31, vectors = segment / 8;
+    uint2 *q = reinterpret_cast<uint2 *>(out + s * segment);
+    if (s >= live) {
+        for (uint32_t c = lane; c < vectors; c += 32) q[c] = make_uint2(0, 0);
+        if (lane == 0) scales[s] = 1.0f;
+        return;
+    }
+    const uint4 *x = reinterpret_cast<const uint4 *>(in + s * segment);
+    uint4 held[ITERS];
+    float peak = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const uint32_t c = lane + i * 32;
+        held[i] = c < vectors ? x[c] : make_uint4(0, 0, 0, 0);
+        const uint32_t w[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            peak = fmaxf(peak, fmaxf(fabsf(bf16_bits_to_f32(w[j] & 0xffffu)), fabsf(bf16_bits_to_f32(w[j] >> 16))));
+    }
+    peak = warp_max(peak);
+    const float clipped = __fmul_rn(peak, clip);
+    const float scale = clipped > 0.0f ? __fdiv_rn(clipped, 127.0f) : __fdiv_rn(1.0f, 127.0f);
+    const float inverse = clipped > 0.0f ? __fdiv_rn(127.0f, clipped) : 127.0f;
+    if (lane == 0) {
+        scales[s] = scale;
+        if (!(peak <= FLT_MAX) && nonfinite) atomicOr(nonfinite, 1u);
+    }
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const uint32_t c = lane + i * 32;
+        if (c >= vectors) break;
+        const uint32_t w[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
+        uint32_t o[2] = {0, 0};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint32_t lo = (uint32_t)quantize_one(bf16_bits_to_f32(w[j] & 0xffffu), inverse) & 0xffu;
+            uint32_t hi = (uint32_t)quantize_one(bf16_bits_to_f32(w[j] >> 16), inverse) & 0xffu;
+            o[j >> 1] |= (lo | (hi << 8)) << ((j & 1) * 16);
+        }
+        q[c] = make_uint2(o[0], o[1]);
+    }
+}
+
+/* Per-row (segment == columns) or per-K-group quantiser launch: the warp kernel when the segment is a
+ * multiple of 8 of at most 4096 elements on 16-byte aligned rows, else one CTA per segment. */
+static inline cudaError_t launch_quantize_rows(const uint16_t *in, int8_t *out, float *scales, uint64_t live, uint64_t total,
+                                               uint32_t segment, float clip, uint32_t *nonfinite, cudaStream_t stream) {
+    const bool aligned = ((reinterpret_cast<uintptr_t>(in) & 15u) | (reinterpret_cast<uintptr_t>(out) & 7u)) == 0;
+    const unsigned grid = (unsigned)((total + 7) / 8);
+    if (aligned && segment % 8 == 0 && segment <= 1024)
+        quantize_segments_warp_kernel<4><<<grid, 256, 0, stream>>>(in, out, scales, live, total, segment, clip, nonfinite);
+    else if (aligned && segment % 8 == 0 && segment <= 3072)
+        quantize_segments_warp_kernel<12><<<grid, 256, 0, stream>>>(in, out, scales, live, total, segment, clip, nonfinite);
+    else if (aligned && segment % 8 == 0 && segment <= 4096)
+        quantize_segments_warp_kernel<16><<<grid, 256, 0, stream>>>(in, out, scales, live, total, segment, clip, nonfinite);
+    else
+        quantize_rows_kernel<<<(unsigned)total, 256, 0, stream>>>(in, out, scales, (uint32_t)live, segment, clip, nonfinite);
+    return cudaGetLastError();
+}
+
 /* Producer-side fusion of the activation quantiser (src/metal/shaders.metal:3390-3473,
  * src/gpu.h:630-642): per row
  *   gated = bf16(residual + branch * gate[class, gate_slot])          -> gated_residual (may alias residual)
@@ -166,6 +237,120 @@ static __global__ void __launch_bounds__(256) gate_adaln_quantize_kernel(
     const float q_scale = peak > 0.0f ? __fdiv_rn(127.0f, peak) : 127.0f;
     if (tid == 0) quantized_scales[row] = out_scale;
     for (uint32_t c = tid; c < width; c += 256) quantized[row_base + c] = (int8_t)quantize_one(bf16_bits_to_f32(row_values[c]), q_scale);
+}
+
+/* The same operator with one WARP per row for rows of at most ITERS * 256 elements: lane t plays
+ * the eight lanes 8t .. 8t+7 of the 256-lane reduction (16-byte loads and stores, eight fma chains
+ * in the same element order), the tree steps 128/64/32/16/8 are shuffles by 16/8/4/2/1 lanes and
+ * the steps 4/2/1 stay inside lane 0, so the sum is formed in exactly the same order; the row
+ * stays in registers between the three passes and no CTA-wide barrier is needed. */
+template <int ITERS>
+static __global__ void __launch_bounds__(128) gate_adaln_quantize_warp_kernel(
+    const uint16_t *residual, const uint16_t *__restrict__ branch, const uint16_t *__restrict__ gate_modulation,
+    const uint32_t *__restrict__ row_map, const uint16_t *__restrict__ norm_weight, const uint16_t *__restrict__ norm_modulation,
+    uint16_t *gated_residual, int8_t *__restrict__ quantized, float *__restrict__ quantized_scales, uint32_t rows, uint32_t padded_rows,
+    uint32_t width, uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= padded_rows) return;
+    const size_t row_base = (size_t)row * width;
+    const uint32_t vectors = width / 8;
+    if (row >= rows) {
+        for (uint32_t c = lane; c < vectors; c += 32) reinterpret_cast<uint2 *>(quantized + row_base)[c] = make_uint2(0, 0);
+        if (lane == 0) quantized_scales[row] = 1.0f;
+        return;
+    }
+    const size_t base = (size_t)(row_map ? row_map[row] : 0) * slots * width;
+    const uint4 *res4 = reinterpret_cast<const uint4 *>(residual + row_base), *br4 = reinterpret_cast<const uint4 *>(branch + row_base);
+    const uint4 *gate4 = reinterpret_cast<const uint4 *>(gate_modulation + base + (size_t)gate_slot * width);
+    static_assert(ITERS % 6 == 0, "rows are processed six vectors at a time");
+    uint4 held[ITERS];
+    float sums[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    /* residual may alias gated_residual, so the compiler cannot move a later residual load above an earlier
+     * store: the loads of six vectors are issued together before any of their results is stored */
+    constexpr int CHUNK = 6;
+#pragma unroll
+    for (int i0 = 0; i0 < ITERS; i0 += CHUNK) {
+        uint4 r[CHUNK], b[CHUNK], g[CHUNK];
+#pragma unroll
+        for (int k = 0; k < CHUNK; k++) {
+            const uint32_t c = lane + (i0 + k) * 32;   /* vector c holds elements 8 * lane + 256 * i .. + 7 */
+            const bool live = c < vectors;
+            r[k] = live ? res4[c] : make_uint4(0, 0, 0, 0);
+            b[k] = live ? br4[c] : make_uint4(0, 0, 0, 0);
+            g[k] = live ? gate4[c] : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int k = 0; k < CHUNK; k++) {
+            const int i = i0 + k;
+            const uint32_t c = lane + i * 32;
+            held[i] = make_uint4(0, 0, 0, 0);
+            if (c < vectors) {
+                const uint32_t rw[4] = {r[k].x, r[k].y, r[k].z, r[k].w}, bw[4] = {b[k].x, b[k].y, b[k].z, b[k].w};
+                const uint32_t gw[4] = {g[k].x, g[k].y, g[k].z, g[k].w};
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    /* cvt.rn.bf16x2.f32 rounds to nearest even like the reference's bit arithmetic on every finite value */
+                    o[j] = pack_bf16_pair(__fadd_rn(bf16_lo(rw[j]), __fmul_rn(bf16_lo(bw[j]), bf16_lo(gw[j]))),
+                                          __fadd_rn(bf16_hi(rw[j]), __fmul_rn(bf16_hi(bw[j]), bf16_hi(gw[j]))));
+                    sums[2 * j] = fmaf(bf16_lo(o[j]), bf16_lo(o[j]), sums[2 * j]);
+                    sums[2 * j + 1] = fmaf(bf16_hi(o[j]), bf16_hi(o[j]), sums[2 * j + 1]);
+                }
+                held[i] = make_uint4(o[0], o[1], o[2], o[3]);
+                reinterpret_cast<uint4 *>(gated_residual + row_base)[c] = held[i];
+            }
+        }
+    }
+    /* 256-lane tree: strides 128, 64, 32 (shared-memory steps of the CTA version), then 16, 8 (its shuffles) */
+#pragma unroll
+    for (int shift = 16; shift; shift >>= 1)
+#pragma unroll
+        for (int j = 0; j < 8; j++) sums[j] = __fadd_rn(sums[j], __shfl_down_sync(0xffffffffu, sums[j], shift));
+    float sum = __fadd_rn(__fadd_rn(__fadd_rn(sums[0], sums[4]), __fadd_rn(sums[2], sums[6])),
+                          __fadd_rn(__fadd_rn(sums[1], sums[5]), __fadd_rn(sums[3], sums[7])));
+    const float inverse = __shfl_sync(0xffffffffu, rsqrtf(__fadd_rn(__fdiv_rn(sum, (float)width), epsilon)), 0);
+    const uint4 *nw4 = reinterpret_cast<const uint4 *>(norm_weight);
+    const uint4 *shift4 = reinterpret_cast<const uint4 *>(norm_modulation + base + (size_t)shift_slot * width);
+    const uint4 *scale4 = reinterpret_cast<const uint4 *>(norm_modulation + base + (size_t)scale_slot * width);
+    float local_max = 0.0f;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const uint32_t c = lane + i * 32;
+        if (c < vectors) {
+            const uint4 n = nw4[c], sh = shift4[c], sc = scale4[c];
+            const uint32_t vw[4] = {held[i].x, held[i].y, held[i].z, held[i].w}, nw[4] = {n.x, n.y, n.z, n.w};
+            const uint32_t hw[4] = {sh.x, sh.y, sh.z, sh.w}, cw[4] = {sc.x, sc.y, sc.z, sc.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float n0 = __fmul_rn(__fmul_rn(bf16_lo(vw[j]), inverse), bf16_lo(nw[j]));
+                const float n1 = __fmul_rn(__fmul_rn(bf16_hi(vw[j]), inverse), bf16_hi(nw[j]));
+                o[j] = pack_bf16_pair(__fadd_rn(__fmul_rn(n0, __fadd_rn(1.0f, bf16_lo(cw[j]))), bf16_lo(hw[j])),
+                                      __fadd_rn(__fmul_rn(n1, __fadd_rn(1.0f, bf16_hi(cw[j]))), bf16_hi(hw[j])));
+                local_max = fmaxf(local_max, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
+            }
+            held[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    const float peak = warp_max(local_max);
+    const float out_scale = peak > 0.0f ? __fdiv_rn(peak, 127.0f) : __fdiv_rn(1.0f, 127.0f);
+    const float q_scale = peak > 0.0f ? __fdiv_rn(127.0f, peak) : 127.0f;
+    if (lane == 0) quantized_scales[row] = out_scale;
+#pragma unroll
+    for (int i = 0; i < ITERS; i++) {
+        const uint32_t c = lane + i * 32;
+        if (c < vectors) {
+            const uint32_t w[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
+            uint32_t o[2] = {0, 0};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                uint32_t lo = (uint32_t)quantize_one(bf16_lo(w[j]), q_scale) & 0xffu;
+                uint32_t hi = (uint32_t)quantize_one(bf16_hi(w[j]), q_scale) & 0xffu;
+                o[j >> 1] |= (lo | (hi << 8)) << ((j & 1) * 16);
+            }
+            reinterpret_cast<uint2 *>(quantized + row_base)[c] = make_uint2(o[0], o[1]);
+        }
+    }
 }
 
 /* Weight-only Q8 group packer on the device: one warp per (row, K-group).

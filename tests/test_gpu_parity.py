@@ -74,7 +74,7 @@ def epilogue_operands(seed, M, N, spec):
 
 
 # --------------------------------------------------------------------------- quantisers
-@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 7), (33, 100), (130, 128), (300, 3072), (17, 5000), (5, 12288)])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (3, 7), (33, 100), (130, 128), (300, 3072), (17, 5000), (5, 12288), (9, 1000), (70, 4096), (11, 3080)])
 def test_row_quantiser_bit_exact(gpu, oracle, rows, cols):
     x = synth.activations(11, 1, rows, cols, outliers=synth.outlier_channels(11, cols)).reshape(rows, cols)
     x[0] = 0  # zero row: scale 1/127
@@ -623,7 +623,7 @@ def test_fused_equals_unfused_chain(gpu):
 
 
 # --------------------------------------------------------------------------- producer-side quantiser fusion
-@pytest.mark.parametrize("rows,width", [(5, 256), (130, 5376), (300, 3072)])
+@pytest.mark.parametrize("rows,width", [(5, 256), (130, 5376), (300, 3072), (7, 1000), (9, 7168), (6, 250)])
 def test_gate_adaln_quantize_feeds_the_int8_gemm(oracle, rows, width):
     """h3_gpu_gate_adaln_quantize_int8 (src/gpu.h:630-642, src/metal/shaders.metal:3390-3473) and the int8
     projection that consumes its output without re-reading bf16 activations.  gated_residual is bit-exact;
