@@ -160,6 +160,8 @@ def main():
                          "(config 5): M=219,600 rows sharded over the GPUs, --layers layers of group-128 weights streamed "
                          "from pinned host memory through two device slots")
     ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--stream-gather", type=int, default=0,
+                    help="--workload stream at N > 1: each rank uploads 1/N of a layer, NCCL all-gather assembles it in the local slot")
     ap.add_argument("--group", type=int, default=-1, help="weight scale group for --case (default: 64 for real W8A16 shapes, else per channel)")
     ap.add_argument("--e2e-depth", type=int, default=4, help="end-to-end steps in flight (buffer sets)")
     ap.add_argument("--e2e-slices", type=int, default=1, help="row slices per end-to-end step (copy/compute overlap inside a step)")
@@ -368,7 +370,7 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel<bf16> (256x256 tile per CTA pair) after q8_dequant_kernel" if args.mode == "w8a16"
-                         else "gemm_tcgen05_pair_kernel<int8> after quantize_rows_kernel (peak is the bf16 figure; no int8 peak is recorded)",
+                         else "gemm_tcgen05_pair_kernel<int8> after quantize_segments_warp_kernel (peak is the bf16 figure; no int8 peak is recorded)",
                          "achieved": achieved, "peak": burst, "unit": UNIT, "frac": achieved / burst if achieved else None,
                          "peak_source": f"bf16_tflops (burst) of {which}", "frac_of_sustained": achieved / sustained if achieved and sustained else None,
                          "launches": int(gemm_launches), "avg_launch_ms": gemm_seconds / max(gemm_launches, 1) * 1e3,
@@ -381,6 +383,13 @@ def main():
     if world > 1:
         dist.destroy_process_group()
     gpu.free()
+
+
+class _ByteSpan:
+    """Zero-copy torch view of device bytes (CUDA array interface)."""
+
+    def __init__(self, pointer, count):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "|u1", "data": (pointer, False), "version": 2}
 
 
 def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
@@ -397,7 +406,8 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
     shapes = [(n, k) for _, k, n, _ in LAYERS]
     sizes = [lib.h3q8_q8_blob_bytes(n, k, group, None) for n, k in shapes]
     offsets = [sum(sizes[:i]) for i in range(len(sizes))]
-    slot_bytes = sum(sizes)
+    align = world * 256                                                    # equal 256-byte aligned slices for --stream-gather
+    slot_bytes = (sum(sizes) + align - 1) // align * align
     host = gpu.tensor_alloc(unique * slot_bytes, 2, 2)                    # int8, pinned host memory
     pointer = lib.h3_gpu_tensor_contents(host.handle)
     view = np.ctypeslib.as_array((ctypes.c_uint8 * (unique * slot_bytes)).from_address(pointer))
@@ -415,10 +425,37 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
     inputs = [x, x, x, hidden]
     outputs = [gpu.tensor_new_bf16(rows * n) for n, _ in shapes]
 
+    # --stream-gather (N > 1): every rank pulls only its 1/N byte slice of the layer over PCIe into a staging buffer and
+    # one NCCL all-gather over NVLink assembles the layer in each rank's local slot, on a communication stream, one layer
+    # ahead of the compute stream.  The slot is local memory before any tensor map points at it.
+    gather = bool(args.stream_gather) and world > 1
+    if gather:
+        piece = slot_bytes // world
+        comm = torch.cuda.Stream()
+        staging = [torch.empty(piece, dtype=torch.uint8, device="cuda") for _ in range(2)]
+        host_bytes = torch.from_numpy(view)                 # the pinned host blobs as a CPU tensor (no copy)
+        turn = [0]
+
+        def fetch(layer):
+            """Enqueue the fill of the next slot with layer `layer` on the communication stream; returns the slot."""
+            blob = (layer % unique) * slot_bytes + rank * piece
+            stage = staging[turn[0] % 2]
+            turn[0] += 1
+            with torch.cuda.stream(comm):
+                slot, address = ring.reserve(comm.cuda_stream)
+                stage.copy_(host_bytes[blob:blob + piece], non_blocking=True)
+                target = torch.as_tensor(_ByteSpan(address, slot_bytes), device=f"cuda:{local}")
+                dist.all_gather_into_tensor(target, stage)
+                ring.publish(slot, comm.cuda_stream, slot_bytes)
+            return slot
+    else:
+        def fetch(layer):
+            return ring.prefetch(pointer + (layer % unique) * slot_bytes, slot_bytes)
+
     def one_pass():
-        slot = ring.prefetch(pointer, slot_bytes)
+        slot = fetch(0)
         for layer in range(args.layers):
-            upcoming = ring.prefetch(pointer + ((layer + 1) % unique) * slot_bytes, slot_bytes) if layer + 1 < args.layers else None
+            upcoming = fetch(layer + 1) if layer + 1 < args.layers else None
             ring.acquire(slot)
             for i, (name, k, n, spec) in enumerate(LAYERS):
                 gpu.linear_fused_bf16(outputs[i], inputs[i], views[slot][i], None, gate if "g" in spec else None,
@@ -454,7 +491,9 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
             "metric": METRIC, "workload": "stream", "value": flop / t / 1e12, "unit": UNIT, "n_gpus": world, "passes": passes,
             "layers": args.layers, "rows_total": total_rows, "rows_this_rank": rows, "scaling": "strong",
             "ms_per_layer": t / passes / args.layers * 1e3, "seconds_per_pass": t / passes,
-            "streamed_bytes_per_layer": slot_bytes, "h2d_gbs_this_rank": (after.streamed_bytes - before.streamed_bytes) / t / 1e9,
+            "streamed_bytes_per_layer": slot_bytes, "pcie_bytes_per_layer_this_rank": slot_bytes // world if gather else slot_bytes,
+            "weights_over": "pcie slice + nccl all-gather" if gather else "pcie (whole layer per rank)",
+            "h2d_gbs_this_rank": (after.streamed_bytes - before.streamed_bytes) / t / 1e9,
             "stream_stalls": int(after.stream_stalls - before.stream_stalls),
             "slot_wait_ms_per_pass": (after.stream_wait_seconds - before.stream_wait_seconds) / passes * 1e3, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "large render (BASELINE config 5): 48-layer DiT linear stack, M=219600, W8A16 group-128, "

@@ -152,6 +152,8 @@ def library():
         "h3q8_gpu_weight_stream_create": (vp, [vp, sz, u32]),
         "h3q8_gpu_weight_stream_prefetch": (C.c_int, [vp, vp, sz]),
         "h3q8_gpu_weight_stream_acquire": (C.c_int, [vp, C.c_int]),
+        "h3q8_gpu_weight_stream_reserve": (C.c_int, [vp, vp, C.POINTER(vp)]),
+        "h3q8_gpu_weight_stream_publish": (C.c_int, [vp, C.c_int, vp, sz]),
         "h3q8_gpu_weight_stream_release": (C.c_int, [vp, C.c_int]),
         "h3q8_gpu_weight_stream_view": (vp, [vp, C.c_int, sz, u32, u32, u32]),
         "h3q8_gpu_weight_stream_free": (None, [vp]),
@@ -259,6 +261,17 @@ class WeightStream:
         if slot < 0:
             raise H3Error(self.gpu.error())
         return slot
+
+    def reserve(self, producer_stream):
+        """Next slot for a caller-filled layer: (slot, device pointer); producer_stream waits for the slot's release."""
+        pointer = C.c_void_p()
+        slot = library().h3q8_gpu_weight_stream_reserve(self.handle, producer_stream, C.byref(pointer))
+        if slot < 0:
+            raise H3Error(self.gpu.error())
+        return slot, pointer.value
+
+    def publish(self, slot, producer_stream, nbytes):
+        return self.gpu._check(library().h3q8_gpu_weight_stream_publish(self.handle, slot, producer_stream, nbytes))
 
     def acquire(self, slot):
         return self.gpu._check(library().h3q8_gpu_weight_stream_acquire(self.handle, slot))

@@ -938,6 +938,34 @@ extern "C" int h3q8_gpu_weight_stream_prefetch(h3q8_weight_stream *s, const void
     return slot;
 }
 
+/* A slot filled by the caller's own stream instead of a host copy (an NCCL all-gather of the ranks'
+ * slices, a peer copy): reserve hands out the next slot and makes `producer_stream` wait until the
+ * compute stream has released it; publish records the slot's ready event on that stream.  The slot is
+ * plain local device memory before any kernel of this library reads it. */
+extern "C" int h3q8_gpu_weight_stream_reserve(h3q8_weight_stream *s, void *producer_stream, void **device_pointer) {
+    if (!s || !device_pointer) return -1;
+    h3_gpu *g = s->owner;
+    std::lock_guard<std::mutex> lock(g->copy_mutex);
+    if (cudaSetDevice(g->device) != cudaSuccess) return -1;
+    const int slot = (int)s->next;
+    s->next = (s->next + 1) % s->slots;
+    if (s->released_recorded[slot] &&
+        !checked(g, cudaStreamWaitEvent((cudaStream_t)producer_stream, s->released[slot], 0), "weight stream reserve")) return -1;
+    *device_pointer = s->memory[slot];
+    return slot;
+}
+extern "C" int h3q8_gpu_weight_stream_publish(h3q8_weight_stream *s, int slot, void *producer_stream, size_t bytes) {
+    if (!s || slot < 0 || (uint32_t)slot >= s->slots) return 0;
+    h3_gpu *g = s->owner;
+    if (bytes > s->slot_bytes) return set_error(g, "weight stream: %zu bytes do not fit a %zu-byte slot", bytes, s->slot_bytes);
+    std::lock_guard<std::mutex> lock(g->copy_mutex);
+    if (cudaSetDevice(g->device) != cudaSuccess) return 0;
+    if (!checked(g, cudaEventRecord(s->ready[slot], (cudaStream_t)producer_stream), "weight stream publish event")) return 0;
+    s->ready_recorded[slot] = true;
+    g->stats.streamed_bytes += bytes;
+    return 1;
+}
+
 extern "C" int h3q8_gpu_weight_stream_acquire(h3q8_weight_stream *s, int slot) {
     if (!s || slot < 0 || (uint32_t)slot >= s->slots) return 0;
     h3_gpu *g = s->owner;

@@ -334,6 +334,10 @@ h3_gpu_tensor *h3q8_gpu_q8_from_host(h3_gpu *gpu, const int8_t *weights, const f
 typedef struct h3q8_weight_stream h3q8_weight_stream;
 h3q8_weight_stream *h3q8_gpu_weight_stream_create(h3_gpu *gpu, size_t slot_bytes, uint32_t slots);
 int h3q8_gpu_weight_stream_prefetch(h3q8_weight_stream *stream, const void *host_blob, size_t bytes);
+/* Slots filled by the caller's own stream (e.g. an all-gather of per-rank slices over NVLink): reserve returns the
+ * next slot and its device pointer after making producer_stream wait for the slot's release; publish marks it ready. */
+int h3q8_gpu_weight_stream_reserve(h3q8_weight_stream *stream, void *producer_stream, void **device_pointer);
+int h3q8_gpu_weight_stream_publish(h3q8_weight_stream *stream, int slot, void *producer_stream, size_t bytes);
 int h3q8_gpu_weight_stream_acquire(h3q8_weight_stream *stream, int slot);
 int h3q8_gpu_weight_stream_release(h3q8_weight_stream *stream, int slot);
 h3_gpu_tensor *h3q8_gpu_weight_stream_view(h3q8_weight_stream *stream, int slot, size_t offset, uint32_t rows,
