@@ -155,7 +155,7 @@ def main():
     ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS] + ["helpers"],
                     help="profiling aid: run only this projection (with --rows) and print a short line")
     ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
-    ap.add_argument("--workload", default="block", choices=["block", "stream"],
+    ap.add_argument("--workload", default="block", choices=["block", "stream", "tp_ffn"],
                     help="block: one DiT block stack, weights resident (default, BASELINE config 2); stream: the large render "
                          "(config 5): M=219,600 rows sharded over the GPUs, --layers layers of group-128 weights streamed "
                          "from pinned host memory through two device slots")
@@ -195,9 +195,9 @@ def main():
         def __init__(self, pointer, count):
             self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<i2", "data": (pointer, False), "version": 2}
 
-    def device_bf16(rows, cols, mean=0.0, std=1.0, seed=0):
-        """A resident h3_gpu bf16 tensor filled on the device with seeded normals."""
-        gen = torch.Generator(device="cuda").manual_seed(1000 * rank + seed)
+    def device_bf16(rows, cols, mean=0.0, std=1.0, seed=0, replicated=False):
+        """A resident h3_gpu bf16 tensor filled on the device with seeded normals (per rank unless replicated)."""
+        gen = torch.Generator(device="cuda").manual_seed(seed if replicated else 1000 * rank + seed)
         t = gpu.tensor_new_bf16(rows * cols)
         view = torch.as_tensor(_Span(t.device_pointer, rows * cols), device=f"cuda:{local}").view(torch.bfloat16)
         chunk = 4096
@@ -214,6 +214,8 @@ def main():
         return run_case(args, gpu, lib, stream, device_bf16)
     if args.workload == "stream":
         return run_stream(args, gpu, lib, stream, device_bf16, rank, world, local)
+    if args.workload == "tp_ffn":
+        return run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local)
 
     # ---- operands (weights replicated on every rank: same seed) ----------------------------------
     weights, inputs, outputs, gates, residuals = {}, {}, {}, {}, {}
@@ -383,6 +385,108 @@ def main():
     if world > 1:
         dist.destroy_process_group()
     gpu.free()
+
+
+def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local):
+    """The optional tensor-parallel FFN: every rank sees all M rows; FFN-up is column-parallel (rank r owns FFN
+    features [f0, f1), GELU stays local), FFN-down is row-parallel over the same features, and one NCCL all-reduce
+    per block sums the bf16 partial outputs before gate + residual are applied by the unfused gate operator.  The
+    rows are cut into chunks so the all-reduce of chunk c (communication stream) overlaps the GEMMs of chunk c+1.
+    Partial sums are rounded to bf16 once each, so parity with the unsharded fused call is by tolerance only."""
+    import torch
+    import torch.distributed as dist
+    from h3cli_b200 import sharding
+    rows_total, chunks = args.rows, 4
+    f0, f1 = sharding.feature_range(FFN, rank, world)
+    width = f1 - f0
+    wgen = np.random.default_rng(42)                        # every rank draws the full weights, keeps its slices
+    wup = wgen.integers(-127, 128, (FFN, HIDDEN), dtype=np.int8)
+    sup = np.exp(wgen.normal(np.log(0.01), 0.3, (FFN, 1))).astype(np.float32)
+    wdn = wgen.integers(-127, 128, (HIDDEN, FFN), dtype=np.int8)
+    sdn = np.exp(wgen.normal(np.log(0.01), 0.3, (HIDDEN, 1))).astype(np.float32)
+    up_slice = gpu.q8_from_host(np.ascontiguousarray(wup[f0:f1]), np.ascontiguousarray(sup[f0:f1]), 0)
+    down_slice = gpu.q8_from_host(np.ascontiguousarray(wdn[:, f0:f1]), sdn, 0)
+    gate = device_bf16(1, HIDDEN, 1.0, 0.1, seed=4, replicated=True)
+    comm = torch.cuda.Stream()
+    parts = []
+    for c, (begin, end) in enumerate(sharding.all_ranges(rows_total, chunks)):
+        rows = end - begin
+        part = dict(rows=rows, x=device_bf16(rows, HIDDEN, seed=10 + c, replicated=True),
+                    residual=device_bf16(rows, HIDDEN, seed=20 + c, replicated=True), hidden=gpu.tensor_new_bf16(rows * width),
+                    partial=gpu.tensor_new_bf16(rows * HIDDEN), y=gpu.tensor_new_bf16(rows * HIDDEN))
+        part["view"] = torch.as_tensor(_Span16(part["partial"].device_pointer, rows * HIDDEN), device=f"cuda:{local}").view(torch.bfloat16)
+        parts.append(part)
+
+    def one_block():
+        for p in parts:
+            gpu.linear_fused_bf16(p["hidden"], p["x"], up_slice, None, None, None, p["rows"], HIDDEN, width, 1)
+            gpu.linear_fused_bf16(p["partial"], p["hidden"], down_slice, None, None, None, p["rows"], width, HIDDEN, 0)
+            gpu.continue_()
+            if world > 1:
+                comm.wait_stream(stream)                    # this chunk's partial sums are complete
+                with torch.cuda.stream(comm):
+                    dist.all_reduce(p["view"])
+        for p in parts:                                     # gate + residual once the reduced sums are there
+            if world > 1:
+                stream.wait_stream(comm)
+            gpu.gate_bf16(p["y"], p["residual"], p["partial"], gate, None, p["rows"], HIDDEN, 1, 0)
+        gpu.continue_()
+
+    gpu.begin()
+    for _ in range(args.warmup):
+        one_block()
+    gpu.submit()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    gpu.begin()
+    start.record(stream)
+    for _ in range(args.steps):
+        one_block()
+    stop.record(stream)
+    gpu.submit()
+    torch.cuda.synchronize()
+    seconds = torch.tensor([start.elapsed_time(stop) * 1e-3], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(seconds, op=dist.ReduceOp.MAX)
+    # parity: rank 0 runs the unsharded fused FFN on the first chunk and compares
+    report = None
+    if rank == 0:
+        p = parts[0]
+        full_up, full_down = gpu.q8_from_host(wup, sup, 0), gpu.q8_from_host(wdn, sdn, 0)
+        hidden, want = gpu.tensor_new_bf16(p["rows"] * FFN), gpu.tensor_new_bf16(p["rows"] * HIDDEN)
+        gpu.begin()
+        gpu.linear_fused_bf16(hidden, p["x"], full_up, None, None, None, p["rows"], HIDDEN, FFN, 1)
+        gpu.linear_fused_bf16(want, hidden, full_down, None, gate, p["residual"], p["rows"], FFN, HIDDEN, 0)
+        gpu.submit()
+        f32 = lambda bits: (np.ascontiguousarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+        got_v, want_v = f32(p["y"].read()), f32(want.read())
+        floor = float(np.sqrt((want_v ** 2).mean()))
+        ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(want_v), floor))) - 7)
+        report = {"rel_l2": float(np.sqrt(((got_v - want_v) ** 2).sum() / (want_v ** 2).sum())),
+                  "max_bf16_ulp": float((np.abs(got_v - want_v) / ulp).max()), "rows_checked": p["rows"]}
+        t = float(seconds.item())
+        flop = 2.0 * rows_total * HIDDEN * FFN * 2 * args.steps
+        print(json.dumps({
+            "metric": METRIC, "workload": "tp_ffn", "value": flop / t / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "ms_per_block_ffn": t / args.steps * 1e3, "rows": rows_total, "ffn_features_this_rank": width, "row_chunks": chunks,
+            "allreduce_bytes_per_block": rows_total * HIDDEN * 2 if world > 1 else 0, "scaling": "strong", "dtype": "bf16",
+            "data": "synthetic", "parity_vs_unsharded_fused_call": report,
+            "config": {"workload": "tensor-parallel FFN (optional variant): FFN-up column-parallel with local GELU, FFN-down "
+                                   "row-parallel, one NCCL all-reduce of the bf16 partial sums per block (chunked over rows, "
+                                   "overlapped with the next chunk's GEMMs), gate + residual after the reduction"}}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    gpu.free()
+
+
+class _Span16:
+    """Zero-copy torch view of device 16-bit words (CUDA array interface)."""
+
+    def __init__(self, pointer, count):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<i2", "data": (pointer, False), "version": 2}
 
 
 class _ByteSpan:

@@ -26,3 +26,25 @@ def row_range(rows, rank, world, tile=128):
 
 def all_ranges(rows, world, tile=128):
     return [row_range(rows, r, world, tile) for r in range(world)]
+
+
+def blob_slices(total_bytes, world, align=256):
+    """(padded_bytes, piece_bytes): a streamed layer blob cut into `world` equal, `align`-byte aligned slices
+    (one per rank over PCIe, assembled by an all-gather); padded_bytes = world * piece_bytes >= total_bytes."""
+    if world < 1 or total_bytes < 0:
+        raise ValueError("invalid blob split")
+    unit = world * align
+    padded = (total_bytes + unit - 1) // unit * unit
+    return padded, padded // world
+
+
+def feature_range(features, rank, world, tile=128):
+    """[begin, end) of the FFN features owned by `rank` in the tensor-parallel FFN: the rows of the FFN-up
+    weight (column-parallel, activation local) and the matching K-slice of the FFN-down weight (row-parallel,
+    partial sums all-reduced).  Boundaries are multiples of `tile` so every slice keeps whole k-blocks."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("rank out of range")
+    if features % (tile * world):
+        raise ValueError("FFN width must be a multiple of tile * world")
+    width = features // world
+    return rank * width, (rank + 1) * width

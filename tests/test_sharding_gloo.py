@@ -48,6 +48,28 @@ def _worker(rank, world, port, result_queue):
     padded[begin:end] = part
     gathered = torch.from_numpy(padded)
     dist.all_reduce(gathered)                               # shards are disjoint: the sum is the concatenation
+    # streamed layers at N > 1: each rank holds one aligned byte slice, an all-gather assembles the blob
+    blob = np.frombuffer(synth.int8_weights(6, 1, 1, 70001).tobytes(), dtype=np.uint8)
+    padded, piece = sharding.blob_slices(blob.size, world)
+    whole_blob = np.zeros(padded, np.uint8)
+    whole_blob[:blob.size] = blob
+    pieces = [torch.zeros(piece, dtype=torch.uint8) for _ in range(world)]
+    dist.all_gather(pieces, torch.from_numpy(whole_blob[rank * piece:(rank + 1) * piece].copy()))
+    assert piece % 256 == 0 and (torch.cat(pieces).numpy() == whole_blob).all()
+    # tensor-parallel FFN: GELU(x Wup[f0:f1]^T) Wdown[:, f0:f1]^T summed over the ranks == the unsharded FFN
+    F, H = 512, 64
+    xin = synth.activations(7, 1, 40, H).reshape(40, H)
+    wup, sup = synth.int8_weights(7, 2, F, H), synth.lognormal_scales(7, 3, F, 1)
+    wdn, sdn = synth.int8_weights(7, 4, H, F), synth.lognormal_scales(7, 5, H, 1)
+    f0, f1 = sharding.feature_range(F, rank, world)
+    hid = oracle.linear(oracle.MODE_W8A16, xin, wup[f0:f1], sup[f0:f1], 0, activation=1)
+    partial = oracle.linear(oracle.MODE_W8A16, hid, np.ascontiguousarray(wdn[:, f0:f1]), sdn, 0)
+    total = torch.from_numpy((partial.astype(np.uint32) << 16).view(np.float32).copy())
+    dist.all_reduce(total)                                  # fp32 sum of the bf16 partial sums
+    hid_all = oracle.linear(oracle.MODE_W8A16, xin, wup, sup, 0, activation=1)
+    whole_ffn = (oracle.linear(oracle.MODE_W8A16, hid_all, wdn, sdn, 0).astype(np.uint32) << 16).view(np.float32)
+    ffn_error = float(np.linalg.norm(total.numpy() - whole_ffn) / np.linalg.norm(whole_ffn))
+    assert ffn_error < 4e-3                                 # each partial is rounded to bf16 once: tolerance parity only
     seconds = torch.tensor([0.5 + rank], dtype=torch.float64)
     dist.all_reduce(seconds, op=dist.ReduceOp.MAX)          # job time = slowest rank
     if rank == 0:
@@ -55,6 +77,16 @@ def _worker(rank, world, port, result_queue):
         result_queue.put((bool((gathered.numpy() == whole.astype(np.int32)).all()), float(seconds.item())))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def test_blob_and_feature_splits():
+    for total in (0, 1, 255, 256, 116785152, 116785153):
+        for world in (1, 2, 4, 8):
+            padded, piece = sharding.blob_slices(total, world)
+            assert padded >= total and padded - total < world * 256 and piece * world == padded and piece % 256 == 0
+    assert [sharding.feature_range(12288, r, 8) for r in (0, 7)] == [(0, 1536), (10752, 12288)]
+    with pytest.raises(ValueError):
+        sharding.feature_range(12288, 0, 5)
 
 
 def test_two_rank_sharded_linear_equals_whole():
