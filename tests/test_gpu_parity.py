@@ -872,6 +872,57 @@ def pinned_bytes(gpu, count):
     return host, pointer, view
 
 
+def test_weight_stream_slots_filled_by_the_callers_stream(oracle):
+    """h3q8_gpu_weight_stream_reserve / _publish: a producer stream of the caller (here torch copies standing in
+    for an all-gather of per-rank slices) fills the slots; compute waits for publish, the producer for release."""
+    import torch
+    M, K, N, group, layers = 200, 256, 384, 128, 7
+    gpu = h.Gpu()
+    gpu.quant_configure(1)
+    x = synth.activations(40, 1, M, K).reshape(M, K)
+    weights = [(synth.int8_weights(40 + l, 2, N, K), synth.lognormal_scales(40 + l, 3, N, K // group)) for l in range(layers)]
+    blobs = [torch.from_numpy(h.q8_blob(wq, ws, group)).pin_memory() for wq, ws in weights]
+    slot_bytes = blobs[0].numel()
+    ring = gpu.weight_stream(slot_bytes, 2)
+    producer = torch.cuda.Stream()
+
+    class Bytes:
+        def __init__(self, pointer, count):
+            self.__cuda_array_interface__ = {"shape": (count,), "typestr": "|u1", "data": (pointer, False), "version": 2}
+
+    def fill(layer):
+        with torch.cuda.stream(producer):
+            slot, address = ring.reserve(producer.cuda_stream)
+            half = slot_bytes // 2 // 256 * 256                        # two "slices" written separately
+            target = torch.as_tensor(Bytes(address, slot_bytes), device="cuda")
+            target[:half].copy_(blobs[layer][:half], non_blocking=True)
+            target[half:].copy_(blobs[layer][half:], non_blocking=True)
+            ring.publish(slot, producer.cuda_stream, slot_bytes)
+        return slot
+
+    tx = gpu.tensor_from_bf16(x)
+    outs = [gpu.tensor_new_bf16(M * N) for _ in range(layers)]
+    views = []
+    slot = fill(0)
+    gpu.begin()
+    for layer in range(layers):
+        upcoming = fill(layer + 1) if layer + 1 < layers else None
+        ring.acquire(slot)
+        views.append(ring.view(slot, 0, N, K, group))
+        gpu.linear_fused_bf16(outs[layer], tx, views[-1], None, None, None, M, K, N, 0)
+        ring.release(slot)
+        gpu.continue_()
+        slot = upcoming
+    gpu.submit()
+    torch.cuda.synchronize()
+    for layer, (wq, ws) in enumerate(weights):
+        check_bf16(outs[layer].read().reshape(M, N), oracle.linear(oracle.MODE_W8A16, x, wq, ws, group))
+    assert gpu.stats().streamed_bytes == layers * slot_bytes
+    with pytest.raises(h.H3Error):
+        ring.publish(0, producer.cuda_stream, slot_bytes + 1)
+    gpu.free()
+
+
 def test_weight_streaming_double_buffered(oracle):
     """Config 5 in miniature: packed group-128 layers streamed from pinned host memory
     through two device slots, one layer prefetched while the previous one computes
