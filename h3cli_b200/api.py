@@ -12,6 +12,7 @@ import numpy as np
 MODE_BF16, MODE_W8A16, MODE_W8A8 = 0, 1, 2
 ACT_NONE, ACT_GELU_TANH, ACT_SWIGLU = 0, 1, 2
 KERNEL_AUTO, KERNEL_PLAIN, KERNEL_TCGEN05, KERNEL_TCGEN05_M256, KERNEL_TCGEN05_N128, KERNEL_TCGEN05_PAIR = 0, 1, 2, 3, 4, 5
+KERNEL_TCGEN05_SPLITK = 6
 F32, BF16, I8, U32, F16 = 0, 1, 2, 3, 4
 HOST_VISIBLE, DEVICE_ONLY, HOST_PINNED = 0, 1, 2
 
@@ -30,7 +31,7 @@ class LinearDesc(C.Structure):
         ("input", C.c_void_p), ("weight", C.c_void_p), ("weight_scales", C.c_void_p), ("weight_group", C.c_uint32),
         ("input_scales", C.c_void_p), ("bias", C.c_void_p), ("gate", C.c_void_p), ("residual", C.c_void_p),
         ("activation", C.c_uint32), ("output", C.c_void_p), ("accumulators", C.c_void_p), ("kernel", C.c_uint32),
-        ("input_group", C.c_uint32), ("rope", C.c_void_p),
+        ("input_group", C.c_uint32), ("rope", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -104,6 +105,7 @@ def library():
         "h3q8_cache_artifact": (C.c_char_p, [vp]),
         "h3q8_cache_close": (None, [vp]),
         "h3q8_linear": (C.c_int, [C.POINTER(LinearDesc), vp]),
+        "h3q8_linear_workspace_bytes": (sz, [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]),
         "h3q8_linear_grouped": (C.c_int, [C.POINTER(LinearDesc), u32, vp]),
         "h3q8_linear_w8a8_static": (C.c_int, [C.POINTER(LinearDesc), vp, vp]),
         "h3q8_quantize_rows": (C.c_int, [vp, vp, vp, u32, u32, u32, C.c_float, vp]),

@@ -47,6 +47,10 @@ struct GemmParams {
     uint32_t *status;       /* device error word, 0 = ok                                     */
     uint32_t m_blocks, n_blocks, tiles, band;
     uint64_t l2_policy_a, l2_policy_b; /* TMA L2 eviction policies for activations / weights (two-CTA kernel) */
+    /* split-K (skinny M): `splits` CTAs share one output tile, each accumulates kb_per_split k-blocks and stores its raw
+     * 32-bit accumulators at partials[(split * M + row) * N + col]; splitk_finish_kernel sums them and runs the epilogue */
+    uint32_t splits, kb_per_split;
+    uint32_t *partials;
 };
 
 template <int MODE, int BN, int MT, bool GROUPED>
@@ -58,7 +62,9 @@ struct GemmConfig {
     static constexpr int B_BYTES = BN * ROW_BYTES;              /* MMA operand tile        */
     static constexpr int RAW_BYTES = MODE == MODE_W8A16 ? BN * 64 : 0;
     static constexpr int STAGE_BYTES = A_BYTES + (MODE == MODE_W8A16 ? RAW_BYTES : B_BYTES);
-    static constexpr int CONV_BUFFERS = MODE == MODE_W8A16 ? 2 : 0;
+    /* converted-tile ring: four deep for the 128-wide tile (16 KB each), where skinny problems live on the latency of
+     * the TMA -> convert -> MMA chain and the dequantisers must be able to run ahead of the tensor core */
+    static constexpr int CONV_BUFFERS = MODE == MODE_W8A16 ? (BN == 128 && MT == 1 ? 4 : 2) : 0;
     static constexpr int SMEM_BUDGET = 227 * 1024 - 2048;
     static constexpr int STAGES_FIT = (SMEM_BUDGET - CONV_BUFFERS * B_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_FIT > 6 ? 6 : STAGES_FIT;
@@ -122,7 +128,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
-template <int MODE, int BN, int MT, bool GROUPED>
+template <int MODE, int BN, int MT, bool GROUPED, bool SPLITK = false>
 __global__ void __launch_bounds__(GemmConfig<MODE, BN, MT, GROUPED>::THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                     const GemmParams p) {
@@ -143,6 +149,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     /* k-blocks accumulated before the accumulator is handed to the epilogue */
     const uint32_t kb_per_chunk = GROUPED ? p.scale_group / C::BKE : num_kb;
     const uint32_t chunks = GROUPED ? (num_kb + kb_per_chunk - 1) / kb_per_chunk : 1;
+    static_assert(!(GROUPED && SPLITK), "split-K hands raw sums to a second kernel; grouped scales are combined in this one");
+    /* work items: output tiles, or (tile, K split) pairs */
+    const uint32_t items = SPLITK ? p.tiles * p.splits : p.tiles;
+#define H3Q8_ITEM(item, tile, kb_first, kb_last)                                                        \
+    const uint32_t tile = SPLITK ? (item) / p.splits : (item);                                           \
+    const uint32_t kb_first = SPLITK ? ((item) - tile * p.splits) * p.kb_per_split : 0;                  \
+    const uint32_t kb_last = SPLITK ? (kb_first + p.kb_per_split < num_kb ? kb_first + p.kb_per_split : num_kb) : num_kb;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -164,10 +177,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         /* ------------------------------------------------ TMA producer */
         if (lane == 0) {
             PipeState st;
-            for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
+            for (uint32_t item = blockIdx.x; item < items && !failure; item += gridDim.x) {
+                H3Q8_ITEM(item, tile, kb_first, kb_last)
                 uint32_t mb, nb;
                 tile_coordinates(p, tile, mb, nb);
-                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                for (uint32_t kb = kb_first; kb < kb_last; kb++) {
                     if (!wait_or_abort(&empty[st.index], st.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
                     uint8_t *stage = stages + st.index * C::STAGE_BYTES;
                     mbar_arrive_expect_tx(&full[st.index], C::STAGE_BYTES);
@@ -184,12 +198,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         /* -------------------------------------------------- MMA issuer */
         if (lane == 0) {
             PipeState st, cv, acc;
-            for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
-                uint32_t kb = 0;
+            for (uint32_t item = blockIdx.x; item < items && !failure; item += gridDim.x) {
+                H3Q8_ITEM(item, tile, kb_first, kb_last)
+                (void)tile;
+                uint32_t kb = kb_first;
                 for (uint32_t chunk = 0; chunk < chunks && !failure; chunk++) {
                     if (!wait_or_abort(&tempty[acc.index], acc.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
                     tc_fence_after_sync();
-                    uint32_t last = kb + kb_per_chunk < num_kb ? kb + kb_per_chunk : num_kb;
+                    uint32_t last = kb + kb_per_chunk < kb_last ? kb + kb_per_chunk : kb_last;
                     uint32_t accumulate = 0;
                     for (; kb < last; kb++) {
                         if (!wait_or_abort(&full[st.index], st.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
@@ -230,7 +246,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t quadrant = warp & 3, half = warp >> 2;
         PipeState acc;
         const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
-        for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
+        for (uint32_t item = blockIdx.x; item < items && !failure; item += gridDim.x) {
+            H3Q8_ITEM(item, tile, kb_first, kb_last)
+            (void)kb_last;
             uint32_t mb, nb;
             tile_coordinates(p, tile, mb, nb);
             const uint32_t n0 = nb * BN;
@@ -265,6 +283,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             if (chunk + 1 < chunks) continue;
                         }
                         if (!row_ok) continue;
+                        if (SPLITK) {   /* raw 32-bit sums of this K range; the finishing kernel owns the epilogue */
+                            uint32_t *dst = p.partials + ((size_t)(kb_first / p.kb_per_split) * p.M + row) * p.N + col0;
+#pragma unroll
+                            for (int j4 = 0; j4 < 8; j4++)
+                                if (col0 + j4 * 4 < p.N)
+                                    reinterpret_cast<uint4 *>(dst)[j4] = make_uint4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
+                            continue;
+                        }
                         if (MODE == MODE_W8A8 && !GROUPED && p.acc_dump) {
 #pragma unroll
                             for (int j8 = 0; j8 < 4; j8++)
@@ -326,12 +352,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t chunk0 = (d % THREADS_PER_ROW) * CHUNKS;
         const uint32_t width = p.scale_group ? p.scale_group : p.K;
         PipeState st, cv;
-        for (uint32_t tile = blockIdx.x; tile < p.tiles && !failure; tile += gridDim.x) {
+        for (uint32_t item = blockIdx.x; item < items && !failure; item += gridDim.x) {
+            H3Q8_ITEM(item, tile, kb_first, kb_last)
             uint32_t mb, nb;
             tile_coordinates(p, tile, mb, nb);
             const uint32_t n = nb * BN + r;
             const float *row_scales = p.w_scales + (size_t)n * p.scale_groups;
-            for (uint32_t kb = 0; kb < num_kb; kb++) {
+            for (uint32_t kb = kb_first; kb < kb_last; kb++) {
                 const float scale = n < p.N ? row_scales[(kb * C::BKE) / width] : 0.0f;
                 bool ready = wait_or_abort(&full[st.index], st.phase, abort_flag) &&
                              wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
@@ -382,6 +409,55 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
     }
+}
+
+#undef H3Q8_ITEM
+
+/* Second half of a split-K linear: sums the `splits` partial accumulators of every output in ascending split order
+ * (int32: exact; fp32: one fixed order, so results do not depend on scheduling) and applies the usual epilogue.
+ * One thread per 8 consecutive outputs of a row. */
+template <int MODE>
+__global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) {
+    const uint32_t per_row = p.N / 8;
+    const uint64_t index = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    if (index >= (uint64_t)p.M * per_row) return;
+    const uint32_t row = (uint32_t)(index / per_row), col = (uint32_t)(index % per_row) * 8;
+    const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
+    const uint32_t *src = p.partials + (size_t)row * p.N + col;
+    const size_t stride = (size_t)p.M * p.N;
+    float lin[8];
+    if (MODE == MODE_W8A8) {
+        int32_t sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (uint32_t s = 0; s < p.splits; s++) {
+            const uint4 a = reinterpret_cast<const uint4 *>(src + s * stride)[0], b = reinterpret_cast<const uint4 *>(src + s * stride)[1];
+            const uint32_t v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int j = 0; j < 8; j++) sum[j] += (int32_t)v[j];
+        }
+        const float a_scale = p.a_scales[row];
+        const float4 s0 = *reinterpret_cast<const float4 *>(p.w_scales + col), s1 = *reinterpret_cast<const float4 *>(p.w_scales + col + 4);
+        const float ws[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int j = 0; j < 8; j++) lin[j] = __fmul_rn(__fmul_rn((float)sum[j], a_scale), ws[j]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; j++) lin[j] = 0.0f;
+        for (uint32_t s = 0; s < p.splits; s++) {
+            const uint4 a = reinterpret_cast<const uint4 *>(src + s * stride)[0], b = reinterpret_cast<const uint4 *>(src + s * stride)[1];
+            const uint32_t v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int j = 0; j < 8; j++) lin[j] = s ? __fadd_rn(lin[j], __uint_as_float(v[j])) : __uint_as_float(v[j]);
+        }
+    }
+    uint32_t bias[4] = {0, 0, 0, 0}, gate[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u}, res[4] = {0, 0, 0, 0};
+    if (p.ep.bias) *reinterpret_cast<uint4 *>(bias) = *reinterpret_cast<const uint4 *>(p.ep.bias + col);
+    if (p.ep.gate) *reinterpret_cast<uint4 *>(gate) = *reinterpret_cast<const uint4 *>(p.ep.gate + col);
+    if (p.ep.residual) *reinterpret_cast<uint4 *>(res) = *reinterpret_cast<const uint4 *>(p.ep.residual + (size_t)row * p.N + col);
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        packed[j] = epilogue_pair(lin[2 * j], lin[2 * j + 1], bias[j], p.ep.bias != nullptr, p.ep.activation, gated, gate[j], res[j]);
+    *reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + col) = *reinterpret_cast<uint4 *>(packed);
 }
 
 } /* namespace h3q8 */

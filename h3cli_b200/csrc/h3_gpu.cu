@@ -57,8 +57,9 @@ struct h3_gpu {
     uint32_t group = 0;
     bool group_set = false;
     int w8a16_scratch_rows = 1; /* rows at or above which W8A16 dequantises to scratch first; 0 = never */
-    void *arena[3] = {nullptr, nullptr, nullptr}; /* 0 int8 activations, 1 activation scales, 2 bf16 weight scratch */
-    size_t arena_bytes[3] = {0, 0, 0};
+    void *arena[4] = {nullptr, nullptr, nullptr, nullptr}; /* 0 int8 activations, 1 activation scales, 2 bf16 weight scratch, 3 split-K partial sums */
+    size_t arena_bytes[4] = {0, 0, 0, 0};
+    int skinny_direct = 1;      /* W8A16 with at most 128 rows: main-loop dequantisation + split-K (the weight is read once as int8) */
     uint32_t *flags = nullptr;  /* [0] kernel wait status, [1] non-finite seen */
     void *bounce[2] = {nullptr, nullptr};
     cudaEvent_t bounce_free[2] = {nullptr, nullptr};
@@ -231,6 +232,8 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
         g->allocation_budget = g->weight_options.allocation_limit;
     }
     g->profiling = getenv("H3_PROFILE") != nullptr;
+    const char *skinny = getenv("H3Q8_SKINNY_DIRECT");
+    if (skinny && *skinny) g->skinny_direct = atoi(skinny);
     const char *policy = getenv("H3Q8_W8A16_SCRATCH_ROWS");
     /* measured on B200 (N, K in 3072..12288, M from 16 to 32400): dequantise-then-GEMM is faster than main-loop
      * dequantisation at every M, so it is the default; 0 selects the main-loop kernel */
@@ -269,7 +272,7 @@ extern "C" void h3_gpu_free(h3_gpu *g) {
     h3_gpu_cancel(g);
     for (auto &s : g->spans) { cudaEventDestroy(s.start); cudaEventDestroy(s.stop); }
     for (cudaEvent_t e : g->spare_events) cudaEventDestroy(e);
-    for (int i = 0; i < 3; i++) if (g->arena[i]) cudaFree(g->arena[i]);
+    for (int i = 0; i < 4; i++) if (g->arena[i]) cudaFree(g->arena[i]);
     for (int i = 0; i < 2; i++) {
         if (g->bounce[i]) cudaFreeHost(g->bounce[i]);
         if (g->bounce_free[i]) cudaEventDestroy(g->bounce_free[i]);
@@ -1006,19 +1009,28 @@ extern "C" h3_gpu_tensor *h3q8_gpu_weight_stream_view(h3q8_weight_stream *s, int
 /* ------------------------------------------------------------------ linears */
 static size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
 
-/* Scratch a problem needs from the context arenas: [0] int8 activations, [1] their scales, [2] bf16 weight. */
-static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size_t need[3]) {
-    need[0] = need[1] = need[2] = 0;
-    if (!q.weight || !q.weight->q8) return;
-    if (g->quant_mode == 2) {
+/* Scratch a problem needs from the context arenas: [0] int8 activations, [1] their scales, [2] bf16 weight,
+ * [3] split-K partial sums (problems of at most 128 rows are spread over all SMs). */
+static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size_t need[4]) {
+    need[0] = need[1] = need[2] = need[3] = 0;
+    if (!q.weight) return;
+    const bool swiglu = q.activation == H3Q8_ACT_SWIGLU;
+    uint32_t mode = H3Q8_MODE_BF16;
+    if (q.weight->q8 && g->quant_mode == 2) {
         size_t padded = ((size_t)q.rows + 127u) & ~(size_t)127u;
         need[0] = round256(padded * q.input_dim);
         need[1] = round256(padded * sizeof(float));
-    } else if (q.input_dim % 16 == 0 && (q.activation == H3Q8_ACT_SWIGLU ||
-               (g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows))) {
-        /* SwiGLU always takes this route: its fused kernel wants bf16 or int8 operands */
-        need[2] = round256((size_t)q.output_dim * (q.activation == H3Q8_ACT_SWIGLU ? 2 : 1) * q.input_dim * 2);
+        mode = H3Q8_MODE_W8A8;
+    } else if (q.weight->q8) {
+        const size_t skinny = g->skinny_direct && !swiglu && q.rows <= 128
+                            ? h3q8_linear_workspace_bytes(H3Q8_MODE_W8A16, q.rows, q.input_dim, q.output_dim) : 0;
+        if (q.input_dim % 16 == 0 && !skinny && (swiglu || (g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows))) {
+            /* SwiGLU always takes this route: its fused kernel wants bf16 or int8 operands */
+            need[2] = round256((size_t)q.output_dim * (swiglu ? 2 : 1) * q.input_dim * 2);
+        } else mode = H3Q8_MODE_W8A16;
     }
+    if (!swiglu && q.rows <= 128 && !(mode == H3Q8_MODE_W8A8 && q.weight->q8_group))
+        need[3] = round256(h3q8_linear_workspace_bytes(mode, q.rows, q.input_dim, q.output_dim));
 }
 
 /* The linear operators: validate every problem, run the conversion kernels each needs
@@ -1027,7 +1039,7 @@ static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size
 static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count, const h3q8_rope_desc *rope = nullptr) {
     if (!launch_ready(g)) return 0;
     if (!problems || !count || count > 16) return set_error(g, "linear: between 1 and 16 problems per call");
-    size_t total[3] = {0, 0, 0};
+    size_t total[4] = {0, 0, 0, 0};
     for (uint32_t i = 0; i < count; i++) {
         const h3_gpu_linear_problem &q = problems[i];
         const uint32_t rows = q.rows, k = q.input_dim, n = q.output_dim;
@@ -1047,15 +1059,15 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
         } else if (q.weight->dtype != H3_GPU_BF16 || q.weight->elements < (size_t)wrows * k) {
             return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
         }
-        size_t need[3];
+        size_t need[4];
         linear_scratch(g, q, need);
-        for (int a = 0; a < 3; a++) total[a] += need[a];
+        for (int a = 0; a < 4; a++) total[a] += need[a];
     }
-    for (int a = 0; a < 3; a++)
+    for (int a = 0; a < 4; a++)
         if (total[a] && !arena(g, a, total[a])) return 0;
 
     h3q8_linear_desc descs[16];
-    size_t offset[3] = {0, 0, 0};
+    size_t offset[4] = {0, 0, 0, 0};
     unsigned dispatches = 0;
     for (uint32_t i = 0; i < count; i++) {
         const h3_gpu_linear_problem &q = problems[i];
@@ -1071,8 +1083,9 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
         d.rope = rope;
         d.input = pointer(q.input);
         d.weight = pointer(w);
-        size_t need[3];
+        size_t need[4];
         linear_scratch(g, q, need);
+        if (need[3] && !rope) { d.workspace = (char *)g->arena[3] + offset[3]; d.workspace_bytes = need[3]; }
         if (w->q8) {
             d.weight_scales = (const float *)((const char *)w->data + w->q8_scale_offset);
             d.weight_group = w->q8_group;
@@ -1106,7 +1119,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
             g->stats.q8_dispatches++;
             g->stats.quant_projection_dispatches++;
         } else d.mode = H3Q8_MODE_BF16;
-        for (int a = 0; a < 3; a++) offset[a] += need[a];
+        for (int a = 0; a < 4; a++) offset[a] += need[a];
     }
     const uint64_t before = h3q8_kernel_launches();
     {

@@ -205,6 +205,62 @@ static int launch_pair_grouped(const h3q8_linear_desc &d, const GemmParams &para
     return launch_pair_grouped_kernel(args, MAGIC, dev->sms, stream);
 }
 
+/* Split-K plan for one problem: how many CTAs share an output tile and how many k-blocks each takes.
+ * At least four k-blocks per split, at most as many CTAs as SMs, bounded by the workspace. */
+static bool plan_splitk(uint32_t mode, uint32_t rows, uint32_t k, uint32_t n, int sms, size_t workspace_bytes, uint32_t &splits,
+                        uint32_t &kb_per_split) {
+    const uint32_t bke = mode == H3Q8_MODE_W8A8 ? 128 : 64, num_kb = (k + bke - 1) / bke;
+    const uint64_t tiles = (uint64_t)((rows + 127) / 128) * ((n + 127) / 128);
+    /* a few work items per SM (the kernel is persistent), unless the tiles alone already fill the GPU */
+    /* measured on B200 at 16 rows (device time, graph replay): three work items per SM and at least eight k-blocks
+     * per split were best for 3072 x 3072 (12.7 us), 12288 x 3072 and 3072 x 12288 (30-32 us) */
+    static const int waves = [] { const char *e = getenv("H3Q8_SPLITK_WAVES"); return e && *e && atoi(e) > 0 ? atoi(e) : 3; }();
+    static const int min_kb = [] { const char *e = getenv("H3Q8_SPLITK_MIN_KB"); return e && *e && atoi(e) > 0 ? atoi(e) : 8; }();
+    uint64_t want = tiles && tiles < (uint64_t)sms ? ((uint64_t)waves * sms + tiles - 1) / tiles : 0;
+    if (want > num_kb / (uint32_t)min_kb) want = num_kb / (uint32_t)min_kb;
+    if (want > 32) want = 32;
+    const uint64_t per_split = (uint64_t)rows * n * 4;
+    /* the partial sums are written and read once: keep them below twice the weight bytes they help to stream */
+    const uint64_t weight_bytes = (uint64_t)n * k * (mode == H3Q8_MODE_BF16 ? 2 : 1);
+    if (per_split && want > 2 * weight_bytes / per_split) want = 2 * weight_bytes / per_split;
+    if (per_split && want > workspace_bytes / per_split) want = workspace_bytes / per_split;
+    if (want < 2) return false;
+    kb_per_split = (uint32_t)((num_kb + want - 1) / want);
+    splits = (num_kb + kb_per_split - 1) / kb_per_split;
+    return splits >= 2;
+}
+
+template <int MODE>
+static int launch_splitk(const h3q8_linear_desc &d, GemmParams p, DeviceState *dev, cudaStream_t stream) {
+    using C = GemmConfig<MODE, 128, 1, false>;
+    if (!plan_splitk(d.mode, d.rows, d.input_dim, d.output_dim, dev->sms, d.workspace_bytes, p.splits, p.kb_per_split))
+        return fail("linear: split-K needs a workspace of at least 2 * rows * output_dim * 4 bytes and K of 16 k-blocks or more");
+    p.partials = static_cast<uint32_t *>(d.workspace);
+    CUtensorMap map_a, map_b;
+    const uint32_t a_bytes = MODE == MODE_W8A8 ? 1 : 2, b_bytes = MODE == MODE_BF16 ? 2 : 1;
+    if (!make_map(&map_a, d.input, a_bytes, d.rows, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    if (!make_map(&map_b, d.weight, b_bytes, d.output_dim, d.input_dim, C::BKE, 128,
+                  MODE == MODE_W8A16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    p.m_blocks = (d.rows + 127) / 128;
+    p.n_blocks = (d.output_dim + 127) / 128;
+    p.tiles = p.m_blocks * p.n_blocks;
+    p.band = p.m_blocks < 16 ? p.m_blocks : 16;
+    auto kernel = gemm_tcgen05_kernel<MODE, 128, 1, false, true>;
+    static bool configured[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (!configured[device]) {
+        if (!cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES), "shared memory opt-in")) return 0;
+        configured[device] = true;
+    }
+    const uint32_t items = p.tiles * p.splits;
+    kernel<<<items < (uint32_t)dev->sms ? items : (uint32_t)dev->sms, C::THREADS, C::SMEM_BYTES, stream>>>(map_a, map_b, p);
+    const uint64_t outputs8 = (uint64_t)d.rows * (d.output_dim / 8);
+    splitk_finish_kernel<MODE><<<(unsigned)((outputs8 + 255) / 256), 256, 0, stream>>>(p);
+    count_launch(2);
+    return cuda_ok(cudaGetLastError(), "tcgen05 split-K linear launch");
+}
+
 template <int MODE>
 static int launch_plain(const h3q8_linear_desc &d, const GemmParams &p, cudaStream_t stream) {
     dim3 grid((d.output_dim + 63) / 64, (d.rows + 63) / 64);
@@ -217,6 +273,7 @@ template <int MODE>
 static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t kernel, DeviceState *dev, cudaStream_t stream) {
     const bool grouped8 = MODE == MODE_W8A8 && p.scale_group != 0;
     if (kernel == H3Q8_KERNEL_PLAIN) return launch_plain<MODE>(d, p, stream);
+    if (kernel == H3Q8_KERNEL_TCGEN05_SPLITK) return launch_splitk<MODE>(d, p, dev, stream);
     if (grouped8) {
         if (MODE != MODE_W8A8) return fail("grouped W8A8 reached a non-W8A8 launch");
         if (kernel == H3Q8_KERNEL_TCGEN05_PAIR)
@@ -293,7 +350,10 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     const bool grouped_pair_ok = d.mode == H3Q8_MODE_W8A8 && p.scale_group && p.scale_group % 128 == 0 &&
                                  d.input_dim % p.scale_group == 0 && !swiglu && !d.rope;
     kernel = d.kernel;
-    if (kernel > H3Q8_KERNEL_TCGEN05_PAIR) return fail("linear: unknown kernel selector %u", kernel);
+    if (kernel > H3Q8_KERNEL_TCGEN05_SPLITK) return fail("linear: unknown kernel selector %u", kernel);
+    /* split-K: raw sums go through the workspace, so no per-group combine, second accumulator, rotary epilogue or dump */
+    const bool splitk_ok = !(d.mode == H3Q8_MODE_W8A8 && p.scale_group) && !swiglu && !d.rope && !d.accumulators && d.workspace &&
+                           aligned16(d.workspace);
     if (kernel == H3Q8_KERNEL_AUTO) {
         const bool tiny = (uint64_t)d.rows * d.input_dim * d.output_dim <= (1u << 22);
         /* two-CTA tiles need both CTAs to have rows; main-loop dequantisation stays single-CTA */
@@ -301,6 +361,11 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
         kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128
                : pair_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_TCGEN05;
         /* SwiGLU runs on the two-CTA kernel (gate rows in one CTA, up rows in its peer) or on the plain kernel */
+        /* one row tile: the weight is streamed once and the problem is bandwidth bound, so spread K over the idle SMs */
+        uint32_t splits, kb_per_split;
+        if (kernel != H3Q8_KERNEL_PLAIN && d.rows <= 128 && splitk_ok &&
+            plan_splitk(d.mode, d.rows, d.input_dim, d.output_dim, dev->sms, d.workspace_bytes, splits, kb_per_split))
+            kernel = H3Q8_KERNEL_TCGEN05_SPLITK;
         if (swiglu) kernel = tma_ok && d.mode != H3Q8_MODE_W8A16 ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_PLAIN;
         if (d.rope) kernel = H3Q8_KERNEL_TCGEN05_PAIR;
     }
@@ -316,6 +381,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
         return fail("linear: SwiGLU is available on the two-CTA and the plain kernel");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && p.scale_group && !grouped_pair_ok))) {
         return fail("linear: the two-CTA kernel takes bf16 or int8 operands (scale groups: multiples of 128 that divide K)");
+    } else if (kernel == H3Q8_KERNEL_TCGEN05_SPLITK && !splitk_ok) {
+        return fail("linear: split-K takes ungrouped scales, no SwiGLU / rotary epilogue / accumulator dump, and a 16-byte aligned workspace");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {
         return fail("linear %ux%ux%u: shape or alignment not supported by the tcgen05 kernel "
                     "(K %% %u, N %% 8, 16-byte aligned operands, scale group %% 64/128)",
@@ -343,6 +410,13 @@ static int linear_one(const h3q8_linear_desc &d, cudaStream_t stream) {
     uint32_t kernel;
     DeviceState *dev;
     return plan_linear(d, p, kernel, dev) && launch_planned(d, p, kernel, dev, stream);
+}
+
+extern "C" size_t h3q8_linear_workspace_bytes(uint32_t mode, uint32_t rows, uint32_t input_dim, uint32_t output_dim) {
+    DeviceState *dev = device_state();
+    uint32_t splits = 0, kb_per_split = 0;
+    if (!dev || rows > 128 || !plan_splitk(mode, rows, input_dim, output_dim, dev->sms, SIZE_MAX, splits, kb_per_split)) return 0;
+    return (size_t)splits * rows * output_dim * 4;
 }
 
 extern "C" int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream) {

@@ -90,8 +90,11 @@ enum { /* kernel selection; AUTO picks by shape */
     H3Q8_KERNEL_TCGEN05 = 2,   /* tcgen05/TMA kernel, 128 x 256 tiles               */
     H3Q8_KERNEL_TCGEN05_M256 = 3, /* tcgen05/TMA kernel, 256 x 256 tiles            */
     H3Q8_KERNEL_TCGEN05_N128 = 4, /* tcgen05/TMA kernel, 128 x 128 tiles            */
-    H3Q8_KERNEL_TCGEN05_PAIR = 5  /* two-CTA tcgen05 kernel, 256 x 256 tiles per CTA
+    H3Q8_KERNEL_TCGEN05_PAIR = 5, /* two-CTA tcgen05 kernel, 256 x 256 tiles per CTA
                                      pair (BF16 and W8A8 per-channel modes)         */
+    H3Q8_KERNEL_TCGEN05_SPLITK = 6 /* skinny M: 128 x 128 tiles, K split over several
+                                     CTAs per tile, partial sums in `workspace`, then
+                                     a finishing kernel (weight-bandwidth bound)     */
 };
 
 /* QKV epilogue (src/cuda/cuda_kernels.cuh:988-1045 with the grouped column layout of
@@ -135,7 +138,12 @@ typedef struct {
                                  src/metal/shaders.metal:2663-2742); 0 = one scale per token   */
     const h3q8_rope_desc *rope; /* optional QKV norm + rotary epilogue; output may then be NULL
                                  (when given it also receives the plain bf16 projection)       */
+    void *workspace;          /* optional device scratch (16-byte aligned) for split-K partial sums: with it, problems of
+                                 at most 128 rows spread over all SMs (AUTO); needs splits * rows * output_dim * 4 bytes  */
+    size_t workspace_bytes;
 } h3q8_linear_desc;
+/* Bytes of workspace that let a rows x output_dim x input_dim problem use every SM (0 when split-K would not help). */
+size_t h3q8_linear_workspace_bytes(uint32_t mode, uint32_t rows, uint32_t input_dim, uint32_t output_dim);
 int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream);
 
 /* Several independent problems in one call (video + audio streams of the DiT):

@@ -316,6 +316,56 @@ def test_w8a8_group128_weight_scales(gpu, oracle, M, N, K, kernel):
     assert (got == want).all()
 
 
+@pytest.mark.parametrize("kernel", [h.KERNEL_TCGEN05_SPLITK, h.KERNEL_AUTO])
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 3072), (16, 3072, 3072), (100, 520, 1536), (128, 1536, 12288), (77, 256, 1000 * 16)])
+@pytest.mark.parametrize("mode", ["bf16", "w8a16", "w8a16g128", "w8a8"])
+def test_skinny_split_k(gpu, oracle, mode, M, N, K, kernel):
+    """At most 128 rows: the K range of every 128 x 128 tile is split over several CTAs (partial sums in a
+    caller-provided workspace, summed in a fixed order by a finishing kernel that owns the epilogue).
+    int32 partial sums are exact, so W8A8 stays bit-equal to the oracle; bf16 / W8A16 change the fp32 order."""
+    group = 128 if mode == "w8a16g128" else 0
+    if group and K % 128:
+        pytest.skip("group width must divide K")
+    x, wq, ws = operands(61, M, N, K, group, outliers=mode == "w8a8")
+    bias, gate, res, act = epilogue_operands(61, M, N, "bgr" if M % 2 else "ba")
+    lib = h.library()
+    mode_id = {"bf16": h.MODE_BF16, "w8a16": h.MODE_W8A16, "w8a16g128": h.MODE_W8A16, "w8a8": h.MODE_W8A8}[mode]
+    nbytes = lib.h3q8_linear_workspace_bytes(mode_id, M, K, N)
+    assert lib.h3q8_linear_workspace_bytes(mode_id, 129, K, N) == 0
+    if not nbytes:                                   # too few k-blocks to split (int8 k-blocks are 128 wide)
+        assert mode == "w8a8" and K < 2048
+        pytest.skip("K too short for split-K in this mode")
+    assert nbytes >= 2 * M * N * 4
+    workspace = gpu.tensor_alloc(nbytes + 64, 2)
+    if mode == "bf16":
+        wb = oracle.q8_dequant(wq, ws, 0)
+        want = oracle.linear(oracle.MODE_BF16, x, wb, bias=bias, gate=gate, residual=res, activation=act)
+        t = upload(gpu, input=x, weight=wb, bias=bias, gate=gate, residual=res)
+    elif mode == "w8a8":
+        xq, xs = oracle.quantize_rows(x)
+        want = oracle.linear(oracle.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, x_scales=xs, bias=bias, gate=gate, residual=res, activation=act, fast=True)
+        t = upload(gpu, input=xq, weight=wq, weight_scales=ws[:, 0].copy(), input_scales=xs, bias=bias, gate=gate, residual=res)
+    else:
+        want = oracle.linear(oracle.MODE_W8A16, x, wq, ws, group, bias=bias, gate=gate, residual=res, activation=act)
+        t = upload(gpu, input=x, weight=wq, weight_scales=ws, bias=bias, gate=gate, residual=res)
+    out = gpu.tensor_from_bf16(np.full(M * N + GUARD, 0x3F80, np.uint16))
+    launches = lib.h3q8_kernel_launches()
+    gpu.raw_linear(mode=mode_id, rows=M, input_dim=K, output_dim=N, weight_group=group, activation=act, kernel=kernel, output=out,
+                   workspace=workspace, workspace_bytes=nbytes, **t)
+    assert gpu.raw_status() == 0 and lib.h3q8_kernel_launches() - launches == 2      # split GEMM + finishing kernel
+    got = out.read()
+    assert (got[M * N:] == 0x3F80).all(), "wrote past the end of the output"
+    if mode == "w8a8" and not act:
+        assert (got[:M * N].reshape(M, N) == want).all()
+    else:
+        check_bf16(got[:M * N].reshape(M, N), want)
+    with pytest.raises(h.H3Error):
+        gpu.raw_linear(mode=mode_id, rows=M, input_dim=K, output_dim=N, weight_group=group, activation=act,
+                       kernel=h.KERNEL_TCGEN05_SPLITK, output=out, workspace=workspace, workspace_bytes=M * N * 4, **t)
+    for tensor in list(t.values()) + [out, workspace]:
+        tensor.free()
+
+
 @pytest.mark.parametrize("spec", ["", "bgr", "ba"])
 @pytest.mark.parametrize("M,N,K,group,both", [(1000, 776, 1024, 128, False), (513, 256, 3072, 256, True), (700, 1032, 2048, 512, False),
                                               (2100, 3072, 1536, 128, True)])
