@@ -13,8 +13,9 @@ collective); the job value is total TFLOP/s with the slowest rank's device time.
 Prints one JSON line (rank 0): `value` with operands resident in HBM, `e2e`
 through the h3_gpu_* operator interface with host buffers, `roofline` of the
 GEMM kernel from CUDA events, `cpu_baseline` = the CPU restatement on a bounded
-row slab.  `--impl reference` times only that CPU restatement (the reference has
-no CPU or CUDA int8 linear of its own to run).
+row slab.  `--impl reference` times only that CPU restatement: the reference's
+int8 linears exist as Metal shaders only, it has no CPU or CUDA implementation
+of this path that could be run here.
 """
 import argparse
 import json
