@@ -358,8 +358,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tile_coordinates(p, tile, mb, nb);
             const uint32_t n = nb * BN + r;
             const float *row_scales = p.w_scales + (size_t)n * p.scale_groups;
+            /* the scale of the next k-block is fetched before this one is converted: an L2 round trip per k-block on
+             * the convert -> MMA chain was the largest stall of skinny problems (one load per tile for per-channel scales) */
+            float upcoming = n < p.N && kb_first < kb_last ? row_scales[(kb_first * C::BKE) / width] : 0.0f;
             for (uint32_t kb = kb_first; kb < kb_last; kb++) {
-                const float scale = n < p.N ? row_scales[(kb * C::BKE) / width] : 0.0f;
+                const float scale = upcoming;
+                if (p.scale_groups > 1 && kb + 1 < kb_last && n < p.N) upcoming = row_scales[((kb + 1) * C::BKE) / width];
                 bool ready = wait_or_abort(&full[st.index], st.phase, abort_flag) &&
                              wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_DEQUANT; break; }
