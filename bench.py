@@ -153,7 +153,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="h3q8")
-    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS] + ["helpers"],
+    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS] + ["helpers", "grouped_streams"],
                     help="profiling aid: run only this projection (with --rows) and print a short line")
     ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
     ap.add_argument("--workload", default="block", choices=["block", "stream", "tp_ffn"],
@@ -212,6 +212,8 @@ def main():
 
     if args.case == "helpers":
         return run_helpers(args, gpu, lib, stream, device_bf16)
+    if args.case == "grouped_streams":
+        return run_grouped_streams(args, gpu, lib, stream, device_bf16)
     if args.case:
         return run_case(args, gpu, lib, stream, device_bf16)
     if args.workload == "stream":
@@ -606,6 +608,43 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
                                    "weights streamed per layer from pinned host memory, 2 device slots"}}), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    gpu.free()
+
+
+def run_grouped_streams(args, gpu, lib, stream, device_bf16):
+    """BASELINE's grouped-GEMM configuration: the video stream (M = 2 x 32 400, K = N = 3072) and the audio stream
+    (M = 2 x 1 152, K = N = 1536) with separate int8 weight sets, as ONE call (one GEMM launch over both problems)
+    and as two calls, same operands."""
+    import torch
+    specs = [("video", 2 * 32400, 3072, 3072), ("audio", 2 * 1152, 1536, 1536)]
+    wgen = np.random.default_rng(42)
+    problems = []
+    for i, (_, rows, k, n) in enumerate(specs):
+        wq = wgen.integers(-127, 128, (n, k), dtype=np.int8)
+        ws = np.exp(wgen.normal(np.log(0.01), 0.3, (n, 1))).astype(np.float32)
+        problems.append(dict(output=gpu.tensor_new_bf16(rows * n), input=device_bf16(rows, k, seed=30 + i), weight=gpu.q8_from_host(wq, ws, 0),
+                             rows=rows, input_dim=k, output_dim=n))
+    flop = sum(2.0 * rows * k * n for _, rows, k, n in specs)
+
+    def timed(call):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        gpu.begin()
+        for i in range(args.warmup + args.steps):
+            if i == args.warmup:
+                start.record(stream)
+            call()
+        stop.record(stream)
+        gpu.submit()
+        return start.elapsed_time(stop) / args.steps
+
+    before = lib.h3q8_kernel_launches()
+    together = timed(lambda: gpu.linear_grouped_bf16(problems))
+    launches = (lib.h3q8_kernel_launches() - before) // (args.warmup + args.steps)
+    separate = timed(lambda: [gpu.linear_fused_bf16(p["output"], p["input"], p["weight"], None, None, None, p["rows"], p["input_dim"],
+                                                    p["output_dim"], 0) for p in problems])
+    print(json.dumps({"case": "grouped_streams", "mode": args.mode, "problems": [dict(name=s[0], rows=s[1], k=s[2], n=s[3]) for s in specs],
+                      "one_call_ms": together, "one_call_tflops": flop / together / 1e9, "kernels_per_call": int(launches),
+                      "two_calls_ms": separate, "two_calls_tflops": flop / separate / 1e9}), flush=True)
     gpu.free()
 
 
