@@ -172,6 +172,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     uint32_t failure = STATUS_OK;
+    /* split-K: let the finishing grid be scheduled as SMs drain (it waits for this grid's completion before reading) */
+    if (SPLITK) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == C::PRODUCER_WARP) {
         /* ------------------------------------------------ TMA producer */
@@ -424,6 +426,9 @@ template <int MODE>
 __global__ void __launch_bounds__(256) splitk_finish_kernel(const GemmParams p) {
     const uint32_t per_row = p.N / 8;
     const uint64_t index = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    /* launched with programmatic stream serialisation: this grid may be resident before the split GEMM has finished;
+     * nothing it wrote is read before this point */
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (index >= (uint64_t)p.M * per_row) return;
     const uint32_t row = (uint32_t)(index / per_row), col = (uint32_t)(index % per_row) * 8;
     const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;

@@ -256,9 +256,20 @@ static int launch_splitk(const h3q8_linear_desc &d, GemmParams p, DeviceState *d
     const uint32_t items = p.tiles * p.splits;
     kernel<<<items < (uint32_t)dev->sms ? items : (uint32_t)dev->sms, C::THREADS, C::SMEM_BYTES, stream>>>(map_a, map_b, p);
     const uint64_t outputs8 = (uint64_t)d.rows * (d.output_dim / 8);
-    splitk_finish_kernel<MODE><<<(unsigned)((outputs8 + 255) / 256), 256, 0, stream>>>(p);
+    /* the finishing grid is launched with programmatic stream serialisation: its blocks become resident while the
+     * GEMM drains and wait (griddepcontrol.wait) for the GEMM's completion before they read the partial sums */
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3((unsigned)((outputs8 + 255) / 256));
+    config.blockDim = dim3(256);
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, splitk_finish_kernel<MODE>, p);
     count_launch(2);
-    return cuda_ok(cudaGetLastError(), "tcgen05 split-K linear launch");
+    return cuda_ok(e != cudaSuccess ? e : cudaGetLastError(), "tcgen05 split-K linear launch");
 }
 
 template <int MODE>
