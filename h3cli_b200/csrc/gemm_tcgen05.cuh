@@ -159,7 +159,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], C::DEQUANT_WARPS); mbar_init(&bempty[s], 1); }
+        for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], C::DEQUANT_WARPS / 2); mbar_init(&bempty[s], 1); }
         for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], C::EPILOGUE_WARPS); }
         *abort_flag = 0;
         fence_barrier_init();
@@ -345,48 +345,65 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (MODE == MODE_W8A16) {
         /* ------------------------------------------------- dequantisers */
-        /* 256 threads convert the BN x 64 int8 tile (64-byte rows, 64-byte swizzle)
-         * into a BN x 64 bf16 tile (128-byte rows, 128-byte swizzle). */
-        constexpr int THREADS_PER_ROW = 256 / BN;           /* 1 (BN=256) or 2 (BN=128) */
-        constexpr int CHUNKS = 4 / THREADS_PER_ROW;         /* 16-byte int8 chunks per thread */
-        const uint32_t d = threadIdx.x - C::FIRST_DEQUANT_WARP * 32;
-        const uint32_t r = d / THREADS_PER_ROW;
-        const uint32_t chunk0 = (d % THREADS_PER_ROW) * CHUNKS;
+        /* Two groups of four warps take alternate k-blocks: a group turns a whole BN x 64 int8 tile (64-byte rows,
+         * 64-byte swizzle) into a BN x 64 bf16 tile (128-byte rows, 128-byte swizzle), one 64-byte row per thread and
+         * pass.  Each warp then pays the wait -> convert -> fence.proxy.async -> arrive latency once per TWO k-blocks,
+         * and the groups overlap each other (that chain, not the arithmetic, set the pace with all eight warps on
+         * every k-block). */
+        constexpr int ROWS = BN / 128;                      /* rows per thread */
+        const uint32_t group = (warp - C::FIRST_DEQUANT_WARP) >> 2;
+        const uint32_t d = threadIdx.x - (C::FIRST_DEQUANT_WARP + 4 * group) * 32;   /* 0..127 inside the group */
         const uint32_t width = p.scale_group ? p.scale_group : p.K;
         PipeState st, cv;
+        uint32_t turn = 0;                                  /* k-blocks seen so far, across tiles */
         for (uint32_t item = blockIdx.x; item < items && !failure; item += gridDim.x) {
             H3Q8_ITEM(item, tile, kb_first, kb_last)
             uint32_t mb, nb;
             tile_coordinates(p, tile, mb, nb);
-            const uint32_t n = nb * BN + r;
-            const float *row_scales = p.w_scales + (size_t)n * p.scale_groups;
-            /* the scale of the next k-block is fetched before this one is converted: an L2 round trip per k-block on
-             * the convert -> MMA chain was the largest stall of skinny problems (one load per tile for per-channel scales) */
-            float upcoming = n < p.N && kb_first < kb_last ? row_scales[(kb_first * C::BKE) / width] : 0.0f;
-            for (uint32_t kb = kb_first; kb < kb_last; kb++) {
-                const float scale = upcoming;
-                if (p.scale_groups > 1 && kb + 1 < kb_last && n < p.N) upcoming = row_scales[((kb + 1) * C::BKE) / width];
+            const float *row_scales[ROWS];
+            bool live[ROWS];
+            float upcoming[ROWS];
+            /* this group's first k-block of the tile; its scales are fetched before they are needed */
+            const uint32_t mine_first = kb_first + ((turn & 1u) == group ? 0u : 1u);
+#pragma unroll
+            for (int rr = 0; rr < ROWS; rr++) {
+                const uint32_t n = nb * BN + d + rr * 128;
+                live[rr] = n < p.N;
+                row_scales[rr] = p.w_scales + (size_t)(live[rr] ? n : 0) * p.scale_groups;
+                upcoming[rr] = live[rr] && mine_first < kb_last ? row_scales[rr][(mine_first * C::BKE) / width] : 0.0f;
+            }
+            for (uint32_t kb = kb_first; kb < kb_last; kb++, turn++) {
+                if ((turn & 1u) != group) { st.advance(C::STAGES); cv.advance(C::CONV_BUFFERS); continue; }
+                float scale[ROWS];
+#pragma unroll
+                for (int rr = 0; rr < ROWS; rr++) {
+                    scale[rr] = upcoming[rr];
+                    if (p.scale_groups > 1 && kb + 2 < kb_last && live[rr]) upcoming[rr] = row_scales[rr][((kb + 2) * C::BKE) / width];
+                }
                 bool ready = wait_or_abort(&full[st.index], st.phase, abort_flag) &&
                              wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_DEQUANT; break; }
                 const uint8_t *raw = stages + st.index * C::STAGE_BYTES + C::A_BYTES;
                 uint8_t *dst = conv + cv.index * C::B_BYTES;
 #pragma unroll
-                for (int c = 0; c < CHUNKS; c++) {
-                    const uint32_t chunk = chunk0 + c;
-                    const uint4 q = *reinterpret_cast<const uint4 *>(raw + r * 64 + ((chunk ^ ((r >> 1) & 3)) << 4));
-                    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-                    uint32_t o[8];
+                for (int rr = 0; rr < ROWS; rr++) {
+                    const uint32_t r = d + rr * 128;
 #pragma unroll
-                    for (int w = 0; w < 4; w++) {
-                        float f[4];
-                        dequant4(words[w], scale, f);
-                        o[2 * w] = pack_bf16x2(f[0], f[1]);
-                        o[2 * w + 1] = pack_bf16x2(f[2], f[3]);
+                    for (int chunk = 0; chunk < 4; chunk++) {
+                        const uint4 q = *reinterpret_cast<const uint4 *>(raw + r * 64 + ((chunk ^ ((r >> 1) & 3)) << 4));
+                        const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+                        uint32_t o[8];
+#pragma unroll
+                        for (int w = 0; w < 4; w++) {
+                            float f[4];
+                            dequant4(words[w], scale[rr], f);
+                            o[2 * w] = pack_bf16x2(f[0], f[1]);
+                            o[2 * w + 1] = pack_bf16x2(f[2], f[3]);
+                        }
+                        uint8_t *row_dst = dst + r * 128;
+                        *reinterpret_cast<uint4 *>(row_dst + (((2 * chunk) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        *reinterpret_cast<uint4 *>(row_dst + (((2 * chunk + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
                     }
-                    uint8_t *row_dst = dst + r * 128;
-                    *reinterpret_cast<uint4 *>(row_dst + (((2 * chunk) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    *reinterpret_cast<uint4 *>(row_dst + (((2 * chunk + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
