@@ -163,6 +163,9 @@ def library():
         "h3_gpu_quantize_weight_int8": (C.c_int, [vp, vp, vp, vp, u32, u32]),
         "h3_gpu_linear_int8_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
         "h3_gpu_gate_adaln_quantize_int8": (C.c_int, [vp] * 10 + [u32] * 7 + [C.c_float]),
+        "h3_gpu_linear_int8_head_major_bf16": (C.c_int, [vp] * 7 + [u32] * 4),
+        "h3_gpu_mlp_int8_bf16": (C.c_int, [vp] * 12 + [u32] * 4 + [C.c_int] * 4),
+        "h3_gpu_grouped_qkv_linear_rope_int8": (C.c_int, [vp] * 13 + [u32] * 5 + [C.c_float] + [C.c_int] * 4),
         "h3_gpu_linear_fused_int8_bf16": (C.c_int, [vp, vp, vp, vp, u32, vp, vp, vp, vp, u32, u32, u32, C.c_int]),
         "h3_gpu_gelu_bf16": (C.c_int, [vp, vp, vp, u32, C.c_int]),
         "h3_gpu_gate_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]),
@@ -443,6 +446,27 @@ class Gpu:
             self.handle, _h(gated_residual), _h(quantized_output), _h(quantized_scales), _h(residual), _h(branch),
             _h(norm_weight), _h(gate_modulation), _h(norm_modulation), _h(row_map), rows, padded_rows, width, slots,
             gate_slot, shift_slot, scale_slot, epsilon))
+
+    def linear_int8_head_major_bf16(self, output, quantized_input, input_scales, input, weight, weight_scales, rows, heads, head_dim,
+                                    output_dim):
+        return self._check(library().h3_gpu_linear_int8_head_major_bf16(
+            self.handle, _h(output), _h(quantized_input), _h(input_scales), _h(input), _h(weight), _h(weight_scales), rows, heads,
+            head_dim, output_dim))
+
+    def mlp_int8_bf16(self, output, activated, quantized_activation, activation_scales, input, fc1_weight, fc1_scales, fc2_weight,
+                      fc2_scales, rows, input_dim, hidden_dim, output_dim, use_int8_row_fc2=0, input_is_quantized=0):
+        return self._check(library().h3_gpu_mlp_int8_bf16(
+            self.handle, _h(output), _h(activated), _h(quantized_activation), _h(activation_scales), _h(input), _h(fc1_weight),
+            _h(fc1_scales), _h(fc2_weight), _h(fc2_scales), None, None, rows, input_dim, hidden_dim, output_dim, 0, 0,
+            use_int8_row_fc2, input_is_quantized))
+
+    def grouped_qkv_linear_rope_int8(self, query, key, value, quantized_input, input_scales, input, weight, weight_scales, q_norm,
+                                     k_norm, rope_cos, rope_sin, rows, input_dim, heads, head_dim, rope_half, epsilon,
+                                     input_is_quantized=0):
+        return self._check(library().h3_gpu_grouped_qkv_linear_rope_int8(
+            self.handle, _h(query), _h(key), _h(value), _h(quantized_input), _h(input_scales), _h(input), _h(weight),
+            _h(weight_scales), _h(q_norm), _h(k_norm), _h(rope_cos), _h(rope_sin), rows, input_dim, heads, head_dim, rope_half,
+            epsilon, input_is_quantized, 0, 0, 0))
 
     def linear_fused_int8_bf16(self, output, quantized_input, input_scales, input_group, weight, bias, gate, residual,
                                rows, input_dim, output_dim, activation):

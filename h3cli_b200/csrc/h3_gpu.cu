@@ -1395,6 +1395,173 @@ extern "C" int h3_gpu_grouped_qkv_linear_rope_bf16(h3_gpu *g, h3_gpu_tensor *q, 
            h3_gpu_grouped_qkv_rope_bf16(g, q, k, v, qkv, qw, kw, c, s, rows, heads, dim, half, epsilon);
 }
 
+/* ----------------------------------------------- the int8 operator family */
+/* One W8A8 projection on int8 activations and a separate int8 weight + fp32 per-channel scale tensor pair
+ * (the layout of the reference's int8 family, src/gpu.h:521-563): optional SwiGLU (weight rows [gate n | up n]),
+ * per-K-group activation scales, or the QKV norm + rotary epilogue. */
+static int int8_projection(h3_gpu *g, const h3_gpu_tensor *q_in, const h3_gpu_tensor *in_scales, uint32_t input_group,
+                           const h3_gpu_tensor *w, const h3_gpu_tensor *w_scales, h3_gpu_tensor *out, uint32_t rows, uint32_t k,
+                           uint32_t n, uint32_t activation, const h3q8_rope_desc *rope, const char *what) {
+    h3q8_linear_desc d = {};
+    d.mode = H3Q8_MODE_W8A8; d.rows = rows; d.input_dim = k; d.output_dim = n; d.activation = activation;
+    d.input = pointer(q_in); d.input_scales = (const float *)pointer(in_scales); d.input_group = input_group;
+    d.weight = pointer(w); d.weight_scales = (const float *)pointer(w_scales);
+    d.output = out ? (uint16_t *)pointer(out) : nullptr;
+    d.rope = rope;
+    {
+        ProfileScope timing(g, 0);
+        if (!h3q8_linear(&d, g->compute)) { g->accessed.clear(); return set_error(g, "%s: %s", what, h3q8_last_error()); }
+    }
+    g->stats.linear_dispatches++;
+    return 1;
+}
+
+/* Per-row int8 of a [head, row, dimension] bf16 tensor gathered into row-major [row, head * dimension]
+ * (src/gpu.h:536-546: the projection after attention reads SDPA's native layout without a bf16 transpose). */
+static __global__ void __launch_bounds__(256) quantize_rows_head_major_kernel(const uint16_t *__restrict__ in, int8_t *__restrict__ out,
+                                                                       float *__restrict__ scales, uint32_t rows, uint32_t heads,
+                                                                       uint32_t head_dim, uint32_t *nonfinite) {
+    __shared__ float scratch[8];
+    const uint32_t row = blockIdx.x, columns = heads * head_dim, vectors = columns / 8;
+    uint2 *q = reinterpret_cast<uint2 *>(out + (size_t)row * columns);
+    if (row >= rows) {
+        for (uint32_t c = threadIdx.x; c < vectors; c += 256) q[c] = make_uint2(0, 0);
+        if (threadIdx.x == 0) scales[row] = 1.0f;
+        return;
+    }
+    auto vector = [&](uint32_t c) {
+        const uint32_t column = c * 8, head = column / head_dim, inside = column - head * head_dim;
+        return *reinterpret_cast<const uint4 *>(in + ((size_t)head * rows + row) * head_dim + inside);
+    };
+    float peak = 0.0f;
+    for (uint32_t c = threadIdx.x; c < vectors; c += 256) {
+        const uint4 v = vector(c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) peak = fmaxf(peak, fmaxf(fabsf(bf16_lo(w[j])), fabsf(bf16_hi(w[j]))));
+    }
+    peak = block_max_256(peak, scratch);
+    const float scale = peak > 0.0f ? __fdiv_rn(peak, 127.0f) : __fdiv_rn(1.0f, 127.0f);
+    const float inverse = peak > 0.0f ? __fdiv_rn(127.0f, peak) : 127.0f;
+    if (threadIdx.x == 0) {
+        scales[row] = scale;
+        if (!(peak <= FLT_MAX) && nonfinite) atomicOr(nonfinite, 1u);
+    }
+    for (uint32_t c = threadIdx.x; c < vectors; c += 256) {
+        const uint4 v = vector(c);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[2] = {0, 0};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            uint32_t lo = (uint32_t)quantize_one(bf16_lo(w[j]), inverse) & 0xffu, hi = (uint32_t)quantize_one(bf16_hi(w[j]), inverse) & 0xffu;
+            o[j >> 1] |= (lo | (hi << 8)) << ((j & 1) * 16);
+        }
+        q[c] = make_uint2(o[0], o[1]);
+    }
+}
+
+extern "C" int h3_gpu_linear_int8_head_major_bf16(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_tensor *qin, h3_gpu_tensor *in_scales,
+                                                  const h3_gpu_tensor *in, const h3_gpu_tensor *w, const h3_gpu_tensor *w_scales,
+                                                  uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t n) {
+    if (!launch_ready(g)) return 0;
+    const uint32_t k = heads * head_dim, padded = (rows + 127u) & ~127u;
+    if (rows < 128 || !heads || !head_dim || head_dim % 8 || k % 128 || n % 128)
+        return set_error(g, "int8 head-major linear needs rows >= 128, head_dim %% 8 == 0 and K, N multiples of 128");
+    if (!require(g, w, H3_GPU_I8, (size_t)n * k, "int8 linear weight") || !require(g, w_scales, H3_GPU_F32, n, "int8 linear weight scales") ||
+        !require(g, out, H3_GPU_BF16, (size_t)rows * n, "int8 linear output") || !require(g, in, H3_GPU_BF16, (size_t)rows * k, "int8 linear input") ||
+        !require(g, qin, H3_GPU_I8, (size_t)padded * k, "int8 quantized output") ||
+        !require(g, in_scales, H3_GPU_F32, padded, "int8 quantization scales")) return 0;
+    {
+        ProfileScope timing(g, 7);
+        quantize_rows_head_major_kernel<<<padded, 256, 0, g->compute>>>((const uint16_t *)pointer(in), (int8_t *)pointer(qin),
+                                                                        (float *)pointer(in_scales), rows, heads, head_dim, g->flags + 1);
+    }
+    count_launch(1);
+    if (!int8_projection(g, qin, in_scales, 0, w, w_scales, out, rows, k, n, H3Q8_ACT_NONE, nullptr, "int8 head-major linear")) return 0;
+    return launch_status(g, "int8 head-major linear", 2);
+}
+
+/* src/gpu.h:547-563, src/metal/gpu.m:3281-3490: the block's MLP on int8 tensor cores.  fc1 + SwiGLU reads the
+ * per-row quantised input (quantised here unless the caller's gate/AdaLN pass already did), `activated` is stored as
+ * bf16, re-quantised per row and per 1024 hidden features (or per row with use_int8_row_fc2) and fed to fc2.
+ * The diagnostic bf16 stages of the reference (H3_INT8_MLP_STAGE, the fc1_bf16 / fc2_bf16 weights) are not part of
+ * this path; the slower-variant switches select equal results there and are accepted and ignored. */
+extern "C" int h3_gpu_mlp_int8_bf16(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_tensor *activated, h3_gpu_tensor *q_act, h3_gpu_tensor *act_scales,
+                                    const h3_gpu_tensor *in, const h3_gpu_tensor *fc1_w, const h3_gpu_tensor *fc1_s,
+                                    const h3_gpu_tensor *fc2_w, const h3_gpu_tensor *fc2_s, const h3_gpu_tensor *, const h3_gpu_tensor *,
+                                    uint32_t rows, uint32_t k, uint32_t hidden, uint32_t n, int, int, int use_int8_row_fc2,
+                                    int input_is_quantized) {
+    if (!launch_ready(g)) return 0;
+    if (getenv("H3_INT8_MLP_STAGE")) return set_error(g, "int8 MLP: the diagnostic bf16 stages are not available on this backend");
+    const uint32_t padded = (rows + 127u) & ~127u, groups = hidden / 1024u;
+    if (rows < 128 || k % 128 || hidden % 128 || n % 128 || (!use_int8_row_fc2 && hidden % 1024))
+        return set_error(g, "int8 MLP needs rows >= 128, dimensions that are multiples of 128 and a hidden width that is a multiple of 1024");
+    const size_t capacity = (size_t)padded * (k > hidden ? k : hidden);
+    if (!require(g, q_act, H3_GPU_I8, capacity, "int8 MLP activation") ||
+        !require(g, act_scales, H3_GPU_F32, (size_t)padded * (groups ? groups : 1u), "int8 MLP activation scales") ||
+        !require(g, fc1_w, H3_GPU_I8, (size_t)hidden * 2 * k, "int8 MLP FC1 weight") || !require(g, fc1_s, H3_GPU_F32, (size_t)hidden * 2, "int8 MLP FC1 scales") ||
+        !require(g, fc2_w, H3_GPU_I8, (size_t)n * hidden, "int8 MLP FC2 weight") || !require(g, fc2_s, H3_GPU_F32, n, "int8 MLP FC2 scales") ||
+        (!input_is_quantized && !require(g, in, H3_GPU_BF16, (size_t)rows * k, "int8 MLP input")) ||
+        !require(g, activated, H3_GPU_BF16, (size_t)rows * hidden, "int8 MLP activated") ||
+        !require(g, out, H3_GPU_BF16, (size_t)rows * n, "int8 MLP output")) return 0;
+    unsigned launched = 0;
+    if (!input_is_quantized) {
+        ProfileScope timing(g, 7);
+        launch_quantize_rows((const uint16_t *)pointer(in), (int8_t *)pointer(q_act), (float *)pointer(act_scales), rows, padded, k, 1.0f,
+                             g->flags + 1, g->compute);
+        count_launch(1);
+        launched++;
+    }
+    if (!int8_projection(g, q_act, act_scales, 0, fc1_w, fc1_s, activated, rows, k, hidden, H3Q8_ACT_SWIGLU, nullptr, "int8 MLP FC1")) return 0;
+    {
+        ProfileScope timing(g, 7);
+        if (use_int8_row_fc2)
+            launch_quantize_rows((const uint16_t *)pointer(activated), (int8_t *)pointer(q_act), (float *)pointer(act_scales), rows, padded, hidden,
+                                 1.0f, g->flags + 1, g->compute);
+        else  /* every (row, 1024-feature group) is a segment of the same contiguous matrix */
+            launch_quantize_rows((const uint16_t *)pointer(activated), (int8_t *)pointer(q_act), (float *)pointer(act_scales),
+                                 (uint64_t)rows * groups, (uint64_t)padded * groups, 1024, 1.0f, g->flags + 1, g->compute);
+        count_launch(1);
+        launched++;
+    }
+    if (!int8_projection(g, q_act, act_scales, use_int8_row_fc2 ? 0u : 1024u, fc2_w, fc2_s, out, rows, hidden, n, H3Q8_ACT_NONE, nullptr,
+                         "int8 MLP FC2")) return 0;
+    return launch_status(g, "int8 MLP", launched + 2);
+}
+
+/* src/gpu.h:682-702: QKV projection on int8 tensor cores with the per-head RMS norm and rotary embedding in the
+ * epilogue.  The input is quantised per row here unless the caller's gate/AdaLN pass already did.  The slower-variant
+ * switches select equal results in the reference and are accepted and ignored. */
+extern "C" int h3_gpu_grouped_qkv_linear_rope_int8(h3_gpu *g, h3_gpu_tensor *q, h3_gpu_tensor *k, h3_gpu_tensor *v, h3_gpu_tensor *qin,
+                                                   h3_gpu_tensor *in_scales, const h3_gpu_tensor *in, const h3_gpu_tensor *w,
+                                                   const h3_gpu_tensor *w_scales, const h3_gpu_tensor *qw, const h3_gpu_tensor *kw,
+                                                   const h3_gpu_tensor *c, const h3_gpu_tensor *s, uint32_t rows, uint32_t width,
+                                                   uint32_t heads, uint32_t dim, uint32_t half, float epsilon, int input_is_quantized,
+                                                   int, int, int) {
+    if (!launch_ready(g)) return 0;
+    if (!rope_operands(g, q, k, v, qw, kw, c, s, rows, heads, dim, half)) return 0;
+    const uint32_t n = heads * dim * 3, padded = (rows + 127u) & ~127u;
+    if (rows < 128 || width % 128 || dim != 128 || (half != 48 && half != 64))
+        return set_error(g, "int8 QKV projection needs rows >= 128, K %% 128 == 0, head_dim 128 and rope_half 48 or 64");
+    if (!require(g, w, H3_GPU_I8, (size_t)n * width, "int8 QKV weight") || !require(g, w_scales, H3_GPU_F32, n, "int8 QKV weight scales") ||
+        !require(g, qin, H3_GPU_I8, (size_t)padded * width, "int8 QKV quantized input") ||
+        !require(g, in_scales, H3_GPU_F32, padded, "int8 QKV input scales") ||
+        (!input_is_quantized && !require(g, in, H3_GPU_BF16, (size_t)rows * width, "int8 QKV input"))) return 0;
+    unsigned launched = 1;
+    if (!input_is_quantized) {
+        ProfileScope timing(g, 7);
+        launch_quantize_rows((const uint16_t *)pointer(in), (int8_t *)pointer(qin), (float *)pointer(in_scales), rows, padded, width, 1.0f,
+                             g->flags + 1, g->compute);
+        count_launch(1);
+        launched++;
+    }
+    h3q8_rope_desc rope = {(const uint16_t *)pointer(qw), (const uint16_t *)pointer(kw), (const uint16_t *)pointer(c),
+                           (const uint16_t *)pointer(s), (uint16_t *)pointer(q), (uint16_t *)pointer(k), (uint16_t *)pointer(v),
+                           heads, dim, half, epsilon};
+    if (!int8_projection(g, qin, in_scales, 0, w, w_scales, nullptr, rows, width, n, H3Q8_ACT_NONE, &rope, "int8 QKV projection")) return 0;
+    return launch_status(g, "int8 QKV projection", launched);
+}
+
 /* src/gpu.h:714-716, src/cuda/cuda_kernels.cuh:1047-1059: fused row = [gate width | up width] */
 static __global__ void swiglu_kernel(const uint16_t *fused, uint16_t *out, uint32_t rows, uint32_t width) {
     uint32_t c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;

@@ -381,6 +381,27 @@ int h3_gpu_linear_fused_int8_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_g
                                   const h3_gpu_tensor *input_scales, uint32_t input_group, const h3_gpu_tensor *weight,
                                   const h3_gpu_tensor *bias, const h3_gpu_tensor *gate, const h3_gpu_tensor *residual,
                                   uint32_t rows, uint32_t input_dim, uint32_t output_dim, int activation);
+/* The rest of the reference's int8 operator family (src/gpu.h:536-563, 682-702), same argument lists.  Weights are plain
+ * int8 tensors with one fp32 scale per output channel; activations are quantised per row on the way in (or arrive
+ * quantised from h3_gpu_gate_adaln_quantize_int8 with input_is_quantized = 1).  The use_slower_* switches pick
+ * alternative kernels with equal results in the reference; here they are accepted and ignored. */
+int h3_gpu_linear_int8_head_major_bf16(h3_gpu *gpu, h3_gpu_tensor *output, h3_gpu_tensor *quantized_input,
+                                       h3_gpu_tensor *input_scales, const h3_gpu_tensor *input /* [head, row, dimension] */,
+                                       const h3_gpu_tensor *weight, const h3_gpu_tensor *weight_scales, uint32_t rows,
+                                       uint32_t heads, uint32_t head_dim, uint32_t output_dim);
+int h3_gpu_mlp_int8_bf16(h3_gpu *gpu, h3_gpu_tensor *output, h3_gpu_tensor *activated, h3_gpu_tensor *quantized_activation,
+                         h3_gpu_tensor *activation_scales, const h3_gpu_tensor *input, const h3_gpu_tensor *fc1_weight,
+                         const h3_gpu_tensor *fc1_scales, const h3_gpu_tensor *fc2_weight, const h3_gpu_tensor *fc2_scales,
+                         const h3_gpu_tensor *fc1_bf16, const h3_gpu_tensor *fc2_bf16, uint32_t rows, uint32_t input_dim,
+                         uint32_t hidden_dim, uint32_t output_dim, int use_slower_grouped_quantizer, int use_slower_dynamic_fc1_k,
+                         int use_int8_row_fc2, int input_is_quantized);
+int h3_gpu_grouped_qkv_linear_rope_int8(h3_gpu *gpu, h3_gpu_tensor *query, h3_gpu_tensor *key, h3_gpu_tensor *value,
+                                        h3_gpu_tensor *quantized_input, h3_gpu_tensor *input_scales, const h3_gpu_tensor *input,
+                                        const h3_gpu_tensor *weight, const h3_gpu_tensor *weight_scales, const h3_gpu_tensor *q_norm,
+                                        const h3_gpu_tensor *k_norm, const h3_gpu_tensor *rope_cos, const h3_gpu_tensor *rope_sin,
+                                        uint32_t rows, uint32_t input_dim, uint32_t heads, uint32_t head_dim, uint32_t rope_half,
+                                        float epsilon, int input_is_quantized, int use_slower_unfused_qkv_rope,
+                                        int use_slower_scalar_qkv_rms, int use_slower_uncached_int8_scales);
 /* Unfused epilogue operators kept for comparison -- src/gpu.h:575-577, 612-617, 750-752 */
 int h3_gpu_gelu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input, uint32_t elements, int approximate);
 int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,

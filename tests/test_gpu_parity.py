@@ -874,6 +874,113 @@ def test_profile_report_lines(oracle, monkeypatch, capfd):
     assert stats.linear_seconds > 0 and stats.h2d_seconds > 0 and stats.d2h_seconds > 0 and stats.quant_conversion_seconds > 0
 
 
+@pytest.mark.parametrize("rows,heads,dim,N", [(130, 3, 128, 256), (300, 6, 64, 384)])
+def test_int8_head_major_projection(oracle, rows, heads, dim, N):
+    """h3_gpu_linear_int8_head_major_bf16 (src/gpu.h:536-546): SDPA's [head, row, dimension] output is quantised per
+    token straight into row-major int8 (no bf16 transpose) and projected; bit-equal to transposing on the host."""
+    K, padded = heads * dim, (rows + 127) // 128 * 128
+    x = synth.activations(71, 1, rows, K, outliers=synth.outlier_channels(71, K)).reshape(rows, K)
+    head_major = np.ascontiguousarray(x.reshape(rows, heads, dim).transpose(1, 0, 2))
+    wq, ws = synth.int8_weights(71, 2, N, K), synth.lognormal_scales(71, 3, N, 1)
+    want_q, want_s = oracle.quantize_rows(x)
+    want = oracle.linear(oracle.MODE_W8A8, want_q, wq, ws[:, 0].copy(), 0, x_scales=want_s, fast=True)
+    gpu = h.Gpu()
+    t_in, t_w, t_ws = gpu.tensor_from_bf16(head_major), gpu.tensor_from_i8(wq), gpu.tensor_from_f32(ws[:, 0].copy())
+    q, sc, out = gpu.tensor_new_i8(padded * K), gpu.tensor_new_f32(padded), gpu.tensor_new_bf16(rows * N)
+    gpu.begin()
+    gpu.linear_int8_head_major_bf16(out, q, sc, t_in, t_w, t_ws, rows, heads, dim, N)
+    gpu.submit()
+    got_q = q.read().reshape(padded, K)
+    assert (got_q[:rows] == want_q).all() and (got_q[rows:] == 0).all()
+    assert (sc.read()[:rows].view(np.uint32) == want_s.view(np.uint32)).all() and (sc.read()[rows:] == 1.0).all()
+    assert (out.read().reshape(rows, N) == want).all()
+    with pytest.raises(h.H3Error):
+        gpu.begin()
+        gpu.linear_int8_head_major_bf16(out, q, sc, t_in, t_w, t_ws, 64, heads, dim, N)     # fewer than 128 rows
+    gpu.cancel()
+    gpu.free()
+
+
+@pytest.mark.parametrize("row_fc2", [0, 1])
+@pytest.mark.parametrize("rows,K,hidden,N", [(130, 256, 1024, 384), (300, 384, 2048, 256)])
+def test_int8_mlp_operator(oracle, rows, K, hidden, N, row_fc2):
+    """h3_gpu_mlp_int8_bf16 (src/gpu.h:547-563, src/metal/gpu.m:3281-3490): per-row int8 of the input, fc1 + SwiGLU,
+    int8 of the activation per row and per 1024 features (or per row), fc2.  Each stage is checked against the oracle
+    on the bytes the previous stage actually produced, so every comparison after the SwiGLU is bit-exact."""
+    padded = (rows + 127) // 128 * 128
+    x = synth.activations(81, 1, rows, K).reshape(rows, K)
+    w1, s1 = synth.int8_weights(81, 2, 2 * hidden, K), synth.lognormal_scales(81, 3, 2 * hidden, 1) * np.float32(0.2)
+    w2, s2 = synth.int8_weights(81, 4, N, hidden), synth.lognormal_scales(81, 5, N, 1)
+    gpu = h.Gpu()
+    t_x, t_w1, t_s1 = gpu.tensor_from_bf16(x), gpu.tensor_from_i8(w1), gpu.tensor_from_f32(s1[:, 0].copy())
+    t_w2, t_s2 = gpu.tensor_from_i8(w2), gpu.tensor_from_f32(s2[:, 0].copy())
+    q = gpu.tensor_new_i8(padded * max(K, hidden))
+    sc = gpu.tensor_new_f32(padded * max(hidden // 1024, 1))
+    act, out = gpu.tensor_new_bf16(rows * hidden), gpu.tensor_new_bf16(rows * N)
+    before = h.library().h3q8_kernel_launches()
+    gpu.begin()
+    gpu.mlp_int8_bf16(out, act, q, sc, t_x, t_w1, t_s1, t_w2, t_s2, rows, K, hidden, N, use_int8_row_fc2=row_fc2)
+    gpu.submit()
+    assert h.library().h3q8_kernel_launches() - before == 4          # quantise, fc1 + SwiGLU, quantise, fc2
+    xq, xs = oracle.quantize_rows(x)
+    want_act = oracle.linear(oracle.MODE_W8A8, xq, w1, s1[:, 0].copy(), 0, x_scales=xs, activation=2, fast=True)
+    got_act = act.read().reshape(rows, hidden)
+    check_bf16(got_act, want_act)
+    assert (got_act != want_act).mean() < 2e-3
+    if row_fc2:
+        aq, a_s = oracle.quantize_rows(got_act)
+        want = oracle.linear(oracle.MODE_W8A8, aq, w2, s2[:, 0].copy(), 0, x_scales=a_s, fast=True)
+        assert (q.read()[:rows * hidden].reshape(rows, hidden) == aq).all()
+    else:
+        aq, a_s = oracle.quantize_rows_grouped(got_act, 1024)
+        want = oracle.linear(oracle.MODE_W8A8, aq, w2, s2[:, 0].copy(), 0, x_scales=a_s, input_group=1024, fast=True)
+        assert (q.read()[:rows * hidden].reshape(rows, hidden) == aq).all()
+        assert (sc.read()[:rows * (hidden // 1024)].view(np.uint32) == a_s.ravel().view(np.uint32)).all()
+    assert (out.read().reshape(rows, N) == want).all()
+    gpu.free()
+
+
+def test_int8_qkv_projection_with_rope(oracle):
+    """h3_gpu_grouped_qkv_linear_rope_int8 (src/gpu.h:682-702): per-row int8 of the input, int8 projection, per-head
+    RMS norm and rotary embedding in the epilogue; equal bit for bit to the q8-descriptor route of the same weights,
+    with and without a pre-quantised input."""
+    rows, heads, width, half, dim = 300, 4, 512, 48, 128
+    n, padded = heads * 3 * dim, 384
+    rng = np.random.default_rng(5)
+    bf = lambda a: synth.to_bf16(a.astype(np.float32)).reshape(a.shape)
+    x, wq, ws = operands(91, rows, n, width, 0)
+    q_norm, k_norm = bf(1 + 0.1 * rng.standard_normal(dim)), bf(1 + 0.1 * rng.standard_normal(dim))
+    angle = rng.uniform(0, 6.28, (rows, half))
+    cos, sin = bf(np.cos(angle)), bf(np.sin(angle))
+    gpu = h.Gpu()
+    gpu.quant_configure(2)
+    tx, tqn, tkn, tc, ts = (gpu.tensor_from_bf16(a) for a in (x, q_norm, k_norm, cos, sin))
+    w_desc = gpu.q8_from_host(wq, ws, 0)
+    t_w, t_ws = gpu.tensor_from_i8(wq), gpu.tensor_from_f32(ws[:, 0].copy())
+    reference = [gpu.tensor_new_bf16(rows * heads * dim) for _ in range(3)]
+    first = [gpu.tensor_new_bf16(rows * heads * dim) for _ in range(3)]
+    second = [gpu.tensor_new_bf16(rows * heads * dim) for _ in range(3)]
+    qin, sc = gpu.tensor_new_i8(padded * width), gpu.tensor_new_f32(padded)
+    gpu.begin()
+    gpu.grouped_qkv_linear_rope_bf16(*reference, None, tx, w_desc, tqn, tkn, tc, ts, rows, width, heads, dim, half, 1e-5)
+    gpu.grouped_qkv_linear_rope_int8(*first, qin, sc, tx, t_w, t_ws, tqn, tkn, tc, ts, rows, width, heads, dim, half, 1e-5)
+    gpu.grouped_qkv_linear_rope_int8(*second, qin, sc, None, t_w, t_ws, tqn, tkn, tc, ts, rows, width, heads, dim, half, 1e-5,
+                                     input_is_quantized=1)
+    gpu.submit()
+    want_q, want_s = oracle.quantize_rows(x)
+    assert (qin.read()[:rows * width].reshape(rows, width) == want_q).all()
+    for a, b, c in zip(reference, first, second):
+        assert (a.read() == b.read()).all() and (a.read() == c.read()).all()
+    linear = oracle.linear(oracle.MODE_W8A8, want_q, wq, ws[:, 0].copy(), 0, x_scales=want_s, fast=True)
+    for got, want in zip(first, oracle.grouped_qkv_rope(linear, q_norm, k_norm, cos, sin, heads, dim, half, 1e-5)):
+        check_bf16(got.read(), want.ravel())
+    with pytest.raises(h.H3Error):
+        gpu.begin()
+        gpu.grouped_qkv_linear_rope_int8(*first, qin, sc, tx, t_w, t_ws, tqn, tkn, tc, ts, rows, width, heads, 64, 32, 1e-5)
+    gpu.cancel()
+    gpu.free()
+
+
 def test_residency_plan_on_the_device(monkeypatch):
     """h3_gpu_plan_bf16_weights (src/cuda/gpu_cuda.cu:559-578): free memory and reserve come from the device;
     the test-only block ceiling and capacity turn the same request into partial and streamed plans."""
