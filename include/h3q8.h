@@ -320,7 +320,9 @@ int h3q8_gpu_tensor_download_async(h3_gpu_tensor *tensor, void *host, size_t byt
 /* Rows at or above which a W8A16 linear first dequantises the weight into
  * context scratch and runs the bf16 GEMM (the reference's policy 0,
  * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop.  Default 1
- * (every call), or H3Q8_W8A16_SCRATCH_ROWS from the environment. */
+ * (every call), or H3Q8_W8A16_SCRATCH_ROWS from the environment.  Problems of at most 128
+ * rows are the exception: they read the int8 weight once with main-loop dequantisation
+ * and split-K (H3Q8_SKINNY_DIRECT=0 turns the exception off). */
 int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *gpu, uint32_t rows);
 /* Per-kernel CUDA-event timing into h3_gpu_stats (on when H3_PROFILE is set). */
 int h3q8_gpu_set_profiling(h3_gpu *gpu, int enabled);
