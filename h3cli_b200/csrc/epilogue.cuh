@@ -41,18 +41,20 @@ struct EpilogueParams {
     RopeParams rope;           /* used when activation == ACT_QKV_ROPE */
 };
 
-/* Branch-free so that the compiler can interleave many elements per thread. */
+/* Branch-free so that the compiler can interleave many elements per thread.
+ *   s = v + 0.044715 v^3,   0.5 v (1 + tanh(c s)) == v / (1 + exp(-2 c s)),   exp(-2 c s) = 2^(s * (-2 c log2 e))
+ * The constants of the exponent are folded into one multiply; the exponential and the reciprocal are the hardware
+ * approximations (relative error about 1e-6), far inside the bf16 rounding that follows; against a correctly rounded
+ * tanhf the stored bf16 differs by one step for a few outputs in ten thousand.  The reference's lower saturation
+ * guard (c s <= -10 -> 0) is kept as a select; its upper guard (c s >= 10 -> v) needs none: there 1 + exp(-2 c s)
+ * rounds to 1 and v / 1 is v. */
 __device__ __forceinline__ float gelu_tanh_f32(float v) {
-    const float cube = __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v);
-    const float inner = __fmul_rn(0.7978845608028654f, __fadd_rn(v, cube));
-    /* 0.5 v (1 + tanh u) == v / (1 + exp(-2u)).  The exponential and the division
-     * use the hardware approximations (relative error about 1e-6), far inside the
-     * bf16 rounding that follows; against a correctly rounded tanhf the stored
-     * bf16 differs by one step for a few outputs in ten thousand. */
-    float r = __fdividef(v, 1.0f + __expf(-2.0f * inner));
-    r = inner <= -10.0f ? 0.0f : r;   /* the reference's saturation guards */
-    r = inner >= 10.0f ? v : r;
-    return r;
+    const float s = __fadd_rn(v, __fmul_rn(__fmul_rn(__fmul_rn(0.044715f, v), v), v));
+    float e, q;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(s, -2.3022082f)));   /* -2 sqrt(2/pi) log2(e) */
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q) : "f"(__fadd_rn(1.0f, e)));
+    const float r = __fmul_rn(v, q);
+    return s <= -12.533141f ? 0.0f : r;   /* c s <= -10 */
 }
 
 /* Round two fp32 values to bf16 (nearest even, one cvt.rn.bf16x2.f32) and keep them
