@@ -153,7 +153,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="h3q8")
-    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS] + ["helpers", "grouped_streams"],
+    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS] + ["helpers", "grouped_streams", "real_block_int8"],
                     help="profiling aid: run only this projection (with --rows) and print a short line")
     ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
     ap.add_argument("--workload", default="block", choices=["block", "stream", "tp_ffn"],
@@ -214,6 +214,8 @@ def main():
         return run_helpers(args, gpu, lib, stream, device_bf16)
     if args.case == "grouped_streams":
         return run_grouped_streams(args, gpu, lib, stream, device_bf16)
+    if args.case == "real_block_int8":
+        return run_real_block_int8(args, gpu, lib, stream, device_bf16)
     if args.case:
         return run_case(args, gpu, lib, stream, device_bf16)
     if args.workload == "stream":
@@ -645,6 +647,60 @@ def run_grouped_streams(args, gpu, lib, stream, device_bf16):
     print(json.dumps({"case": "grouped_streams", "mode": args.mode, "problems": [dict(name=s[0], rows=s[1], k=s[2], n=s[3]) for s in specs],
                       "one_call_ms": together, "one_call_tflops": flop / together / 1e9, "kernels_per_call": int(launches),
                       "two_calls_ms": separate, "two_calls_tflops": flop / separate / 1e9}), flush=True)
+    gpu.free()
+
+
+def run_real_block_int8(args, gpu, lib, stream, device_bf16):
+    """The real model's block (hidden 5376, 56 heads of 128, FFN 14336, SwiGLU) on the int8 operator family with the
+    reference's own entry points, chained as run_block() chains them; attention itself is outside this path, so its
+    output is a resident synthetic tensor in SDPA's [head, row, dimension] layout."""
+    import torch
+    rows, hidden, heads, dim, half, ffn = args.rows, 5376, 56, 128, 48, 14336
+    padded = (rows + 127) // 128 * 128
+    wgen = np.random.default_rng(42)
+
+    def weight(n, k, scale):
+        w = gpu.tensor_from_i8(wgen.integers(-127, 128, (n, k), dtype=np.int8))
+        return w, gpu.tensor_from_f32(np.exp(wgen.normal(np.log(scale), 0.3, n)).astype(np.float32))
+
+    w_qkv, s_qkv = weight(3 * heads * dim, hidden, 0.01)
+    w_out, s_out = weight(hidden, heads * dim, 0.01)
+    w_fc1, s_fc1 = weight(2 * ffn, hidden, 0.002)
+    w_fc2, s_fc2 = weight(hidden, ffn, 0.01)
+    x, attention = device_bf16(rows, hidden, seed=1), device_bf16(rows, heads * dim, seed=2)
+    branch = gpu.tensor_new_bf16(rows * hidden)
+    q, k, v = (gpu.tensor_new_bf16(rows * heads * dim) for _ in range(3))
+    qn, kn = device_bf16(1, dim, 1.0, 0.1, seed=5), device_bf16(1, dim, 1.0, 0.1, seed=6)
+    cos, sin = device_bf16(rows, half, 0.0, 0.7, seed=7), device_bf16(rows, half, 0.0, 0.7, seed=8)
+    norm_w, modulation = device_bf16(1, hidden, 1.0, 0.1, seed=9), device_bf16(1, 6 * hidden, 0.0, 0.1, seed=10)
+    q_in, in_scales = gpu.tensor_new_i8(padded * max(hidden, heads * dim)), gpu.tensor_new_f32(padded)
+    q_act, act_scales = gpu.tensor_new_i8(padded * ffn), gpu.tensor_new_f32(padded * (ffn // 1024))
+    activated, mlp_out = gpu.tensor_new_bf16(rows * ffn), gpu.tensor_new_bf16(rows * hidden)
+
+    def block():
+        gpu.grouped_qkv_linear_rope_int8(q, k, v, q_in, in_scales, x, w_qkv, s_qkv, qn, kn, cos, sin, rows, hidden, heads, dim, half, 1e-6)
+        gpu.linear_int8_head_major_bf16(branch, q_in, in_scales, attention, w_out, s_out, rows, heads, dim, hidden)
+        # x <- x + branch * gate; RMS norm + AdaLN; per-row int8 of the MLP input, all in one pass
+        gpu.gate_adaln_quantize_int8(x, q_act, act_scales, x, branch, norm_w, modulation, modulation, None, rows, padded, hidden, 6, 0, 1, 2, 1e-6)
+        gpu.mlp_int8_bf16(mlp_out, activated, q_act, act_scales, None, w_fc1, s_fc1, w_fc2, s_fc2, rows, hidden, ffn, hidden,
+                          input_is_quantized=1)
+        gpu.continue_()
+
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    before = lib.h3q8_kernel_launches()
+    gpu.begin()
+    for i in range(args.warmup + args.steps):
+        if i == args.warmup:
+            start.record(stream)
+        block()
+    stop.record(stream)
+    gpu.submit()
+    ms = start.elapsed_time(stop) / args.steps
+    ops = 2.0 * rows * (hidden * 3 * heads * dim + heads * dim * hidden + hidden * 2 * ffn + ffn * hidden)
+    print(json.dumps({"case": "real_block_int8", "rows": rows, "hidden": hidden, "heads": heads, "ffn": ffn, "ms_per_block": ms,
+                      "tops": ops / ms / 1e9, "kernels_per_block": int((lib.h3q8_kernel_launches() - before) // (args.warmup + args.steps)),
+                      "calls": ["h3_gpu_grouped_qkv_linear_rope_int8", "h3_gpu_linear_int8_head_major_bf16",
+                                "h3_gpu_gate_adaln_quantize_int8", "h3_gpu_mlp_int8_bf16"]}), flush=True)
     gpu.free()
 
 
