@@ -677,13 +677,21 @@ def run_real_block_int8(args, gpu, lib, stream, device_bf16):
     q_act, act_scales = gpu.tensor_new_i8(padded * ffn), gpu.tensor_new_f32(padded * (ffn // 1024))
     activated, mlp_out = gpu.tensor_new_bf16(rows * ffn), gpu.tensor_new_bf16(rows * hidden)
 
-    def block():
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+
+    def block(timed=False):
+        mark = (lambda i: marks[i].record(stream)) if timed else (lambda i: None)
+        mark(0)
         gpu.grouped_qkv_linear_rope_int8(q, k, v, q_in, in_scales, x, w_qkv, s_qkv, qn, kn, cos, sin, rows, hidden, heads, dim, half, 1e-6)
+        mark(1)
         gpu.linear_int8_head_major_bf16(branch, q_in, in_scales, attention, w_out, s_out, rows, heads, dim, hidden)
+        mark(2)
         # x <- x + branch * gate; RMS norm + AdaLN; per-row int8 of the MLP input, all in one pass
         gpu.gate_adaln_quantize_int8(x, q_act, act_scales, x, branch, norm_w, modulation, modulation, None, rows, padded, hidden, 6, 0, 1, 2, 1e-6)
+        mark(3)
         gpu.mlp_int8_bf16(mlp_out, activated, q_act, act_scales, None, w_fc1, s_fc1, w_fc2, s_fc2, rows, hidden, ffn, hidden,
                           input_is_quantized=1)
+        mark(4)
         gpu.continue_()
 
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -694,11 +702,14 @@ def run_real_block_int8(args, gpu, lib, stream, device_bf16):
             start.record(stream)
         block()
     stop.record(stream)
+    block(timed=True)
     gpu.submit()
     ms = start.elapsed_time(stop) / args.steps
+    parts = [marks[i].elapsed_time(marks[i + 1]) for i in range(4)]
     ops = 2.0 * rows * (hidden * 3 * heads * dim + heads * dim * hidden + hidden * 2 * ffn + ffn * hidden)
     print(json.dumps({"case": "real_block_int8", "rows": rows, "hidden": hidden, "heads": heads, "ffn": ffn, "ms_per_block": ms,
-                      "tops": ops / ms / 1e9, "kernels_per_block": int((lib.h3q8_kernel_launches() - before) // (args.warmup + args.steps)),
+                      "tops": ops / ms / 1e9, "kernels_per_block": int((lib.h3q8_kernel_launches() - before) // (args.warmup + args.steps + 1)),
+                      "ms_per_call": dict(zip(["qkv_rope", "attn_out_head_major", "gate_adaln_quantize", "mlp"], parts)),
                       "calls": ["h3_gpu_grouped_qkv_linear_rope_int8", "h3_gpu_linear_int8_head_major_bf16",
                                 "h3_gpu_gate_adaln_quantize_int8", "h3_gpu_mlp_int8_bf16"]}), flush=True)
     gpu.free()
@@ -723,6 +734,10 @@ def run_helpers(args, gpu, lib, stream, device_bf16):
     wout = gpu.tensor_new_bf16(ffn * ffn)
     norm_w, mod = device_bf16(1, hidden, 1.0, 0.1, seed=5), device_bf16(1, 3 * hidden, 0.0, 0.1, seed=6)
     gated, q3, s3 = gpu.tensor_new_bf16(rows * hidden), gpu.tensor_new_i8(rows * hidden), gpu.tensor_new_f32(rows)
+    wide = 5376
+    branch5, residual5 = device_bf16(rows, wide, seed=12), device_bf16(rows, wide, seed=13)
+    norm5, mod5 = device_bf16(1, wide, 1.0, 0.1, seed=14), device_bf16(1, 3 * wide, 0.0, 0.1, seed=15)
+    gated5, q5 = gpu.tensor_new_bf16(rows * wide), gpu.tensor_new_i8(rows * wide)
     p = lambda t: t.device_pointer
     cases = [
         ("quantize_rows_kernel [M,3072]", lambda: lib.h3q8_quantize_rows(p(branch), p(q3), p(s3), rows, rows, hidden, 1.0, gpu.stream),
@@ -738,6 +753,9 @@ def run_helpers(args, gpu, lib, stream, device_bf16):
         ("gate_adaln_quantize_kernel [M,3072]", lambda: gpu.gate_adaln_quantize_int8(gated, q3, s3, residual, branch, norm_w, mod, mod, None, rows, rows,
                                                                                   hidden, 3, 0, 1, 2, 1e-6),
          rows * hidden * (2 + 2 + 2 + 1) + rows * 4),
+        ("gate_adaln_quantize_kernel [M,5376]", lambda: gpu.gate_adaln_quantize_int8(gated5, q5, s3, residual5, branch5, norm5, mod5, mod5, None, rows,
+                                                                                  rows, wide, 3, 0, 1, 2, 1e-6),
+         rows * wide * (2 + 2 + 2 + 1) + rows * 4),
     ]
     out = []
     for name, call, nbytes in cases:

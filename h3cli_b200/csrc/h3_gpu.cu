@@ -1223,14 +1223,18 @@ extern "C" int h3_gpu_gate_adaln_quantize_int8(h3_gpu *g, h3_gpu_tensor *gated_r
     const uintptr_t alignment = (uintptr_t)res_p | (uintptr_t)branch_p | (uintptr_t)gate_p | (uintptr_t)norm_p | (uintptr_t)mod_p |
                                 (uintptr_t)gated_p | (uintptr_t)q_p;
     /* rows of at most 6144 elements on 16-byte aligned operands: one warp per row, the row stays in registers */
-    if (width % 8 == 0 && width <= 6144 && (alignment & 15u) == 0) {
-        const unsigned grid = (padded_rows + 3) / 4;
-        if (width <= 3072)
-            gate_adaln_quantize_warp_kernel<12><<<grid, 128, 0, g->compute>>>(res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows,
-                                                                            padded_rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);
-        else
-            gate_adaln_quantize_warp_kernel<24><<<grid, 128, 0, g->compute>>>(res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows,
-                                                                            padded_rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);
+    /* rows on 16-byte aligned operands: one warp per row, the row in that warp's shared memory */
+    const size_t row_bytes = (size_t)4 * width * 2;
+    if (width % 8 == 0 && row_bytes <= 200 * 1024 && (alignment & 15u) == 0) {
+        static bool opted_in[64] = {};
+        if (row_bytes > 48 * 1024 && !opted_in[g->device]) {
+            if (!checked(g, cudaFuncSetAttribute(gate_adaln_quantize_warp_smem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024),
+                         "shared memory opt-in")) return 0;
+            opted_in[g->device] = true;
+        }
+        gate_adaln_quantize_warp_smem_kernel<<<(padded_rows + 3) / 4, 128, row_bytes, g->compute>>>(
+            res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows, padded_rows, width, slots, gate_slot, shift_slot,
+            scale_slot, epsilon);
     } else
         gate_adaln_quantize_kernel<<<padded_rows, 256, width * sizeof(uint16_t), g->compute>>>(
             res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);

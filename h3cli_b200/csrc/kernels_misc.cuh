@@ -239,21 +239,25 @@ static __global__ void __launch_bounds__(256) gate_adaln_quantize_kernel(
     for (uint32_t c = tid; c < width; c += 256) quantized[row_base + c] = (int8_t)quantize_one(bf16_bits_to_f32(row_values[c]), q_scale);
 }
 
-/* The same operator with one WARP per row for rows of at most ITERS * 256 elements: lane t plays
- * the eight lanes 8t .. 8t+7 of the 256-lane reduction (16-byte loads and stores, eight fma chains
- * in the same element order), the tree steps 128/64/32/16/8 are shuffles by 16/8/4/2/1 lanes and
- * the steps 4/2/1 stay inside lane 0, so the sum is formed in exactly the same order; the row
- * stays in registers between the three passes and no CTA-wide barrier is needed. */
-template <int ITERS>
-static __global__ void __launch_bounds__(128) gate_adaln_quantize_warp_kernel(
+/* The same operator with one WARP per row: lane t plays the eight lanes 8t .. 8t+7 of the 256-lane reduction
+ * (16-byte loads and stores, eight fma chains in the same element order), the tree steps 128/64/32/16/8 are shuffles
+ * by 16/8/4/2/1 lanes and the steps 4/2/1 stay inside lane 0, so the sum is formed in exactly the same order, and no
+ * CTA-wide barrier is needed.  The row is kept in the warp's own slice of shared memory between the three passes, not
+ * in registers: with about 90 registers per thread five CTAs are resident per SM, and the operator, which is bound by
+ * instruction issue and by its dependent passes rather than by HBM, lives on latency hiding (a register-resident
+ * version ran at 0.57 / 0.34 of the HBM peak for widths 3072 / 5376, this one at 0.78 / 0.66).  Any width that is a
+ * multiple of 8; dynamic shared memory = 4 warps x width x 2 bytes. */
+static __global__ void __launch_bounds__(128) gate_adaln_quantize_warp_smem_kernel(
     const uint16_t *residual, const uint16_t *__restrict__ branch, const uint16_t *__restrict__ gate_modulation,
     const uint32_t *__restrict__ row_map, const uint16_t *__restrict__ norm_weight, const uint16_t *__restrict__ norm_modulation,
     uint16_t *gated_residual, int8_t *__restrict__ quantized, float *__restrict__ quantized_scales, uint32_t rows, uint32_t padded_rows,
     uint32_t width, uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    extern __shared__ uint4 row_store[];
     const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= padded_rows) return;
     const size_t row_base = (size_t)row * width;
     const uint32_t vectors = width / 8;
+    uint4 *held = row_store + (threadIdx.x >> 5) * vectors;
     if (row >= rows) {
         for (uint32_t c = lane; c < vectors; c += 32) reinterpret_cast<uint2 *>(quantized + row_base)[c] = make_uint2(0, 0);
         if (lane == 0) quantized_scales[row] = 1.0f;
@@ -262,46 +266,38 @@ static __global__ void __launch_bounds__(128) gate_adaln_quantize_warp_kernel(
     const size_t base = (size_t)(row_map ? row_map[row] : 0) * slots * width;
     const uint4 *res4 = reinterpret_cast<const uint4 *>(residual + row_base), *br4 = reinterpret_cast<const uint4 *>(branch + row_base);
     const uint4 *gate4 = reinterpret_cast<const uint4 *>(gate_modulation + base + (size_t)gate_slot * width);
-    static_assert(ITERS % 6 == 0, "rows are processed six vectors at a time");
-    uint4 held[ITERS];
     float sums[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-    /* residual may alias gated_residual, so the compiler cannot move a later residual load above an earlier
-     * store: the loads of six vectors are issued together before any of their results is stored */
-    constexpr int CHUNK = 6;
+    /* residual may alias gated_residual: the loads of four vectors are issued before any of their results is stored */
+    for (uint32_t c0 = lane; c0 < vectors; c0 += 128) {
+        uint4 r[4], b[4], g[4];
 #pragma unroll
-    for (int i0 = 0; i0 < ITERS; i0 += CHUNK) {
-        uint4 r[CHUNK], b[CHUNK], g[CHUNK];
-#pragma unroll
-        for (int k = 0; k < CHUNK; k++) {
-            const uint32_t c = lane + (i0 + k) * 32;   /* vector c holds elements 8 * lane + 256 * i .. + 7 */
+        for (int k = 0; k < 4; k++) {
+            const uint32_t c = c0 + k * 32;
             const bool live = c < vectors;
             r[k] = live ? res4[c] : make_uint4(0, 0, 0, 0);
             b[k] = live ? br4[c] : make_uint4(0, 0, 0, 0);
             g[k] = live ? gate4[c] : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
-        for (int k = 0; k < CHUNK; k++) {
-            const int i = i0 + k;
-            const uint32_t c = lane + i * 32;
-            held[i] = make_uint4(0, 0, 0, 0);
+        for (int k = 0; k < 4; k++) {
+            const uint32_t c = c0 + k * 32;
             if (c < vectors) {
                 const uint32_t rw[4] = {r[k].x, r[k].y, r[k].z, r[k].w}, bw[4] = {b[k].x, b[k].y, b[k].z, b[k].w};
                 const uint32_t gw[4] = {g[k].x, g[k].y, g[k].z, g[k].w};
                 uint32_t o[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-                    /* cvt.rn.bf16x2.f32 rounds to nearest even like the reference's bit arithmetic on every finite value */
                     o[j] = pack_bf16_pair(__fadd_rn(bf16_lo(rw[j]), __fmul_rn(bf16_lo(bw[j]), bf16_lo(gw[j]))),
                                           __fadd_rn(bf16_hi(rw[j]), __fmul_rn(bf16_hi(bw[j]), bf16_hi(gw[j]))));
                     sums[2 * j] = fmaf(bf16_lo(o[j]), bf16_lo(o[j]), sums[2 * j]);
                     sums[2 * j + 1] = fmaf(bf16_hi(o[j]), bf16_hi(o[j]), sums[2 * j + 1]);
                 }
-                held[i] = make_uint4(o[0], o[1], o[2], o[3]);
-                reinterpret_cast<uint4 *>(gated_residual + row_base)[c] = held[i];
+                const uint4 gated = make_uint4(o[0], o[1], o[2], o[3]);
+                held[c] = gated;
+                reinterpret_cast<uint4 *>(gated_residual + row_base)[c] = gated;
             }
         }
     }
-    /* 256-lane tree: strides 128, 64, 32 (shared-memory steps of the CTA version), then 16, 8 (its shuffles) */
 #pragma unroll
     for (int shift = 16; shift; shift >>= 1)
 #pragma unroll
@@ -313,43 +309,38 @@ static __global__ void __launch_bounds__(128) gate_adaln_quantize_warp_kernel(
     const uint4 *shift4 = reinterpret_cast<const uint4 *>(norm_modulation + base + (size_t)shift_slot * width);
     const uint4 *scale4 = reinterpret_cast<const uint4 *>(norm_modulation + base + (size_t)scale_slot * width);
     float local_max = 0.0f;
+#pragma unroll 2
+    for (uint32_t c = lane; c < vectors; c += 32) {   /* each lane reads back only what it wrote itself */
+        const uint4 n = nw4[c], sh = shift4[c], sc = scale4[c], own = held[c];
+        const uint32_t vw[4] = {own.x, own.y, own.z, own.w}, nw[4] = {n.x, n.y, n.z, n.w};
+        const uint32_t hw[4] = {sh.x, sh.y, sh.z, sh.w}, cw[4] = {sc.x, sc.y, sc.z, sc.w};
+        uint32_t o[4];
 #pragma unroll
-    for (int i = 0; i < ITERS; i++) {
-        const uint32_t c = lane + i * 32;
-        if (c < vectors) {
-            const uint4 n = nw4[c], sh = shift4[c], sc = scale4[c];
-            const uint32_t vw[4] = {held[i].x, held[i].y, held[i].z, held[i].w}, nw[4] = {n.x, n.y, n.z, n.w};
-            const uint32_t hw[4] = {sh.x, sh.y, sh.z, sh.w}, cw[4] = {sc.x, sc.y, sc.z, sc.w};
-            uint32_t o[4];
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float n0 = __fmul_rn(__fmul_rn(bf16_lo(vw[j]), inverse), bf16_lo(nw[j]));
-                const float n1 = __fmul_rn(__fmul_rn(bf16_hi(vw[j]), inverse), bf16_hi(nw[j]));
-                o[j] = pack_bf16_pair(__fadd_rn(__fmul_rn(n0, __fadd_rn(1.0f, bf16_lo(cw[j]))), bf16_lo(hw[j])),
-                                      __fadd_rn(__fmul_rn(n1, __fadd_rn(1.0f, bf16_hi(cw[j]))), bf16_hi(hw[j])));
-                local_max = fmaxf(local_max, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
-            }
-            held[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        for (int j = 0; j < 4; j++) {
+            const float n0 = __fmul_rn(__fmul_rn(bf16_lo(vw[j]), inverse), bf16_lo(nw[j]));
+            const float n1 = __fmul_rn(__fmul_rn(bf16_hi(vw[j]), inverse), bf16_hi(nw[j]));
+            o[j] = pack_bf16_pair(__fadd_rn(__fmul_rn(n0, __fadd_rn(1.0f, bf16_lo(cw[j]))), bf16_lo(hw[j])),
+                                  __fadd_rn(__fmul_rn(n1, __fadd_rn(1.0f, bf16_hi(cw[j]))), bf16_hi(hw[j])));
+            local_max = fmaxf(local_max, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
         }
+        held[c] = make_uint4(o[0], o[1], o[2], o[3]);
     }
     const float peak = warp_max(local_max);
     const float out_scale = peak > 0.0f ? __fdiv_rn(peak, 127.0f) : __fdiv_rn(1.0f, 127.0f);
     const float q_scale = peak > 0.0f ? __fdiv_rn(127.0f, peak) : 127.0f;
     if (lane == 0) quantized_scales[row] = out_scale;
+#pragma unroll 2
+    for (uint32_t c = lane; c < vectors; c += 32) {
+        const uint4 own = held[c];
+        const uint32_t w[4] = {own.x, own.y, own.z, own.w};
+        uint32_t o[2] = {0, 0};
 #pragma unroll
-    for (int i = 0; i < ITERS; i++) {
-        const uint32_t c = lane + i * 32;
-        if (c < vectors) {
-            const uint32_t w[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
-            uint32_t o[2] = {0, 0};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                uint32_t lo = (uint32_t)quantize_one(bf16_lo(w[j]), q_scale) & 0xffu;
-                uint32_t hi = (uint32_t)quantize_one(bf16_hi(w[j]), q_scale) & 0xffu;
-                o[j >> 1] |= (lo | (hi << 8)) << ((j & 1) * 16);
-            }
-            reinterpret_cast<uint2 *>(quantized + row_base)[c] = make_uint2(o[0], o[1]);
+        for (int j = 0; j < 4; j++) {
+            uint32_t lo = (uint32_t)quantize_one(bf16_lo(w[j]), q_scale) & 0xffu;
+            uint32_t hi = (uint32_t)quantize_one(bf16_hi(w[j]), q_scale) & 0xffu;
+            o[j >> 1] |= (lo | (hi << 8)) << ((j & 1) * 16);
         }
+        reinterpret_cast<uint2 *>(quantized + row_base)[c] = make_uint2(o[0], o[1]);
     }
 }
 
