@@ -29,22 +29,30 @@
 
 namespace h3q8 {
 
+/* WIDE = false: the shape described above, for narrow groups where the combine is the bound.
+ * WIDE = true: 256 x 256 tiles, two accumulators, 8 epilogue warps with one row x 128 columns of totals per thread
+ * (a quarter of the register file again, now in half as many threads): for groups of 512 and more the combine runs
+ * once per four or more k-blocks and no longer bounds anything, so the tile that halves the operand traffic per flop
+ * wins (the reference's per-1024 FC2 recipe). */
+template <bool WIDE>
 struct PairGroupedConfig {
-    static constexpr int BM = 256, BN = 128, BKE = 128, ROW_BYTES = 128;
-    static constexpr int A_BYTES = 128 * ROW_BYTES, B_BYTES = 64 * ROW_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = 8;
-    static constexpr int ACC_COLS = BN, ACC_BUFFERS = 4;
-    static constexpr int EPILOGUE_WARPS = 16, PRODUCER_WARP = 16, MMA_WARP = 17, WARPS = 18, THREADS = WARPS * 32;
-    static constexpr int SCALE_BYTES = EPILOGUE_WARPS * 2 * 32 * 4; /* per warp: two buffers of 32 floats */
+    static constexpr int BM = 256, BN = WIDE ? 256 : 128, BKE = 128, ROW_BYTES = 128;
+    static constexpr int A_BYTES = 128 * ROW_BYTES, B_BYTES = (BN / 2) * ROW_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = WIDE ? 6 : 8;
+    static constexpr int ACC_COLS = BN, ACC_BUFFERS = 512 / BN;
+    static constexpr int EPILOGUE_WARPS = WIDE ? 8 : 16, PRODUCER_WARP = EPILOGUE_WARPS, MMA_WARP = EPILOGUE_WARPS + 1;
+    static constexpr int WARPS = EPILOGUE_WARPS + 2, THREADS = WARPS * 32;
+    static constexpr int COLS = BN / (EPILOGUE_WARPS / 4);          /* output columns per epilogue thread: 32 or 128 */
+    static constexpr int SCALE_BYTES = EPILOGUE_WARPS * 2 * COLS * 4; /* per warp: two buffers of COLS floats */
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + SCALE_BYTES + 1024 + 256;
     static constexpr uint32_t IDESC = umma_idesc(2, 1, 256, BN);
 };
 
 /* MAGIC: scale groups of at most 256 elements, so every group sum fits the 2^22 bias trick. */
-template <bool MAGIC>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairGroupedConfig::THREADS, 1)
+template <bool MAGIC, bool WIDE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairGroupedConfig<WIDE>::THREADS, 1)
 gemm_tcgen05_pair_grouped_kernel(const __grid_constant__ PairArgs args) {
-    using C = PairGroupedConfig;
+    using C = PairGroupedConfig<WIDE>;
     const uint32_t total_tiles = args.tile_start[args.count];
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -93,7 +101,7 @@ gemm_tcgen05_pair_grouped_kernel(const __grid_constant__ PairArgs args) {
                     if (rank == 0) mbar_arrive_expect_tx(&full[st.index], 2 * C::STAGE_BYTES);
                     const uint32_t leader_full = map_to_cta(smem_u32(&full[st.index]), 0);
                     tma_load_2d_pair(stage, &map_a, leader_full, (int32_t)(kb * C::BKE), (int32_t)(mb * C::BM + rank * 128), p.l2_policy_a);
-                    tma_load_2d_pair(stage + C::A_BYTES, &map_b, leader_full, (int32_t)(kb * C::BKE), (int32_t)(nb * C::BN + rank * 64),
+                    tma_load_2d_pair(stage + C::A_BYTES, &map_b, leader_full, (int32_t)(kb * C::BKE), (int32_t)(nb * C::BN + rank * (C::BN / 2)),
                                      p.l2_policy_b);
                     st.advance(C::STAGES);
                 }
@@ -128,9 +136,10 @@ gemm_tcgen05_pair_grouped_kernel(const __grid_constant__ PairArgs args) {
             }
         }
     } else {
-        /* epilogue: this CTA's 128 rows; TMEM lane quadrant warp % 4, columns (warp / 4) * 32 .. + 31 */
+        /* epilogue: this CTA's 128 rows; TMEM lane quadrant warp % 4, columns (warp / 4) * COLS .. + COLS - 1 */
+        constexpr int COLS = C::COLS, PER_LANE = COLS / 32;
         const uint32_t quadrant = warp & 3, quarter = warp >> 2;
-        float *my_scales = scale_stage + warp * 64;
+        float *my_scales = scale_stage + warp * 2 * COLS;
         const uint64_t bias2 = f32x2(-12582912.0f, -12582912.0f);
         PipeState acc;
         for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
@@ -139,39 +148,49 @@ gemm_tcgen05_pair_grouped_kernel(const __grid_constant__ PairArgs args) {
             const GemmParams &p = args.p[problem];
             const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
             tile_coordinates(p, local, mb, nb);
-            const uint32_t n0 = nb * C::BN + quarter * 32;
+            const uint32_t n0 = nb * C::BN + quarter * COLS;
             const uint32_t groups = p.K / p.scale_group, wg = p.scale_groups, ag = p.a_scale_groups;
             const uint32_t row = mb * C::BM + rank * 128 + quadrant * 32 + lane;
             const bool row_ok = row < p.M;
             const float *a_row = p.a_scales + (size_t)(row_ok ? row : 0) * ag;
-            /* this lane fetches the scale of column n0 + lane for the whole warp */
-            const bool c_ok = n0 + lane < p.N;
-            const float *w_col = p.w_scales + (size_t)(c_ok ? n0 + lane : 0) * wg;
-            float next_w = c_ok ? w_col[0] : 0.0f, next_a = row_ok ? a_row[0] : 0.0f;
-            /* -0 + x == x for every x, so the first group's value is taken as it is */
-            float total[32];
+            /* this lane fetches the scales of columns n0 + lane + 32 i for the whole warp */
+            float next_w[PER_LANE], next_a = row_ok ? a_row[0] : 0.0f;
+            auto weight_scale = [&](int i, uint32_t group) {
+                const uint32_t column = n0 + lane + 32 * i;
+                return column < p.N ? p.w_scales[(size_t)column * wg + group] : 0.0f;
+            };
 #pragma unroll
-            for (int i = 0; i < 32; i++) total[i] = -0.0f;
+            for (int i = 0; i < PER_LANE; i++) next_w[i] = weight_scale(i, 0);
+            /* -0 + x == x for every x, so the first group's value is taken as it is */
+            float total[COLS];
+#pragma unroll
+            for (int i = 0; i < COLS; i++) total[i] = -0.0f;
 
             for (uint32_t group = 0; group < groups; group++) {
-                float *buffer = my_scales + (wg > 1 ? (group & 1u) * 32u : 0u);
-                if (group == 0 || wg > 1) buffer[lane] = next_w;
+                float *buffer = my_scales + (wg > 1 ? (group & 1u) * COLS : 0u);
+                if (group == 0 || wg > 1) {
+#pragma unroll
+                    for (int i = 0; i < PER_LANE; i++) buffer[lane + 32 * i] = next_w[i];
+                }
                 const uint64_t a2 = f32x2(next_a, next_a);
                 __syncwarp();
                 if (group + 1 < groups) {           /* next group's scales travel while this group is combined */
-                    if (wg > 1) next_w = c_ok ? w_col[group + 1] : 0.0f;
+                    if (wg > 1) {
+#pragma unroll
+                        for (int i = 0; i < PER_LANE; i++) next_w[i] = weight_scale(i, group + 1);
+                    }
                     if (ag > 1) next_a = row_ok ? a_row[group + 1] : 0.0f;
                 }
                 bool ready = wait_or_abort(&tfull[acc.index], acc.phase, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_EPILOGUE; break; }
                 tc_fence_after_sync();
-                const uint32_t taddr = tmem_base + ((quadrant * 32u) << 16) + acc.index * C::ACC_COLS + quarter * 32;
+                const uint32_t taddr = tmem_base + ((quadrant * 32u) << 16) + acc.index * C::ACC_COLS + quarter * COLS;
 #pragma unroll
-                for (int c2 = 0; c2 < 2; c2++) {
+                for (int c2 = 0; c2 < COLS / 16; c2++) {
                     uint32_t v[16];
                     tmem_load_32x16(taddr + c2 * 16, v);
                     tmem_load_wait();
-                    if (c2 == 1) {                  /* everything this warp needs is in registers: the MMA issuer may refill */
+                    if (c2 == COLS / 16 - 1) {      /* everything this warp needs is in registers: the MMA issuer may refill */
                         tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) {
@@ -205,7 +224,7 @@ gemm_tcgen05_pair_grouped_kernel(const __grid_constant__ PairArgs args) {
             if (failure) break;
             if (row_ok) {
 #pragma unroll
-                for (int j8 = 0; j8 < 4; j8++) {
+                for (int j8 = 0; j8 < COLS / 8; j8++) {
                     const uint32_t col = n0 + j8 * 8;
                     if (col >= p.N) continue;       /* N is a multiple of 8 on this path */
                     float lin[8];

@@ -7,5 +7,5 @@ void count_launch(unsigned kernels);    /* bumps the library-wide launch counter
 uint32_t *device_status_word();         /* per-device error word, allocated on demand */
 struct PairArgs;
 /* grouped-scale two-CTA W8A8 kernel (its own translation unit, built with --fmad=false) */
-int launch_pair_grouped_kernel(const PairArgs &args, bool magic, int sms, void *stream);
+int launch_pair_grouped_kernel(const PairArgs &args, bool magic, bool wide, int sms, void *stream);
 }

@@ -8,10 +8,10 @@
 
 namespace h3q8 {
 
-template <bool MAGIC>
+template <bool MAGIC, bool WIDE>
 static int launch(const PairArgs &args, int sms, cudaStream_t stream) {
-    using C = PairGroupedConfig;
-    auto kernel = gemm_tcgen05_pair_grouped_kernel<MAGIC>;
+    using C = PairGroupedConfig<WIDE>;
+    auto kernel = gemm_tcgen05_pair_grouped_kernel<MAGIC, WIDE>;
     static int clusters[64] = {};
     int device = 0;
     cudaGetDevice(&device);
@@ -42,8 +42,9 @@ static int launch(const PairArgs &args, int sms, cudaStream_t stream) {
     return e == cudaSuccess ? 1 : fail("CUDA tcgen05 grouped pair linear launch: %s", cudaGetErrorString(e));
 }
 
-int launch_pair_grouped_kernel(const PairArgs &args, bool magic, int sms, void *stream) {
-    return magic ? launch<true>(args, sms, (cudaStream_t)stream) : launch<false>(args, sms, (cudaStream_t)stream);
+int launch_pair_grouped_kernel(const PairArgs &args, bool magic, bool wide, int sms, void *stream) {
+    if (wide) return launch<false, true>(args, sms, (cudaStream_t)stream);     /* wide tiles serve groups of 512 and more */
+    return magic ? launch<true, false>(args, sms, (cudaStream_t)stream) : launch<false, false>(args, sms, (cudaStream_t)stream);
 }
 
 } /* namespace h3q8 */

@@ -185,14 +185,18 @@ static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, 
 /* W8A8 with per-K-group scales on the two-CTA kernel (one problem per launch). */
 template <bool MAGIC>
 static int launch_pair_grouped(const h3q8_linear_desc &d, const GemmParams &params, DeviceState *dev, cudaStream_t stream) {
-    constexpr uint32_t BM = 256, BN = 128, BKE = 128; /* PairGroupedConfig: 256 x 128 tile, each CTA stages 64 weight rows */
+    /* PairGroupedConfig: 256 x 128 tiles while the per-group combine is the bound, 256 x 256 for groups of 512 and more;
+     * each CTA stages half of the tile's weight rows */
+    static const int wide_tiles = [] { const char *e = getenv("H3Q8_GROUPED_WIDE"); return e && *e ? atoi(e) : 0; }();
+    const bool wide = wide_tiles && params.scale_group >= 512;
+    const uint32_t BM = 256, BN = wide ? 256 : 128, BKE = 128;
     PairArgs args;
     memset(&args, 0, sizeof args);
     args.count = 1;
     GemmParams &p = args.p[0];
     p = params;
     if (!make_map(&args.map_a[0], d.input, 1, d.rows, d.input_dim, BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
-    if (!make_map(&args.map_b[0], d.weight, 1, d.output_dim, d.input_dim, BKE, 64, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    if (!make_map(&args.map_b[0], d.weight, 1, d.output_dim, d.input_dim, BKE, BN / 2, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
     p.m_blocks = (d.rows + BM - 1) / BM;
     p.n_blocks = (d.output_dim + BN - 1) / BN;
     p.tiles = p.m_blocks * p.n_blocks;
@@ -202,7 +206,7 @@ static int launch_pair_grouped(const h3q8_linear_desc &d, const GemmParams &para
     p.l2_policy_b = L2_EVICT_NORMAL;
     args.tile_start[0] = 0;
     args.tile_start[1] = p.tiles;
-    return launch_pair_grouped_kernel(args, MAGIC, dev->sms, stream);
+    return launch_pair_grouped_kernel(args, MAGIC, wide, dev->sms, stream);
 }
 
 /* Split-K plan for one problem: how many CTAs share an output tile and how many k-blocks each takes.
