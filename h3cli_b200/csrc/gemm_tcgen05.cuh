@@ -32,6 +32,7 @@ enum : uint32_t {
     STATUS_WAIT_MMA = 2,       /* MMA issuer gave up waiting for operands / TMEM  */
     STATUS_WAIT_EPILOGUE = 3,  /* epilogue gave up waiting for an accumulator     */
     STATUS_WAIT_DEQUANT = 4,   /* dequantiser gave up waiting                     */
+    STATUS_NONFINITE = 0x80000000u, /* OR-ed in by a quantiser or packer that met an Inf or a NaN */
 };
 
 struct GemmParams {

@@ -166,6 +166,8 @@ gemm_tcgen05_pair_grouped_kernel(const __grid_constant__ PairArgs args) {
 #pragma unroll
             for (int i = 0; i < COLS; i++) total[i] = -0.0f;
 
+            /* every lane has finished reading the scales the previous tile staged (lanes diverge on row_ok before this) */
+            __syncwarp();
             for (uint32_t group = 0; group < groups; group++) {
                 float *buffer = my_scales + (wg > 1 ? (group & 1u) * COLS : 0u);
                 if (group == 0 || wg > 1) {

@@ -1234,10 +1234,11 @@ extern "C" int h3_gpu_gate_adaln_quantize_int8(h3_gpu *g, h3_gpu_tensor *gated_r
         }
         gate_adaln_quantize_warp_smem_kernel<<<(padded_rows + 3) / 4, 128, row_bytes, g->compute>>>(
             res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows, padded_rows, width, slots, gate_slot, shift_slot,
-            scale_slot, epsilon);
+            scale_slot, epsilon, g->flags + 1);
     } else
         gate_adaln_quantize_kernel<<<padded_rows, 256, width * sizeof(uint16_t), g->compute>>>(
-            res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon);
+            res_p, branch_p, gate_p, map_p, norm_p, mod_p, gated_p, q_p, s_p, rows, width, slots, gate_slot, shift_slot, scale_slot, epsilon,
+            g->flags + 1);
     count_launch(1);
     return launch_status(g, "gate/AdaLN/quantize", 1);
 }
@@ -1425,7 +1426,7 @@ static int int8_projection(h3_gpu *g, const h3_gpu_tensor *q_in, const h3_gpu_te
 static __global__ void __launch_bounds__(256) quantize_rows_head_major_kernel(const uint16_t *__restrict__ in, int8_t *__restrict__ out,
                                                                        float *__restrict__ scales, uint32_t rows, uint32_t heads,
                                                                        uint32_t head_dim, uint32_t *nonfinite) {
-    __shared__ float scratch[8];
+    __shared__ uint32_t scratch[8];
     const uint32_t row = blockIdx.x, columns = heads * head_dim, vectors = columns / 8;
     uint2 *q = reinterpret_cast<uint2 *>(out + (size_t)row * columns);
     if (row >= rows) {
@@ -1437,19 +1438,20 @@ static __global__ void __launch_bounds__(256) quantize_rows_head_major_kernel(co
         const uint32_t column = c * 8, head = column / head_dim, inside = column - head * head_dim;
         return *reinterpret_cast<const uint4 *>(in + ((size_t)head * rows + row) * head_dim + inside);
     };
-    float peak = 0.0f;
+    uint32_t peak_bits = 0;
     for (uint32_t c = threadIdx.x; c < vectors; c += 256) {
         const uint4 v = vector(c);
         const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-        for (int j = 0; j < 4; j++) peak = fmaxf(peak, fmaxf(fabsf(bf16_lo(w[j])), fabsf(bf16_hi(w[j]))));
+        for (int j = 0; j < 4; j++) peak_bits = absmax2(peak_bits, w[j]);
     }
-    peak = block_max_256(peak, scratch);
+    peak_bits = block_max_256_u32(absmax_fold(peak_bits), scratch);
+    const float peak = bf16_bits_to_f32(peak_bits);
     const float scale = peak > 0.0f ? __fdiv_rn(peak, 127.0f) : __fdiv_rn(1.0f, 127.0f);
     const float inverse = peak > 0.0f ? __fdiv_rn(127.0f, peak) : 127.0f;
     if (threadIdx.x == 0) {
         scales[row] = scale;
-        if (!(peak <= FLT_MAX) && nonfinite) atomicOr(nonfinite, 1u);
+        if (absmax_nonfinite(peak_bits) && nonfinite) atomicOr(nonfinite, STATUS_NONFINITE);
     }
     for (uint32_t c = threadIdx.x; c < vectors; c += 256) {
         const uint4 v = vector(c);

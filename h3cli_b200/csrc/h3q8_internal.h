@@ -5,7 +5,8 @@ namespace h3q8 {
 int fail(const char *format, ...);      /* records the thread's error text, returns 0 */
 void count_launch(unsigned kernels);    /* bumps the library-wide launch counter     */
 uint32_t *device_status_word();         /* per-device error word, allocated on demand */
+uint32_t static_status_take();          /* error word inside the static scratch of h3q8_linear_w8a8_static, read and cleared */
 struct PairArgs;
-/* grouped-scale two-CTA W8A8 kernel (its own translation unit, built with --fmad=false) */
+/* grouped-scale two-CTA W8A8 kernel (its own translation unit; every fp32 step is an explicit __fmul_rn / __fadd_rn) */
 int launch_pair_grouped_kernel(const PairArgs &args, bool magic, bool wide, int sms, void *stream);
 }

@@ -471,7 +471,7 @@ extern "C" int h3q8_quantize_rows(const uint16_t *input, int8_t *output, float *
     if (!(clip > 0.0f) || clip > 1.0f) return fail("quantize rows: clip must be in (0, 1]");
     uint32_t *status = device_status_word();
     if (!status) return 0;
-    cudaError_t e = launch_quantize_rows(input, output, scales, rows, dispatch_rows, columns, clip, nullptr, (cudaStream_t)cuda_stream);
+    cudaError_t e = launch_quantize_rows(input, output, scales, rows, dispatch_rows, columns, clip, status, (cudaStream_t)cuda_stream);
     count_launch(1);
     return cuda_ok(e, "quantize rows launch");
 }
@@ -490,12 +490,13 @@ extern "C" int h3q8_q8_pack_rows_device(const uint16_t *source, int8_t *weights,
     size_t offset, bytes;
     if (!source || !weights || !scales || !h3q8_q8_layout(rows, columns, group, &offset, &bytes))
         return fail("q8 pack: invalid arguments");
-    if (!device_status_word()) return 0;
+    uint32_t *status = device_status_word();
+    if (!status) return 0;
     const uint32_t width = group ? group : columns;
     const uint32_t groups = (uint32_t)(((uint64_t)columns + width - 1) / width);
     const uint64_t items = (uint64_t)rows * groups;
     q8_pack_rows_kernel<<<(unsigned)((items + 7) / 8), 256, 0, (cudaStream_t)cuda_stream>>>(source, weights, scales, rows, columns,
-                                                                                           width, groups, nullptr);
+                                                                                           width, groups, status);
     count_launch(1);
     return cuda_ok(cudaGetLastError(), "q8 pack launch");
 }
@@ -522,10 +523,11 @@ extern "C" uint32_t h3q8_device_status(void *cuda_stream) {
         fail("CUDA error while reading the device status: %s", cudaGetErrorString(cudaGetLastError()));
         return 0xffffffffu;
     }
-    if (value) {
-        cudaMemset(word, 0, sizeof value);
-        fail("a kernel gave up a bounded wait: code %u in CTA %u", value & 0xffu, value >> 8);
-    }
+    if (value) cudaMemset(word, 0, sizeof value);
+    else value = static_status_take();   /* h3q8_linear_w8a8_static called without a status word of the caller's */
+    if (value == 0xffffffffu) fail("CUDA error while reading the device status: %s", cudaGetErrorString(cudaGetLastError()));
+    else if (value & STATUS_NONFINITE) fail("non-finite value (Inf or NaN) in the input of a quantiser or of the weight packer");
+    else if (value) fail("a kernel gave up a bounded wait: code %u in CTA %u", value & 0xffu, value >> 8);
     return value;
 }
 

@@ -124,6 +124,23 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 } /* namespace */
 
+/* The status word inside the static array, for calls that passed device_status == NULL: read (and cleared when set) by
+ * h3q8_device_status after it has synchronised the stream.  0 when this device never ran the static entry point. */
+uint32_t h3q8::static_status_take() {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+    unsigned char *base;
+    {
+        std::lock_guard<std::mutex> lock(setup_mutex);
+        if (!per_device[device].ready) return 0;
+        base = per_device[device].base;
+    }
+    uint32_t value = 0;
+    if (cudaMemcpy(&value, base + STATUS_OFFSET, sizeof value, cudaMemcpyDeviceToHost) != cudaSuccess) return 0xffffffffu;
+    if (value) cudaMemset(base + STATUS_OFFSET, 0, sizeof value);
+    return value;
+}
+
 extern "C" int h3q8_linear_w8a8_static(const h3q8_linear_desc *desc, uint32_t *device_status, void *cuda_stream) {
     if (!desc) return fail("static W8A8: null descriptor");
     const h3q8_linear_desc &d = *desc;
@@ -134,6 +151,9 @@ extern "C" int h3q8_linear_w8a8_static(const h3q8_linear_desc *desc, uint32_t *d
     if (d.input_scales) return fail("static W8A8: input is bf16 here; leave input_scales NULL (the scales live in the static scratch)");
     if (d.weight_group || d.input_group || d.accumulators) return fail("static W8A8: per-channel weight scales only, no accumulator dump");
     if (d.activation > H3Q8_ACT_GELU_TANH) return fail("static W8A8: unknown activation %u", d.activation);
+    if (d.rope) return fail("static W8A8: the QKV rotary epilogue is not available here; use h3q8_linear");
+    if (d.workspace || d.workspace_bytes) return fail("static W8A8: takes no workspace (split-K is not available here)");
+    if (d.kernel != H3Q8_KERNEL_AUTO) return fail("static W8A8: desc.kernel must be H3Q8_KERNEL_AUTO (one fixed kernel runs here)");
     if (d.rows > MAX_ROWS || (uint64_t)d.rows * d.input_dim > ACTIVATION_BYTES)
         return fail("static W8A8: %u x %u activations exceed the built-in scratch (rows <= %u and rows * input_dim <= %zu bytes); "
                     "use h3q8_quantize_rows + h3q8_linear with your own scratch instead",

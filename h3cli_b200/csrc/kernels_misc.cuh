@@ -31,6 +31,29 @@ __device__ __forceinline__ float block_max_256(float v, float *scratch8) {
     __syncthreads();
     return r;
 }
+/* Largest |x| of bf16 values as BIT PATTERNS.  For bf16, |a| <= |b| exactly when (a & 0x7fff) <= (b & 0x7fff) as
+ * integers, and Inf / NaN are exactly the patterns >= 0x7f80: an integer maximum therefore carries a NaN to the end of
+ * the reduction, where fmaxf would silently drop it (the reference rejects NaN and Inf alike, src/weights/q8.c:38-41,
+ * tests/quant_native.c:64-74).  Two elements per instruction on packed pairs. */
+__device__ __forceinline__ uint32_t absmax2(uint32_t running, uint32_t packed_pair) { return __vmaxu2(running, packed_pair & 0x7fff7fffu); }
+__device__ __forceinline__ uint32_t absmax_fold(uint32_t packed) { return max(packed & 0xffffu, packed >> 16); }
+__device__ __forceinline__ bool absmax_nonfinite(uint32_t folded) { return folded >= 0x7f80u; }
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+/* max over a 256-thread CTA; every thread gets the result */
+__device__ __forceinline__ uint32_t block_max_256_u32(uint32_t v, uint32_t *scratch8) {
+    v = warp_max_u32(v);
+    if ((threadIdx.x & 31) == 0) scratch8[threadIdx.x >> 5] = v;
+    __syncthreads();
+    uint32_t r = scratch8[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) r = max(r, scratch8[i]);
+    __syncthreads();
+    return r;
+}
 __device__ __forceinline__ int quantize_one(float x, float inverse) {
     int q = __float2int_rn(__fmul_rn(x, inverse)); /* rint: ties to even */
     return q < -127 ? -127 : q > 127 ? 127 : q;
@@ -38,11 +61,11 @@ __device__ __forceinline__ int quantize_one(float x, float inverse) {
 
 /* Per-token (per-row) dynamic int8 quantiser.  Rows >= rows are padding: zero
  * bytes and scale 1.  One CTA per dispatched row.  Sets *nonfinite when a row
- * maximum is Inf/NaN. */
+ * holds an Inf or a NaN. */
 static __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_t *__restrict__ in, int8_t *__restrict__ out,
                                                             float *__restrict__ scales, uint32_t rows, uint32_t columns,
                                                             float clip, uint32_t *nonfinite) {
-    __shared__ float scratch[8];
+    __shared__ uint32_t scratch[8];
     const uint32_t row = blockIdx.x;
     int8_t *q = out + (size_t)row * columns;
     const bool vec = (columns & 7u) == 0;
@@ -53,7 +76,7 @@ static __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_
         return;
     }
     const uint16_t *x = in + (size_t)row * columns;
-    float peak = 0.0f;
+    uint32_t peak_bits = 0;
     uint4 held[2]; /* up to 4096 columns stay in registers between the two passes */
     const uint32_t vectors = columns / 8;
     if (vec) {
@@ -63,26 +86,25 @@ static __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_
             held[i] = c < vectors ? reinterpret_cast<const uint4 *>(x)[c] : make_uint4(0, 0, 0, 0);
             const uint32_t w[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-                peak = fmaxf(peak, fmaxf(fabsf(bf16_bits_to_f32(w[j] & 0xffffu)), fabsf(bf16_bits_to_f32(w[j] >> 16))));
+            for (int j = 0; j < 4; j++) peak_bits = absmax2(peak_bits, w[j]);
         }
         for (uint32_t c = threadIdx.x + 512; c < vectors; c += 256) {
             uint4 v = reinterpret_cast<const uint4 *>(x)[c];
             const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int j = 0; j < 4; j++)
-                peak = fmaxf(peak, fmaxf(fabsf(bf16_bits_to_f32(w[j] & 0xffffu)), fabsf(bf16_bits_to_f32(w[j] >> 16))));
+            for (int j = 0; j < 4; j++) peak_bits = absmax2(peak_bits, w[j]);
         }
     } else {
-        for (uint32_t c = threadIdx.x; c < columns; c += 256) peak = fmaxf(peak, fabsf(bf16_bits_to_f32(x[c])));
+        for (uint32_t c = threadIdx.x; c < columns; c += 256) peak_bits = absmax2(peak_bits, x[c]);
     }
-    peak = block_max_256(peak, scratch);
+    peak_bits = block_max_256_u32(absmax_fold(peak_bits), scratch);
+    const float peak = bf16_bits_to_f32(peak_bits);
     const float clipped = __fmul_rn(peak, clip);
     const float scale = clipped > 0.0f ? __fdiv_rn(clipped, 127.0f) : __fdiv_rn(1.0f, 127.0f);
     const float inverse = clipped > 0.0f ? __fdiv_rn(127.0f, clipped) : 127.0f;
     if (threadIdx.x == 0) {
         scales[row] = scale;
-        if (!(peak <= FLT_MAX) && nonfinite) atomicOr(nonfinite, 1u);
+        if (absmax_nonfinite(peak_bits) && nonfinite) atomicOr(nonfinite, STATUS_NONFINITE);
     }
     if (vec) {
         for (uint32_t c = threadIdx.x, i = 0; c < vectors; c += 256, i++) {
@@ -122,23 +144,23 @@ static __global__ void __launch_bounds__(256) quantize_segments_warp_kernel(cons
     }
     const uint4 *x = reinterpret_cast<const uint4 *>(in + s * segment);
     uint4 held[ITERS];
-    float peak = 0.0f;
+    uint32_t peak_bits = 0;
 #pragma unroll
     for (int i = 0; i < ITERS; i++) {
         const uint32_t c = lane + i * 32;
         held[i] = c < vectors ? x[c] : make_uint4(0, 0, 0, 0);
         const uint32_t w[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
 #pragma unroll
-        for (int j = 0; j < 4; j++)
-            peak = fmaxf(peak, fmaxf(fabsf(bf16_bits_to_f32(w[j] & 0xffffu)), fabsf(bf16_bits_to_f32(w[j] >> 16))));
+        for (int j = 0; j < 4; j++) peak_bits = absmax2(peak_bits, w[j]);
     }
-    peak = warp_max(peak);
+    peak_bits = warp_max_u32(absmax_fold(peak_bits));
+    const float peak = bf16_bits_to_f32(peak_bits);
     const float clipped = __fmul_rn(peak, clip);
     const float scale = clipped > 0.0f ? __fdiv_rn(clipped, 127.0f) : __fdiv_rn(1.0f, 127.0f);
     const float inverse = clipped > 0.0f ? __fdiv_rn(127.0f, clipped) : 127.0f;
     if (lane == 0) {
         scales[s] = scale;
-        if (!(peak <= FLT_MAX) && nonfinite) atomicOr(nonfinite, 1u);
+        if (absmax_nonfinite(peak_bits) && nonfinite) atomicOr(nonfinite, STATUS_NONFINITE);
     }
 #pragma unroll
     for (int i = 0; i < ITERS; i++) {
@@ -177,7 +199,7 @@ static inline cudaError_t launch_quantize_rows(const uint16_t *in, int8_t *out, 
  * src/gpu.h:630-642): per row
  *   gated = bf16(residual + branch * gate[class, gate_slot])          -> gated_residual (may alias residual)
  *   inv   = rsqrt(mean(gated^2) + epsilon)                             (fp32, fma accumulation, 256-way tree)
- *   v     = bf16(gated * inv * norm_weight * (1 + scale[class]) + shift[class])
+ *   v     = bf16(fma(gated * inv * norm_weight, 1 + scale[class], shift[class]))
  *   q     = per-row int8 of v (scale = max|v|/127)                    -> quantized, quantized_scales
  * so the W8A8 GEMM that follows reads int8 directly and the bf16 activation is never
  * re-read.  One 256-thread CTA per row; the row lives in shared memory between passes.
@@ -187,10 +209,10 @@ static __global__ void __launch_bounds__(256) gate_adaln_quantize_kernel(
     const uint16_t *residual, const uint16_t *__restrict__ branch, const uint16_t *__restrict__ gate_modulation,
     const uint32_t *__restrict__ row_map, const uint16_t *__restrict__ norm_weight, const uint16_t *__restrict__ norm_modulation,
     uint16_t *gated_residual, int8_t *__restrict__ quantized, float *__restrict__ quantized_scales, uint32_t rows, uint32_t width,
-    uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon, uint32_t *nonfinite) {
     extern __shared__ uint16_t row_values[];
     __shared__ float reductions[256];
-    __shared__ float max_scratch[8];
+    __shared__ uint32_t max_scratch[8];
     const uint32_t row = blockIdx.x, tid = threadIdx.x;
     const size_t row_base = (size_t)row * width;
     if (row >= rows) {
@@ -223,16 +245,18 @@ static __global__ void __launch_bounds__(256) gate_adaln_quantize_kernel(
     }
     __syncthreads();
     const float inverse = reductions[0];
-    float local_max = 0.0f;
+    uint32_t local_max = 0;
     for (uint32_t c = tid; c < width; c += 256) {
         const float normalized = __fmul_rn(__fmul_rn(bf16_bits_to_f32(row_values[c]), inverse), bf16_bits_to_f32(norm_weight[c]));
         const float shift = bf16_bits_to_f32(norm_modulation[base + (size_t)shift_slot * width + c]);
         const float scale = bf16_bits_to_f32(norm_modulation[base + (size_t)scale_slot * width + c]);
-        const uint32_t v = f32_to_bf16_bits(__fadd_rn(__fmul_rn(normalized, __fadd_rn(1.0f, scale)), shift));
+        const uint32_t v = f32_to_bf16_bits(fmaf(normalized, __fadd_rn(1.0f, scale), shift));   /* src/cuda/cuda_kernels.cuh:966-967 */
         row_values[c] = (uint16_t)v;
-        local_max = fmaxf(local_max, fabsf(bf16_bits_to_f32(v)));
+        local_max = absmax2(local_max, v & 0xffffu);
     }
-    const float peak = block_max_256(local_max, max_scratch);
+    const uint32_t peak_bits = block_max_256_u32(absmax_fold(local_max), max_scratch);
+    const float peak = bf16_bits_to_f32(peak_bits);
+    if (tid == 0 && absmax_nonfinite(peak_bits) && nonfinite) atomicOr(nonfinite, STATUS_NONFINITE);
     const float out_scale = peak > 0.0f ? __fdiv_rn(peak, 127.0f) : __fdiv_rn(1.0f, 127.0f);
     const float q_scale = peak > 0.0f ? __fdiv_rn(127.0f, peak) : 127.0f;
     if (tid == 0) quantized_scales[row] = out_scale;
@@ -251,7 +275,7 @@ static __global__ void __launch_bounds__(128) gate_adaln_quantize_warp_smem_kern
     const uint16_t *residual, const uint16_t *__restrict__ branch, const uint16_t *__restrict__ gate_modulation,
     const uint32_t *__restrict__ row_map, const uint16_t *__restrict__ norm_weight, const uint16_t *__restrict__ norm_modulation,
     uint16_t *gated_residual, int8_t *__restrict__ quantized, float *__restrict__ quantized_scales, uint32_t rows, uint32_t padded_rows,
-    uint32_t width, uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    uint32_t width, uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon, uint32_t *nonfinite) {
     extern __shared__ uint4 row_store[];
     const uint32_t row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= padded_rows) return;
@@ -308,7 +332,7 @@ static __global__ void __launch_bounds__(128) gate_adaln_quantize_warp_smem_kern
     const uint4 *nw4 = reinterpret_cast<const uint4 *>(norm_weight);
     const uint4 *shift4 = reinterpret_cast<const uint4 *>(norm_modulation + base + (size_t)shift_slot * width);
     const uint4 *scale4 = reinterpret_cast<const uint4 *>(norm_modulation + base + (size_t)scale_slot * width);
-    float local_max = 0.0f;
+    uint32_t local_max = 0;
 #pragma unroll 2
     for (uint32_t c = lane; c < vectors; c += 32) {   /* each lane reads back only what it wrote itself */
         const uint4 n = nw4[c], sh = shift4[c], sc = scale4[c], own = held[c];
@@ -319,16 +343,21 @@ static __global__ void __launch_bounds__(128) gate_adaln_quantize_warp_smem_kern
         for (int j = 0; j < 4; j++) {
             const float n0 = __fmul_rn(__fmul_rn(bf16_lo(vw[j]), inverse), bf16_lo(nw[j]));
             const float n1 = __fmul_rn(__fmul_rn(bf16_hi(vw[j]), inverse), bf16_hi(nw[j]));
-            o[j] = pack_bf16_pair(__fadd_rn(__fmul_rn(n0, __fadd_rn(1.0f, bf16_lo(cw[j]))), bf16_lo(hw[j])),
-                                  __fadd_rn(__fmul_rn(n1, __fadd_rn(1.0f, bf16_hi(cw[j]))), bf16_hi(hw[j])));
-            local_max = fmaxf(local_max, fmaxf(fabsf(bf16_lo(o[j])), fabsf(bf16_hi(o[j]))));
+            /* one fused multiply-add, as the reference's CUDA build of this formula has it (src/cuda/cuda_kernels.cuh:966-967) */
+            o[j] = pack_bf16_pair(fmaf(n0, __fadd_rn(1.0f, bf16_lo(cw[j])), bf16_lo(hw[j])),
+                                  fmaf(n1, __fadd_rn(1.0f, bf16_hi(cw[j])), bf16_hi(hw[j])));
+            local_max = absmax2(local_max, o[j]);
         }
         held[c] = make_uint4(o[0], o[1], o[2], o[3]);
     }
-    const float peak = warp_max(local_max);
+    const uint32_t peak_bits = warp_max_u32(absmax_fold(local_max));
+    const float peak = bf16_bits_to_f32(peak_bits);
     const float out_scale = peak > 0.0f ? __fdiv_rn(peak, 127.0f) : __fdiv_rn(1.0f, 127.0f);
     const float q_scale = peak > 0.0f ? __fdiv_rn(127.0f, peak) : 127.0f;
-    if (lane == 0) quantized_scales[row] = out_scale;
+    if (lane == 0) {
+        quantized_scales[row] = out_scale;
+        if (absmax_nonfinite(peak_bits) && nonfinite) atomicOr(nonfinite, STATUS_NONFINITE);
+    }
 #pragma unroll 2
     for (uint32_t c = lane; c < vectors; c += 32) {
         const uint4 own = held[c];
@@ -354,10 +383,11 @@ static __global__ void __launch_bounds__(256) q8_pack_rows_kernel(const uint16_t
     const uint32_t row = (uint32_t)(item / groups), g = (uint32_t)(item % groups), lane = threadIdx.x & 31;
     const uint32_t first = g * width, last = columns - first < width ? columns : first + width;
     const uint16_t *x = src + (size_t)row * columns;
-    float peak = 0.0f;
-    for (uint32_t k = first + lane; k < last; k += 32) peak = fmaxf(peak, fabsf(bf16_bits_to_f32(x[k])));
-    peak = warp_max(peak);
-    if (!(peak <= FLT_MAX) && lane == 0 && nonfinite) atomicOr(nonfinite, 1u);
+    uint32_t peak_bits = 0;
+    for (uint32_t k = first + lane; k < last; k += 32) peak_bits = absmax2(peak_bits, x[k]);
+    peak_bits = warp_max_u32(absmax_fold(peak_bits));
+    const float peak = bf16_bits_to_f32(peak_bits);
+    if (absmax_nonfinite(peak_bits) && lane == 0 && nonfinite) atomicOr(nonfinite, STATUS_NONFINITE);
     const float scale = peak == 0.0f ? 1.0f : fmaxf(__fdiv_rn(peak, 127.0f), FLT_MIN);
     if (lane == 0) scales[(size_t)row * groups + g] = scale;
     for (uint32_t k = first + lane; k < last; k += 32) {

@@ -162,8 +162,11 @@ int h3q8_linear_grouped(const h3q8_linear_desc *problems, uint32_t count, void *
  * Every GPU that loads the library holds that array until exit.  All calls on a
  * device share it: calls that overlap on the GPU race.  The first call on a
  * device looks up the array's address and configures the kernel; make it
- * outside stream capture.  device_status may be NULL, or a zeroed device word
- * that receives a code if a bounded wait inside the kernel runs out. */
+ * outside stream capture.  device_status is a zeroed device word of the
+ * caller's that receives a code if a bounded wait inside the kernel runs out;
+ * with NULL the code goes to a word inside the built-in array, which
+ * h3q8_device_status() reads and clears.  desc->rope, desc->workspace and a
+ * kernel selector other than AUTO are refused. */
 #define H3Q8_STATIC_MAX_ACTIVATION_BYTES (16u << 20)
 #define H3Q8_STATIC_MAX_ROWS 16384u
 int h3q8_linear_w8a8_static(const h3q8_linear_desc *desc, uint32_t *device_status, void *cuda_stream);
@@ -185,8 +188,10 @@ int h3q8_q8_pack_rows_device(const uint16_t *source, int8_t *weights, float *sca
 int h3q8_q8_dequant(const int8_t *weights, const float *scales, uint16_t *output, uint32_t rows,
                     uint32_t columns, uint32_t group, void *cuda_stream);
 /* Reads and clears the device error word of the current device (0 = ok);
- * synchronises the stream first.  Non-zero: a bounded wait inside a kernel ran
- * out (code in the low byte, CTA index above it). */
+ * synchronises the stream first.  Bit 31 set: h3q8_quantize_rows[_grouped] or
+ * h3q8_q8_pack_rows_device met an Inf or a NaN (the reference rejects both,
+ * src/weights/q8.c:38-41).  Otherwise non-zero: a bounded wait inside a kernel
+ * ran out (code in the low byte, CTA index above it).  h3q8_last_error() says which. */
 uint32_t h3q8_device_status(void *cuda_stream);
 /* Message of the last failed h3q8_* call on this thread. */
 const char *h3q8_last_error(void);

@@ -19,9 +19,20 @@ MODE_BF16, MODE_W8A16, MODE_W8A8 = 0, 1, 2
 ACT_NONE, ACT_GELU_TANH, ACT_SWIGLU = 0, 1, 2
 
 
+def _reference_tree():
+    """Where the reference sources lie on this machine, or None: $H3_REFERENCE, else a `reference`
+    directory beside the repository (the layout of the build container)."""
+    for candidate in (os.environ.get("H3_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if candidate and os.path.isfile(os.path.join(candidate, "src", "weights", "q8.c")):
+            return candidate
+    return None
+
+
 def build():
     """Compile the checker (and, when the reference tree is present, `_ref`)."""
-    subprocess.run(["make", "-s", "-C", _HERE], check=True, stdout=subprocess.DEVNULL)
+    tree = _reference_tree()
+    subprocess.run(["make", "-s", "-C", _HERE] + ([f"REFERENCE={tree}"] if tree else []), check=True,
+                   stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL if not os.environ.get("H3_ORACLE_VERBOSE") else None)
 
 
 class _Args(ctypes.Structure):
@@ -185,3 +196,103 @@ def linear(mode, x, w, w_scales=None, group=0, x_scales=None, bias=None, gate=No
     if not lib().h3o_linear(ctypes.byref(a)):
         raise ValueError("oracle rejected the arguments")
     return (out, acc) if want_acc else out
+
+
+# --------------------------------------------------------------------------- the reference's own CUDA element kernels
+_REF_CUDA = os.path.join(_HERE, "_ref", "libh3_cuda_kernels_ref.so")
+_ref_cuda = None
+
+
+class ReferenceCuda:
+    """src/cuda/cuda_kernels.cuh of the reference, compiled unmodified with its own flags
+    (oracle/ref_cuda_kernels.cu), run on the current CUDA device.  Arrays in and out are numpy."""
+
+    def __init__(self, library):
+        self._lib = library
+        for name in ("gelu_bf16", "gate_bf16", "adaln_bf16", "rms_norm_bf16", "qkv_rope_bf16", "swiglu_bf16", "add_bf16", "linear_bf16"):
+            getattr(library, "h3ref_" + name).restype = ctypes.c_int
+
+    @staticmethod
+    def _check(ok, what):
+        if not ok:
+            raise RuntimeError(f"reference CUDA kernel {what} failed")
+
+    def gelu(self, bits, approximate=1):
+        bits = np.ascontiguousarray(bits, np.uint16)
+        out = np.empty_like(bits)
+        self._lib.h3ref_gelu_bf16.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32]
+        self._check(self._lib.h3ref_gelu_bf16(_ptr(bits), _ptr(out), bits.size, approximate), "h3_gelu_bf16")
+        return out
+
+    def gate(self, residual, branch, modulation, row_map, slots, gate_slot):
+        rows, width = residual.shape
+        keep = [np.ascontiguousarray(a) for a in (residual, branch, modulation, np.asarray(row_map, np.uint32))]
+        out = np.empty((rows, width), np.uint16)
+        f = self._lib.h3ref_gate_bf16
+        f.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_uint32] * 5
+        self._check(f(*[_ptr(a) for a in keep], _ptr(out), rows, width, slots, gate_slot, keep[2].size // (slots * width)), "h3_gate_bf16")
+        return out
+
+    def adaln(self, x, norm_weight, modulation, row_map, slots, shift_slot, scale_slot, epsilon):
+        rows, width = x.shape
+        keep = [np.ascontiguousarray(a) for a in (x, norm_weight, modulation, np.asarray(row_map, np.uint32))]
+        out = np.empty((rows, width), np.uint16)
+        f = self._lib.h3ref_adaln_bf16
+        f.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_uint32] * 5 + [ctypes.c_float, ctypes.c_uint32]
+        self._check(f(*[_ptr(a) for a in keep], _ptr(out), rows, width, slots, shift_slot, scale_slot, epsilon,
+                      keep[2].size // (slots * width)), "h3_adaln_bf16")
+        return out
+
+    def rms_norm(self, x, weight, epsilon):
+        rows, width = x.shape
+        keep = [np.ascontiguousarray(a) for a in (x, weight)]
+        out = np.empty((rows, width), np.uint16)
+        f = self._lib.h3ref_rms_norm_bf16
+        f.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_uint32] * 2 + [ctypes.c_float]
+        self._check(f(_ptr(keep[0]), _ptr(keep[1]), _ptr(out), rows, width, epsilon), "h3_rms_norm_bf16")
+        return out
+
+    def qkv_rope(self, qkv, q_weight, k_weight, rope_cos, rope_sin, heads, head_dim, rope_half, epsilon, grouped=1):
+        rows = qkv.shape[0]
+        keep = [np.ascontiguousarray(a) for a in (qkv, q_weight, k_weight, rope_cos, rope_sin)]
+        out = [np.empty((rows, heads, head_dim), np.uint16) for _ in range(3)]
+        f = self._lib.h3ref_qkv_rope_bf16
+        f.argtypes = [ctypes.c_void_p] * 8 + [ctypes.c_uint32] * 5 + [ctypes.c_float]
+        self._check(f(*[_ptr(a) for a in keep], *[_ptr(a) for a in out], rows, heads, head_dim, rope_half, grouped, epsilon),
+                    "h3_qkv_rope_bf16")
+        return out
+
+    def swiglu(self, fused):
+        rows, width = fused.shape[0], fused.shape[1] // 2
+        fused = np.ascontiguousarray(fused, np.uint16)
+        out = np.empty((rows, width), np.uint16)
+        f = self._lib.h3ref_swiglu_bf16
+        f.argtypes = [ctypes.c_void_p] * 2 + [ctypes.c_uint32] * 2
+        self._check(f(_ptr(fused), _ptr(out), rows, width), "h3_swiglu_bf16")
+        return out
+
+    def add(self, left, right):
+        keep = [np.ascontiguousarray(a, np.uint16) for a in (left, right)]
+        out = np.empty_like(keep[0])
+        f = self._lib.h3ref_add_bf16
+        f.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_uint32]
+        self._check(f(_ptr(keep[0]), _ptr(keep[1]), _ptr(out), out.size), "h3_add_bf16")
+        return out
+
+    def linear(self, x, w, bias=None):
+        rows, k = x.shape
+        n = w.shape[0]
+        keep = [np.ascontiguousarray(a) if a is not None else None for a in (x, w, bias)]
+        out = np.empty((rows, n), np.uint16)
+        f = self._lib.h3ref_linear_bf16
+        f.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_uint32] * 3
+        self._check(f(*[_ptr(a) for a in keep], _ptr(out), rows, k, n), "h3_linear_bf16")
+        return out
+
+
+def reference_cuda():
+    """The reference's CUDA element kernels (needs a GPU), or None if `_ref` was never built."""
+    global _ref_cuda
+    if _ref_cuda is None and os.path.exists(_REF_CUDA):
+        _ref_cuda = ReferenceCuda(ctypes.CDLL(_REF_CUDA))
+    return _ref_cuda

@@ -181,13 +181,16 @@ void h3o_gate_adaln_quantize(const uint16_t *residual, const uint16_t *branch, c
         }
         for (int stride = 128; stride >= 1; stride >>= 1) /* :3433-3444 */
             for (int t = 0; t < stride; t++) lanes[t] += lanes[t + stride];
+        /* the reference calls rsqrt (shaders.metal:3446, cuda_kernels.cuh:957), which on a GPU is the hardware's
+         * approximate instruction; a CPU has no bit-equal of it, so this restatement uses the correctly rounded value
+         * and the GPU tests pin this operator against the reference's own CUDA kernels instead */
         float inverse = 1.0f / sqrtf(lanes[0] / (float)width + epsilon);
         float peak = 0.0f;
         for (uint32_t c = 0; c < width; c++) { /* :3450-3461 */
             float normalized = h3o_bf16_to_f32(gated_residual[row_base + c]) * inverse * h3o_bf16_to_f32(norm_weight[c]);
             float shift = h3o_bf16_to_f32(norm_modulation[base + (size_t)shift_slot * width + c]);
             float scale = h3o_bf16_to_f32(norm_modulation[base + (size_t)scale_slot * width + c]);
-            uint16_t v = h3o_f32_to_bf16(normalized * (1.0f + scale) + shift);
+            uint16_t v = h3o_f32_to_bf16(fmaf(normalized, 1.0f + scale, shift)); /* one fused step: src/cuda/cuda_kernels.cuh:966-967 */
             normalized_out[row_base + c] = v;
             peak = fmaxf(peak, fabsf(h3o_bf16_to_f32(v)));
         }

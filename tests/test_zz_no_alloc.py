@@ -5,7 +5,7 @@ stops at the first failure has then already run every other test.
 The entry point must give the same bits as the regular route (h3q8_quantize_rows
 into caller-owned scratch, then h3q8_linear in W8A8 mode), call after call, even
 though all calls share one built-in scratch array that keeps whatever the
-previous call left in it.
+previous call left in it; both are also held against the CPU checker.
 """
 import ctypes
 
@@ -14,6 +14,7 @@ import pytest
 
 import h3cli_b200 as h
 from h3cli_b200 import synth
+from parity import check_bf16
 
 pytestmark = pytest.mark.gpu
 
@@ -55,7 +56,7 @@ def static_route(gpu, lib, x, wq, ws, bias, gate, res, activation):
     return got[:M * N].reshape(M, N)
 
 
-def test_static_scratch_entry_point_matches_regular_route():
+def test_static_scratch_entry_point_matches_regular_route(oracle):
     gpu = h.Gpu()
     lib = h.library()
     # two calls in a row: the second is smaller and uses different data, so anything the
@@ -70,6 +71,24 @@ def test_static_scratch_entry_point_matches_regular_route():
         want = regular_route(gpu, lib, x, wq, ws, bias, gate, res, activation)
         got = static_route(gpu, lib, x, wq, ws, bias, gate, res, activation)
         assert (got == want).all(), f"{(got != want).sum()} of {got.size} outputs differ"
+        # and against the CPU restatement of the reference's arithmetic: the fp32 epilogue is deterministic, so
+        # without GELU the bits are equal; with GELU (hardware exponential) within the bf16 bar
+        xq, xs = oracle.quantize_rows(x)
+        expected = oracle.linear(oracle.MODE_W8A8, xq, wq, ws, 0, x_scales=xs, bias=bias, gate=gate, residual=res,
+                                 activation=activation, fast=True)
+        if activation == h.ACT_NONE:
+            assert (got == expected).all()
+        else:
+            check_bf16(got, expected)
+    # operands this entry point does not take are refused, not ignored
+    scratch = gpu.tensor_new_bf16(16)
+    for field, value in (("workspace", scratch.device_pointer), ("kernel", h.KERNEL_TCGEN05_PAIR)):
+        bad = h.LinearDesc(mode=h.MODE_W8A8, rows=16, input_dim=16, output_dim=8, input=scratch.device_pointer,
+                           weight=scratch.device_pointer, weight_scales=scratch.device_pointer, output=scratch.device_pointer)
+        setattr(bad, field, value)
+        assert lib.h3q8_linear_w8a8_static(ctypes.byref(bad), None, gpu.stream) == 0
+    scratch.free()
+    assert gpu.raw_status() == 0      # also reads the status word inside the built-in array
     # beyond the built-in scratch: refused with a clear message, nothing launched
     before = lib.h3q8_kernel_launches()
     dummy = gpu.tensor_new_bf16(16)
