@@ -1,0 +1,352 @@
+/* W8A16 with dequantisation in the main loop on the two-CTA tile.
+ *
+ *   out[M,N] = epilogue( X[M,K] (bf16) . bf16(float(Wq[N,K]) * scale[n, k/group])^T )
+ *
+ * A cluster of two CTAs computes a 256 x 256 output tile with `tcgen05.mma.cta_group::2`
+ * exactly as gemm_tcgen05_pair_kernel does, but the weight arrives as int8: each CTA's TMA
+ * brings its own 128 weight rows of a k-block as 64 raw bytes per row, dequantiser warps
+ * (two groups of four on alternate k-blocks) turn them into the bf16 operand tile (128-byte rows, 128-byte swizzle) with the
+ * reference's arithmetic, bf16(float(q) * scale) (src/metal/shaders.metal:825-827), and the
+ * leader's MMA issuer consumes the converted tiles of BOTH CTAs.
+ *
+ * Why two CTAs: a CTA converts only its own 128 of the tile's 256 weight rows, i.e. half
+ * of the conversions per SM and MMA clock of a one-CTA 128 x 256 tile, and its tensor core
+ * reads half of the B operand from its own shared memory.
+ *
+ * Per CTA and k-block (64 elements of K, 512 MMA clocks at full rate):
+ *   TMA writes    A 16 KB (bf16, 128-byte swizzle) + raw W 8 KB (int8, 64-byte swizzle)
+ *   dequantisers  read 8 KB, write 16 KB (converted ring)
+ *   tensor core   reads A 16 KB + converted W 16 KB
+ *
+ * Barriers (count; who arrives):
+ *   afull[s]   leader only; 1 + tx bytes of both CTAs' A tiles      (producers of both CTAs)
+ *   rfull[s]   per CTA;     1 + tx bytes of the CTA's own raw tile   (its own producer)
+ *   empty[s]   per CTA;     1   tcgen05.commit of the leader, sent to both CTAs
+ *   bfull[c]   leader only; 8   one arrival per warp of the dequantiser group (four warps) of both CTAs
+ *   bempty[c]  per CTA;     1   tcgen05.commit of the leader, sent to both CTAs
+ *   tfull[a] / tempty[a]    as in the bf16 pair kernel
+ * Every wait is bounded; a role that gives up raises the CTA's abort flag and all roles
+ * fall through to the common exit, where the status word is set and TMEM is freed.
+ */
+#pragma once
+#include "gemm_tcgen05_pair.cuh"
+
+namespace h3q8 {
+
+struct PairW8A16Config {
+    static constexpr int BM = 256, BN = 256, BKE = 64;
+    static constexpr int A_BYTES = 128 * 128;           /* this CTA's 128 rows of X, 64 bf16 each       */
+    static constexpr int RAW_BYTES = 128 * 64;           /* this CTA's 128 weight rows, 64 int8 each     */
+    static constexpr int STAGE_BYTES = A_BYTES + RAW_BYTES;
+    static constexpr int B_BYTES = 128 * 128;            /* converted tile                               */
+    static constexpr int STAGES = 5, CONV_BUFFERS = 5;
+    static constexpr int ACC_COLS = BN, ACC_BUFFERS = 2;
+    static constexpr int EPILOGUE_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, FIRST_DEQUANT_WARP = 10, DEQUANT_WARPS = 8;
+    static constexpr int WARPS = FIRST_DEQUANT_WARP + DEQUANT_WARPS, THREADS = WARPS * 32;
+    static constexpr int BARRIERS = 3 * STAGES + 2 * CONV_BUFFERS + 2 * ACC_BUFFERS;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CONV_BUFFERS * B_BYTES + 1024 + 512;
+    static constexpr uint32_t IDESC = umma_idesc(1, 1, 256, BN);
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
+    static_assert(BARRIERS * 8 + 16 <= 512, "barrier block");
+};
+
+/* sixteen int8 (one 16-byte vector) -> sixteen bf16 = bf16(float(q) * scale), as two 16-byte vectors.
+ * (q ^ 0x80) in the low mantissa byte of 2^23 is 2^23 + 128 + q exactly; subtracting 2^23 + 128 and multiplying by the
+ * scale are IEEE fp32 operations, then one round-to-nearest-even conversion per pair.  PACKED uses the two-lane fp32
+ * instructions of sm_100 for the subtraction and the multiplication. */
+template <bool PACKED>
+__device__ __forceinline__ void dequant16(const uint4 q, const float scale, uint4 &lo, uint4 &hi) {
+    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+    uint32_t o[8];
+    if (PACKED) {
+        const uint64_t scale2 = f32x2(scale, scale), magic2 = f32x2(-8388736.0f, -8388736.0f);
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const uint32_t biased = words[w] ^ 0x80808080u;
+            const uint64_t p01 = f32x2(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7650)), __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7651)));
+            const uint64_t p23 = f32x2(__uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7652)), __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7653)));
+            float f0, f1, f2, f3;
+            f32x2_unpack(mul_f32x2(add_f32x2(p01, magic2), scale2), f0, f1);
+            f32x2_unpack(mul_f32x2(add_f32x2(p23, magic2), scale2), f2, f3);
+            o[2 * w] = pack_bf16_pair(f0, f1);
+            o[2 * w + 1] = pack_bf16_pair(f2, f3);
+        }
+    } else {
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            float f[4];
+            dequant4(words[w], scale, f);
+            o[2 * w] = pack_bf16_pair(f[0], f[1]);
+            o[2 * w + 1] = pack_bf16_pair(f[2], f[3]);
+        }
+    }
+    lo = make_uint4(o[0], o[1], o[2], o[3]);
+    hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+template <bool PACKED>
+static __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairW8A16Config::THREADS, 1)
+gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
+    using C = PairW8A16Config;
+    const GemmParams &p = args.p[0];
+    const CUtensorMap &map_a = args.map_a[0], &map_b = args.map_b[0];
+    const uint32_t total_tiles = p.tiles;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *stages = smem;
+    uint8_t *conv = stages + C::STAGES * C::STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(conv + C::CONV_BUFFERS * C::B_BYTES);
+    uint64_t *afull = bars, *rfull = afull + C::STAGES, *empty = rfull + C::STAGES;
+    uint64_t *bfull = empty + C::STAGES, *bempty = bfull + C::CONV_BUFFERS;
+    uint64_t *tfull = bempty + C::CONV_BUFFERS, *tempty = tfull + C::ACC_BUFFERS;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + C::ACC_BUFFERS);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();               /* 0 = leader */
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const uint32_t num_kb = (p.K + C::BKE - 1) / C::BKE;
+    const bool swiglu = p.ep.activation == ACT_SWIGLU;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; s++) { mbar_init(&afull[s], 1); mbar_init(&rfull[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], C::DEQUANT_WARPS); mbar_init(&bempty[s], 1); }
+        for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 2 * C::EPILOGUE_WARPS); }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    if (warp == C::PRODUCER_WARP && lane == 0) { tma_prefetch_descriptor(&map_a); tma_prefetch_descriptor(&map_b); }
+    if (warp == C::MMA_WARP) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync();           /* both CTAs' barriers exist before anything crosses the pair */
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    uint32_t failure = STATUS_OK;
+
+    if (warp == C::PRODUCER_WARP) {
+        /* ------------------------------------------------ TMA producer (both CTAs) */
+        if (lane == 0) {
+            PipeState st;
+            for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
+                uint32_t mb, nb;
+                tile_coordinates(p, tile, mb, nb);
+                /* SwiGLU: the leader stages 128 gate rows, its peer the matching 128 up rows (weight rows N + n) */
+                const uint32_t b_row = swiglu ? nb * 128 + rank * p.N : nb * C::BN + rank * 128;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!wait_or_abort(&empty[st.index], st.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
+                    uint8_t *stage = stages + st.index * C::STAGE_BYTES;
+                    if (rank == 0) mbar_arrive_expect_tx(&afull[st.index], 2 * C::A_BYTES);
+                    mbar_arrive_expect_tx(&rfull[st.index], C::RAW_BYTES);
+                    /* the weight first: the dequantisers are the longer chain */
+                    tma_load_2d(stage + C::A_BYTES, &map_b, &rfull[st.index], (int32_t)(kb * C::BKE), (int32_t)b_row);
+                    tma_load_2d_pair(stage, &map_a, map_to_cta(smem_u32(&afull[st.index]), 0), (int32_t)(kb * C::BKE),
+                                     (int32_t)(mb * C::BM + rank * 128), p.l2_policy_a);
+                    st.advance(C::STAGES);
+                }
+            }
+        }
+    } else if (warp == C::MMA_WARP) {
+        /* ------------------------------------------------ MMA issuer (leader only) */
+        if (lane == 0 && rank == 0) {
+            PipeState st, cv, acc;
+            for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
+                if (!wait_or_abort(&tempty[acc.index], acc.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                tc_fence_after_sync();
+                const uint32_t d = tmem_base + acc.index * C::ACC_COLS;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!wait_or_abort(&afull[st.index], st.phase, abort_flag) ||
+                        !wait_or_abort(&bfull[cv.index], cv.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                    tc_fence_after_sync();
+                    const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(stages + st.index * C::STAGE_BYTES));
+                    const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(conv + cv.index * C::B_BYTES));
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; k4++) umma_bf16_pair(d, a_desc + 2 * k4, b_desc + 2 * k4, C::IDESC, kb | k4);
+                    umma_commit_pair(&empty[st.index], 3);    /* frees the stage in both CTAs          */
+                    umma_commit_pair(&bempty[cv.index], 3);   /* frees the converted tile in both CTAs */
+                    st.advance(C::STAGES);
+                    cv.advance(C::CONV_BUFFERS);
+                }
+                if (failure) break;
+                umma_commit_pair(&tfull[acc.index], 3);
+                acc.advance(C::ACC_BUFFERS);
+            }
+        }
+    } else if (warp >= C::FIRST_DEQUANT_WARP) {
+        /* ------------------------------------------------ dequantisers (both CTAs) */
+        /* Two groups of four warps take alternate k-blocks.  Thread d of a group owns weight row d of this CTA's 128:
+         * four 16-byte loads from the raw tile (64-byte rows, 64-byte swizzle), sixty-four conversions, eight 16-byte
+         * stores into the operand tile (128-byte rows, 128-byte swizzle); consecutive lanes take consecutive rows,
+         * which keeps both swizzles free of bank conflicts.  A warp then pays one wait, one proxy fence and one
+         * arrival per TWO k-blocks, and while one group sits in its fence the other converts. */
+        const uint32_t group = (warp - C::FIRST_DEQUANT_WARP) >> 2;
+        const uint32_t r = threadIdx.x - (C::FIRST_DEQUANT_WARP + 4 * group) * 32;       /* 0..127 */
+        const uint32_t raw_row = r * 64, raw_twist = (r >> 1) & 3, conv_row = r * 128, conv_twist = r & 7;
+        const uint32_t width = p.scale_group ? p.scale_group : p.K;
+        const uint32_t leader_bfull = map_to_cta(smem_u32(bfull), 0);
+        auto scale_pointer = [&](uint32_t tile, bool &live) {
+            uint32_t mb, nb;
+            tile_coordinates(p, tile, mb, nb);
+            const uint32_t n = swiglu ? nb * 128 + r : nb * C::BN + rank * 128 + r;       /* output channel (bounds)  */
+            live = n < p.N;
+            const size_t scale_row = swiglu ? (size_t)rank * p.N + n : n;                  /* row of the weight matrix */
+            return p.w_scales + (live ? scale_row : 0) * p.scale_groups;
+        };
+        PipeState st, cv;
+        uint32_t turn = 0;                                  /* k-blocks seen so far, across tiles */
+        bool live = false;
+        const float *row_scales = pair < total_tiles ? scale_pointer(pair, live) : p.w_scales;
+        float first_scale = live ? row_scales[0] : 0.0f;   /* fetched one tile ahead */
+        for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
+            const float *scales_now = row_scales;
+            const bool live_now = live;
+            float upcoming = first_scale;
+            const uint32_t mine_first = (turn & 1u) == group ? 0u : 1u;   /* this group's first k-block of the tile */
+            if (p.scale_groups > 1 && mine_first && live_now && mine_first < num_kb) upcoming = scales_now[(mine_first * C::BKE) / width];
+            if (tile + pairs < total_tiles) {
+                row_scales = scale_pointer(tile + pairs, live);
+                first_scale = live ? row_scales[0] : 0.0f;
+            }
+            for (uint32_t kb = 0; kb < num_kb; kb++, turn++) {
+                if ((turn & 1u) != group) { st.advance(C::STAGES); cv.advance(C::CONV_BUFFERS); continue; }
+                const float scale = upcoming;
+                if (p.scale_groups > 1 && kb + 2 < num_kb && live_now) upcoming = scales_now[((kb + 2) * C::BKE) / width];
+                bool ready = wait_or_abort(&rfull[st.index], st.phase, abort_flag) &&
+                             wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
+                if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_DEQUANT; break; }
+                const uint8_t *raw = stages + st.index * C::STAGE_BYTES + C::A_BYTES + raw_row;
+                uint8_t *dst = conv + cv.index * C::B_BYTES + conv_row;
+                uint4 q[4];
+#pragma unroll
+                for (int c = 0; c < 4; c++) q[c] = *reinterpret_cast<const uint4 *>(raw + ((c ^ raw_twist) << 4));
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint4 lo, hi;
+                    dequant16<PACKED>(q[c], scale, lo, hi);
+                    *reinterpret_cast<uint4 *>(dst + (((2 * c) ^ conv_twist) << 4)) = lo;
+                    *reinterpret_cast<uint4 *>(dst + (((2 * c + 1) ^ conv_twist) << 4)) = hi;
+                }
+                /* The converted tile is read by the tensor core of THIS SM (each CTA supplies its own half of B), so all
+                 * that has to cross the pair is the news that the writes are done: every writer makes its stores visible
+                 * to the async proxy, then one lane per warp arrives on the leader's barrier with the plain remote arrive.
+                 * (A cluster-scope release here costs a memory barrier of about 900 clocks per warp and k-block: measured,
+                 * it alone held the kernel to a third of the MMA rate.) */
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank == 0) mbar_arrive(&bfull[cv.index]);
+                    else mbar_arrive_remote(leader_bfull + cv.index * 8);
+                }
+                st.advance(C::STAGES);
+                cv.advance(C::CONV_BUFFERS);
+            }
+        }
+    } else {
+        /* ------------------------------------------------ epilogue (both CTAs, own 128 rows) */
+        /* TMEM lane quadrant warp % 4, column half warp / 4; the reference's operator chain in registers (epilogue.cuh) */
+        const uint32_t quadrant = warp & 3, half = warp >> 2;
+        const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
+        PipeState acc;
+        for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
+            uint32_t mb, nb;
+            tile_coordinates(p, tile, mb, nb);
+            const uint32_t n0 = swiglu ? nb * 128 : nb * C::BN;
+            bool ready = wait_or_abort(&tfull[acc.index], acc.phase, abort_flag);
+            if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_EPILOGUE; break; }
+            tc_fence_after_sync();
+            const uint32_t row = mb * C::BM + rank * 128 + quadrant * 32 + lane;
+            const bool row_ok = row < p.M;
+            const uint32_t lane_base = tmem_base + ((quadrant * 32u) << 16) + acc.index * C::ACC_COLS;
+            if (swiglu) {
+                /* accumulator columns 0..127 hold the gate, 128..255 the up projection of the same 128 outputs */
+#pragma unroll 1
+                for (int hc = 0; hc < 4; hc++) {
+                    const int c = half * 4 + hc;
+                    uint32_t vg[16], vu[16];
+                    tmem_load_32x16(lane_base + c * 16, vg);
+                    tmem_load_32x16(lane_base + 128 + c * 16, vu);
+                    tmem_load_wait();
+                    if (!row_ok) continue;
+#pragma unroll
+                    for (int j8 = 0; j8 < 2; j8++) {
+                        const uint32_t col = n0 + c * 16 + j8 * 8;
+                        if (col >= p.N) continue;
+                        uint32_t bg[4] = {0, 0, 0, 0}, bu[4] = {0, 0, 0, 0};
+                        if (p.ep.bias) {
+                            *reinterpret_cast<uint4 *>(bg) = *reinterpret_cast<const uint4 *>(p.ep.bias + col);
+                            *reinterpret_cast<uint4 *>(bu) = *reinterpret_cast<const uint4 *>(p.ep.bias + p.N + col);
+                        }
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            float g0 = __uint_as_float(vg[j8 * 8 + 2 * j]), g1 = __uint_as_float(vg[j8 * 8 + 2 * j + 1]);
+                            float u0 = __uint_as_float(vu[j8 * 8 + 2 * j]), u1 = __uint_as_float(vu[j8 * 8 + 2 * j + 1]);
+                            if (p.ep.bias) {
+                                g0 = __fadd_rn(g0, bf16_lo(bg[j])); g1 = __fadd_rn(g1, bf16_hi(bg[j]));
+                                u0 = __fadd_rn(u0, bf16_lo(bu[j])); u1 = __fadd_rn(u1, bf16_hi(bu[j]));
+                            }
+                            packed[j] = pack_bf16_pair(swiglu_f32(g0, u0, true), swiglu_f32(g1, u1, true));
+                        }
+                        *reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + col) = *reinterpret_cast<uint4 *>(packed);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int hc = 0; hc < 8; hc++) {
+                    const int c = half * 8 + hc;
+                    uint32_t v[16];
+                    tmem_load_32x16(lane_base + c * 16, v);
+                    tmem_load_wait();
+                    if (!row_ok) continue;
+#pragma unroll
+                    for (int j8 = 0; j8 < 2; j8++) {
+                        const uint32_t col = n0 + c * 16 + j8 * 8;
+                        if (col >= p.N) continue;
+                        uint32_t bias[4] = {0, 0, 0, 0}, gate[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+                        uint32_t res[4] = {0, 0, 0, 0};
+                        if (p.ep.bias) *reinterpret_cast<uint4 *>(bias) = *reinterpret_cast<const uint4 *>(p.ep.bias + col);
+                        if (p.ep.gate) *reinterpret_cast<uint4 *>(gate) = *reinterpret_cast<const uint4 *>(p.ep.gate + col);
+                        if (p.ep.residual)
+                            *reinterpret_cast<uint4 *>(res) = *reinterpret_cast<const uint4 *>(p.ep.residual + (size_t)row * p.N + col);
+                        uint32_t packed[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            packed[j] = epilogue_pair(__uint_as_float(v[j8 * 8 + 2 * j]), __uint_as_float(v[j8 * 8 + 2 * j + 1]), bias[j],
+                                                      p.ep.bias != nullptr, p.ep.activation, gated, gate[j], res[j]);
+                        *reinterpret_cast<uint4 *>(p.out + (size_t)row * p.N + col) = *reinterpret_cast<uint4 *>(packed);
+                    }
+                }
+            }
+            /* this warp is done with the accumulator: tell the leader's MMA issuer */
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(&tempty[acc.index]);
+                else mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc.index]), 0));
+            }
+            acc.advance(C::ACC_BUFFERS);
+        }
+    }
+
+    /* ---------------------------------------------------------- teardown */
+    if (failure) {
+        *abort_flag = 1;
+        atomicCAS(p.status, 0u, failure | (blockIdx.x << 8));
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_flag) {
+        /* give any TMA copy still in flight time to land before the shared memory is released */
+        long long start = clock64();
+        while (clock64() - start < 2000000ll) { }
+        __syncthreads();
+    }
+    cluster_sync();           /* the peer's shared memory and TMEM are in use by the leader's MMAs until here */
+    if (warp == C::MMA_WARP) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+} /* namespace h3q8 */

@@ -1024,8 +1024,7 @@ static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size
     } else if (q.weight->q8) {
         const size_t skinny = g->skinny_direct && !swiglu && q.rows <= 128
                             ? h3q8_linear_workspace_bytes(H3Q8_MODE_W8A16, q.rows, q.input_dim, q.output_dim) : 0;
-        if (q.input_dim % 16 == 0 && !skinny && (swiglu || (g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows))) {
-            /* SwiGLU always takes this route: its fused kernel wants bf16 or int8 operands */
+        if (q.input_dim % 16 == 0 && !skinny && g->w8a16_scratch_rows && (swiglu || q.rows >= (uint32_t)g->w8a16_scratch_rows)) {
             need[2] = round256((size_t)q.output_dim * (swiglu ? 2 : 1) * q.input_dim * 2);
         } else mode = H3Q8_MODE_W8A16;
     }

@@ -182,6 +182,54 @@ static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, 
     return cuda_ok(cudaGetLastError(), "tcgen05 pair linear launch");
 }
 
+/* W8A16 with main-loop dequantisation on the two-CTA tile (one problem per launch). */
+static int launch_pair_w8a16(const h3q8_linear_desc &d, const GemmParams &params, DeviceState *dev, cudaStream_t stream) {
+    using C = PairW8A16Config;
+    PairArgs args;
+    memset(&args, 0, sizeof args);
+    args.count = 1;
+    GemmParams &p = args.p[0];
+    p = params;
+    const bool swiglu = d.activation == H3Q8_ACT_SWIGLU; /* weight rows [gate N | up N], 128 outputs per tile */
+    if (!make_map(&args.map_a[0], d.input, 2, d.rows, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    if (!make_map(&args.map_b[0], d.weight, 1, (uint64_t)d.output_dim * (swiglu ? 2 : 1), d.input_dim, C::BKE, 128,
+                  CU_TENSOR_MAP_SWIZZLE_64B)) return 0;
+    p.m_blocks = (d.rows + C::BM - 1) / C::BM;
+    p.n_blocks = swiglu ? (d.output_dim + 127) / 128 : (d.output_dim + C::BN - 1) / C::BN;
+    p.tiles = p.m_blocks * p.n_blocks;
+    const uint32_t band = (uint64_t)d.input_dim * 2 <= 8192 ? 16 : 8;
+    p.band = p.m_blocks < band ? p.m_blocks : band;
+    p.l2_policy_a = L2_EVICT_NORMAL;
+    p.l2_policy_b = L2_EVICT_NORMAL;
+    args.tile_start[0] = 0;
+    args.tile_start[1] = p.tiles;
+    static const bool packed = [] { const char *e = getenv("H3Q8_W8A16_PACKED"); return e && *e ? atoi(e) != 0 : true; }();
+    auto kernel = packed ? gemm_tcgen05_pair_w8a16_kernel<true> : gemm_tcgen05_pair_w8a16_kernel<false>;
+    static int clusters[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (!clusters[device]) {
+        if (!cuda_ok(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES), "shared memory opt-in")) return 0;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(dev->sms & ~1u);
+        config.blockDim = dim3(C::THREADS);
+        config.dynamicSmemBytes = C::SMEM_BYTES;
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = 2; attribute.val.clusterDim.y = 1; attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        int active = 0;
+        if (!cuda_ok(cudaOccupancyMaxActiveClusters(&active, kernel, &config), "cluster occupancy query")) return 0;
+        if (active < 1) return fail("the device cannot co-schedule a two-CTA cluster of the W8A16 pair kernel");
+        clusters[device] = active < dev->sms / 2 ? active : dev->sms / 2;
+    }
+    const uint32_t pairs = p.tiles < (uint32_t)clusters[device] ? p.tiles : (uint32_t)clusters[device];
+    kernel<<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(args);
+    count_launch(1);
+    return cuda_ok(cudaGetLastError(), "tcgen05 pair W8A16 linear launch");
+}
+
 /* W8A8 with per-K-group scales on the two-CTA kernel (one problem per launch). */
 template <bool MAGIC>
 static int launch_pair_grouped(const h3q8_linear_desc &d, const GemmParams &params, DeviceState *dev, cudaStream_t stream) {
@@ -297,7 +345,7 @@ static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t 
         return launch_tcgen05<MODE_W8A8, 128, 1, true>(d, p, dev, stream);
     }
     if (kernel == H3Q8_KERNEL_TCGEN05_PAIR) {
-        if constexpr (MODE == MODE_W8A16) return fail("the two-CTA kernel takes bf16 or int8 operands, not main-loop dequantisation");
+        if constexpr (MODE == MODE_W8A16) return launch_pair_w8a16(d, p, dev, stream);
         else return d.rope ? launch_pair<MODE, true>(&d, &p, 1, dev, stream) : launch_pair<MODE>(&d, &p, 1, dev, stream);
     }
     if (kernel == H3Q8_KERNEL_TCGEN05_M256) return launch_tcgen05<MODE, 256, 2, false>(d, p, dev, stream);
@@ -372,8 +420,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
                            aligned16(d.workspace);
     if (kernel == H3Q8_KERNEL_AUTO) {
         const bool tiny = (uint64_t)d.rows * d.input_dim * d.output_dim <= (1u << 22);
-        /* two-CTA tiles need both CTAs to have rows; main-loop dequantisation stays single-CTA */
-        const bool pair_ok = d.rows > 128 && (d.mode == H3Q8_MODE_BF16 || (d.mode == H3Q8_MODE_W8A8 && (!p.scale_group || grouped_pair_ok)));
+        /* two-CTA tiles need both CTAs to have rows */
+        const bool pair_ok = d.rows > 128 && (d.mode != H3Q8_MODE_W8A8 || !p.scale_group || grouped_pair_ok);
         kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128
                : pair_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_TCGEN05;
         /* SwiGLU runs on the two-CTA kernel (gate rows in one CTA, up rows in its peer) or on the plain kernel */
@@ -382,7 +430,7 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
         if (kernel != H3Q8_KERNEL_PLAIN && d.rows <= 128 && splitk_ok &&
             plan_splitk(d.mode, d.rows, d.input_dim, d.output_dim, dev->sms, d.workspace_bytes, splits, kb_per_split))
             kernel = H3Q8_KERNEL_TCGEN05_SPLITK;
-        if (swiglu) kernel = tma_ok && d.mode != H3Q8_MODE_W8A16 ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_PLAIN;
+        if (swiglu) kernel = tma_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_PLAIN;
         if (d.rope) kernel = H3Q8_KERNEL_TCGEN05_PAIR;
     }
     if (d.rope) {
@@ -395,8 +443,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     /* an explicitly requested kernel must be able to take the problem */
     if (swiglu && kernel != H3Q8_KERNEL_PLAIN && kernel != H3Q8_KERNEL_TCGEN05_PAIR) {
         return fail("linear: SwiGLU is available on the two-CTA and the plain kernel");
-    } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && (d.mode == H3Q8_MODE_W8A16 || (d.mode == H3Q8_MODE_W8A8 && p.scale_group && !grouped_pair_ok))) {
-        return fail("linear: the two-CTA kernel takes bf16 or int8 operands (scale groups: multiples of 128 that divide K)");
+    } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && d.mode == H3Q8_MODE_W8A8 && p.scale_group && !grouped_pair_ok) {
+        return fail("linear: the two-CTA W8A8 kernel takes scale groups that are multiples of 128 and divide K");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_SPLITK && !splitk_ok) {
         return fail("linear: split-K takes ungrouped scales, no SwiGLU / rotary epilogue / accumulator dump, and a 16-byte aligned workspace");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {
@@ -453,6 +501,7 @@ extern "C" int h3q8_linear_grouped(const h3q8_linear_desc *problems, uint32_t co
             uint32_t kernel;
             if (!plan_linear(problems[i], params[i], kernel, dev)) return 0;
             together = together && kernel == H3Q8_KERNEL_TCGEN05_PAIR && problems[i].mode == problems[0].mode && !problems[i].rope &&
+                       problems[i].mode != H3Q8_MODE_W8A16 &&
                        !(problems[i].mode == H3Q8_MODE_W8A8 && params[i].scale_group);
         }
         if (together && count > 1)

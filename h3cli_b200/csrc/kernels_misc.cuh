@@ -11,7 +11,7 @@
  */
 #pragma once
 #include <float.h>
-#include "gemm_tcgen05_pair.cuh"
+#include "gemm_tcgen05_pair_w8a16.cuh"
 
 namespace h3q8 {
 

@@ -19,7 +19,7 @@ from parity import bf16_to_f32, check_bf16, rel_l2
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 TC_KERNELS = [h.KERNEL_TCGEN05, h.KERNEL_TCGEN05_M256, h.KERNEL_TCGEN05_N128]
-PAIR = [h.KERNEL_TCGEN05_PAIR]   # two-CTA kernel: bf16 and per-channel int8 operands only
+PAIR = [h.KERNEL_TCGEN05_PAIR]   # two-CTA kernels (bf16, int8, and W8A16 with main-loop dequantisation)
 GUARD = 64
 
 
@@ -242,8 +242,7 @@ def test_exact_patterns_bit_exact(gpu, oracle, rows, kernel):
     N, K = 256, 512
     x, wq, ws = exact_pattern(rows, N, K)
     want = oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0)
-    if kernel not in PAIR:
-        assert (raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, kernel=kernel) == want).all()
+    assert (raw_linear(gpu, h.MODE_W8A16, x, wq, ws, 0, kernel=kernel) == want).all()
     wb = oracle.q8_dequant(wq, ws, 0)
     assert (raw_linear(gpu, h.MODE_BF16, x, wb, kernel=kernel) == want).all()
     xq, xs = oracle.quantize_rows(x)
@@ -263,8 +262,8 @@ def test_all_zero_input(gpu, oracle):
 SHAPES = [(1, 8, 16), (17, 40, 80), (129, 256, 256), (300, 520, 512), (128, 256, 64), (257, 264, 1040), (64, 3072, 3072)]
 
 
-@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS)
-@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("kernel", [h.KERNEL_PLAIN] + TC_KERNELS + PAIR)
+@pytest.mark.parametrize("M,N,K", SHAPES + [(1000, 776, 1024), (513, 1032, 3072)])
 @pytest.mark.parametrize("group,spec", [(0, ""), (64, "b"), (128, "ba"), (0, "gr"), (64, "bgra")])
 def test_w8a16_parity(gpu, oracle, M, N, K, group, spec, kernel):
     x, wq, ws = operands(21, M, N, K, group)

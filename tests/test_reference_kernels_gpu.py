@@ -36,6 +36,14 @@ def bf(a):
     return synth.to_bf16(a).reshape(a.shape)
 
 
+def within_one_step(a_bits, b_bits, floor):
+    """|a - b| <= one bf16 step taken at max(|a|, |b|, floor): for results that are differences of larger terms
+    (a rotation, a shifted product) the step of the terms, not of the tiny result, is the honest unit."""
+    a, b = bf16_to_f32(a_bits).astype(np.float64), bf16_to_f32(b_bits).astype(np.float64)
+    step = 2.0 ** (np.floor(np.log2(np.maximum(np.maximum(np.abs(a), np.abs(b)), floor))) - 7)
+    return bool((np.abs(a - b) <= step).all())
+
+
 def steps_apart(a_bits, b_bits):
     """Distance in bf16 steps between two arrays of finite bf16 bit patterns (sign-magnitude -> ordered ints)."""
     def ordered(bits):
@@ -133,7 +141,7 @@ def test_qkv_norm_rope_against_the_reference_kernel(gpu, oracle, ref, rows, head
     want = ref.qkv_rope(qkv, q_norm, k_norm, cos, sin, heads, dim, half, 1e-5, grouped=1)
     restated = oracle.grouped_qkv_rope(qkv, q_norm, k_norm, cos, sin, heads, dim, half, 1e-5)
     for r, w in zip(restated, want):
-        assert steps_apart(r, w).max() <= 1
+        assert within_one_step(r, w, 1.0)          # inputs are N(0, 4^2) normalised to unit RMS
         check_bf16(r.ravel(), w.ravel())
     assert (restated[2] == want[2]).all()
     t_qkv, t_qn, t_kn, t_c, t_s = (gpu.tensor_from_bf16(a) for a in (qkv, q_norm, k_norm, cos, sin))
@@ -164,7 +172,7 @@ def test_gate_adaln_quantize_against_the_reference_chain(oracle, ref, rows, widt
     want_q, want_s = oracle.quantize_rows(normalized, padded)
     o_gated, o_norm, o_q, o_s = oracle.gate_adaln_quantize(res, branch, mod, norm_w, mod, row_map, padded, slots, 2, 3, 4, 1e-5)
     assert (o_gated == gated).all()
-    assert steps_apart(o_norm, normalized).max() <= 1
+    assert within_one_step(o_norm, normalized, 0.25)
     assert np.abs(o_q.astype(np.int32) - want_q.astype(np.int32)).max() <= 1
     gpu = h.Gpu()
     t_res, t_br, t_mod, t_nw = (gpu.tensor_from_bf16(a) for a in (res, branch, mod, norm_w))
