@@ -10,7 +10,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libh3q8.so")
 PREPARE = os.path.join(HERE, "h3q8_prepare")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "-Xcompiler", "-fPIC", "-Xcompiler", "-pthread"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-pthread"] + os.environ.get("H3Q8_NVCC_EXTRA", "").split()
 
 
 def _nvcc():

@@ -20,9 +20,10 @@
  *
  * Barriers (count; who arrives):
  *   afull[s]   leader only; 1 + tx bytes of both CTAs' A tiles      (producers of both CTAs)
+ *   aempty[s]  per CTA;     1   tcgen05.commit of the leader, sent to both CTAs
  *   rfull[s]   per CTA;     1 + tx bytes of the CTA's own raw tile   (its own producer)
- *   empty[s]   per CTA;     1   tcgen05.commit of the leader, sent to both CTAs
- *   bfull[c]   leader only; 8   one arrival per warp of the dequantiser group (four warps) of both CTAs
+ *   rempty[s]  per CTA;     4   the warps of the group that converts the tile, once it is in registers
+ *   bfull[c]   leader only; 8   one arrival per warp of that group in both CTAs
  *   bempty[c]  per CTA;     1   tcgen05.commit of the leader, sent to both CTAs
  *   tfull[a] / tempty[a]    as in the bf16 pair kernel
  * Every wait is bounded; a role that gives up raises the CTA's abort flag and all roles
@@ -35,16 +36,24 @@ namespace h3q8 {
 
 struct PairW8A16Config {
     static constexpr int BM = 256, BN = 256, BKE = 64;
-    static constexpr int A_BYTES = 128 * 128;           /* this CTA's 128 rows of X, 64 bf16 each       */
+    static constexpr int A_BYTES = 128 * 128;            /* this CTA's 128 rows of X, 64 bf16 each       */
     static constexpr int RAW_BYTES = 128 * 64;           /* this CTA's 128 weight rows, 64 int8 each     */
-    static constexpr int STAGE_BYTES = A_BYTES + RAW_BYTES;
     static constexpr int B_BYTES = 128 * 128;            /* converted tile                               */
-    static constexpr int STAGES = 5, CONV_BUFFERS = 5;
+    /* three rings: a raw tile is free again as soon as it has been converted, the X tile and the converted tile only
+     * when the MMAs that read them are done; raw tiles are small, so that ring is the deep one */
+    static constexpr int A_STAGES = 5, RAW_STAGES = 8, CONV_BUFFERS = 5;
     static constexpr int ACC_COLS = BN, ACC_BUFFERS = 2;
-    static constexpr int EPILOGUE_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, FIRST_DEQUANT_WARP = 10, DEQUANT_WARPS = 8;
+    /* warps: epilogue (TMEM lane quadrant = warp % 4, column half = warp / 4), weight producer, activation producer,
+     * MMA issuer and TMEM owner, dequantisers in two groups */
+    /* measured at M = 32 400 (QKV / FFN-up / FFN-down, TFLOP/s): 8 epilogue + 2 x 4 dequantiser warps 1 100 / 1 062 / 1 049;
+     * 4 + 2 x 4: 1 081 / 1 053 / 1 007; 8 + 2 x 8: 1 034 / 967 / 962; ring depths (5,8,5) (6,6,5) (6,8,4) (7,4,5) within 1 % */
+    static constexpr int EPILOGUE_WARPS = 8, RAW_PRODUCER_WARP = EPILOGUE_WARPS, A_PRODUCER_WARP = EPILOGUE_WARPS + 1,
+                         MMA_WARP = EPILOGUE_WARPS + 2, FIRST_DEQUANT_WARP = EPILOGUE_WARPS + 3;
+    static constexpr int GROUP_WARPS = 4, DEQUANT_WARPS = 2 * GROUP_WARPS;
+    static_assert((EPILOGUE_WARPS == 4 || EPILOGUE_WARPS == 8) && (GROUP_WARPS == 4 || GROUP_WARPS == 8), "role layout");
     static constexpr int WARPS = FIRST_DEQUANT_WARP + DEQUANT_WARPS, THREADS = WARPS * 32;
-    static constexpr int BARRIERS = 3 * STAGES + 2 * CONV_BUFFERS + 2 * ACC_BUFFERS;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CONV_BUFFERS * B_BYTES + 1024 + 512;
+    static constexpr int BARRIERS = 2 * A_STAGES + 2 * RAW_STAGES + 2 * CONV_BUFFERS + 2 * ACC_BUFFERS;
+    static constexpr int SMEM_BYTES = A_STAGES * A_BYTES + RAW_STAGES * RAW_BYTES + CONV_BUFFERS * B_BYTES + 1024 + 512;
     static constexpr uint32_t IDESC = umma_idesc(1, 1, 256, BN);
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static_assert(BARRIERS * 8 + 16 <= 512, "barrier block");
@@ -93,11 +102,13 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
     const uint32_t total_tiles = p.tiles;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *stages = smem;
-    uint8_t *conv = stages + C::STAGES * C::STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(conv + C::CONV_BUFFERS * C::B_BYTES);
-    uint64_t *afull = bars, *rfull = afull + C::STAGES, *empty = rfull + C::STAGES;
-    uint64_t *bfull = empty + C::STAGES, *bempty = bfull + C::CONV_BUFFERS;
+    uint8_t *a_ring = smem;
+    uint8_t *conv = a_ring + C::A_STAGES * C::A_BYTES;
+    uint8_t *raw_ring = conv + C::CONV_BUFFERS * C::B_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ring + C::RAW_STAGES * C::RAW_BYTES);
+    uint64_t *afull = bars, *aempty = afull + C::A_STAGES;
+    uint64_t *rfull = aempty + C::A_STAGES, *rempty = rfull + C::RAW_STAGES;
+    uint64_t *bfull = rempty + C::RAW_STAGES, *bempty = bfull + C::CONV_BUFFERS;
     uint64_t *tfull = bempty + C::CONV_BUFFERS, *tempty = tfull + C::ACC_BUFFERS;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tempty + C::ACC_BUFFERS);
     volatile uint32_t *abort_flag = tmem_slot + 1;
@@ -109,14 +120,16 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
     const bool swiglu = p.ep.activation == ACT_SWIGLU;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; s++) { mbar_init(&afull[s], 1); mbar_init(&rfull[s], 1); mbar_init(&empty[s], 1); }
-        for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], C::DEQUANT_WARPS); mbar_init(&bempty[s], 1); }
+        for (int s = 0; s < C::A_STAGES; s++) { mbar_init(&afull[s], 1); mbar_init(&aempty[s], 1); }
+        for (int s = 0; s < C::RAW_STAGES; s++) { mbar_init(&rfull[s], 1); mbar_init(&rempty[s], C::GROUP_WARPS); }
+        for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], 2 * C::GROUP_WARPS); mbar_init(&bempty[s], 1); }
         for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 2 * C::EPILOGUE_WARPS); }
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
     }
-    if (warp == C::PRODUCER_WARP && lane == 0) { tma_prefetch_descriptor(&map_a); tma_prefetch_descriptor(&map_b); }
+    if (warp == C::RAW_PRODUCER_WARP && lane == 0) tma_prefetch_descriptor(&map_b);
+    if (warp == C::A_PRODUCER_WARP && lane == 0) tma_prefetch_descriptor(&map_a);
     if (warp == C::MMA_WARP) { tmem_alloc_pair(tmem_slot, 512); tmem_relinquish_pair(); }
     tc_fence_before_sync();
     __syncthreads();
@@ -125,25 +138,37 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
     const uint32_t tmem_base = *tmem_slot;
     uint32_t failure = STATUS_OK;
 
-    if (warp == C::PRODUCER_WARP) {
-        /* ------------------------------------------------ TMA producer (both CTAs) */
+    if (warp == C::RAW_PRODUCER_WARP) {
+        /* ------------------------------------------------ weight producer (both CTAs): raw int8 tiles */
         if (lane == 0) {
-            PipeState st;
+            PipeState sr;
             for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
                 uint32_t mb, nb;
                 tile_coordinates(p, tile, mb, nb);
                 /* SwiGLU: the leader stages 128 gate rows, its peer the matching 128 up rows (weight rows N + n) */
                 const uint32_t b_row = swiglu ? nb * 128 + rank * p.N : nb * C::BN + rank * 128;
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!wait_or_abort(&empty[st.index], st.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
-                    uint8_t *stage = stages + st.index * C::STAGE_BYTES;
-                    if (rank == 0) mbar_arrive_expect_tx(&afull[st.index], 2 * C::A_BYTES);
-                    mbar_arrive_expect_tx(&rfull[st.index], C::RAW_BYTES);
-                    /* the weight first: the dequantisers are the longer chain */
-                    tma_load_2d(stage + C::A_BYTES, &map_b, &rfull[st.index], (int32_t)(kb * C::BKE), (int32_t)b_row);
-                    tma_load_2d_pair(stage, &map_a, map_to_cta(smem_u32(&afull[st.index]), 0), (int32_t)(kb * C::BKE),
+                    if (!wait_or_abort(&rempty[sr.index], sr.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
+                    mbar_arrive_expect_tx(&rfull[sr.index], C::RAW_BYTES);
+                    tma_load_2d(raw_ring + sr.index * C::RAW_BYTES, &map_b, &rfull[sr.index], (int32_t)(kb * C::BKE), (int32_t)b_row);
+                    sr.advance(C::RAW_STAGES);
+                }
+            }
+        }
+    } else if (warp == C::A_PRODUCER_WARP) {
+        /* ------------------------------------------------ activation producer (both CTAs): bf16 tiles of X */
+        if (lane == 0) {
+            PipeState sa;
+            for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
+                uint32_t mb, nb;
+                tile_coordinates(p, tile, mb, nb);
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                    if (!wait_or_abort(&aempty[sa.index], sa.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
+                    /* the leader arms its barrier for the bytes of both CTAs */
+                    if (rank == 0) mbar_arrive_expect_tx(&afull[sa.index], 2 * C::A_BYTES);
+                    tma_load_2d_pair(a_ring + sa.index * C::A_BYTES, &map_a, map_to_cta(smem_u32(&afull[sa.index]), 0), (int32_t)(kb * C::BKE),
                                      (int32_t)(mb * C::BM + rank * 128), p.l2_policy_a);
-                    st.advance(C::STAGES);
+                    sa.advance(C::A_STAGES);
                 }
             }
         }
@@ -156,16 +181,16 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
                 tc_fence_after_sync();
                 const uint32_t d = tmem_base + acc.index * C::ACC_COLS;
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!wait_or_abort(&afull[st.index], st.phase, abort_flag) ||
-                        !wait_or_abort(&bfull[cv.index], cv.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                    if (!wait_or_abort(&afull[st.index], st.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                    if (!wait_or_abort(&bfull[cv.index], cv.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
                     tc_fence_after_sync();
-                    const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(stages + st.index * C::STAGE_BYTES));
+                    const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(a_ring + st.index * C::A_BYTES));
                     const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(conv + cv.index * C::B_BYTES));
 #pragma unroll
                     for (int k4 = 0; k4 < 4; k4++) umma_bf16_pair(d, a_desc + 2 * k4, b_desc + 2 * k4, C::IDESC, kb | k4);
-                    umma_commit_pair(&empty[st.index], 3);    /* frees the stage in both CTAs          */
+                    umma_commit_pair(&aempty[st.index], 3);   /* frees the X tile in both CTAs         */
                     umma_commit_pair(&bempty[cv.index], 3);   /* frees the converted tile in both CTAs */
-                    st.advance(C::STAGES);
+                    st.advance(C::A_STAGES);
                     cv.advance(C::CONV_BUFFERS);
                 }
                 if (failure) break;
@@ -175,14 +200,17 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
         }
     } else if (warp >= C::FIRST_DEQUANT_WARP) {
         /* ------------------------------------------------ dequantisers (both CTAs) */
-        /* Two groups of four warps take alternate k-blocks.  Thread d of a group owns weight row d of this CTA's 128:
-         * four 16-byte loads from the raw tile (64-byte rows, 64-byte swizzle), sixty-four conversions, eight 16-byte
-         * stores into the operand tile (128-byte rows, 128-byte swizzle); consecutive lanes take consecutive rows,
-         * which keeps both swizzles free of bank conflicts.  A warp then pays one wait, one proxy fence and one
-         * arrival per TWO k-blocks, and while one group sits in its fence the other converts. */
-        const uint32_t group = (warp - C::FIRST_DEQUANT_WARP) >> 2;
-        const uint32_t r = threadIdx.x - (C::FIRST_DEQUANT_WARP + 4 * group) * 32;       /* 0..127 */
-        const uint32_t raw_row = r * 64, raw_twist = (r >> 1) & 3, conv_row = r * 128, conv_twist = r & 7;
+        /* Two groups of warps take alternate k-blocks.  With four warps per group thread t owns weight row t of this
+         * CTA's 128 (with eight, half h = t / 128 of row t % 128): 16-byte loads from the raw tile (64-byte rows, 64-byte
+         * swizzle), 16 conversions per load, 16-byte stores into the operand tile (128-byte rows, 128-byte swizzle);
+         * consecutive lanes take consecutive rows, which keeps both swizzles free of bank conflicts.  A warp pays one
+         * wait, one proxy fence and one arrival per TWO k-blocks, and while one group sits in its fence the other
+         * converts. */
+        const uint32_t group = (warp - C::FIRST_DEQUANT_WARP) / C::GROUP_WARPS;
+        constexpr int HALVES = C::GROUP_WARPS / 4, CHUNKS = 4 / HALVES;   /* 16-byte raw vectors per thread */
+        const uint32_t t = threadIdx.x - (C::FIRST_DEQUANT_WARP + C::GROUP_WARPS * group) * 32;
+        const uint32_t r = t & 127, h = t >> 7;
+        const uint32_t raw_twist = (r >> 1) & 3, conv_twist = r & 7;
         const uint32_t width = p.scale_group ? p.scale_group : p.K;
         const uint32_t leader_bfull = map_to_cta(smem_u32(bfull), 0);
         auto scale_pointer = [&](uint32_t tile, bool &live) {
@@ -209,23 +237,26 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
                 first_scale = live ? row_scales[0] : 0.0f;
             }
             for (uint32_t kb = 0; kb < num_kb; kb++, turn++) {
-                if ((turn & 1u) != group) { st.advance(C::STAGES); cv.advance(C::CONV_BUFFERS); continue; }
+                if ((turn & 1u) != group) { st.advance(C::RAW_STAGES); cv.advance(C::CONV_BUFFERS); continue; }
                 const float scale = upcoming;
                 if (p.scale_groups > 1 && kb + 2 < num_kb && live_now) upcoming = scales_now[((kb + 2) * C::BKE) / width];
-                bool ready = wait_or_abort(&rfull[st.index], st.phase, abort_flag) &&
-                             wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
+                bool ready = wait_or_abort(&rfull[st.index], st.phase, abort_flag);
+                ready = ready && wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_DEQUANT; break; }
-                const uint8_t *raw = stages + st.index * C::STAGE_BYTES + C::A_BYTES + raw_row;
-                uint8_t *dst = conv + cv.index * C::B_BYTES + conv_row;
-                uint4 q[4];
+                const uint8_t *raw = raw_ring + st.index * C::RAW_BYTES + r * 64;
+                uint8_t *dst = conv + cv.index * C::B_BYTES + r * 128;
+                uint4 q[CHUNKS];
 #pragma unroll
-                for (int c = 0; c < 4; c++) q[c] = *reinterpret_cast<const uint4 *>(raw + ((c ^ raw_twist) << 4));
+                for (int c = 0; c < CHUNKS; c++) q[c] = *reinterpret_cast<const uint4 *>(raw + (((CHUNKS * h + c) ^ raw_twist) << 4));
+                /* the raw tile is in registers: its slot may be refilled */
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&rempty[st.index]);
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
+                for (int c = 0; c < CHUNKS; c++) {
                     uint4 lo, hi;
                     dequant16<PACKED>(q[c], scale, lo, hi);
-                    *reinterpret_cast<uint4 *>(dst + (((2 * c) ^ conv_twist) << 4)) = lo;
-                    *reinterpret_cast<uint4 *>(dst + (((2 * c + 1) ^ conv_twist) << 4)) = hi;
+                    *reinterpret_cast<uint4 *>(dst + (((2 * (CHUNKS * h + c)) ^ conv_twist) << 4)) = lo;
+                    *reinterpret_cast<uint4 *>(dst + (((2 * (CHUNKS * h + c) + 1) ^ conv_twist) << 4)) = hi;
                 }
                 /* The converted tile is read by the tensor core of THIS SM (each CTA supplies its own half of B), so all
                  * that has to cross the pair is the news that the writes are done: every writer makes its stores visible
@@ -238,13 +269,15 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
                     if (rank == 0) mbar_arrive(&bfull[cv.index]);
                     else mbar_arrive_remote(leader_bfull + cv.index * 8);
                 }
-                st.advance(C::STAGES);
+                st.advance(C::RAW_STAGES);
                 cv.advance(C::CONV_BUFFERS);
             }
         }
     } else {
         /* ------------------------------------------------ epilogue (both CTAs, own 128 rows) */
-        /* TMEM lane quadrant warp % 4, column half warp / 4; the reference's operator chain in registers (epilogue.cuh) */
+        /* warp w owns TMEM lane quadrant w (rows 32 w .. 32 w + 31 of this CTA's 128) and walks all 256 columns; the
+         * reference's operator chain in registers (epilogue.cuh) */
+        constexpr int SPLIT = C::EPILOGUE_WARPS / 4;   /* column halves */
         const uint32_t quadrant = warp & 3, half = warp >> 2;
         const bool gated = p.ep.gate != nullptr || p.ep.residual != nullptr;
         PipeState acc;
@@ -261,8 +294,8 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
             if (swiglu) {
                 /* accumulator columns 0..127 hold the gate, 128..255 the up projection of the same 128 outputs */
 #pragma unroll 1
-                for (int hc = 0; hc < 4; hc++) {
-                    const int c = half * 4 + hc;
+                for (int hc = 0; hc < 8 / SPLIT; hc++) {
+                    const int c = half * (8 / SPLIT) + hc;
                     uint32_t vg[16], vu[16];
                     tmem_load_32x16(lane_base + c * 16, vg);
                     tmem_load_32x16(lane_base + 128 + c * 16, vu);
@@ -293,8 +326,8 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
                 }
             } else {
 #pragma unroll 1
-                for (int hc = 0; hc < 8; hc++) {
-                    const int c = half * 8 + hc;
+                for (int hc = 0; hc < 16 / SPLIT; hc++) {
+                    const int c = half * (16 / SPLIT) + hc;
                     uint32_t v[16];
                     tmem_load_32x16(lane_base + c * 16, v);
                     tmem_load_wait();
