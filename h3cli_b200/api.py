@@ -35,23 +35,42 @@ class LinearDesc(C.Structure):
     ]
 
 
+def _u64(*names):
+    return [(n, C.c_uint64) for n in names]
+
+
+def _f64(*names):
+    return [(n, C.c_double) for n in names]
+
+
 class Stats(C.Structure):
-    """h3_gpu_stats"""
-    _fields_ = ([(n, C.c_uint64) for n in ("q8_weights", "q8_source_bytes", "q8_storage_bytes", "q8_dispatches")] +
-                [("q8_load_seconds", C.c_double)] +
-                [(n, C.c_uint64) for n in ("allocated_bytes", "live_bytes", "peak_live_bytes", "tensor_allocations",
-                                           "direct_dispatches", "submissions", "linear_dispatches", "h2d_bytes",
-                                           "d2h_bytes", "d2d_bytes", "streamed_bytes", "stream_stalls", "pinned_bytes",
-                                           "stream_slot_bytes")] +
-                [("stream_wait_seconds", C.c_double), ("quant_conversion_seconds", C.c_double)] +
-                [(n, C.c_uint64) for n in ("quant_projection_dispatches", "quant_cache_hits", "quant_cache_misses",
-                                           "native_scratch_bytes", "native_scratch_allocations",
-                                           "native_scratch_reuses")] +
-                [("linear_seconds", C.c_double), ("linear_kernel_launches", C.c_uint64),
-                 ("conversion_kernel_launches", C.c_uint64)] +
-                [(n, C.c_uint64) for n in ("resident_weight_bytes", "resident_blocks", "active_weight_blocks",
-                                           "resident_block_mask")] +
-                [("h2d_seconds", C.c_double), ("d2h_seconds", C.c_double)])
+    """h3_gpu_stats: the reference's layout (src/gpu.h:99-142), field for field."""
+    _fields_ = (_u64("q8_weights", "q8_source_bytes", "q8_storage_bytes", "q8_dispatches") + _f64("q8_load_seconds") +
+                _u64("layout_prepares", "layout_inplace_packs", "layout_scan_replaced_bytes", "layout_partial_bytes",
+                     "allocated_bytes", "live_bytes", "peak_live_bytes", "tensor_allocations", "direct_dispatches",
+                     "mps_linear_dispatches", "mps_conv_dispatches", "mps_sdpa_dispatches", "native_attention_dispatches",
+                     "metal_current_allocated_bytes", "blit_copies", "submissions") +
+                _f64("command_encode_seconds", "command_wait_seconds", "gpu_seconds") +
+                _u64("linear_dispatches", "conv_dispatches", "attention_dispatches", "h2d_bytes", "d2h_bytes", "d2d_bytes",
+                     "streamed_bytes", "resident_weight_bytes", "stream_slot_bytes", "resident_block_mask") +
+                [("resident_blocks", C.c_uint), ("active_weight_blocks", C.c_uint)] +
+                _u64("device_bytes", "managed_bytes", "pinned_bytes", "peak_pinned_bytes", "stream_stalls") +
+                _f64("transfer_seconds", "stream_wait_seconds", "linear_seconds", "attention_seconds", "conv_seconds",
+                     "h2d_seconds", "d2h_seconds", "slot_wait_seconds", "normalization_seconds") +
+                _u64("weight_cache_bytes", "weight_cache_hits", "weight_cache_hit_bytes", "weight_cache_misses",
+                     "weight_cache_evictions") + _f64("quant_conversion_seconds") +
+                _u64("quant_clipped_values", "quant_zeroed_values", "quant_projection_dispatches", "quant_cache_hits",
+                     "quant_cache_misses", "sage2_attention_dispatches", "sage3_attention_dispatches",
+                     "attention_workspace_bytes", "inflight_peak", "command_retirements", "bounded_waits", "pressure_drains",
+                     "native_scratch_bytes", "native_scratch_allocations", "native_scratch_reuses", "native_pipeline_count",
+                     "main_dense_calls", "subblock_calls", "subblock_bypass", "subblock_protected_calls", "subblock_selected",
+                     "subblock_possible", "subblock_router_calls", "attention_timing_samples", "attention_timing_missed") +
+                _f64("main_attention_seconds", "subblock_router_seconds", "subblock_kernel_seconds"))
+
+
+class Profile(C.Structure):
+    """h3q8_gpu_profile"""
+    _fields_ = _u64("linear_kernel_launches", "conversion_kernel_launches")
 
 
 class WeightOptions(C.Structure):
@@ -119,6 +138,8 @@ def library():
         "h3_gpu_free": (None, [vp]), "h3_gpu_cancel": (None, [vp]),
         "h3_gpu_error": (C.c_char_p, [vp]),
         "h3_gpu_get_stats": (C.c_int, [vp, C.POINTER(Stats)]),
+        "h3q8_gpu_get_profile": (C.c_int, [vp, C.POINTER(Profile)]),
+        "h3_weight_packed_size": (C.c_int, [u32, u32, C.c_int, C.POINTER(u64), C.POINTER(u64), C.POINTER(u64)]),
         "h3_gpu_backend_name": (C.c_char_p, [vp]), "h3_gpu_has_int8_mlp": (C.c_int, [vp]),
         "h3_gpu_begin": (C.c_int, [vp]), "h3_gpu_continue": (C.c_int, [vp]),
         "h3_gpu_submit": (C.c_int, [vp]), "h3_gpu_synchronize": (C.c_int, [vp]),
@@ -329,6 +350,11 @@ class Gpu:
         s = Stats()
         self._check(library().h3_gpu_get_stats(self.handle, C.byref(s)))
         return s
+
+    def profile(self):
+        p = Profile()
+        self._check(library().h3q8_gpu_get_profile(self.handle, C.byref(p)))
+        return p
 
     def backend_name(self):
         return library().h3_gpu_backend_name(self.handle).decode()

@@ -53,6 +53,7 @@ struct h3_gpu {
     bool active = false, deferred_error = false;
     char error[1024] = {0};
     h3_gpu_stats stats = {};
+    h3q8_gpu_profile profile = {};
     int quant_mode = 0;         /* 0 off, 1 W8A16, 2 W8A8 */
     uint32_t group = 0;
     bool group_set = false;
@@ -117,14 +118,14 @@ static void harvest_profile(h3_gpu *g) {
         float ms = 0;
         if (cudaEventQuery(s.stop) == cudaErrorNotReady) { pending.push_back(s); continue; } /* a copy still in flight */
         if (cudaEventElapsedTime(&ms, s.start, s.stop) == cudaSuccess) {
-            if (s.category == 0) { g->stats.linear_seconds += ms * 1e-3; g->stats.linear_kernel_launches++; }
+            if (s.category == 0) { g->stats.linear_seconds += ms * 1e-3; g->profile.linear_kernel_launches++; }
             else if (s.category == 3) { /* slot wait: time the compute stream sat idle waiting for a weight copy */
                 g->stats.stream_wait_seconds += ms * 1e-3;
                 if (ms > 0.02f) g->stats.stream_stalls++;
             }
             else if (s.category == 4) g->stats.h2d_seconds += ms * 1e-3;
             else if (s.category == 5) g->stats.d2h_seconds += ms * 1e-3;
-            else { g->stats.quant_conversion_seconds += ms * 1e-3; g->stats.conversion_kernel_launches++; }
+            else { g->stats.quant_conversion_seconds += ms * 1e-3; g->profile.conversion_kernel_launches++; }
         }
         g->spare_events.push_back(s.start);
         g->spare_events.push_back(s.stop);
@@ -303,12 +304,12 @@ extern "C" void h3_gpu_profile_mark(h3_gpu *g, const char *phase) {
         fprintf(stderr, "h3cli: quant profile %s / %s: mode=%s group=%u native_calls=%llu cache_hits=%llu prepared=%llu conversion=%.6fs (%llu kernels)\n",
                 g->label.c_str(), phase, g->quant_mode == 2 ? "w8a8" : "w8a16", g->group,
                 (unsigned long long)s.quant_projection_dispatches, (unsigned long long)s.quant_cache_hits,
-                (unsigned long long)s.quant_cache_misses, s.quant_conversion_seconds, (unsigned long long)s.conversion_kernel_launches);
+                (unsigned long long)s.quant_cache_misses, s.quant_conversion_seconds, (unsigned long long)g->profile.conversion_kernel_launches);
     fprintf(stderr, "h3cli: CUDA profile %s / %s: wall %.3fs peak %.3f GiB, GEMM %llu, H2D %.3f GiB D2H %.3f GiB stream %.3f GiB wait %.3fs\n",
             g->label.c_str(), phase, now_seconds() - g->created, s.peak_live_bytes / gib, (unsigned long long)s.linear_dispatches,
             s.h2d_bytes / gib, s.d2h_bytes / gib, s.streamed_bytes / gib, s.stream_wait_seconds);
     fprintf(stderr, "h3cli: CUDA category seconds: GEMM %.6f (%llu kernels) conversion %.6f; stream stalls %llu / %.6fs\n", s.linear_seconds,
-            (unsigned long long)s.linear_kernel_launches, s.quant_conversion_seconds, (unsigned long long)s.stream_stalls, s.stream_wait_seconds);
+            (unsigned long long)g->profile.linear_kernel_launches, s.quant_conversion_seconds, (unsigned long long)s.stream_stalls, s.stream_wait_seconds);
     fprintf(stderr, "h3cli: CUDA transfer events: H2D %.6fs (%.3f GiB/s), D2H %.6fs (%.3f GiB/s)\n", s.h2d_seconds,
             s.h2d_seconds > 0 ? s.h2d_bytes / gib / s.h2d_seconds : 0.0, s.d2h_seconds, s.d2h_seconds > 0 ? s.d2h_bytes / gib / s.d2h_seconds : 0.0);
 }
@@ -317,6 +318,11 @@ extern "C" const char *h3_gpu_error(const h3_gpu *g) { return g ? g->error : "no
 extern "C" int h3_gpu_get_stats(const h3_gpu *g, h3_gpu_stats *stats) {
     if (!g || !stats) return 0;
     *stats = g->stats;
+    return 1;
+}
+extern "C" int h3q8_gpu_get_profile(const h3_gpu *g, h3q8_gpu_profile *profile) {
+    if (!g || !profile) return 0;
+    *profile = g->profile;
     return 1;
 }
 extern "C" const char *h3_gpu_backend_name(const h3_gpu *) { return "cuda-b200-q8"; }
@@ -390,7 +396,10 @@ extern "C" h3_gpu_tensor *h3_gpu_tensor_alloc(h3_gpu *g, size_t elements, h3_gpu
     g->stats.tensor_allocations++;
     g->stats.allocated_bytes += bytes;
     g->stats.live_bytes += bytes;
-    if (storage == H3_GPU_HOST_PINNED) g->stats.pinned_bytes += bytes;
+    if (storage == H3_GPU_HOST_PINNED) {
+        g->stats.pinned_bytes += bytes;
+        if (g->stats.pinned_bytes > g->stats.peak_pinned_bytes) g->stats.peak_pinned_bytes = g->stats.pinned_bytes;
+    } else if (storage == H3_GPU_DEVICE_ONLY) g->stats.device_bytes += bytes;
     if (g->stats.live_bytes > g->stats.peak_live_bytes) g->stats.peak_live_bytes = g->stats.live_bytes;
     return t;
 }
@@ -406,6 +415,7 @@ extern "C" void h3_gpu_tensor_free(h3_gpu_tensor *t) {
         else { if (t->ready_recorded) cudaEventSynchronize(t->ready); cudaFree(t->data); }
         if (!t->borrowed) g->stats.live_bytes -= t->bytes;
         if (!t->borrowed && t->storage == H3_GPU_HOST_PINNED) g->stats.pinned_bytes -= t->bytes;
+        if (!t->borrowed && t->storage == H3_GPU_DEVICE_ONLY && g->stats.device_bytes >= t->bytes) g->stats.device_bytes -= t->bytes;
     }
     if (t->ready) cudaEventDestroy(t->ready);
     if (t->released) cudaEventDestroy(t->released);
@@ -874,6 +884,26 @@ extern "C" size_t h3q8_q8_blob_bytes(uint32_t rows, uint32_t columns, uint32_t g
     size_t aligned = (offset + 15) & ~(size_t)15;
     if (scale_offset) *scale_offset = aligned;
     return (aligned + (bytes - offset) + 255) & ~(size_t)255;
+}
+
+/* src/weights/residency.h:31-33, for this library's packing: payload = int8 [rows, columns], scale plane at the next
+ * 16-byte boundary (fp32 [rows, ceil(columns / group)]), no global-scale slot (global == end of the scales), total
+ * rounded up to 256 bytes.  mode 1 (W8A16) uses the process default group (H3Q8_GROUP, else the reference's 64),
+ * mode 2 (W8A8) per-channel scales. */
+extern "C" int h3_weight_packed_size(uint32_t rows, uint32_t columns, int mode, uint64_t *scale, uint64_t *global, uint64_t *bytes) {
+    if (!rows || !columns || (mode != 1 && mode != 2) || !scale || !global || !bytes) return 0;
+    uint32_t group = 0;
+    if (mode == 1) {
+        const char *env = getenv("H3Q8_GROUP");
+        group = env && *env ? (uint32_t)strtoul(env, nullptr, 10) : H3_Q8_GROUP;
+    }
+    size_t offset = 0, raw_offset = 0, raw_bytes = 0;
+    const size_t total = h3q8_q8_blob_bytes(rows, columns, group, &offset);
+    if (!total || !h3q8_q8_layout(rows, columns, group, &raw_offset, &raw_bytes)) return 0;
+    *scale = offset;
+    *global = offset + (raw_bytes - raw_offset);
+    *bytes = total;
+    return 1;
 }
 
 extern "C" h3q8_weight_stream *h3q8_gpu_weight_stream_create(h3_gpu *g, size_t slot_bytes, uint32_t slots) {

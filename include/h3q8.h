@@ -59,6 +59,11 @@ int h3_weight_options_equal(const h3_weight_options *a, const h3_weight_options 
 int h3_weight_plan_build(h3_weight_plan *out, h3_weight_options options, uint64_t active_mask, uint64_t block_bytes,
                          uint64_t available, uint64_t live, uint64_t future, uint64_t reserve, char *error, size_t size);
 int h3_weight_retry_cap(unsigned count);
+/* src/weights/residency.h:31-33 for this library's q8 packing: *scale = offset of the fp32 scale plane (16-byte
+ * aligned, after the int8 [rows, columns] payload), *global = end of the scale plane (q8 has no global-scale slot),
+ * *bytes = blob size rounded up to 256.  mode 1 = W8A16 with the default scale group (H3Q8_GROUP, else 64),
+ * mode 2 = W8A8 with per-channel scales; 0 for anything else or a blob beyond 32-bit indexing. */
+int h3_weight_packed_size(uint32_t rows, uint32_t columns, int mode, uint64_t *scale, uint64_t *global, uint64_t *bytes);
 
 /* On-disk cache of packed q8 weights (host only), after src/weights/quant_cache.h:14-41:
  * artifacts are keyed by source path + file identity + offset + shape + group + recipe
@@ -208,28 +213,60 @@ typedef enum { H3_GPU_F32 = 0, H3_GPU_BF16, H3_GPU_I8, H3_GPU_U32, H3_GPU_F16 } 
 typedef enum { H3_GPU_HOST_VISIBLE, H3_GPU_DEVICE_ONLY, H3_GPU_HOST_PINNED } h3_gpu_storage;   /* src/gpu.h:24-25 */
 typedef enum { H3_WEIGHT_BF16 = 0, H3_WEIGHT_Q8 = 1 } h3_weight_format;                        /* src/backend.h:9 */
 
-/* Counters of src/gpu.h:99-142 that this path maintains (same names; the
- * reference struct has more fields -- an integrating build copies these). */
+/* h3_gpu_stats: field for field the struct of src/gpu.h:99-142 (same order and types, so that
+ * src/denoise/dit.c:3425, 3534, 3865, 3986 can keep passing their own h3_gpu_stats to
+ * h3_gpu_get_stats).  This library maintains the counters of the linear / quantisation / streaming
+ * path; everything that belongs to other subsystems (Metal layout, attention, convolution, weight
+ * cache, sparse routing) stays 0. */
 typedef struct {
     uint64_t q8_weights, q8_source_bytes, q8_storage_bytes, q8_dispatches;
     double q8_load_seconds;
-    uint64_t allocated_bytes, live_bytes, peak_live_bytes, tensor_allocations;
-    uint64_t direct_dispatches, submissions, linear_dispatches;
-    uint64_t h2d_bytes, d2h_bytes, d2d_bytes, streamed_bytes, stream_stalls;
-    uint64_t pinned_bytes, stream_slot_bytes;
-    double stream_wait_seconds, quant_conversion_seconds;
+    uint64_t layout_prepares, layout_inplace_packs, layout_scan_replaced_bytes, layout_partial_bytes;
+    uint64_t allocated_bytes;
+    uint64_t live_bytes;
+    uint64_t peak_live_bytes;
+    uint64_t tensor_allocations;
+    uint64_t direct_dispatches;
+    uint64_t mps_linear_dispatches;
+    uint64_t mps_conv_dispatches;
+    uint64_t mps_sdpa_dispatches;
+    uint64_t native_attention_dispatches;
+    uint64_t metal_current_allocated_bytes;
+    uint64_t blit_copies;
+    uint64_t submissions;
+    double command_encode_seconds;
+    double command_wait_seconds;
+    double gpu_seconds;
+    uint64_t linear_dispatches, conv_dispatches, attention_dispatches;
+    uint64_t h2d_bytes, d2h_bytes, d2d_bytes, streamed_bytes;
+    uint64_t resident_weight_bytes, stream_slot_bytes, resident_block_mask;
+    unsigned resident_blocks, active_weight_blocks;
+    uint64_t device_bytes, managed_bytes, pinned_bytes, peak_pinned_bytes;
+    uint64_t stream_stalls;
+    /* H3_PROFILE categories of src/cuda/gpu_cuda.cu:231-273, harvested at submit while profiling is on:
+     * linear_seconds = CUDA-event time of the GEMM launches (0), stream_wait_seconds = slot waits (3),
+     * h2d_seconds / d2h_seconds = asynchronous copies (4, 5), quant_conversion_seconds = quantise / dequantise (7) */
+    double transfer_seconds, stream_wait_seconds, linear_seconds, attention_seconds;
+    double conv_seconds;
+    double h2d_seconds, d2h_seconds, slot_wait_seconds, normalization_seconds;
+    uint64_t weight_cache_bytes, weight_cache_hits, weight_cache_hit_bytes;
+    uint64_t weight_cache_misses, weight_cache_evictions;
+    double quant_conversion_seconds;
+    uint64_t quant_clipped_values, quant_zeroed_values;
     uint64_t quant_projection_dispatches, quant_cache_hits, quant_cache_misses;
-    uint64_t native_scratch_bytes, native_scratch_allocations, native_scratch_reuses;
-    /* H3_PROFILE categories 0 (GEMM) and 7 (quant conversion) of
-     * src/cuda/gpu_cuda.cu:231-273: CUDA-event time of the linear kernels and of
-     * the quantise / dequantise kernels, harvested at submit while profiling is on. */
-    double linear_seconds;
-    uint64_t linear_kernel_launches, conversion_kernel_launches;
-    /* last accepted residency plan (src/gpu.h:99-142, same names) */
-    uint64_t resident_weight_bytes, resident_blocks, active_weight_blocks, resident_block_mask;
-    /* H3_PROFILE categories 4 and 5: event time of the asynchronous copies (uploads, weight streaming; downloads) */
-    double h2d_seconds, d2h_seconds;
+    uint64_t sage2_attention_dispatches, sage3_attention_dispatches, attention_workspace_bytes;
+    uint64_t inflight_peak, command_retirements, bounded_waits, pressure_drains;
+    uint64_t native_scratch_bytes, native_scratch_allocations, native_scratch_reuses, native_pipeline_count;
+    uint64_t main_dense_calls, subblock_calls, subblock_bypass, subblock_protected_calls;
+    uint64_t subblock_selected, subblock_possible, subblock_router_calls;
+    uint64_t attention_timing_samples, attention_timing_missed;
+    double main_attention_seconds, subblock_router_seconds, subblock_kernel_seconds;
 } h3_gpu_stats;
+/* Counters the reference's struct has no field for (no counterpart in src/gpu.h). */
+typedef struct {
+    uint64_t linear_kernel_launches;      /* GEMM launches timed under H3_PROFILE category 0       */
+    uint64_t conversion_kernel_launches;  /* quantise / dequantise launches timed under category 7 */
+} h3q8_gpu_profile;
 
 /* Context -- src/gpu.h:144-145, 180-182, 203, 207, 267-268 */
 h3_gpu *h3_gpu_create(const char *shader_source_path, char *error, size_t error_size);
@@ -241,6 +278,7 @@ const char *h3_gpu_error(const h3_gpu *gpu);
 void h3_gpu_profile_set_label(h3_gpu *gpu, const char *label);
 void h3_gpu_profile_mark(h3_gpu *gpu, const char *phase);
 int h3_gpu_get_stats(const h3_gpu *gpu, h3_gpu_stats *stats);
+int h3q8_gpu_get_profile(const h3_gpu *gpu, h3q8_gpu_profile *profile);
 const char *h3_gpu_backend_name(const h3_gpu *gpu);
 int h3_gpu_has_int8_mlp(const h3_gpu *gpu);
 /* Command scope -- src/gpu.h:260-266 */

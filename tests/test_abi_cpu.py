@@ -88,3 +88,76 @@ def test_no_cpu_fallback(lib):
         h3cli_b200.Gpu()
     d = h3cli_b200.LinearDesc(mode=1, rows=4, input_dim=16, output_dim=8)
     assert lib.h3q8_linear(ctypes.byref(d), None) == 0 and lib.h3q8_last_error()
+
+
+# --------------------------------------------------------------------------- drop-in checks against the reference's headers
+REF_BUILD = os.path.join(ROOT, "oracle", "_ref")
+
+
+def reference_tree():
+    import oracle
+    return oracle._reference_tree()
+
+
+def test_stats_layout_equals_the_reference_struct(lib, tmp_path):
+    """h3_gpu_stats as include/h3q8.h declares it, as ctypes mirrors it and as the reference's src/gpu.h:99-142
+    lays it out (oracle/_ref/abi_layout_reference.txt, written by tests/abi/contract.c compiled against that
+    header): same size, same offset for every counter this path feeds."""
+    import subprocess
+    import h3cli_b200
+    binary = tmp_path / "layout_mine"
+    subprocess.run(["gcc", "-std=c11", "-I", os.path.join(ROOT, "include"), os.path.join(ROOT, "tests", "abi", "layout_mine.c"),
+                    "-o", str(binary)], check=True)
+    mine = subprocess.run([str(binary)], check=True, capture_output=True, text=True).stdout
+    fields = dict(line.split() for line in mine.splitlines())
+    assert int(fields.pop("sizeof")) == ctypes.sizeof(h3cli_b200.api.Stats)
+    for name, offset in fields.items():
+        assert getattr(h3cli_b200.api.Stats, name).offset == int(offset), name
+    reference = os.path.join(REF_BUILD, "abi_layout_reference.txt")
+    if not os.path.exists(reference):
+        pytest.skip("oracle/_ref was built without the reference tree")
+    assert open(reference).read() == mine
+
+
+def test_contract_binary_links_every_symbol_through_the_reference_header():
+    """tests/abi/contract.c includes only the reference's headers and links libh3q8: every symbol of the path resolves."""
+    import subprocess
+    binary = os.path.join(REF_BUILD, "abi_contract")
+    if not os.path.exists(binary):
+        pytest.skip("oracle/_ref/abi_contract was not built (no reference tree at build time)")
+    out = subprocess.run([binary], check=True, capture_output=True, text=True).stdout
+    assert int(out.split()[0]) >= 60
+
+
+def prototypes(text, wanted=None):
+    """name -> normalised 'return type | parameter types' of every function declared in a C header."""
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+    text = re.sub(r"//[^\n]*", " ", text)
+    text = re.sub(r"#[^\n]*", " ", text)
+    found = {}
+    for match in re.finditer(r"([A-Za-z_][A-Za-z0-9_ \t\n\*]*?)\b(h3_[a-z0-9_]+)\s*\(([^;{}]*?)\)\s*;", text):
+        ret, name, params = match.groups()
+        if wanted is not None and name not in wanted:
+            continue
+        def kind(p):
+            p = re.sub(r"\s+", " ", p.strip())
+            p = re.sub(r"\b[a-z_][a-z0-9_]*$", "", p) if not p.endswith("*") and " " in p else p   # drop the parameter name
+            return re.sub(r"\s*\*\s*", "*", p).strip()
+        found[name] = (re.sub(r"\s+", " ", ret.strip()), [kind(p) for p in params.split(",")])
+    return found
+
+
+def test_prototypes_equal_the_reference_headers():
+    """Every h3_* function this header shares with src/gpu.h / src/weights/residency.h / src/weights/q8.h has the
+    reference's return type and parameter types (names may differ).  Needs the reference tree; skipped without it."""
+    tree = reference_tree()
+    if not tree:
+        pytest.skip("reference tree not present")
+    mine = prototypes(open(os.path.join(ROOT, "include", "h3q8.h")).read())
+    theirs = {}
+    for header in ("src/gpu.h", "src/weights/residency.h", "src/weights/q8.h", "src/weights/quant.h"):
+        theirs.update(prototypes(open(os.path.join(tree, header)).read()))
+    shared = sorted(set(mine) & set(theirs))
+    assert len(shared) >= 55
+    for name in shared:
+        assert mine[name] == theirs[name], f"{name}: {mine[name]} != reference {theirs[name]}"
