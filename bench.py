@@ -94,6 +94,8 @@ def oracle_slab(rows, steps, warmup, mode="w8a16"):
     """Times the CPU restatement (oracle fast path, all host threads) on `rows` rows of each GEMM shape."""
     import oracle
     oracle.build()
+    # every core this process may run on, whatever OMP_NUM_THREADS a launcher exported (torch.distributed.run sets 1)
+    oracle.lib().h3o_set_threads(len(os.sched_getaffinity(0)))
     rng = np.random.default_rng(0)
     work = []
     for name, k, n, spec in LAYERS:
@@ -167,6 +169,7 @@ def main():
     ap.add_argument("--group", type=int, default=-1, help="weight scale group for --case (default: 64 for real W8A16 shapes, else per channel)")
     ap.add_argument("--e2e-depth", type=int, default=4, help="end-to-end steps in flight (buffer sets)")
     ap.add_argument("--e2e-slices", type=int, default=1, help="row slices per end-to-end step (copy/compute overlap inside a step)")
+    ap.add_argument("--no-subrecords", action="store_true", help="default run: skip the w8a8 / config5_stream / tp_ffn sub-records")
     ap.add_argument("--mode", default="w8a16", choices=["w8a16", "w8a8"],
                     help="w8a16 (default, BASELINE config 2) or the W8A8 variant: per-token int8 activations, int8 MMAs")
     args = ap.parse_args()
@@ -223,8 +226,142 @@ def main():
     if args.workload == "tp_ffn":
         return run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local)
 
+    # ---- the headline record (and, in the default W8A16 run, the W8A8 variant of the same step as a sub-record) ----
+    dev = dict(torch=torch, dist=dist, rank=rank, world=world, local=local, lib=lib, stream=stream, device_bf16=device_bf16)
+    line = measure_block(args, gpu, args.mode, dev)
+    extra = {}
+    if args.mode == "w8a16" and not args.no_subrecords:
+        gpu.free()
+        # W8A8 on the record: same step, per-token int8 activations, int8 MMAs, against a measured int8 peak
+        gpu8 = h.Gpu()
+        gpu8.quant_configure(2)
+        dev8 = dict(dev, stream=torch.cuda.ExternalStream(gpu8.stream, device=local),
+                    device_bf16=make_device_bf16(torch, gpu8, rank, local))
+        sub = measure_block(args, gpu8, "w8a8", dev8, steps=max(5, args.steps // 2))
+        gpu8.free()
+        if sub:
+            extra["w8a8"] = {k: sub[k] for k in ("value", "unit", "ms_per_step", "dtype", "roofline", "e2e", "gpu_launches", "int8_peak")}
+        # the multi-GPU configuration (BASELINE config 5) strong-scaled over the ranks, and the tensor-parallel FFN:
+        # short sub-records so that every N of a scaling run exercises the all-gather and the all-reduce
+        gpu5 = h.Gpu()
+        gpu5.quant_configure(1)
+        dev5 = dict(dev, stream=torch.cuda.ExternalStream(gpu5.stream, device=local), device_bf16=make_device_bf16(torch, gpu5, rank, local))
+        sub_args = argparse.Namespace(**vars(args))
+        sub_args.layers, sub_args.steps, sub_args.stream_gather = 8, 10, 1
+        stream_record = run_stream(sub_args, gpu5, lib, dev5["stream"], dev5["device_bf16"], rank, world, local, standalone=False)
+        sub_args.steps, sub_args.warmup, sub_args.rows = 10, 3, M_TOKENS
+        tp_record = run_tp_ffn(sub_args, gpu5, lib, dev5["stream"], dev5["device_bf16"], rank, world, local, standalone=False)
+        gpu5.free()
+        if stream_record:
+            extra["config5_stream"] = {k: stream_record[k] for k in ("value", "unit", "n_gpus", "layers", "rows_total", "rows_this_rank", "scaling",
+                                                                     "ms_per_layer", "seconds_per_pass", "weights_over", "allgather_ms_per_layer_comm_stream",
+                                                                     "pcie_bytes_per_layer_this_rank", "stream_stalls", "slot_wait_ms_per_pass")}
+            extra["config5_stream"]["note"] = "M = 219 600 rows over all ranks (strong scaling), 8 of the 48 layers, group-128 weights streamed from pinned host memory"
+        if tp_record:
+            extra["tp_ffn"] = {k: tp_record[k] for k in ("value", "unit", "n_gpus", "ms_per_block_ffn", "rows", "scaling", "allreduce_bytes_per_block",
+                                                         "allreduce_ms_per_block_comm_stream", "parity_vs_unsharded_fused_call")}
+    else:
+        gpu.free()
+    if rank == 0:
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bind_to_gpu_numa_node(torch, local):
+    """Runs this process (and so the threads that allocate and fill its pinned buffers) on the CPUs of the NUMA node
+    the GPU hangs off: pinned memory is then first-touched next to the GPU's PCIe root.  Returns the node or None."""
+    try:
+        bus = torch.cuda.get_device_properties(local).pci_bus_id
+        domain = torch.cuda.get_device_properties(local).pci_domain_id
+        device = torch.cuda.get_device_properties(local).pci_device_id
+        node = int(open(f"/sys/bus/pci/devices/{domain:04x}:{bus:02x}:{device:02x}.0/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return node
+    except Exception:
+        pass
+    return None
+
+
+_INT8_PEAK = {}
+
+
+def int8_peak(torch):
+    """Dense int8 tensor-core rate of this GPU, measured the way MEASURED_PEAKS.json measures bf16: torch._int_mm
+    8192^3 (2 N^3 operations), best of 10 launches (burst) and back to back for about 2 s (sustained)."""
+    if _INT8_PEAK:
+        return _INT8_PEAK
+    try:
+        n = 8192
+        a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+        b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8).t()      # column-major right operand
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None or ms < best else best
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        count = max(10, int(2000.0 / best))
+        e0.record()
+        for _ in range(count):
+            torch._int_mm(a, b)
+        e1.record()
+        torch.cuda.synchronize()
+        ops = 2.0 * n ** 3
+        _INT8_PEAK.update({"tops": ops / best / 1e9, "tops_sustained": ops * count / e0.elapsed_time(e1) / 1e9,
+                           "how": "torch._int_mm int8 8192^3 (2*N^3): best of 10 (burst) and back to back for ~2 s (sustained), CUDA events"})
+        del a, b
+        torch.cuda.empty_cache()
+    except Exception as error:   # the library GEMM is only the yardstick; without it the bf16 figure is reported instead
+        _INT8_PEAK.update({"tops": None, "tops_sustained": None, "how": f"torch._int_mm unavailable: {error}"})
+    return _INT8_PEAK
+
+
+def make_device_bf16(torch, gpu, rank, local):
+    class _Span:
+        """Zero-copy torch view of an h3_gpu tensor (CUDA array interface)."""
+
+        def __init__(self, pointer, count):
+            self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<i2", "data": (pointer, False), "version": 2}
+
+    def device_bf16(rows, cols, mean=0.0, std=1.0, seed=0, replicated=False):
+        """A resident h3_gpu bf16 tensor filled on the device with seeded normals (per rank unless replicated)."""
+        gen = torch.Generator(device="cuda").manual_seed(seed if replicated else 1000 * rank + seed)
+        t = gpu.tensor_new_bf16(rows * cols)
+        view = torch.as_tensor(_Span(t.device_pointer, rows * cols), device=f"cuda:{local}").view(torch.bfloat16)
+        chunk = 4096
+        for r0 in range(0, rows, chunk):
+            r1 = min(rows, r0 + chunk)
+            block = torch.randn(r1 - r0, cols, generator=gen, device="cuda", dtype=torch.float32) * std + mean
+            view[r0 * cols:r1 * cols].copy_(block.to(torch.bfloat16).reshape(-1))
+        torch.cuda.synchronize()
+        return t
+    return device_bf16
+
+
+def measure_block(args, gpu, mode, dev, steps=None):
+    """One DiT block's four projections in `mode` on context `gpu`: resident value, roofline, end-to-end.  Returns the
+    record (rank 0) or None."""
+    torch, dist, rank, world, local, lib, stream, device_bf16 = (dev[k] for k in ("torch", "dist", "rank", "world", "local", "lib", "stream", "device_bf16"))
+    steps = steps or args.steps
     # ---- operands (weights replicated on every rank: same seed) ----------------------------------
-    weights, inputs, outputs, gates, residuals = {}, {}, {}, {}, {}
+    weights, inputs, outputs = {}, {}, {}
     wgen = np.random.default_rng(42)
     for name, k, n, spec in LAYERS:
         wq = wgen.integers(-127, 128, (n, k), dtype=np.int8)
@@ -263,7 +400,7 @@ def main():
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     gpu.begin()
     start.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         enqueue_step()
     stop.record(stream)
     barrier()
@@ -277,12 +414,12 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     job_seconds = float(t.item())
-    value = world * FLOP_PER_STEP * args.steps / job_seconds / 1e12
+    value = world * FLOP_PER_STEP * steps / job_seconds / 1e12
 
     gemm_seconds = after.linear_seconds - before.linear_seconds
     gemm_launches = gpu.profile().linear_kernel_launches - gemm_launches_before
     burst, sustained, which = measured_peak()
-    achieved = FLOP_PER_STEP * args.steps / gemm_seconds / 1e12 if gemm_seconds > 0 else None
+    achieved = FLOP_PER_STEP * steps / gemm_seconds / 1e12 if gemm_seconds > 0 else None
 
     # ---- e2e: the same four operators, host buffers in, host buffer out ------------------------------
     # Chain as a DiT block calls them: x -> qkv; x -> attn_out (+gate, residual x) -> ffn_up (GELU) ->
@@ -290,11 +427,12 @@ def main():
     # The rows are cut into E2E_CHUNKS slices with their own tensors, so that the upload of slice c+1 and the
     # download of slice c-1 (copy stream, h3q8_gpu_tensor_upload_async / _download_async) overlap the GEMMs of slice c.
     from h3cli_b200 import sharding
+    numa_node = bind_to_gpu_numa_node(torch, local)    # before the pinned buffers are allocated and first touched
     host_x = torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory()
     host_y = torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory()
     lib.h3_gpu_tensor_read_bf16(x.handle, host_x.data_ptr(), M_TOKENS * HIDDEN)
-    for t in list(outputs.values()) + [hidden, residual]:
-        t.free()                                      # the resident-run tensors are no longer needed
+    for tensor in list(outputs.values()) + [hidden, residual]:
+        tensor.free()                                 # the resident-run tensors are no longer needed
     # DEPTH sets of slice tensors and host output buffers: steps i+1 .. i+DEPTH-1 are enqueued (their uploads start
     # at once on the upload stream) before the host waits for step i's output, so a stream of independent batches
     # keeps the upload stream, the compute stream and the download stream busy at the same time.
@@ -328,15 +466,15 @@ def main():
         for c in sets[index % DEPTH]:
             c["y"].wait()                             # this step's block output is in host memory
 
-    def run_e2e(steps, depth):
+    def run_e2e(count, depth):
         """depth 1: each step ends before the next is enqueued; depth d: d-1 steps in flight behind the current one."""
         begin = time.perf_counter()
         gpu.begin()                                   # one command scope; h3_gpu_continue commits each slice
-        for i in range(steps):
+        for i in range(count):
             enqueue_e2e(i)
             if i >= depth - 1:
                 finish_e2e(i - (depth - 1))
-        for i in range(max(0, steps - (depth - 1)), steps):
+        for i in range(max(0, count - (depth - 1)), count):
             finish_e2e(i)
         gpu.submit()                                  # surfaces deferred kernel errors; everything is already done
         return time.perf_counter() - begin
@@ -345,61 +483,91 @@ def main():
         run_e2e(3, depth)
         gpu.synchronize()
         barrier()
-        seconds = run_e2e(args.steps, depth)
+        elapsed = run_e2e(steps, depth)
         barrier()
-        t = torch.tensor([seconds], device="cuda", dtype=torch.float64)
+        t = torch.tensor([elapsed], device="cuda", dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
     e_serial = timed_e2e(1)
+    gpu.set_profiling(True)                           # event pairs around the asynchronous copies (categories 4 and 5)
+    copies_before = gpu.stats()
     e_seconds = timed_e2e(DEPTH)
-    e2e_value = world * FLOP_PER_STEP * args.steps / e_seconds / 1e12
+    copies_after = gpu.stats()
+    gpu.set_profiling(False)
+    e2e_value = world * FLOP_PER_STEP * steps / e_seconds / 1e12
+    h2d_seconds, d2h_seconds = copies_after.h2d_seconds - copies_before.h2d_seconds, copies_after.d2h_seconds - copies_before.d2h_seconds
+    for slices in sets:
+        for c in slices:
+            for key in ("x", "qkv", "h1", "up", "y"):
+                c[key].free()
+    for tensor in list(weights.values()) + [x, gate]:
+        tensor.free()
+    del host_out, host_x, host_y
 
-    if rank == 0:
-        cpu_value, cpu_seconds, cores = (None, None, None)
-        if world == 1:
-            cpu_value, cpu_seconds, cores = oracle_slab(1024, 2, 1, args.mode)
-        clocks = sampler.summary()
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": job_seconds / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16" if args.mode == "w8a16" else "int8", "data": "synthetic", "config": workload_config(args.mode),
-            "dit_block_linear_ms": job_seconds / args.steps * 1e3,
-            "tensor_peak_fraction_per_gpu": value / world / burst,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": M_TOKENS * HIDDEN * 2,
-                    "d2h_bytes_per_step": M_TOKENS * HIDDEN * 2,
-                    "ms_per_step": e_seconds / args.steps * 1e3,
-                    "ms_per_step_one_at_a_time": e_serial / args.steps * 1e3,
-                    "path": "pinned host x -> h3q8_gpu_tensor_upload_async -> 4 x h3_gpu_linear_fused_bf16 per row slice (chained as "
-                            "the DiT block calls them, " + str(E2E_CHUNKS) + " row slices so copies overlap compute) -> h3q8_gpu_tensor_download_async -> "
-                            "pinned host y -> h3q8_gpu_tensor_wait; steps are independent batches with " + str(DEPTH) + " buffer sets: "
-                            "later steps are enqueued before the host waits for step i's output (ms_per_step_one_at_a_time: no "
-                            "step in flight behind the current one); host wall clock over all steps, max over ranks"},
-            "gpu_launches": int(launches),
-            "clocks": clocks,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel<bf16> (256x256 tile per CTA pair) after q8_dequant_kernel" if args.mode == "w8a16"
-                         else "gemm_tcgen05_pair_kernel<int8> after quantize_segments_warp_kernel (peak is the bf16 figure; no int8 peak is recorded)",
-                         "achieved": achieved, "peak": burst, "unit": UNIT, "frac": achieved / burst if achieved else None,
-                         "peak_source": f"bf16_tflops (burst) of {which}", "frac_of_sustained": achieved / sustained if achieved and sustained else None,
-                         "launches": int(gemm_launches), "avg_launch_ms": gemm_seconds / max(gemm_launches, 1) * 1e3,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
-            "cpu_baseline": None if cpu_value is None else {
-                "value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
-                "sample": "1024-row slab of each of the 4 GEMM shapes (0.232 TFLOP), blocked fp32 OpenMP restatement"},
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-    gpu.free()
+    if rank != 0:
+        return None
+    cpu_value, cpu_seconds, cores = (None, None, None)
+    if world == 1 and mode == args.mode:
+        cpu_value, cpu_seconds, cores = oracle_slab(1024, 2, 1, mode)
+    clocks = sampler.summary()
+    step_bytes = M_TOKENS * HIDDEN * 2
+    if mode == "w8a16":
+        roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel<bf16> (256x256 tile per CTA pair) after q8_dequant_kernel "
+                                                 "(dequantise-to-scratch policy; the main-loop kernel gemm_tcgen05_pair_w8a16_kernel is slower, see DESIGN.md)",
+                    "achieved": achieved, "peak": burst, "unit": UNIT, "frac": achieved / burst if achieved else None,
+                    "peak_source": f"bf16_tflops (burst) of {which}", "frac_of_sustained": achieved / sustained if achieved and sustained else None,
+                    "launches": int(gemm_launches), "avg_launch_ms": gemm_seconds / max(gemm_launches, 1) * 1e3,
+                    "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH}
+        peak8 = None
+    else:
+        peak8 = int8_peak(torch)
+        peak = peak8["tops"] or 2.0 * burst
+        roofline = {"bound": "tensor", "kernel": "gemm_tcgen05_pair_kernel<int8> (256x256 tile per CTA pair) after quantize_segments_warp_kernel",
+                    "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak if achieved else None,
+                    "peak_source": "int8 dense rate measured in this run (int8_peak.tops, burst)" if peak8["tops"] else "2 x bf16_tflops (no int8 GEMM to measure with)",
+                    "frac_of_sustained": achieved / peak8["tops_sustained"] if achieved and peak8["tops_sustained"] else None,
+                    "launches": int(gemm_launches), "avg_launch_ms": gemm_seconds / max(gemm_launches, 1) * 1e3, "traffic": None}
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT if mode == "w8a16" else "TOP/s", "n_gpus": world, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": job_seconds / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if mode == "w8a16" else "int8", "data": "synthetic", "config": workload_config(mode),
+        "dit_block_linear_ms": job_seconds / steps * 1e3,
+        "tensor_peak_fraction_per_gpu": value / world / burst,
+        "e2e": {"value": e2e_value, "unit": UNIT if mode == "w8a16" else "TOP/s", "h2d_bytes_per_step": step_bytes,
+                "d2h_bytes_per_step": step_bytes,
+                "ms_per_step": e_seconds / steps * 1e3,
+                "ms_per_step_one_at_a_time": e_serial / steps * 1e3,
+                "h2d_gbs": step_bytes * steps / h2d_seconds / 1e9 if h2d_seconds > 0 else None,
+                "d2h_gbs": step_bytes * steps / d2h_seconds / 1e9 if d2h_seconds > 0 else None,
+                "pcie_gbs_needed_per_direction": step_bytes / (job_seconds / steps) / 1e9,
+                "host_numa_node": numa_node,
+                "path": "pinned host x -> h3q8_gpu_tensor_upload_async -> 4 x h3_gpu_linear_fused_bf16 per row slice (chained as "
+                        "the DiT block calls them, " + str(E2E_CHUNKS) + " row slices so copies overlap compute) -> h3q8_gpu_tensor_download_async -> "
+                        "pinned host y -> h3q8_gpu_tensor_wait; steps are independent batches with " + str(DEPTH) + " buffer sets: "
+                        "later steps are enqueued before the host waits for step i's output (ms_per_step_one_at_a_time: no "
+                        "step in flight behind the current one); host wall clock over all steps, max over ranks; h2d_gbs / d2h_gbs: "
+                        "bytes / CUDA-event time of this rank's copies; the process is bound to the CPUs of the GPU's NUMA node "
+                        "before its pinned buffers are allocated"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": roofline,
+        "cpu_baseline": None if cpu_value is None else {
+            "value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": "1024-row slab of each of the 4 GEMM shapes (0.232 TFLOP), blocked fp32 OpenMP restatement"},
+    }
+    if peak8:
+        line["int8_peak"] = peak8
+    return line
 
 
-def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local):
+def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local, standalone=True):
     """The optional tensor-parallel FFN: every rank sees all M rows; FFN-up is column-parallel (rank r owns FFN
-    features [f0, f1), GELU stays local), FFN-down is row-parallel over the same features, and one NCCL all-reduce
-    per block sums the bf16 partial outputs before gate + residual are applied by the unfused gate operator.  The
-    rows are cut into chunks so the all-reduce of chunk c (communication stream) overlaps the GEMMs of chunk c+1.
-    Partial sums are rounded to bf16 once each, so parity with the unsharded fused call is by tolerance only."""
+    features [f0, f1), GELU stays local), FFN-down is row-parallel over the same features and stores fp32 partial
+    sums, one NCCL all-reduce per block adds them in fp32, and the finishing call applies gate + residual with the
+    single bf16 rounding -- so the result meets the same tolerance as the unsharded fused call.  The rows are cut
+    into chunks so the all-reduce of chunk c (communication stream) overlaps the GEMMs of chunk c+1."""
     import torch
     import torch.distributed as dist
     from h3cli_b200 import sharding
@@ -420,23 +588,30 @@ def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local):
         rows = end - begin
         part = dict(rows=rows, x=device_bf16(rows, HIDDEN, seed=10 + c, replicated=True),
                     residual=device_bf16(rows, HIDDEN, seed=20 + c, replicated=True), hidden=gpu.tensor_new_bf16(rows * width),
-                    partial=gpu.tensor_new_bf16(rows * HIDDEN), y=gpu.tensor_new_bf16(rows * HIDDEN))
-        part["view"] = torch.as_tensor(_Span16(part["partial"].device_pointer, rows * HIDDEN), device=f"cuda:{local}").view(torch.bfloat16)
+                    partial=gpu.tensor_new_f32(rows * HIDDEN), y=gpu.tensor_new_bf16(rows * HIDDEN))
+        part["view"] = torch.as_tensor(_Span32(part["partial"].device_pointer, rows * HIDDEN), device=f"cuda:{local}")
         parts.append(part)
+    reduce_events = []
 
-    def one_block():
+    def one_block(timed=False):
         for p in parts:
             gpu.linear_fused_bf16(p["hidden"], p["x"], up_slice, None, None, None, p["rows"], HIDDEN, width, 1)
-            gpu.linear_fused_bf16(p["partial"], p["hidden"], down_slice, None, None, None, p["rows"], width, HIDDEN, 0)
+            gpu.linear_partial_f32(p["partial"], p["hidden"], down_slice, p["rows"], width, HIDDEN)
             gpu.continue_()
             if world > 1:
                 comm.wait_stream(stream)                    # this chunk's partial sums are complete
                 with torch.cuda.stream(comm):
-                    dist.all_reduce(p["view"])
-        for p in parts:                                     # gate + residual once the reduced sums are there
+                    if timed:
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(comm)
+                    dist.all_reduce(p["view"])              # fp32 sum over the ranks, in place
+                    if timed:
+                        e1.record(comm)
+                        reduce_events.append((e0, e1))
+        for p in parts:                                     # gate + residual + the one bf16 rounding on the reduced sums
             if world > 1:
                 stream.wait_stream(comm)
-            gpu.gate_bf16(p["y"], p["residual"], p["partial"], gate, None, p["rows"], HIDDEN, 1, 0)
+            gpu.linear_finish_bf16(p["y"], p["partial"], None, gate, p["residual"], p["rows"], HIDDEN, 0)
         gpu.continue_()
 
     gpu.begin()
@@ -450,15 +625,16 @@ def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local):
     gpu.begin()
     start.record(stream)
     for _ in range(args.steps):
-        one_block()
+        one_block(timed=True)
     stop.record(stream)
     gpu.submit()
     torch.cuda.synchronize()
     seconds = torch.tensor([start.elapsed_time(stop) * 1e-3], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(seconds, op=dist.ReduceOp.MAX)
+    reduce_ms = sum(a.elapsed_time(b) for a, b in reduce_events) / max(args.steps, 1)
     # parity: rank 0 runs the unsharded fused FFN on the first chunk and compares
-    report = None
+    record = None
     if rank == 0:
         p = parts[0]
         full_up, full_down = gpu.q8_from_host(wup, sup, 0), gpu.q8_from_host(wdn, sdn, 0)
@@ -472,21 +648,40 @@ def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local):
         floor = float(np.sqrt((want_v ** 2).mean()))
         ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(want_v), floor))) - 7)
         report = {"rel_l2": float(np.sqrt(((got_v - want_v) ** 2).sum() / (want_v ** 2).sum())),
-                  "max_bf16_ulp": float((np.abs(got_v - want_v) / ulp).max()), "rows_checked": p["rows"]}
+                  "max_bf16_ulp": float((np.abs(got_v - want_v) / ulp).max()), "rows_checked": p["rows"],
+                  "bar": "rel-L2 <= 2e-3 and <= 2 bf16 ulp"}
+        for t in (full_up, full_down, hidden, want):
+            t.free()
         t = float(seconds.item())
         flop = 2.0 * rows_total * HIDDEN * FFN * 2 * args.steps
-        print(json.dumps({
+        record = {
             "metric": METRIC, "workload": "tp_ffn", "value": flop / t / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "ms_per_block_ffn": t / args.steps * 1e3, "rows": rows_total, "ffn_features_this_rank": width, "row_chunks": chunks,
-            "allreduce_bytes_per_block": rows_total * HIDDEN * 2 if world > 1 else 0, "scaling": "strong", "dtype": "bf16",
-            "data": "synthetic", "parity_vs_unsharded_fused_call": report,
+            "allreduce_bytes_per_block": rows_total * HIDDEN * 4 if world > 1 else 0, "allreduce_ms_per_block_comm_stream": reduce_ms,
+            "scaling": "strong", "dtype": "bf16", "data": "synthetic", "parity_vs_unsharded_fused_call": report,
             "config": {"workload": "tensor-parallel FFN (optional variant): FFN-up column-parallel with local GELU, FFN-down "
-                                   "row-parallel, one NCCL all-reduce of the bf16 partial sums per block (chunked over rows, "
-                                   "overlapped with the next chunk's GEMMs), gate + residual after the reduction"}}), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
-    gpu.free()
+                                   "row-parallel into fp32 partial sums, one NCCL all-reduce (fp32) per block, chunked over rows and "
+                                   "overlapped with the next chunk's GEMMs, gate + residual + bf16 rounding after the reduction"}}
+    for p in parts:
+        for key in ("x", "residual", "hidden", "partial", "y"):
+            p[key].free()
+    for t in (up_slice, down_slice, gate):
+        t.free()
+    if standalone:
+        if record:
+            print(json.dumps(record), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        gpu.free()
+    return record
+
+
+class _Span32:
+    """Zero-copy torch view of device fp32 words (CUDA array interface)."""
+
+    def __init__(self, pointer, count):
+        self.__cuda_array_interface__ = {"shape": (count,), "typestr": "<f4", "data": (pointer, False), "version": 2}
 
 
 class _Span16:
@@ -503,7 +698,7 @@ class _ByteSpan:
         self.__cuda_array_interface__ = {"shape": (count,), "typestr": "|u1", "data": (pointer, False), "version": 2}
 
 
-def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
+def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local, standalone=True):
     """BASELINE config 5: 48 layers x 4 projections at M = 219,600 (rows sharded over the ranks, strong scaling),
     W8A16 per-group-128 weights (116.8 MB per layer) streamed from pinned host memory, two device slots, the copy
     of layer l+1 overlapping the compute of layer l."""
@@ -540,6 +735,7 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
     # one NCCL all-gather over NVLink assembles the layer in each rank's local slot, on a communication stream, one layer
     # ahead of the compute stream.  The slot is local memory before any tensor map points at it.
     gather = bool(args.stream_gather) and world > 1
+    gather_events = []
     if gather:
         piece = slot_bytes // world
         comm = torch.cuda.Stream()
@@ -556,7 +752,11 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
                 slot, address = ring.reserve(comm.cuda_stream)
                 stage.copy_(host_bytes[blob:blob + piece], non_blocking=True)
                 target = torch.as_tensor(_ByteSpan(address, slot_bytes), device=f"cuda:{local}")
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(comm)
                 dist.all_gather_into_tensor(target, stage)
+                e1.record(comm)
+                gather_events.append((e0, e1))
                 ring.publish(slot, comm.cuda_stream, slot_bytes)
             return slot
     else:
@@ -583,6 +783,7 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
+    gather_events.clear()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     passes = max(1, args.steps // 10)
     gpu.begin()
@@ -596,22 +797,35 @@ def run_stream(args, gpu, lib, stream, device_bf16, rank, world, local):
         dist.all_reduce(seconds, op=dist.ReduceOp.MAX)
     after = gpu.stats()
     flop = sum(2.0 * total_rows * k * n for _, k, n, _ in LAYERS) * args.layers * passes
+    torch.cuda.synchronize()
+    gather_ms = sum(a.elapsed_time(b) for a, b in gather_events) / max(passes * args.layers, 1)
+    gpu.set_profiling(False)
+    record = None
     if rank == 0:
         t = float(seconds.item())
-        print(json.dumps({
+        record = {
             "metric": METRIC, "workload": "stream", "value": flop / t / 1e12, "unit": UNIT, "n_gpus": world, "passes": passes,
             "layers": args.layers, "rows_total": total_rows, "rows_this_rank": rows, "scaling": "strong",
             "ms_per_layer": t / passes / args.layers * 1e3, "seconds_per_pass": t / passes,
             "streamed_bytes_per_layer": slot_bytes, "pcie_bytes_per_layer_this_rank": slot_bytes // world if gather else slot_bytes,
             "weights_over": "pcie slice + nccl all-gather" if gather else "pcie (whole layer per rank)",
+            "allgather_ms_per_layer_comm_stream": gather_ms if gather else 0.0,
             "h2d_gbs_this_rank": (after.streamed_bytes - before.streamed_bytes) / t / 1e9,
             "stream_stalls": int(after.stream_stalls - before.stream_stalls),
             "slot_wait_ms_per_pass": (after.stream_wait_seconds - before.stream_wait_seconds) / passes * 1e3, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "large render (BASELINE config 5): 48-layer DiT linear stack, M=219600, W8A16 group-128, "
-                                   "weights streamed per layer from pinned host memory, 2 device slots"}}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-    gpu.free()
+            "config": {"workload": f"large render (BASELINE config 5): {args.layers}-layer DiT linear stack, M=219600 over all ranks, W8A16 "
+                                   "group-128, weights streamed per layer from pinned host memory, 2 device slots"}}
+    for t in views[0] + views[1] + outputs + [x, hidden, residual, gate]:
+        t.free()
+    ring.free()
+    host.free()
+    if standalone:
+        if record:
+            print(json.dumps(record), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        gpu.free()
+    return record
 
 
 def run_grouped_streams(args, gpu, lib, stream, device_bf16):

@@ -140,6 +140,9 @@ def library():
         "h3_gpu_get_stats": (C.c_int, [vp, C.POINTER(Stats)]),
         "h3q8_gpu_get_profile": (C.c_int, [vp, C.POINTER(Profile)]),
         "h3_weight_packed_size": (C.c_int, [u32, u32, C.c_int, C.POINTER(u64), C.POINTER(u64), C.POINTER(u64)]),
+        "h3q8_linear_finish": (C.c_int, [vp, u32, u32, vp, vp, vp, u32, vp, vp]),
+        "h3q8_gpu_linear_partial_f32": (C.c_int, [vp, vp, vp, vp, u32, u32, u32]),
+        "h3q8_gpu_linear_finish_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, C.c_int]),
         "h3_gpu_backend_name": (C.c_char_p, [vp]), "h3_gpu_has_int8_mlp": (C.c_int, [vp]),
         "h3_gpu_begin": (C.c_int, [vp]), "h3_gpu_continue": (C.c_int, [vp]),
         "h3_gpu_submit": (C.c_int, [vp]), "h3_gpu_synchronize": (C.c_int, [vp]),
@@ -449,6 +452,13 @@ class Gpu:
         return self._check(library().h3_gpu_linear_fused_bf16(self.handle, _h(output), _h(input), _h(weight), _h(bias),
                                                               _h(gate), _h(residual), rows, input_dim, output_dim,
                                                               activation))
+
+    def linear_partial_f32(self, sums, input, weight, rows, input_dim, output_dim):
+        return self._check(library().h3q8_gpu_linear_partial_f32(self.handle, _h(sums), _h(input), _h(weight), rows, input_dim, output_dim))
+
+    def linear_finish_bf16(self, output, sums, bias, gate, residual, rows, output_dim, activation):
+        return self._check(library().h3q8_gpu_linear_finish_bf16(self.handle, _h(output), _h(sums), _h(bias), _h(gate), _h(residual),
+                                                                 rows, output_dim, activation))
 
     def linear_grouped_bf16(self, problems):
         array = (Problem * len(problems))(*[Problem(_h(p["output"]), _h(p["input"]), _h(p["weight"]), _h(p.get("bias")),

@@ -44,7 +44,7 @@ struct GemmParams {
     const float *a_scales;  /* [M] per-token scales (MODE_W8A8)                              */
     EpilogueParams ep;
     uint16_t *out;          /* bf16 [M,N]                                                    */
-    int32_t *acc_dump;      /* optional int32 [M,N] raw accumulators (MODE_W8A8, ungrouped)  */
+    int32_t *acc_dump;      /* optional [M,N] raw accumulators: int32 (MODE_W8A8, ungrouped) or fp32 bits */
     uint32_t *status;       /* device error word, 0 = ok                                     */
     uint32_t m_blocks, n_blocks, tiles, band;
     uint64_t l2_policy_a, l2_policy_b; /* TMA L2 eviction policies for activations / weights (two-CTA kernel) */
@@ -294,7 +294,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                     reinterpret_cast<uint4 *>(dst)[j4] = make_uint4(v[j4 * 4], v[j4 * 4 + 1], v[j4 * 4 + 2], v[j4 * 4 + 3]);
                             continue;
                         }
-                        if (MODE == MODE_W8A8 && !GROUPED && p.acc_dump) {
+                        if (!GROUPED && p.acc_dump) {   /* raw accumulators: int32 sums (W8A8) or fp32 partial sums */
 #pragma unroll
                             for (int j8 = 0; j8 < 4; j8++)
                                 if (col0 + j8 * 8 < p.N) {
@@ -302,6 +302,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                     dst[0] = make_int4(v[j8 * 8 + 0], v[j8 * 8 + 1], v[j8 * 8 + 2], v[j8 * 8 + 3]);
                                     dst[1] = make_int4(v[j8 * 8 + 4], v[j8 * 8 + 5], v[j8 * 8 + 6], v[j8 * 8 + 7]);
                                 }
+                            if (!p.out) continue;   /* a partial-sum call stores nothing else */
                         }
 #pragma unroll
                         for (int j8 = 0; j8 < 4; j8++) {

@@ -281,7 +281,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
                 tmem_load_wait();
                 const uint32_t col0 = n0 + c * 32;
                 if (!row_ok) continue;
-                if (MODE == MODE_W8A8 && p.acc_dump) {
+                if (p.acc_dump) {   /* raw accumulators: int32 sums (W8A8) or fp32 partial sums (bf16 operands) */
 #pragma unroll
                     for (int j8 = 0; j8 < 4; j8++)
                         if (col0 + j8 * 8 < p.N) {
@@ -289,6 +289,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
                             dst[0] = make_int4(v[j8 * 8 + 0], v[j8 * 8 + 1], v[j8 * 8 + 2], v[j8 * 8 + 3]);
                             dst[1] = make_int4(v[j8 * 8 + 4], v[j8 * 8 + 5], v[j8 * 8 + 6], v[j8 * 8 + 7]);
                         }
+                    if (!p.out) continue;   /* a partial-sum call stores nothing else */
                 }
 #pragma unroll
                 for (int j8 = 0; j8 < 4; j8++) {

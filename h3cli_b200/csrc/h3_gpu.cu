@@ -1065,8 +1065,14 @@ static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size
 /* The linear operators: validate every problem, run the conversion kernels each needs
  * (per-token quantiser for W8A8, weight dequantiser for the W8A16 scratch policy), then
  * hand all of them to the raw layer in one grouped call. */
-static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count, const h3q8_rope_desc *rope = nullptr) {
+static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count, const h3q8_rope_desc *rope = nullptr,
+                                h3_gpu_tensor *partial_sums = nullptr) {
     if (!launch_ready(g)) return 0;
+    if (partial_sums) {
+        if (!problems || count != 1 || rope || g->quant_mode == 2 || problems[0].output || problems[0].activation != H3Q8_ACT_NONE)
+            return set_error(g, "linear partial sums: one problem with bf16 or W8A16 operands, no output tensor and no activation");
+        if (!require(g, partial_sums, H3_GPU_F32, (size_t)problems[0].rows * problems[0].output_dim, "linear partial sums")) return 0;
+    }
     if (!problems || !count || count > 16) return set_error(g, "linear: between 1 and 16 problems per call");
     size_t total[4] = {0, 0, 0, 0};
     for (uint32_t i = 0; i < count; i++) {
@@ -1075,7 +1081,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
         if (!rows || !k || !n) return set_error(g, "linear %ux%ux%u: invalid tensor shape/type", rows, n, k);
         if (!q.weight || q.weight->owner != g) return set_error(g, "linear %ux%ux%u: weight is missing or foreign", rows, n, k);
         if (!require(g, q.input, H3_GPU_BF16, (size_t)rows * k, "linear input") ||
-            ((q.output || !rope) && !require(g, q.output, H3_GPU_BF16, (size_t)rows * n, "linear output"))) return 0;
+            ((q.output || (!rope && !partial_sums)) && !require(g, q.output, H3_GPU_BF16, (size_t)rows * n, "linear output"))) return 0;
         const uint32_t wrows = q.activation == H3Q8_ACT_SWIGLU ? 2 * n : n; /* SwiGLU weight: [gate n | up n] rows */
         if (q.bias && !require(g, q.bias, H3_GPU_BF16, wrows, "linear bias")) return 0;
         if (q.gate && !require(g, q.gate, H3_GPU_BF16, n, "linear gate")) return 0;
@@ -1109,6 +1115,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
         d.residual = q.residual ? (const uint16_t *)pointer(q.residual) : nullptr;
         d.activation = (uint32_t)q.activation;
         d.output = q.output ? (uint16_t *)pointer(q.output) : nullptr;
+        d.accumulators = partial_sums ? (int32_t *)pointer(partial_sums) : nullptr;
         d.rope = rope;
         d.input = pointer(q.input);
         d.weight = pointer(w);
@@ -1177,6 +1184,29 @@ extern "C" int h3_gpu_linear_fused_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_
                                         uint32_t rows, uint32_t k, uint32_t n, int activation) {
     return linear_dispatch(g, out, in, w, bias, gate, residual, rows, k, n, activation);
 }
+/* A linear cut along K (or across GPUs): the fp32 partial sums of one K slice, before any epilogue term, and the
+ * call that turns summed partial sums into the bf16 result with the usual epilogue. */
+extern "C" int h3q8_gpu_linear_partial_f32(h3_gpu *g, h3_gpu_tensor *sums, const h3_gpu_tensor *in, const h3_gpu_tensor *w,
+                                           uint32_t rows, uint32_t k, uint32_t n) {
+    h3_gpu_linear_problem q = {nullptr, in, w, nullptr, nullptr, nullptr, rows, k, n, H3Q8_ACT_NONE};
+    return linear_dispatch_many(g, &q, 1, nullptr, sums);
+}
+extern "C" int h3q8_gpu_linear_finish_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *sums, const h3_gpu_tensor *bias,
+                                           const h3_gpu_tensor *gate, const h3_gpu_tensor *residual, uint32_t rows, uint32_t n, int activation) {
+    if (!launch_ready(g)) return 0;
+    if (!require(g, out, H3_GPU_BF16, (size_t)rows * n, "linear finish output") || !require(g, sums, H3_GPU_F32, (size_t)rows * n, "linear finish sums") ||
+        (bias && !require(g, bias, H3_GPU_BF16, n, "linear finish bias")) || (gate && !require(g, gate, H3_GPU_BF16, n, "linear finish gate")) ||
+        (residual && !require(g, residual, H3_GPU_BF16, (size_t)rows * n, "linear finish residual"))) return 0;
+    if (activation < 0 || activation > H3Q8_ACT_GELU_TANH) return set_error(g, "linear finish: activation must be none or GELU-tanh");
+    if (!h3q8_linear_finish((const float *)pointer(sums), rows, n, bias ? (const uint16_t *)pointer(bias) : nullptr,
+                            gate ? (const uint16_t *)pointer(gate) : nullptr, residual ? (const uint16_t *)pointer(residual) : nullptr,
+                            (uint32_t)activation, (uint16_t *)pointer(out), g->compute)) {
+        g->accessed.clear();
+        return set_error(g, "%s", h3q8_last_error());
+    }
+    return launch_status(g, "linear finish", 1);
+}
+
 /* Several projections of different shapes in one call: with bf16 or W8A8 operands (and
  * the W8A16 scratch policy) all of them run in ONE GEMM launch on the two-CTA kernel. */
 extern "C" int h3_gpu_linear_grouped_bf16(h3_gpu *g, const h3_gpu_linear_problem *problems, uint32_t count) {

@@ -356,7 +356,7 @@ static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t 
 /* Validation, kernel parameters and kernel choice for one problem. */
 static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kernel, DeviceState *&dev) {
     if (!d.rows || !d.input_dim || !d.output_dim) return fail("linear %ux%ux%u: empty dimension", d.rows, d.output_dim, d.input_dim);
-    if (!d.input || !d.weight || (!d.output && !d.rope)) return fail("linear %ux%ux%u: null operand", d.rows, d.output_dim, d.input_dim);
+    if (!d.input || !d.weight || (!d.output && !d.rope && !d.accumulators)) return fail("linear %ux%ux%u: null operand", d.rows, d.output_dim, d.input_dim);
     if (d.rope) {
         const h3q8_rope_desc &r = *d.rope;
         if (d.activation || d.bias || d.gate || d.residual || d.accumulators || d.weight_group || d.input_group || d.mode == H3Q8_MODE_W8A16)
@@ -374,8 +374,9 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     if (swiglu && d.output_dim % 8) return fail("linear: SwiGLU needs output_dim %% 8 == 0");
     if (d.mode != H3Q8_MODE_BF16 && !d.weight_scales) return fail("linear: int8 weights need weight_scales");
     if (d.mode == H3Q8_MODE_W8A8 && !d.input_scales) return fail("linear: W8A8 needs per-token input_scales");
-    if (d.accumulators && (d.mode != H3Q8_MODE_W8A8 || d.weight_group))
+    if (d.accumulators && d.mode == H3Q8_MODE_W8A8 && d.weight_group)
         return fail("linear: the int32 dump exists only for W8A8 with per-channel weight scales");
+    if (d.accumulators && swiglu) return fail("linear: no accumulator dump with SwiGLU");
     if ((uint64_t)d.output_dim * (swiglu ? 2u : 1u) * d.input_dim > UINT32_MAX - 31u) return fail("linear: weight exceeds 32-bit indexing");
     if (static_cast<const void *>(d.output) == d.input) return fail("linear: output aliases the input");
     dev = device_state();
@@ -421,7 +422,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     if (kernel == H3Q8_KERNEL_AUTO) {
         const bool tiny = (uint64_t)d.rows * d.input_dim * d.output_dim <= (1u << 22);
         /* two-CTA tiles need both CTAs to have rows */
-        const bool pair_ok = d.rows > 128 && (d.mode != H3Q8_MODE_W8A8 || !p.scale_group || grouped_pair_ok);
+        const bool pair_ok = d.rows > 128 && (d.mode != H3Q8_MODE_W8A8 || !p.scale_group || grouped_pair_ok) &&
+                             !(d.mode == H3Q8_MODE_W8A16 && d.accumulators);
         kernel = !tma_ok || tiny ? H3Q8_KERNEL_PLAIN : d.output_dim <= 128 ? H3Q8_KERNEL_TCGEN05_N128
                : pair_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_TCGEN05;
         /* SwiGLU runs on the two-CTA kernel (gate rows in one CTA, up rows in its peer) or on the plain kernel */
@@ -445,6 +447,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
         return fail("linear: SwiGLU is available on the two-CTA and the plain kernel");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && d.mode == H3Q8_MODE_W8A8 && p.scale_group && !grouped_pair_ok) {
         return fail("linear: the two-CTA W8A8 kernel takes scale groups that are multiples of 128 and divide K");
+    } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && d.mode == H3Q8_MODE_W8A16 && d.accumulators) {
+        return fail("linear: the two-CTA W8A16 kernel has no accumulator dump");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_SPLITK && !splitk_ok) {
         return fail("linear: split-K takes ungrouped scales, no SwiGLU / rotary epilogue / accumulator dump, and a 16-byte aligned workspace");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {
@@ -481,6 +485,28 @@ extern "C" size_t h3q8_linear_workspace_bytes(uint32_t mode, uint32_t rows, uint
     uint32_t splits = 0, kb_per_split = 0;
     if (!dev || rows > 128 || !plan_splitk(mode, rows, input_dim, output_dim, dev->sms, SIZE_MAX, splits, kb_per_split)) return 0;
     return (size_t)splits * rows * output_dim * 4;
+}
+
+/* Second half of a linear whose fp32 partial sums were produced elsewhere (several K slices summed by the caller, or by
+ * an all-reduce across GPUs): sums fp32 [rows, output_dim] -> the usual epilogue -> bf16. */
+extern "C" int h3q8_linear_finish(const float *sums, uint32_t rows, uint32_t output_dim, const uint16_t *bias, const uint16_t *gate,
+                                  const uint16_t *residual, uint32_t activation, uint16_t *output, void *cuda_stream) {
+    if (!sums || !output || !rows || !output_dim) return fail("linear finish: null operand or empty dimension");
+    if (activation > H3Q8_ACT_GELU_TANH) return fail("linear finish: activation must be none or GELU-tanh");
+    if (output_dim % 8 || !aligned16(sums) || !aligned16(output) || (bias && !aligned16(bias)) || (gate && !aligned16(gate)) ||
+        (residual && !aligned16(residual)))
+        return fail("linear finish: needs output_dim %% 8 == 0 and 16-byte aligned operands");
+    uint32_t *status = device_status_word();
+    if (!status) return 0;
+    GemmParams p = {};
+    p.M = rows; p.N = output_dim; p.K = 0;
+    p.ep.bias = bias; p.ep.gate = gate; p.ep.residual = residual; p.ep.activation = activation;
+    p.out = output; p.status = status;
+    p.splits = 1; p.partials = reinterpret_cast<uint32_t *>(const_cast<float *>(sums));
+    const uint64_t outputs8 = (uint64_t)rows * (output_dim / 8);
+    splitk_finish_kernel<MODE_BF16><<<(unsigned)((outputs8 + 255) / 256), 256, 0, (cudaStream_t)cuda_stream>>>(p);
+    count_launch(1);
+    return cuda_ok(cudaGetLastError(), "linear finish launch");
 }
 
 extern "C" int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream) {

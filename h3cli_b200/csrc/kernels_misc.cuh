@@ -529,7 +529,13 @@ __global__ void __launch_bounds__(256) linear_plain_kernel(const void *__restric
                     if (p.acc_dump) p.acc_dump[(size_t)r * p.N + c] = (int32_t)acc[i][j];
                     linear = __fmul_rn(__fmul_rn((float)acc[i][j], p.a_scales[r]), p.w_scales[c]);
                 }
-            } else linear = (float)acc[i][j];
+            } else {
+                linear = (float)acc[i][j];
+                if (p.acc_dump) {   /* fp32 partial sum */
+                    p.acc_dump[(size_t)r * p.N + c] = __float_as_int(linear);
+                    if (!p.out) continue;
+                }
+            }
             if (swiglu) { /* ungrouped scales only */
                 float up = MODE == MODE_W8A8 ? __fmul_rn(__fmul_rn((float)acc2[i][j], p.a_scales[r]), p.w_scales[p.N + c]) : (float)acc2[i][j];
                 if (p.ep.bias) { linear = __fadd_rn(linear, bf16_bits_to_f32(p.ep.bias[c])); up = __fadd_rn(up, bf16_bits_to_f32(p.ep.bias[p.N + c])); }

@@ -136,7 +136,8 @@ typedef struct {
     const uint16_t *residual; /* bf16 [M,N] or NULL                                        */
     uint32_t activation;      /* H3Q8_ACT_*                                                */
     uint16_t *output;         /* bf16 [M,N]                                                */
-    int32_t *accumulators;    /* optional int32 [M,N] dump (W8A8, per-channel scales)      */
+    int32_t *accumulators;    /* optional [M,N] dump: int32 sums (W8A8, per-channel scales)
+                                 or fp32 partial sums as bit patterns (bf16 operands)      */
     uint32_t kernel;          /* H3Q8_KERNEL_*                                             */
     uint32_t input_group;     /* W8A8: K elements per activation scale, input_scales is then
                                  [M, K/input_group] (the reference's per-1024 FC2 scales,
@@ -150,6 +151,13 @@ typedef struct {
 /* Bytes of workspace that let a rows x output_dim x input_dim problem use every SM (0 when split-K would not help). */
 size_t h3q8_linear_workspace_bytes(uint32_t mode, uint32_t rows, uint32_t input_dim, uint32_t output_dim);
 int h3q8_linear(const h3q8_linear_desc *desc, void *cuda_stream);
+/* Partial sums: a call with `accumulators` set and bf16 operands (BF16, or W8A16 on the one-CTA kernels) stores the raw
+ * fp32 accumulators [M,N] there (as bit patterns) before any epilogue term; `output` may then be NULL.  The caller adds
+ * partial sums of several K slices in fp32 (on one GPU, or with an all-reduce across GPUs: the tensor-parallel FFN) and
+ * h3q8_linear_finish applies bias / GELU-tanh / gate / residual and the single bf16 rounding (no counterpart in the
+ * reference, which is single-device: src/cuda/cuda_probe.c:31-40). */
+int h3q8_linear_finish(const float *sums, uint32_t rows, uint32_t output_dim, const uint16_t *bias, const uint16_t *gate,
+                       const uint16_t *residual, uint32_t activation, uint16_t *output, void *cuda_stream);
 
 /* Several independent problems in one call (video + audio streams of the DiT):
  * every problem is enqueued back to back on the stream with no host sync. */
@@ -367,6 +375,16 @@ int h3q8_gpu_tensor_download_async(h3_gpu_tensor *tensor, void *host, size_t byt
  * rows are the exception: they read the int8 weight once with main-loop dequantisation
  * and split-K (H3Q8_SKINNY_DIRECT=0 turns the exception off). */
 int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *gpu, uint32_t rows);
+/* A linear cut along K, or across GPUs (the tensor-parallel FFN): h3q8_gpu_linear_partial_f32 stores the fp32 partial
+ * sums [rows, output_dim] of one K slice (bf16 or W8A16 weights, no epilogue term); the caller adds the slices in fp32
+ * (an NCCL all-reduce across GPUs) and h3q8_gpu_linear_finish_bf16 applies bias / GELU-tanh / gate / residual and the
+ * single bf16 rounding, so that the result meets the same tolerance as the unsplit call.  No counterpart in the
+ * reference (single device). */
+int h3q8_gpu_linear_partial_f32(h3_gpu *gpu, h3_gpu_tensor *sums, const h3_gpu_tensor *input, const h3_gpu_tensor *weight,
+                                uint32_t rows, uint32_t input_dim, uint32_t output_dim);
+int h3q8_gpu_linear_finish_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *sums, const h3_gpu_tensor *bias,
+                                const h3_gpu_tensor *gate, const h3_gpu_tensor *residual, uint32_t rows, uint32_t output_dim,
+                                int activation);
 /* Per-kernel CUDA-event timing into h3_gpu_stats (on when H3_PROFILE is set). */
 int h3q8_gpu_set_profiling(h3_gpu *gpu, int enabled);
 /* Same descriptor built from int8 weights + scales already in host memory. */

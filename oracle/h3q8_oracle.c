@@ -20,6 +20,16 @@ int h3o_threads(void) {
 #endif
 }
 
+/* A launcher may have exported OMP_NUM_THREADS=1 (torch.distributed.run does); the timed CPU baseline asks for the
+ * cores it is allowed to run on instead. */
+void h3o_set_threads(int count) {
+#ifdef _OPENMP
+    if (count > 0) omp_set_num_threads(count);
+#else
+    (void)count;
+#endif
+}
+
 /* src/metal/shaders.metal:11-13 */
 float h3o_bf16_to_f32(uint16_t bits) {
     uint32_t word = (uint32_t)bits << 16;

@@ -103,6 +103,7 @@ void h3o_grouped_qkv_rope(const uint16_t *qkv, const uint16_t *q_weight, const u
                           uint32_t heads, uint32_t head_dim, uint32_t rope_half, float epsilon);
 
 int h3o_threads(void);
+void h3o_set_threads(int count);   /* OpenMP threads of the blocked (timed) path */
 #ifdef __cplusplus
 }
 #endif

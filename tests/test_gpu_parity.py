@@ -655,6 +655,47 @@ def test_grouped_launch_equals_separate_launches(gpu, oracle):
             tensor.free()
 
 
+@pytest.mark.parametrize("quant_mode", [0, 1])
+@pytest.mark.parametrize("rows,N,K", [(300, 520, 1024), (1000, 3072, 2048), (64, 264, 512)])
+def test_partial_sums_of_two_k_slices_meet_the_bar(oracle, quant_mode, rows, N, K):
+    """A linear cut along K the way the tensor-parallel FFN cuts FFN-down across GPUs: two half-K calls
+    store fp32 partial sums (h3q8_gpu_linear_partial_f32), the sums are added in fp32 (what an all-reduce
+    does) and h3q8_gpu_linear_finish_bf16 applies gate + residual with the single bf16 rounding.  The result
+    meets the same bar against the oracle as the unsplit fused call (rel-L2 <= 2e-3, <= 2 bf16 ulp)."""
+    x, wq, ws = operands(61, rows, N, K, 0)
+    bias, gate, res, act = epilogue_operands(61, rows, N, "bgr")
+    want = oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0, bias=bias, gate=gate, residual=res)
+    gpu = h.Gpu()
+    if quant_mode:
+        gpu.quant_configure(1)
+    half = K // 2
+    total = np.zeros(rows * N, np.float32)
+    for k0, k1 in ((0, half), (half, K)):
+        xs = np.ascontiguousarray(x[:, k0:k1])
+        w = (gpu.q8_from_host(np.ascontiguousarray(wq[:, k0:k1]), ws, 0) if quant_mode
+             else gpu.tensor_from_bf16(oracle.q8_dequant(np.ascontiguousarray(wq[:, k0:k1]), ws, 0)))
+        tx, sums = gpu.tensor_from_bf16(xs), gpu.tensor_from_f32(np.full(rows * N + GUARD, 7.0, np.float32))
+        gpu.begin()
+        gpu.linear_partial_f32(sums, tx, w, rows, k1 - k0, N)
+        gpu.submit()
+        got = sums.read()
+        assert (got[rows * N:] == 7.0).all(), "wrote past the end of the partial sums"
+        total += got[:rows * N]                       # fp32 addition, as NCCL's sum does
+        for t in (tx, w, sums):
+            t.free()
+    t_sum, out = gpu.tensor_from_f32(total), gpu.tensor_new_bf16(rows * N)
+    tb, tg, tr = (gpu.tensor_from_bf16(a) for a in (bias, gate, res))
+    gpu.begin()
+    gpu.linear_finish_bf16(out, t_sum, tb, tg, tr, rows, N, 0)
+    gpu.submit()
+    check_bf16(out.read().reshape(rows, N), want)
+    with pytest.raises(h.H3Error):
+        gpu.begin()
+        gpu.linear_partial_f32(out, tb, tg, rows, K, N)      # sums must be an fp32 tensor
+    gpu.cancel()
+    gpu.free()
+
+
 def test_fused_equals_unfused_chain(gpu):
     """linear -> gelu and linear -> gate as separate operators give the same bits
     as the fused projection (the fused epilogue rounds where the chain rounds)."""
