@@ -85,6 +85,29 @@ class WeightPlan(C.Structure):
         "resident_bytes", "slot_bytes")] + [("active_count", C.c_uint), ("resident_count", C.c_uint), ("effective_mode", C.c_int)]
 
 
+class DitPolicy(C.Structure):
+    """h3q8_dit_linear_policy"""
+    _fields_ = [(n, C.c_int) for n in ("int8_qkv", "int8_attention_out", "int8_mlp", "head_major_attention_out",
+                                       "fuse_int8_mlp_input", "fuse_int8_qkv_input", "int8_row_fc2")]
+
+
+class DitShape(C.Structure):
+    """h3q8_dit_shape"""
+    _fields_ = [(n, C.c_uint32) for n in ("rows", "hidden", "heads", "head_dim", "rope_half", "ffn", "slots")] + [("epsilon", C.c_float)]
+
+
+class DitWeights(C.Structure):
+    """h3q8_dit_block_weights"""
+    _fields_ = [(n, C.c_void_p) for n in ("qkv", "out", "fc1", "fc2", "qkv_int8", "qkv_scales", "out_int8", "out_scales", "fc1_int8",
+                                          "fc1_scales", "fc2_int8", "fc2_scales", "q_norm", "k_norm", "norm1", "norm2")]
+
+
+class DitBuffers(C.Structure):
+    """h3q8_dit_block_buffers"""
+    _fields_ = [(n, C.c_void_p) for n in ("hidden", "mod_attention", "qkv", "query", "key", "value", "attention_heads", "attention_output",
+                                          "mod_mlp", "mlp_output", "activated", "int8_activation", "int8_activation_scales")]
+
+
 class Problem(C.Structure):
     """h3_gpu_linear_problem"""
     _fields_ = [("output", C.c_void_p), ("input", C.c_void_p), ("weight", C.c_void_p), ("bias", C.c_void_p),
@@ -141,6 +164,16 @@ def library():
         "h3q8_gpu_get_profile": (C.c_int, [vp, C.POINTER(Profile)]),
         "h3_weight_packed_size": (C.c_int, [u32, u32, C.c_int, C.POINTER(u64), C.POINTER(u64), C.POINTER(u64)]),
         "h3q8_linear_finish": (C.c_int, [vp, u32, u32, vp, vp, vp, u32, vp, vp]),
+        "h3_gpu_adaln_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, u32, C.c_float]),
+        "h3_gpu_gate_adaln_bf16": (C.c_int, [vp] * 9 + [u32] * 6 + [C.c_float]),
+        "h3_gpu_mlp_bf16": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u32]),
+        "h3_quant_projection": (C.c_int, [C.c_char_p, C.c_int]),
+        "h3_quant_projection_policy": (C.c_int, [C.c_char_p, C.c_int, C.c_int]),
+        "h3q8_dit_linear_policy_resolve": (C.c_int, [vp, u32, C.c_int, C.POINTER(DitPolicy)]),
+        "h3q8_dit_block_attention_input": (C.c_int, [vp, C.POINTER(DitPolicy), C.POINTER(DitShape), C.POINTER(DitWeights),
+                                                     C.POINTER(DitBuffers), vp, vp, vp, vp, C.c_int, C.c_int]),
+        "h3q8_dit_block_after_attention": (C.c_int, [vp, C.POINTER(DitPolicy), C.POINTER(DitShape), C.POINTER(DitWeights), vp,
+                                                     C.POINTER(DitBuffers), vp, vp, vp, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)]),
         "h3q8_gpu_linear_partial_f32": (C.c_int, [vp, vp, vp, vp, u32, u32, u32]),
         "h3q8_gpu_linear_finish_bf16": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, C.c_int]),
         "h3_gpu_backend_name": (C.c_char_p, [vp]), "h3_gpu_has_int8_mlp": (C.c_int, [vp]),
@@ -528,6 +561,20 @@ class Gpu:
         return self._check(library().h3_gpu_grouped_qkv_linear_rope_bf16(
             self.handle, _h(query), _h(key), _h(value), _h(qkv), _h(input), _h(weight), _h(q_norm), _h(k_norm),
             _h(rope_cos), _h(rope_sin), rows, input_dim, heads, head_dim, rope_half, epsilon))
+
+    def adaln_bf16(self, output, input, norm_weight, modulation, row_map, rows, width, slots, shift_slot, scale_slot, epsilon):
+        return self._check(library().h3_gpu_adaln_bf16(self.handle, _h(output), _h(input), _h(norm_weight), _h(modulation), _h(row_map),
+                                                       rows, width, slots, shift_slot, scale_slot, epsilon))
+
+    def gate_adaln_bf16(self, gated_residual, output, residual, branch, norm_weight, gate_modulation, norm_modulation, row_map, rows,
+                        width, slots, gate_slot, shift_slot, scale_slot, epsilon):
+        return self._check(library().h3_gpu_gate_adaln_bf16(self.handle, _h(gated_residual), _h(output), _h(residual), _h(branch),
+                                                            _h(norm_weight), _h(gate_modulation), _h(norm_modulation), _h(row_map), rows,
+                                                            width, slots, gate_slot, shift_slot, scale_slot, epsilon))
+
+    def mlp_bf16(self, output, input, fc1, fc2, rows, input_dim, hidden_dim, output_dim):
+        return self._check(library().h3_gpu_mlp_bf16(self.handle, _h(output), _h(input), _h(fc1), _h(fc2), rows, input_dim, hidden_dim,
+                                                     output_dim))
 
     def swiglu_bf16(self, output, fused, rows, width):
         return self._check(library().h3_gpu_swiglu_bf16(self.handle, _h(output), _h(fused), rows, width))

@@ -43,7 +43,9 @@ def build(force=False, verbose=False):
     run(["gcc", "-O2", "-std=c11", "-fPIC", "-I", include, "-c", os.path.join(CSRC, "q8_cache.c"), "-o", cache_o])
     plan_o = os.path.join(build_dir, "weight_plan.o")
     run(["gcc", "-O2", "-std=c11", "-fPIC", "-D_GNU_SOURCE", "-I", include, "-c", os.path.join(CSRC, "weight_plan.c"), "-o", plan_o])
-    objects = [pack_o, cache_o, plan_o]
+    dit_o = os.path.join(build_dir, "dit_linear.o")
+    run(["gcc", "-O2", "-std=c11", "-fPIC", "-D_GNU_SOURCE", "-Wall", "-I", include, "-c", os.path.join(CSRC, "dit_linear.c"), "-o", dit_o])
+    objects = [pack_o, cache_o, plan_o, dit_o]
     for unit in ("h3q8_raw.cu", "h3_gpu.cu", "h3q8_static.cu", "h3q8_pair_grouped.cu"):
         obj = os.path.join(build_dir, unit.replace(".cu", ".o"))
         run([_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-I", include, "-I", CSRC, "-c",

@@ -1375,6 +1375,71 @@ extern "C" int h3_gpu_gate_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tens
     count_launch(1);
     return launch_status(g, "gate", 1);
 }
+/* RMS norm with the AdaLN modulation, the producer of every block linear's input (src/cuda/cuda_kernels.cuh:936-971,
+ * src/gpu.h:586-592): out = bf16(fma(x * rsqrt(mean(x^2) + eps) * weight, 1 + scale[class], shift[class])).  One
+ * 256-thread CTA per row; lane t sums columns t, t + 256, ... in order with fma and the lanes are combined by the
+ * reference's halving tree, so the mean has the reference's bits. */
+static __global__ void __launch_bounds__(256) adaln_rows_kernel(const uint16_t *__restrict__ input, const uint16_t *__restrict__ norm_weight,
+                                                               const uint16_t *__restrict__ modulation, const uint32_t *__restrict__ row_map,
+                                                               uint16_t *__restrict__ output, uint32_t width, uint32_t slots,
+                                                               uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    __shared__ float lanes[256];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const uint16_t *x = input + (size_t)row * width;
+    float sum = 0.0f;
+    for (uint32_t c = tid; c < width; c += 256) {
+        const float v = bf16_bits_to_f32(x[c]);
+        sum = fmaf(v, v, sum);
+    }
+    lanes[tid] = sum;
+    __syncthreads();
+    for (uint32_t stride = 128; stride; stride >>= 1) {
+        if (tid < stride) lanes[tid] = __fadd_rn(lanes[tid], lanes[tid + stride]);
+        __syncthreads();
+    }
+    const float inverse = rsqrtf(__fadd_rn(__fdiv_rn(lanes[0], (float)width), epsilon));
+    const size_t base = (size_t)(row_map ? row_map[row] : 0) * slots * width;
+    const uint16_t *shift = modulation + base + (size_t)shift_slot * width, *scale = modulation + base + (size_t)scale_slot * width;
+    for (uint32_t c = tid; c < width; c += 256) {
+        const float normalized = __fmul_rn(__fmul_rn(bf16_bits_to_f32(x[c]), inverse), bf16_bits_to_f32(norm_weight[c]));
+        output[(size_t)row * width + c] = (uint16_t)f32_to_bf16_bits(fmaf(normalized, __fadd_rn(1.0f, bf16_bits_to_f32(scale[c])), bf16_bits_to_f32(shift[c])));
+    }
+}
+extern "C" int h3_gpu_adaln_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *in, const h3_gpu_tensor *norm_weight,
+                                 const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
+                                 uint32_t slots, uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    if (!launch_ready(g)) return 0;
+    const size_t n = (size_t)rows * width;
+    if (!rows || !width || !slots || shift_slot >= slots || scale_slot >= slots) return set_error(g, "AdaLN: invalid arguments");
+    if (!require(g, in, H3_GPU_BF16, n, "AdaLN input") || !require(g, out, H3_GPU_BF16, n, "AdaLN output") ||
+        !require(g, norm_weight, H3_GPU_BF16, width, "AdaLN norm weight") ||
+        !require(g, modulation, H3_GPU_BF16, (size_t)slots * width, "AdaLN modulation") ||
+        (row_map && !require(g, row_map, H3_GPU_U32, rows, "AdaLN row map"))) return 0;
+    adaln_rows_kernel<<<rows, 256, 0, g->compute>>>((const uint16_t *)pointer(in), (const uint16_t *)pointer(norm_weight),
+                                                     (const uint16_t *)pointer(modulation), row_map ? (const uint32_t *)pointer(row_map) : nullptr,
+                                                     (uint16_t *)pointer(out), width, slots, shift_slot, scale_slot, epsilon);
+    count_launch(1);
+    return launch_status(g, "AdaLN", 1);
+}
+/* src/gpu.h:618-629; on CUDA the reference composes the two operators (src/cuda/gpu_cuda.cu:1118-1120) and so does this. */
+extern "C" int h3_gpu_gate_adaln_bf16(h3_gpu *g, h3_gpu_tensor *gated_residual, h3_gpu_tensor *out, const h3_gpu_tensor *residual,
+                                      const h3_gpu_tensor *branch, const h3_gpu_tensor *norm_weight, const h3_gpu_tensor *gate_modulation,
+                                      const h3_gpu_tensor *norm_modulation, const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
+                                      uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon) {
+    return h3_gpu_gate_bf16(g, gated_residual, residual, branch, gate_modulation, row_map, rows, width, slots, gate_slot) &&
+           h3_gpu_adaln_bf16(g, out, gated_residual, norm_weight, norm_modulation, row_map, rows, width, slots, shift_slot, scale_slot, epsilon);
+}
+/* src/gpu.h:506-511: fc1 over the [gate | up] weight with SwiGLU in its epilogue, then fc2 (weights: bf16 or q8 descriptors). */
+extern "C" int h3_gpu_mlp_bf16(h3_gpu *g, h3_gpu_tensor *out, const h3_gpu_tensor *in, const h3_gpu_tensor *fc1, const h3_gpu_tensor *fc2,
+                               uint32_t rows, uint32_t input_dim, uint32_t hidden_dim, uint32_t output_dim) {
+    if (!launch_ready(g)) return 0;
+    h3_gpu_tensor *activated = h3_gpu_tensor_new_bf16(g, (size_t)rows * hidden_dim);
+    if (!activated) return 0;
+    const int ok = linear_dispatch(g, activated, in, fc1, nullptr, nullptr, nullptr, rows, input_dim, hidden_dim, H3Q8_ACT_SWIGLU) &&
+                   linear_dispatch(g, out, activated, fc2, nullptr, nullptr, nullptr, rows, hidden_dim, output_dim, H3Q8_ACT_NONE);
+    h3_gpu_tensor_free(activated);   /* legal with work in flight: the release waits for it */
+    return ok;
+}
 /* src/cuda/cuda_kernels.cuh:988-1045 with grouped = 1: one thread per (row, head, dimension);
  * every thread accumulates the head's squares in dimension order like the reference. */
 static __global__ void __launch_bounds__(128) grouped_qkv_rope_kernel(const uint16_t *__restrict__ qkv, const uint16_t *__restrict__ q_weight,

@@ -465,6 +465,17 @@ int h3_gpu_grouped_qkv_linear_rope_int8(h3_gpu *gpu, h3_gpu_tensor *query, h3_gp
                                         uint32_t rows, uint32_t input_dim, uint32_t heads, uint32_t head_dim, uint32_t rope_half,
                                         float epsilon, int input_is_quantized, int use_slower_unfused_qkv_rope,
                                         int use_slower_scalar_qkv_rms, int use_slower_uncached_int8_scales);
+/* The bf16 side of the block (src/gpu.h:506-511, 586-592, 618-629): RMS norm + AdaLN modulation producing a linear's
+ * input, the same after gate * branch + residual, and the MLP with bf16 or q8-descriptor weights (fc1 + SwiGLU fused). */
+int h3_gpu_adaln_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input, const h3_gpu_tensor *norm_weight,
+                      const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
+                      uint32_t slots, uint32_t shift_slot, uint32_t scale_slot, float epsilon);
+int h3_gpu_gate_adaln_bf16(h3_gpu *gpu, h3_gpu_tensor *gated_residual, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
+                           const h3_gpu_tensor *branch, const h3_gpu_tensor *norm_weight, const h3_gpu_tensor *gate_modulation,
+                           const h3_gpu_tensor *norm_modulation, const h3_gpu_tensor *row_map, uint32_t rows, uint32_t width,
+                           uint32_t slots, uint32_t gate_slot, uint32_t shift_slot, uint32_t scale_slot, float epsilon);
+int h3_gpu_mlp_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input, const h3_gpu_tensor *fc1_weight,
+                    const h3_gpu_tensor *fc2_weight, uint32_t rows, uint32_t input_dim, uint32_t hidden_dim, uint32_t output_dim);
 /* Unfused epilogue operators kept for comparison -- src/gpu.h:575-577, 612-617, 750-752 */
 int h3_gpu_gelu_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *input, uint32_t elements, int approximate);
 int h3_gpu_gate_bf16(h3_gpu *gpu, h3_gpu_tensor *output, const h3_gpu_tensor *residual,
@@ -505,6 +516,50 @@ typedef struct {
     int activation;
 } h3_gpu_linear_problem;
 int h3_gpu_linear_grouped_bf16(h3_gpu *gpu, const h3_gpu_linear_problem *problems, uint32_t count);
+
+/* ---------------------------------------------------------------------
+ * The linear dispatch of one DiT block (src/denoise/dit.c:2286-2537 and the flags of :1956-1990), as C above the
+ * operators: which family runs each projection, and the "input already quantised" state handed from the tail of one
+ * block to the QKV projection of the next.  Attention sits between the two calls and stays with the caller.
+ * --------------------------------------------------------------------- */
+/* src/weights/quant.c:22-40: `requested` for the four projection matrices of a block, 0 for anything else; with the
+ * adaptive cache block 0 stays unquantised. */
+int h3_quant_projection(const char *name, int requested);
+int h3_quant_projection_policy(const char *name, int requested, int adaptive_cache);
+typedef struct {
+    int int8_qkv, int8_attention_out, int8_mlp;  /* run that projection on the W8A8 operator family                    */
+    int head_major_attention_out;                /* the attention output arrives as [head, row, dimension]             */
+    int fuse_int8_mlp_input, fuse_int8_qkv_input;/* gate + AdaLN + quantise in one pass in front of that projection    */
+    int int8_row_fc2;                            /* per-row instead of per-1024 re-quantisation in front of fc2        */
+} h3q8_dit_linear_policy;
+typedef struct { uint32_t rows, hidden, heads, head_dim, rope_half, ffn, slots; float epsilon; } h3q8_dit_shape;
+typedef struct {
+    const h3_gpu_tensor *qkv, *out, *fc1, *fc2;              /* bf16 tensors or quantised descriptors (may be NULL when   */
+    const h3_gpu_tensor *qkv_int8, *qkv_scales;              /* the int8 pair of the projection is given, and vice versa) */
+    const h3_gpu_tensor *out_int8, *out_scales;
+    const h3_gpu_tensor *fc1_int8, *fc1_scales, *fc2_int8, *fc2_scales;
+    const h3_gpu_tensor *q_norm, *k_norm, *norm1, *norm2;
+} h3q8_dit_block_weights;
+typedef struct {                                              /* the block loop's activations, owned by the caller         */
+    h3_gpu_tensor *hidden, *mod_attention, *qkv, *query, *key, *value;
+    h3_gpu_tensor *attention_heads, *attention_output, *mod_mlp, *mlp_output, *activated;
+    h3_gpu_tensor *int8_activation, *int8_activation_scales;
+} h3q8_dit_block_buffers;
+/* Flags as src/denoise/dit.c:1956-1990 resolves them: the backend's int8 operators, resident (not streamed) weights,
+ * rows >= 128 for the attention-side projections, and the H3_DISABLE_* environment switches dit.c reads. */
+int h3q8_dit_linear_policy_resolve(const h3_gpu *gpu, uint32_t rows, int streaming, h3q8_dit_linear_policy *policy);
+/* (attention AdaLN unless the previous tail did it) -> QKV projection + per-head norm + RoPE into query / key / value. */
+int h3q8_dit_block_attention_input(h3_gpu *gpu, const h3q8_dit_linear_policy *policy, const h3q8_dit_shape *shape,
+                                   const h3q8_dit_block_weights *weights, const h3q8_dit_block_buffers *buffers,
+                                   const h3_gpu_tensor *modulation, const h3_gpu_tensor *row_map, const h3_gpu_tensor *rope_cos,
+                                   const h3_gpu_tensor *rope_sin, int attention_adaln_ready, int attention_input_quantized);
+/* attention output projection -> gate + MLP AdaLN (+ quantise) -> MLP -> MLP gate, fused with the next block's
+ * attention AdaLN (+ quantise) when fuse_next_attention; the two out-flags are the next call's in-flags. */
+int h3q8_dit_block_after_attention(h3_gpu *gpu, const h3q8_dit_linear_policy *policy, const h3q8_dit_shape *shape,
+                                   const h3q8_dit_block_weights *weights, const h3_gpu_tensor *next_norm1,
+                                   const h3q8_dit_block_buffers *buffers, const h3_gpu_tensor *modulation,
+                                   const h3_gpu_tensor *next_modulation, const h3_gpu_tensor *row_map, int fuse_next_attention,
+                                   int *next_attention_adaln_ready, int *next_attention_input_quantized);
 
 #ifdef __cplusplus
 }
