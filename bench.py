@@ -884,11 +884,15 @@ def run_grouped_streams(args, gpu, lib, stream, device_bf16):
 
 
 def run_real_block_int8(args, gpu, lib, stream, device_bf16):
-    """The real model's block (hidden 5376, 56 heads of 128, FFN 14336, SwiGLU) on the int8 operator family with the
-    reference's own entry points, chained as run_block() chains them; attention itself is outside this path, so its
-    output is a resident synthetic tensor in SDPA's [head, row, dimension] layout."""
+    """The real model's block (hidden 5376, 56 heads of 128, FFN 14336, SwiGLU) on the int8 operator family, issued by
+    the C dispatcher (h3q8_dit_block_attention_input / _after_attention, the job of run_block()) with the policy the
+    reference resolves on a backend with int8 operators: int8 QKV + norm + RoPE, head-major int8 attention output,
+    gate + AdaLN + quantise in front of the MLP and in front of the next block's QKV.  Attention itself is outside this
+    path, so its output is a resident synthetic tensor in SDPA's [head, row, dimension] layout."""
+    import ctypes
     import torch
-    rows, hidden, heads, dim, half, ffn = args.rows, 5376, 56, 128, 48, 14336
+    from h3cli_b200 import api
+    rows, hidden, heads, dim, half, ffn, slots = args.rows, 5376, 56, 128, 48, 14336, 6
     padded = (rows + 127) // 128 * 128
     wgen = np.random.default_rng(42)
 
@@ -900,51 +904,65 @@ def run_real_block_int8(args, gpu, lib, stream, device_bf16):
     w_out, s_out = weight(hidden, heads * dim, 0.01)
     w_fc1, s_fc1 = weight(2 * ffn, hidden, 0.002)
     w_fc2, s_fc2 = weight(hidden, ffn, 0.01)
-    x, attention = device_bf16(rows, hidden, seed=1), device_bf16(rows, heads * dim, seed=2)
-    branch = gpu.tensor_new_bf16(rows * hidden)
-    q, k, v = (gpu.tensor_new_bf16(rows * heads * dim) for _ in range(3))
     qn, kn = device_bf16(1, dim, 1.0, 0.1, seed=5), device_bf16(1, dim, 1.0, 0.1, seed=6)
+    norm1, norm2 = device_bf16(1, hidden, 1.0, 0.1, seed=9), device_bf16(1, hidden, 1.0, 0.1, seed=11)
+    modulation = device_bf16(1, slots * hidden, 0.0, 0.1, seed=10)
     cos, sin = device_bf16(rows, half, 0.0, 0.7, seed=7), device_bf16(rows, half, 0.0, 0.7, seed=8)
-    norm_w, modulation = device_bf16(1, hidden, 1.0, 0.1, seed=9), device_bf16(1, 6 * hidden, 0.0, 0.1, seed=10)
-    q_in, in_scales = gpu.tensor_new_i8(padded * max(hidden, heads * dim)), gpu.tensor_new_f32(padded)
-    q_act, act_scales = gpu.tensor_new_i8(padded * ffn), gpu.tensor_new_f32(padded * (ffn // 1024))
-    activated, mlp_out = gpu.tensor_new_bf16(rows * ffn), gpu.tensor_new_bf16(rows * hidden)
-
-    marks = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+    buffers = dict(hidden=device_bf16(rows, hidden, seed=1), mod_attention=gpu.tensor_new_bf16(rows * hidden), qkv=None,
+                   query=gpu.tensor_new_bf16(rows * heads * dim), key=gpu.tensor_new_bf16(rows * heads * dim),
+                   value=gpu.tensor_new_bf16(rows * heads * dim), attention_heads=device_bf16(rows, heads * dim, seed=2),
+                   attention_output=gpu.tensor_new_bf16(rows * hidden), mod_mlp=gpu.tensor_new_bf16(rows * hidden),
+                   mlp_output=gpu.tensor_new_bf16(rows * hidden), activated=gpu.tensor_new_bf16(rows * ffn),
+                   int8_activation=gpu.tensor_new_i8(padded * ffn), int8_activation_scales=gpu.tensor_new_f32(padded * (ffn // 1024)))
+    c_buffers = api.DitBuffers(**{name: t.handle if t else None for name, t in buffers.items()})
+    c_weights = api.DitWeights(qkv_int8=w_qkv.handle, qkv_scales=s_qkv.handle, out_int8=w_out.handle, out_scales=s_out.handle,
+                               fc1_int8=w_fc1.handle, fc1_scales=s_fc1.handle, fc2_int8=w_fc2.handle, fc2_scales=s_fc2.handle,
+                               q_norm=qn.handle, k_norm=kn.handle, norm1=norm1.handle, norm2=norm2.handle)
+    shape = api.DitShape(rows, hidden, heads, dim, half, ffn, slots, 1e-6)
+    policy = api.DitPolicy()
+    assert lib.h3q8_dit_linear_policy_resolve(gpu.handle, rows, 0, ctypes.byref(policy))
+    ready, quantized = ctypes.c_int(0), ctypes.c_int(0)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
 
     def block(timed=False):
+        """One block; its tail is fused with the next block's attention AdaLN + quantiser (same weights stand in)."""
         mark = (lambda i: marks[i].record(stream)) if timed else (lambda i: None)
         mark(0)
-        gpu.grouped_qkv_linear_rope_int8(q, k, v, q_in, in_scales, x, w_qkv, s_qkv, qn, kn, cos, sin, rows, hidden, heads, dim, half, 1e-6)
+        if not lib.h3q8_dit_block_attention_input(gpu.handle, ctypes.byref(policy), ctypes.byref(shape), ctypes.byref(c_weights),
+                                                  ctypes.byref(c_buffers), modulation.handle, None, cos.handle, sin.handle, ready.value,
+                                                  quantized.value):
+            raise RuntimeError(gpu.error())
         mark(1)
-        gpu.linear_int8_head_major_bf16(branch, q_in, in_scales, attention, w_out, s_out, rows, heads, dim, hidden)
+        if not lib.h3q8_dit_block_after_attention(gpu.handle, ctypes.byref(policy), ctypes.byref(shape), ctypes.byref(c_weights), norm1.handle,
+                                                  ctypes.byref(c_buffers), modulation.handle, modulation.handle, None, 1, ctypes.byref(ready),
+                                                  ctypes.byref(quantized)):
+            raise RuntimeError(gpu.error())
         mark(2)
-        # x <- x + branch * gate; RMS norm + AdaLN; per-row int8 of the MLP input, all in one pass
-        gpu.gate_adaln_quantize_int8(x, q_act, act_scales, x, branch, norm_w, modulation, modulation, None, rows, padded, hidden, 6, 0, 1, 2, 1e-6)
-        mark(3)
-        gpu.mlp_int8_bf16(mlp_out, activated, q_act, act_scales, None, w_fc1, s_fc1, w_fc2, s_fc2, rows, hidden, ffn, hidden,
-                          input_is_quantized=1)
-        mark(4)
         gpu.continue_()
 
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    before = lib.h3q8_kernel_launches()
     gpu.begin()
+    block()                                                   # the first block still runs the attention AdaLN itself
+    before = lib.h3q8_kernel_launches()
     for i in range(args.warmup + args.steps):
         if i == args.warmup:
             start.record(stream)
         block()
     stop.record(stream)
+    launches = lib.h3q8_kernel_launches() - before
     block(timed=True)
     gpu.submit()
     ms = start.elapsed_time(stop) / args.steps
-    parts = [marks[i].elapsed_time(marks[i + 1]) for i in range(4)]
+    parts = [marks[i].elapsed_time(marks[i + 1]) for i in range(2)]
     ops = 2.0 * rows * (hidden * 3 * heads * dim + heads * dim * hidden + hidden * 2 * ffn + ffn * hidden)
     print(json.dumps({"case": "real_block_int8", "rows": rows, "hidden": hidden, "heads": heads, "ffn": ffn, "ms_per_block": ms,
-                      "tops": ops / ms / 1e9, "kernels_per_block": int((lib.h3q8_kernel_launches() - before) // (args.warmup + args.steps + 1)),
-                      "ms_per_call": dict(zip(["qkv_rope", "attn_out_head_major", "gate_adaln_quantize", "mlp"], parts)),
-                      "calls": ["h3_gpu_grouped_qkv_linear_rope_int8", "h3_gpu_linear_int8_head_major_bf16",
-                                "h3_gpu_gate_adaln_quantize_int8", "h3_gpu_mlp_int8_bf16"]}), flush=True)
+                      "tops": ops / ms / 1e9, "kernels_per_block": int(launches // (args.warmup + args.steps)),
+                      "policy": {name: int(getattr(policy, name)) for name, _ in api.DitPolicy._fields_},
+                      "next_block_flags": {"attention_adaln_ready": ready.value, "attention_input_quantized": quantized.value},
+                      "ms_per_call": dict(zip(["h3q8_dit_block_attention_input", "h3q8_dit_block_after_attention"], parts)),
+                      "operators": ["h3_gpu_grouped_qkv_linear_rope_int8 (pre-quantised input)", "h3_gpu_linear_int8_head_major_bf16",
+                                    "h3_gpu_gate_adaln_quantize_int8", "h3_gpu_mlp_int8_bf16",
+                                    "h3_gpu_gate_adaln_quantize_int8 (MLP gate + next attention AdaLN)"]}), flush=True)
     gpu.free()
 
 

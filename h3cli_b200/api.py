@@ -140,6 +140,8 @@ def library():
         "h3_weight_plan_build": (C.c_int, [C.POINTER(WeightPlan), WeightOptions, u64, u64, u64, u64, u64, u64, C.c_char_p, sz]),
         "h3_weight_retry_cap": (C.c_int, [C.c_uint]),
         "h3q8_cache_open": (vp, [C.c_char_p, C.c_char_p, u64, u32, u32, u32, C.c_char_p, sz]),
+        "h3q8_cache_open_content": (vp, [C.c_char_p, C.c_char_p, u64, u32, u32, u32, C.c_char_p, sz]),
+        "h3q8_sha256": (None, [vp, sz, vp]),
         "h3q8_cache_read": (C.c_int, [vp, vp, C.c_char_p, sz]),
         "h3q8_cache_write": (C.c_int, [vp, vp, C.c_char_p, sz]),
         "h3q8_cache_unchanged": (C.c_int, [vp, C.c_char_p, sz]),

@@ -826,7 +826,11 @@ extern "C" h3_gpu_tensor *h3_gpu_quant_load(h3_gpu *g, const char *path, uint64_
     }
     /* src/cuda/cuda_quant.cuh:292-333: artifact hit -> upload the packed bytes; miss -> pack on the
      * device, read the blob back, publish it; the source is re-checked before either is accepted */
-    h3q8_cache *entry = h3q8_cache_open(g->quant_cache.c_str(), path, offset, rows, columns, g->group, g->error, sizeof g->error);
+    /* H3_QUANT_VERIFY=1 selects the content-keyed, payload-verified kind (src/weights/quant.c:10-13) */
+    const char *verify = getenv("H3_QUANT_VERIFY");
+    h3q8_cache *entry = verify && !strcmp(verify, "1")
+        ? h3q8_cache_open_content(g->quant_cache.c_str(), path, offset, rows, columns, g->group, g->error, sizeof g->error)
+        : h3q8_cache_open(g->quant_cache.c_str(), path, offset, rows, columns, g->group, g->error, sizeof g->error);
     if (!entry) return nullptr;
     const size_t bytes = h3q8_cache_payload_bytes(entry);
     std::vector<unsigned char> payload;

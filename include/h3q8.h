@@ -65,14 +65,21 @@ int h3_weight_retry_cap(unsigned count);
  * mode 2 = W8A8 with per-channel scales; 0 for anything else or a blob beyond 32-bit indexing. */
 int h3_weight_packed_size(uint32_t rows, uint32_t columns, int mode, uint64_t *scale, uint64_t *global, uint64_t *bytes);
 
-/* On-disk cache of packed q8 weights (host only), after src/weights/quant_cache.h:14-41:
- * artifacts are keyed by source path + file identity + offset + shape + group + recipe
- * (no weight bytes are hashed), writers hold a per-artifact flock from open to close,
- * publishing is tmp + fsync + rename, a malformed artifact is an error and never a miss.
- * read: 1 hit, 0 absent, -1 invalid; payload buffers have h3q8_cache_payload_bytes(). */
+/* On-disk cache of packed q8 weights (host only), with the guarantees of src/weights/quant_cache.h:14-41 and of the
+ * strict mode of src/cuda/cuda_quant.cuh:186-256.  Two kinds of key, both SHA-256:
+ *   h3q8_cache_open          source path + file identity and timestamps + offset + shape + group + recipe
+ *                            (no weight byte is read to open a hit);
+ *   h3q8_cache_open_content  the source matrix bytes + shape + group + recipe (the same weights under any path are
+ *                            the same artifact; the artifact also carries a SHA-256 of its payload, verified by every
+ *                            read).  h3_gpu_quant_load takes this kind when H3_QUANT_VERIFY=1 (src/weights/quant.c:10-13).
+ * Writers hold a per-artifact flock from open to close, publishing is tmp + fsync + rename, a malformed artifact is
+ * an error and never a miss.  read: 1 hit, 0 absent, -1 invalid; payload buffers have h3q8_cache_payload_bytes(). */
 typedef struct h3q8_cache h3q8_cache;
 h3q8_cache *h3q8_cache_open(const char *directory, const char *source, uint64_t offset, uint32_t rows, uint32_t columns,
                             uint32_t group, char *error, size_t size);
+h3q8_cache *h3q8_cache_open_content(const char *directory, const char *source, uint64_t offset, uint32_t rows, uint32_t columns,
+                                    uint32_t group, char *error, size_t size);
+void h3q8_sha256(const void *data, size_t bytes, unsigned char digest[32]);   /* FIPS 180-4, the digest of both key kinds */
 int h3q8_cache_read(h3q8_cache *cache, void *payload, char *error, size_t size);
 int h3q8_cache_write(h3q8_cache *cache, const void *payload, char *error, size_t size);
 int h3q8_cache_unchanged(const h3q8_cache *cache, char *error, size_t size);

@@ -132,3 +132,79 @@ def test_concurrent_preparers_publish_once(lib, tmp_path):
         results = pool.map(_writer, [(str(cache), str(source), i) for i in range(8)])
     assert sorted(results) == [0] + [1] * 7, results       # one preparation, seven hits, no torn reads
     assert len([f for f in os.listdir(cache) if f.endswith(".h3q8")]) == 1
+
+
+def test_sha256_known_answers(lib):
+    """FIPS 180-4 vectors and agreement with hashlib across block boundaries."""
+    import hashlib
+    out = ctypes.create_string_buffer(32)
+    for message in (b"", b"abc", b"abcdbcdecdefdefgefghfghighijhijkijkljklmklmnlmnomnopnopq", b"a" * 55, b"a" * 56, b"a" * 63, b"a" * 64,
+                    b"a" * 65, b"a" * 119, b"a" * 120, bytes(range(256)) * 1000):
+        lib.h3q8_sha256(message, len(message), out)
+        assert out.raw == hashlib.sha256(message).digest(), len(message)
+    lib.h3q8_sha256(b"abc", 3, out)
+    assert out.raw.hex() == "ba7816bf8f01cfea414140de5dae2223b00361a396177a9cb410ff61f20015ad"
+
+
+def test_two_sources_never_validate_each_others_artifact(lib, tmp_path):
+    """Different files of the same shape (paths that differ in one character, equal sizes) get different keys, and an
+    artifact copied under the other key's name is refused because the key is also inside the header."""
+    cache = tmp_path / "cache"
+    cache.mkdir()
+    a, b = make_source(tmp_path / "weights-a.bin", seed=1), make_source(tmp_path / "weights-b.bin", seed=2)
+    error = ctypes.create_string_buffer(512)
+    entry_a, _ = open_entry(lib, cache, a)
+    entry_b, _ = open_entry(lib, cache, b)
+    path_a, path_b = lib.h3q8_cache_artifact(entry_a).decode(), lib.h3q8_cache_artifact(entry_b).decode()
+    assert path_a != path_b
+    size = lib.h3q8_cache_payload_bytes(entry_a)
+    payload, back = np.full(size, 3, np.uint8), np.zeros(size, np.uint8)
+    assert lib.h3q8_cache_write(entry_a, payload.ctypes.data, error, len(error))
+    open(path_b, "wb").write(open(path_a, "rb").read())                 # a's artifact under b's name
+    assert lib.h3q8_cache_read(entry_b, back.ctypes.data, error, len(error)) == -1 and b"corrupt or incompatible" in error.value
+    lib.h3q8_cache_close(entry_a)
+    lib.h3q8_cache_close(entry_b)
+
+
+def test_content_keyed_artifacts(lib, tmp_path):
+    """The strict kind (src/cuda/cuda_quant.cuh:186-256): keyed by the matrix bytes, so the same weights under another
+    path or at another offset are the same artifact, different weights are another one, and a flipped payload bit is
+    caught by the payload digest."""
+    cache = tmp_path / "cache"
+    cache.mkdir()
+    source = make_source(tmp_path / "weights.bin", matrices=2, seed=5)
+    matrix = ROWS * COLS * 2
+    data = source.read_bytes()
+    copy = tmp_path / "elsewhere.bin"
+    copy.write_bytes(b"\0" * 64 + data[:matrix])                       # same first matrix at offset 64 of another file
+
+    def open_content(path, offset):
+        error = ctypes.create_string_buffer(512)
+        entry = lib.h3q8_cache_open_content(str(cache).encode(), str(path).encode(), offset, ROWS, COLS, GROUP, error, len(error))
+        assert entry, error.value
+        return entry
+
+    # an open entry holds its artifact's lock, so entries of the SAME artifact are opened one after the other
+    first, other = open_content(source, 0), open_content(source, matrix)
+    name = lambda e: lib.h3q8_cache_artifact(e).decode()
+    first_name = name(first)
+    assert first_name != name(other) and "content" in first_name
+    error = ctypes.create_string_buffer(512)
+    size = lib.h3q8_cache_payload_bytes(first)
+    payload, back = np.random.default_rng(9).integers(0, 255, size, dtype=np.uint8), np.zeros(size, np.uint8)
+    assert lib.h3q8_cache_read(first, back.ctypes.data, error, len(error)) == 0
+    assert lib.h3q8_cache_write(first, payload.ctypes.data, error, len(error))
+    lib.h3q8_cache_close(first)
+    same = open_content(copy, 64)
+    assert name(same) == first_name
+    assert lib.h3q8_cache_read(same, back.ctypes.data, error, len(error)) == 1 and (back == payload).all()
+    assert lib.h3q8_cache_read(other, back.ctypes.data, error, len(error)) == 0
+    good = open(name(same), "rb").read()
+    flipped = bytearray(good)
+    flipped[128 + size // 2] ^= 1                                           # one payload bit
+    open(name(same), "wb").write(bytes(flipped))
+    assert lib.h3q8_cache_read(same, back.ctypes.data, error, len(error)) == -1 and b"corrupt" in error.value
+    open(name(same), "wb").write(good)
+    assert lib.h3q8_cache_read(same, back.ctypes.data, error, len(error)) == 1
+    lib.h3q8_cache_close(same)
+    lib.h3q8_cache_close(other)
