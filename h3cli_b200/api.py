@@ -159,6 +159,7 @@ def library():
         "h3q8_device_status": (u32, [vp]),
         "h3q8_last_error": (C.c_char_p, []),
         "h3q8_kernel_launches": (u64, []),
+        "h3q8_fault_injection": (None, [u64, u32]),
         "h3_gpu_create": (vp, [C.c_char_p, C.c_char_p, sz]),
         "h3_gpu_free": (None, [vp]), "h3_gpu_cancel": (None, [vp]),
         "h3_gpu_error": (C.c_char_p, [vp]),

@@ -52,6 +52,10 @@ struct GemmParams {
      * 32-bit accumulators at partials[(split * M + row) * N + col]; splitk_finish_kernel sums them and runs the epilogue */
     uint32_t splits, kb_per_split;
     uint32_t *partials;
+    /* failure-path testing, set from the host (h3q8_fault_injection): a shorter limit for every bounded wait, and a
+     * producer that leaves out the very first operand load, so that a wait runs out and the error path is exercised */
+    long long wait_limit;
+    uint32_t skip_first_load;
 };
 
 template <int MODE, int BN, int MT, bool GROUPED>
@@ -91,15 +95,22 @@ struct PipeState {
     }
 };
 
+/* Shared-memory control block behind the barriers of every kernel here: [0] TMEM base, [1] abort flag, [2..3] the
+ * wait limit in clocks (GemmParams::wait_limit, else WAIT_LIMIT_CYCLES), written once by thread 0. */
+__device__ __forceinline__ void control_block_init(uint32_t *tmem_slot, long long wait_limit) {
+    tmem_slot[1] = 0;
+    *reinterpret_cast<volatile long long *>(tmem_slot + 2) = wait_limit > 0 ? wait_limit : WAIT_LIMIT_CYCLES;
+}
+/* Bounded wait of a pipeline role.  False: this wait ran out, or another role of the CTA already gave up. */
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile uint32_t *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    long long start = clock64();
+    const long long start = clock64(), limit = *reinterpret_cast<const volatile long long *>(abort_flag + 1);
     for (;;) {
 #pragma unroll 1
         for (int spin = 0; spin < 128; spin++)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - start > WAIT_LIMIT_CYCLES) return false;
+        if (clock64() - start > limit) return false;
     }
 }
 
@@ -162,7 +173,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], C::DEQUANT_WARPS / 2); mbar_init(&bempty[s], 1); }
         for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], C::EPILOGUE_WARPS); }
-        *abort_flag = 0;
+        control_block_init(tmem_slot, p.wait_limit);
         fence_barrier_init();
         fence_proxy_async_smem();
     }
@@ -187,6 +198,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (uint32_t kb = kb_first; kb < kb_last; kb++) {
                     if (!wait_or_abort(&empty[st.index], st.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
                     uint8_t *stage = stages + st.index * C::STAGE_BYTES;
+                    if (p.skip_first_load && item == blockIdx.x && kb == kb_first) { st.advance(C::STAGES); continue; }   /* injected fault */
                     mbar_arrive_expect_tx(&full[st.index], C::STAGE_BYTES);
 #pragma unroll
                     for (int mt = 0; mt < MT; mt++)

@@ -91,7 +91,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 2 * C::EPILOGUE_WARPS); }
-        *abort_flag = 0;
+        control_block_init(tmem_slot, args.p[0].wait_limit);
         fence_barrier_init();
         fence_proxy_async_smem();
     }
@@ -118,6 +118,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
                 for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!wait_or_abort(&empty[st.index], st.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
                     uint8_t *stage = stages + st.index * C::STAGE_BYTES;
+                    if (p.skip_first_load && tile == pair && kb == 0) { st.advance(C::STAGES); continue; }   /* injected fault */
                     /* the leader arms its barrier for the bytes of both CTAs */
                     if (rank == 0) mbar_arrive_expect_tx(&full[st.index], 2 * C::STAGE_BYTES);
                     const uint32_t leader_full = map_to_cta(smem_u32(&full[st.index]), 0);

@@ -71,7 +71,7 @@ gemm_tcgen05_pair_grouped_kernel(const __grid_constant__ PairArgs args) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 2 * C::EPILOGUE_WARPS); }
-        *abort_flag = 0;
+        control_block_init(tmem_slot, args.p[0].wait_limit);
         fence_barrier_init();
         fence_proxy_async_smem();
     }

@@ -124,7 +124,7 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
         for (int s = 0; s < C::RAW_STAGES; s++) { mbar_init(&rfull[s], 1); mbar_init(&rempty[s], C::GROUP_WARPS); }
         for (int s = 0; s < C::CONV_BUFFERS; s++) { mbar_init(&bfull[s], 2 * C::GROUP_WARPS); mbar_init(&bempty[s], 1); }
         for (int s = 0; s < C::ACC_BUFFERS; s++) { mbar_init(&tfull[s], 1); mbar_init(&tempty[s], 2 * C::EPILOGUE_WARPS); }
-        *abort_flag = 0;
+        control_block_init(tmem_slot, p.wait_limit);
         fence_barrier_init();
         fence_proxy_async_smem();
     }

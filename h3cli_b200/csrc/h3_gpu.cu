@@ -348,7 +348,7 @@ static int drain(h3_gpu *g) {
     if (flags[0] || flags[1] || shared_status) {
         cudaMemset(g->flags, 0, sizeof flags);
         g->deferred_error = true;
-        if (flags[1]) return set_error(g, "non-finite activation reached the int8 quantiser");
+        if (flags[1] || (!flags[0] && (shared_status & 0x80000000u))) return set_error(g, "non-finite activation reached the int8 quantiser");
         uint32_t code = flags[0] ? flags[0] : shared_status;
         return set_error(g, "a linear kernel gave up a bounded wait (code %u, CTA %u)", code & 0xffu, code >> 8);
     }
@@ -588,7 +588,12 @@ static int file_into(h3_gpu_tensor *t, size_t dst_offset, const char *path, uint
             }
             g->stats.pinned_bytes += BOUNCE_BYTES;
         }
-        if (g->bounce_used[slot]) cudaEventSynchronize(g->bounce_free[slot]);
+        if (g->bounce_used[slot]) {   /* only time spent waiting for a busy staging buffer is a stream wait (src/cuda/gpu_cuda.cu:823-827) */
+            const double waiting = now_seconds();
+            if (cudaEventQuery(g->bounce_free[slot]) == cudaErrorNotReady) g->stats.stream_stalls++;
+            cudaEventSynchronize(g->bounce_free[slot]);
+            g->stats.stream_wait_seconds += now_seconds() - waiting;
+        }
         size_t chunk = bytes - done < BOUNCE_BYTES ? bytes - done : BOUNCE_BYTES, got = 0;
         while (got < chunk) {
             ssize_t r = pread(fd, (char *)g->bounce[slot] + got, chunk - got, (off_t)(file_offset + done + got));
@@ -612,7 +617,7 @@ static int file_into(h3_gpu_tensor *t, size_t dst_offset, const char *path, uint
         t->ready_recorded = true;
         g->stats.h2d_bytes += bytes;
         g->stats.streamed_bytes += bytes;
-        g->stats.stream_wait_seconds += now_seconds() - start;
+        g->stats.transfer_seconds += now_seconds() - start;
     }
     return ok;
 }

@@ -17,6 +17,9 @@ namespace h3q8 {
 
 static thread_local char last_error[512];
 static std::atomic<uint64_t> launches{0};
+/* host-side fault injection for the failure-path tests (h3q8_fault_injection) */
+static std::atomic<long long> injected_wait_limit{0};
+static std::atomic<uint32_t> injected_skip_first_load{0};
 
 int fail(const char *format, ...) {
     va_list args;
@@ -396,6 +399,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     p.w_scales = d.weight_scales; p.a_scales = d.input_scales;
     p.ep.bias = d.bias; p.ep.gate = d.gate; p.ep.residual = d.residual; p.ep.activation = d.activation;
     p.out = d.output; p.acc_dump = d.accumulators; p.status = dev->status;
+    p.wait_limit = injected_wait_limit.load(std::memory_order_relaxed);
+    p.skip_first_load = injected_skip_first_load.load(std::memory_order_relaxed);
     if (d.rope) {
         const h3q8_rope_desc &r = *d.rope;
         p.ep.activation = ACT_QKV_ROPE;
@@ -606,5 +611,9 @@ extern "C" uint32_t h3q8_device_status(void *cuda_stream) {
     return value;
 }
 
+extern "C" void h3q8_fault_injection(uint64_t wait_limit_cycles, uint32_t skip_first_load) {
+    injected_wait_limit.store((long long)wait_limit_cycles);
+    injected_skip_first_load.store(skip_first_load);
+}
 extern "C" const char *h3q8_last_error(void) { return last_error; }
 extern "C" uint64_t h3q8_kernel_launches(void) { return launches.load(); }

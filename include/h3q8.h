@@ -213,6 +213,13 @@ int h3q8_q8_dequant(const int8_t *weights, const float *scales, uint16_t *output
  * src/weights/q8.c:38-41).  Otherwise non-zero: a bounded wait inside a kernel
  * ran out (code in the low byte, CTA index above it).  h3q8_last_error() says which. */
 uint32_t h3q8_device_status(void *cuda_stream);
+/* Failure-path testing, on the host side only (the reference provokes its faults with host flags and budgets too,
+ * src/cuda/gpu_cuda.cu:63-66, 603-606): every wait inside the GEMM kernels is bounded, by two seconds' worth of clocks
+ * unless wait_limit_cycles says otherwise, and with skip_first_load the TMA producer of the tcgen05 kernels leaves out
+ * its very first operand load, so that the MMA issuer's wait runs out, every role unwinds through the kernel's normal
+ * exit, and the status word carries the code.  Nothing traps, nothing spins without a limit.  (0, 0) restores normal
+ * operation.  No counterpart in the reference. */
+void h3q8_fault_injection(uint64_t wait_limit_cycles, uint32_t skip_first_load);
 /* Message of the last failed h3q8_* call on this thread. */
 const char *h3q8_last_error(void);
 /* Launch counter: kernels this library has launched in this process. */
