@@ -9,6 +9,7 @@
  *     non-finite activations seen by the quantiser)
  *   - the caller owns tensors, the context owns scratch
  * (src/cuda/gpu_cuda.cu:128-230, 429-489, 595-666 are the behaviour followed.) */
+#include <algorithm>
 #include <cerrno>
 #include <chrono>
 #include <cstdarg>
@@ -62,6 +63,7 @@ struct h3_gpu {
     size_t arena_bytes[4] = {0, 0, 0, 0};
     int skinny_direct = 1;      /* W8A16 with at most 128 rows: main-loop dequantisation + split-K (the weight is read once as int8) */
     uint32_t *flags = nullptr;  /* [0] kernel wait status, [1] non-finite seen */
+    unsigned long long *diagnostics = nullptr;   /* [0] clipped, [1] non-zero values quantised to zero; H3_QUANT_DIAGNOSTICS=1 */
     void *bounce[2] = {nullptr, nullptr};
     cudaEvent_t bounce_free[2] = {nullptr, nullptr};
     bool bounce_used[2] = {false, false};
@@ -245,6 +247,10 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
               cudaStreamCreateWithFlags(&g->copy_out, cudaStreamNonBlocking) == cudaSuccess &&
               cudaMalloc(&g->flags, 2 * sizeof(uint32_t)) == cudaSuccess &&
               cudaMemset(g->flags, 0, 2 * sizeof(uint32_t)) == cudaSuccess;
+    const char *diagnose = getenv("H3_QUANT_DIAGNOSTICS");   /* src/cuda/cuda_quant.cuh:156 */
+    if (ok && diagnose && !strcmp(diagnose, "1"))
+        ok = cudaMalloc(&g->diagnostics, 2 * sizeof(unsigned long long)) == cudaSuccess &&
+             cudaMemset(g->diagnostics, 0, 2 * sizeof(unsigned long long)) == cudaSuccess;
     if (!ok) {
         snprintf(error ? error : g->error, error ? error_size : sizeof g->error, "CUDA context setup failed: %s",
                  cudaGetErrorString(cudaGetLastError()));
@@ -279,6 +285,7 @@ extern "C" void h3_gpu_free(h3_gpu *g) {
         if (g->bounce_free[i]) cudaEventDestroy(g->bounce_free[i]);
     }
     if (g->flags) cudaFree(g->flags);
+    if (g->diagnostics) cudaFree(g->diagnostics);
     if (g->compute) cudaStreamDestroy(g->compute);
     if (g->copy) cudaStreamDestroy(g->copy);
     if (g->copy_out) cudaStreamDestroy(g->copy_out);
@@ -344,6 +351,13 @@ static int drain(h3_gpu *g) {
     harvest_profile(g);
     uint32_t flags[2] = {0, 0};
     if (!checked(g, cudaMemcpy(flags, g->flags, sizeof flags, cudaMemcpyDeviceToHost), "read device flags")) return 0;
+    if (g->diagnostics) {   /* cumulative, like the reference's counters (src/cuda/gpu_cuda.cu:447-449) */
+        unsigned long long counts[2] = {0, 0};
+        if (cudaMemcpy(counts, g->diagnostics, sizeof counts, cudaMemcpyDeviceToHost) == cudaSuccess) {
+            g->stats.quant_clipped_values = counts[0];
+            g->stats.quant_zeroed_values = counts[1];
+        }
+    }
     uint32_t shared_status = h3q8_device_status(g->compute);
     if (flags[0] || flags[1] || shared_status) {
         cudaMemset(g->flags, 0, sizeof flags);
@@ -796,6 +810,10 @@ static h3_gpu_tensor *q8_load_file(h3_gpu *g, const char *path, uint64_t offset,
         q8_pack_rows_kernel<<<(unsigned)((items + 7) / 8), 256, 0, g->compute>>>(
             (const uint16_t *)staging->data, (int8_t *)t->data + (size_t)r * columns,
             (float *)((char *)t->data + t->q8_scale_offset) + (size_t)r * groups, n, columns, width, groups, g->flags + 1);
+        if (g->diagnostics)   /* weights count on cold preparation, as in the reference */
+            quant_diagnostics_kernel<<<(unsigned)std::min<uint64_t>(4096, ((uint64_t)n * columns + 255) / 256), 256, 0, g->compute>>>(
+                (const uint16_t *)staging->data, (const int8_t *)t->data + (size_t)r * columns,
+                (const float *)((char *)t->data + t->q8_scale_offset) + (size_t)r * groups, n, columns, width, groups, g->diagnostics);
         count_launch(1);
         ok = checked(g, cudaGetLastError(), "q8 pack launch");
     }
@@ -1045,6 +1063,22 @@ extern "C" h3_gpu_tensor *h3q8_gpu_weight_stream_view(h3q8_weight_stream *s, int
     return t;
 }
 
+/* The row / K-group activation quantiser on the compute stream, followed by the diagnostics scan when that is on. */
+static void quantise_activations(h3_gpu *g, const uint16_t *in, int8_t *out, float *scales, uint64_t live, uint64_t total, uint32_t segment,
+                                 float clip) {
+    launch_quantize_rows(in, out, scales, live, total, segment, clip, g->flags + 1, g->compute);
+    if (g->diagnostics && live)
+        quant_diagnostics_kernel<<<(unsigned)std::min<uint64_t>(4096, (live * segment + 255) / 256), 256, 0, g->compute>>>(
+            in, out, scales, live, segment, segment, 1, g->diagnostics);
+}
+/* src/metal/gpu.m:3379-3384: H3_INT8_ACTIVATION_CLIP in [0.1, 1] shrinks the range the MLP's row quantisers map to +-127 */
+static float mlp_activation_clip() {
+    const char *text = getenv("H3_INT8_ACTIVATION_CLIP");
+    if (!text) return 1.0f;
+    const float parsed = strtof(text, nullptr);
+    return parsed >= 0.1f && parsed <= 1.0f ? parsed : 1.0f;
+}
+
 /* ------------------------------------------------------------------ linears */
 static size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
 
@@ -1140,7 +1174,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
                 float *xs = (float *)((char *)g->arena[1] + offset[1]);
                 {
                     ProfileScope timing(g, 7);
-                    launch_quantize_rows((const uint16_t *)d.input, xq, xs, q.rows, padded, q.input_dim, 1.0f, g->flags + 1, g->compute);
+                    quantise_activations(g, (const uint16_t *)d.input, xq, xs, q.rows, padded, q.input_dim, 1.0f);
                 }
                 count_launch(1);
                 dispatches++;
@@ -1229,8 +1263,7 @@ extern "C" int h3_gpu_quantize_weight_int8(h3_gpu *g, h3_gpu_tensor *out, h3_gpu
     if (!rows || !columns || !require(g, in, H3_GPU_BF16, (size_t)rows * columns, "BF16 weight to quantize") ||
         !require(g, out, H3_GPU_I8, (size_t)rows * columns, "int8 quantized output") ||
         !require(g, scales, H3_GPU_F32, rows, "int8 quantization scales")) return 0;
-    launch_quantize_rows((const uint16_t *)pointer(in), (int8_t *)pointer(out), (float *)pointer(scales), rows, rows, columns, 1.0f,
-                         g->flags + 1, g->compute);
+    quantise_activations(g, (const uint16_t *)pointer(in), (int8_t *)pointer(out), (float *)pointer(scales), rows, rows, columns, 1.0f);
     count_launch(1);
     return launch_status(g, "weight quantiser", 1);
 }
@@ -1247,8 +1280,7 @@ extern "C" int h3_gpu_linear_int8_bf16(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_ten
         !require(g, out, H3_GPU_BF16, (size_t)rows * n, "int8 linear output") || !require(g, in, H3_GPU_BF16, (size_t)rows * k, "int8 linear input") ||
         !require(g, qin, H3_GPU_I8, (size_t)padded * k, "int8 quantized output") ||
         !require(g, in_scales, H3_GPU_F32, padded, "int8 quantization scales")) return 0;
-    launch_quantize_rows((const uint16_t *)pointer(in), (int8_t *)pointer(qin), (float *)pointer(in_scales), rows, padded, k, 1.0f,
-                         g->flags + 1, g->compute);
+    quantise_activations(g, (const uint16_t *)pointer(in), (int8_t *)pointer(qin), (float *)pointer(in_scales), rows, padded, k, 1.0f);
     count_launch(1);
     h3q8_linear_desc d = {};
     d.mode = H3Q8_MODE_W8A8; d.rows = rows; d.input_dim = k; d.output_dim = n;
@@ -1644,10 +1676,10 @@ extern "C" int h3_gpu_mlp_int8_bf16(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_tensor
         !require(g, activated, H3_GPU_BF16, (size_t)rows * hidden, "int8 MLP activated") ||
         !require(g, out, H3_GPU_BF16, (size_t)rows * n, "int8 MLP output")) return 0;
     unsigned launched = 0;
+    const float clip = mlp_activation_clip();   /* the MLP's row quantisers only; the per-1024 one has no clip (gpu.m:3405-3451) */
     if (!input_is_quantized) {
         ProfileScope timing(g, 7);
-        launch_quantize_rows((const uint16_t *)pointer(in), (int8_t *)pointer(q_act), (float *)pointer(act_scales), rows, padded, k, 1.0f,
-                             g->flags + 1, g->compute);
+        quantise_activations(g, (const uint16_t *)pointer(in), (int8_t *)pointer(q_act), (float *)pointer(act_scales), rows, padded, k, clip);
         count_launch(1);
         launched++;
     }
@@ -1655,11 +1687,11 @@ extern "C" int h3_gpu_mlp_int8_bf16(h3_gpu *g, h3_gpu_tensor *out, h3_gpu_tensor
     {
         ProfileScope timing(g, 7);
         if (use_int8_row_fc2)
-            launch_quantize_rows((const uint16_t *)pointer(activated), (int8_t *)pointer(q_act), (float *)pointer(act_scales), rows, padded, hidden,
-                                 1.0f, g->flags + 1, g->compute);
+            quantise_activations(g, (const uint16_t *)pointer(activated), (int8_t *)pointer(q_act), (float *)pointer(act_scales), rows, padded, hidden,
+                                 clip);
         else  /* every (row, 1024-feature group) is a segment of the same contiguous matrix */
-            launch_quantize_rows((const uint16_t *)pointer(activated), (int8_t *)pointer(q_act), (float *)pointer(act_scales),
-                                 (uint64_t)rows * groups, (uint64_t)padded * groups, 1024, 1.0f, g->flags + 1, g->compute);
+            quantise_activations(g, (const uint16_t *)pointer(activated), (int8_t *)pointer(q_act), (float *)pointer(act_scales),
+                                 (uint64_t)rows * groups, (uint64_t)padded * groups, 1024, 1.0f);
         count_launch(1);
         launched++;
     }
@@ -1689,8 +1721,7 @@ extern "C" int h3_gpu_grouped_qkv_linear_rope_int8(h3_gpu *g, h3_gpu_tensor *q, 
     unsigned launched = 1;
     if (!input_is_quantized) {
         ProfileScope timing(g, 7);
-        launch_quantize_rows((const uint16_t *)pointer(in), (int8_t *)pointer(qin), (float *)pointer(in_scales), rows, padded, width, 1.0f,
-                             g->flags + 1, g->compute);
+        quantise_activations(g, (const uint16_t *)pointer(in), (int8_t *)pointer(qin), (float *)pointer(in_scales), rows, padded, width, 1.0f);
         count_launch(1);
         launched++;
     }

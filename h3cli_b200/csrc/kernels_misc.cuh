@@ -195,6 +195,26 @@ static inline cudaError_t launch_quantize_rows(const uint16_t *in, int8_t *out, 
     return cudaGetLastError();
 }
 
+/* Optional diagnostics of a quantisation (the job of quant_diagnostics, src/cuda/cuda_quant.cuh:72-87): a separate
+ * scan, so the normal path pays nothing.  counts[0] += values whose magnitude exceeded the int8 range before clamping
+ * (possible only with an activation clip below 1), counts[1] += non-zero values that became 0.  The scale of element
+ * (r, c) is scales[r * groups + c / width]. */
+static __global__ void __launch_bounds__(256) quant_diagnostics_kernel(const uint16_t *__restrict__ source, const int8_t *__restrict__ quantized,
+                                                                      const float *__restrict__ scales, uint64_t rows, uint32_t columns,
+                                                                      uint32_t width, uint32_t groups, unsigned long long *counts) {
+    unsigned clipped = 0, zeroed = 0;
+    const uint64_t total = rows * columns;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)blockDim.x * gridDim.x) {
+        const uint64_t r = i / columns;
+        const uint32_t c = (uint32_t)(i - r * columns);
+        const float x = bf16_bits_to_f32(source[i]), scale = scales[r * groups + c / width];
+        clipped += fabsf(__fdiv_rn(x, scale)) > 127.5f;
+        zeroed += x != 0.0f && quantized[i] == 0;
+    }
+    if (clipped) atomicAdd(counts, (unsigned long long)clipped);
+    if (zeroed) atomicAdd(counts + 1, (unsigned long long)zeroed);
+}
+
 /* Producer-side fusion of the activation quantiser (src/metal/shaders.metal:3390-3473,
  * src/gpu.h:630-642): per row
  *   gated = bf16(residual + branch * gate[class, gate_slot])          -> gated_residual (may alias residual)

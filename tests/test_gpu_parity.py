@@ -1289,6 +1289,49 @@ def test_nonfinite_weight_is_rejected_and_never_cached(poison, tmp_path):
     gpu.free()
 
 
+def test_quant_diagnostics_and_activation_clip(oracle, monkeypatch):
+    """H3_QUANT_DIAGNOSTICS=1 (src/cuda/cuda_quant.cuh:72-87, 156; counters of src/gpu.h:131) counts values the quantiser
+    clipped and non-zero values it turned into 0; H3_INT8_ACTIVATION_CLIP (src/metal/gpu.m:3379-3384) shrinks the range
+    of the MLP's row quantisers, which is what makes clipping possible at all."""
+    rows, K, hidden, N = 130, 256, 1024, 256
+    x = synth.activations(83, 1, rows, K, outliers=synth.outlier_channels(83, K)).reshape(rows, K)
+    w1, s1 = synth.int8_weights(83, 2, 2 * hidden, K), synth.lognormal_scales(83, 3, 2 * hidden, 1) * np.float32(0.2)
+    w2, s2 = synth.int8_weights(83, 4, N, hidden), synth.lognormal_scales(83, 5, N, 1)
+    padded = 256
+
+    def run(clip):
+        if clip is None:
+            monkeypatch.delenv("H3_INT8_ACTIVATION_CLIP", raising=False)
+        else:
+            monkeypatch.setenv("H3_INT8_ACTIVATION_CLIP", str(clip))
+        gpu = h.Gpu()
+        t_x, t_w1, t_s1 = gpu.tensor_from_bf16(x), gpu.tensor_from_i8(w1), gpu.tensor_from_f32(s1[:, 0].copy())
+        t_w2, t_s2 = gpu.tensor_from_i8(w2), gpu.tensor_from_f32(s2[:, 0].copy())
+        q, sc = gpu.tensor_new_i8(padded * hidden), gpu.tensor_new_f32(padded)
+        act, out = gpu.tensor_new_bf16(rows * hidden), gpu.tensor_new_bf16(rows * N)
+        gpu.begin()
+        gpu.mlp_int8_bf16(out, act, q, sc, t_x, t_w1, t_s1, t_w2, t_s2, rows, K, hidden, N, use_int8_row_fc2=1)
+        gpu.submit()
+        stats, scales = gpu.stats(), sc.read()[:rows].copy()
+        gpu.free()
+        return stats, scales
+
+    monkeypatch.setenv("H3_QUANT_DIAGNOSTICS", "1")
+    plain, plain_scales = run(None)
+    assert plain.quant_clipped_values == 0 and plain.quant_zeroed_values > 0           # outlier rows push small values to 0
+    clipped, clipped_scales = run(0.5)
+    assert clipped.quant_clipped_values > 0
+    # what is left in the scale buffer are the fc2-input scales = clip * max|activated| / 127; the activations themselves
+    # moved a little because the fc1 input was clipped too, so the halving is approximate
+    ratio = clipped_scales / plain_scales
+    assert 0.3 < np.median(ratio) < 0.7
+    xq, _ = oracle.quantize_rows(x)
+    assert plain.quant_zeroed_values >= int(((xq == 0) & (synth.from_bf16(x) != 0)).sum())   # at least the MLP input's
+    monkeypatch.delenv("H3_QUANT_DIAGNOSTICS")
+    quiet, _ = run(None)
+    assert quiet.quant_clipped_values == 0 and quiet.quant_zeroed_values == 0           # off: no scan, no counts
+
+
 def test_allocation_budget_fault_injection(monkeypatch):
     """Host-side fault injection as in the reference (H3_CUDA_TEST_MEMORY_BUDGET,
     src/weights/residency.c:31-32): allocations beyond the budget fail cleanly and
