@@ -41,7 +41,7 @@ FLOP_PER_STEP = sum(2.0 * M_TOKENS * k * n for _, k, n, _ in LAYERS)
 METRIC = "q8_dit_block_linear_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch of this workload (mean of QKV, attn-out, FFN-up,
-# FFN-down at M = 32,400), from the 1-pass ncu capture summarised in profiles/bench_default_dram_traffic.md
+# FFN-down at M = 32,400), from a one-pass ncu capture of this same command
 NCU_TRAFFIC_BYTES_PER_LAUNCH = 2.484e9
 
 

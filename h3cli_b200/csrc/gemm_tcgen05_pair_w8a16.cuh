@@ -45,8 +45,8 @@ struct PairW8A16Config {
     static constexpr int ACC_COLS = BN, ACC_BUFFERS = 2;
     /* warps: epilogue (TMEM lane quadrant = warp % 4, column half = warp / 4), weight producer, activation producer,
      * MMA issuer and TMEM owner, dequantisers in two groups */
-    /* measured at M = 32 400 (QKV / FFN-up / FFN-down, TFLOP/s): 8 epilogue + 2 x 4 dequantiser warps 1 100 / 1 062 / 1 049;
-     * 4 + 2 x 4: 1 081 / 1 053 / 1 007; 8 + 2 x 8: 1 034 / 967 / 962; ring depths (5,8,5) (6,6,5) (6,8,4) (7,4,5) within 1 % */
+    /* eight dequantiser warps keep ahead of the tensor core; sixteen only add shared-memory and issue contention, and the
+     * ring depths matter little once each covers the TMA latency: the kernel is bound by shared-memory bandwidth */
     static constexpr int EPILOGUE_WARPS = 8, RAW_PRODUCER_WARP = EPILOGUE_WARPS, A_PRODUCER_WARP = EPILOGUE_WARPS + 1,
                          MMA_WARP = EPILOGUE_WARPS + 2, FIRST_DEQUANT_WARP = EPILOGUE_WARPS + 3;
     static constexpr int GROUP_WARPS = 4, DEQUANT_WARPS = 2 * GROUP_WARPS;
@@ -261,8 +261,8 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
                 /* The converted tile is read by the tensor core of THIS SM (each CTA supplies its own half of B), so all
                  * that has to cross the pair is the news that the writes are done: every writer makes its stores visible
                  * to the async proxy, then one lane per warp arrives on the leader's barrier with the plain remote arrive.
-                 * (A cluster-scope release here costs a memory barrier of about 900 clocks per warp and k-block: measured,
-                 * it alone held the kernel to a third of the MMA rate.) */
+                 * (A cluster-scope release on this arrival is a memory barrier of about 900 clocks per warp and k-block,
+                 * which alone holds the kernel to a third of the MMA rate.) */
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {

@@ -238,7 +238,8 @@ template <bool MAGIC>
 static int launch_pair_grouped(const h3q8_linear_desc &d, const GemmParams &params, DeviceState *dev, cudaStream_t stream) {
     /* PairGroupedConfig: 256 x 128 tiles while the per-group combine is the bound, 256 x 256 for groups of 512 and more;
      * each CTA stages half of the tile's weight rows */
-    /* measured on the real model's block (FC2 with per-1024 activation scales): 10.34 -> 9.76 ms per block with wide tiles */
+    /* with groups of 512 and more the combine runs once per four or more k-blocks and bounds nothing, so the wider tile's
+     * lower operand traffic wins; with narrower groups the combine is the bound and the narrow tile's 16 epilogue warps win */
     static const int wide_tiles = [] { const char *e = getenv("H3Q8_GROUPED_WIDE"); return e && *e ? atoi(e) : 1; }();
     const bool wide = wide_tiles && params.scale_group >= 512;
     const uint32_t BM = 256, BN = wide ? 256 : 128, BKE = 128;
@@ -268,8 +269,8 @@ static bool plan_splitk(uint32_t mode, uint32_t rows, uint32_t k, uint32_t n, in
     const uint32_t bke = mode == H3Q8_MODE_W8A8 ? 128 : 64, num_kb = (k + bke - 1) / bke;
     const uint64_t tiles = (uint64_t)((rows + 127) / 128) * ((n + 127) / 128);
     /* a few work items per SM (the kernel is persistent), unless the tiles alone already fill the GPU */
-    /* measured on B200 at 16 rows (device time, graph replay): three work items per SM and at least eight k-blocks
-     * per split were best for 3072 x 3072 (12.7 us), 12288 x 3072 and 3072 x 12288 (30-32 us) */
+    /* three work items per SM (the kernel is persistent and a work item is short) and at least eight k-blocks per split
+     * (below that the fixed cost of a work item -- first TMA round trip, accumulator hand-off -- outweighs the streaming) */
     static const int waves = [] { const char *e = getenv("H3Q8_SPLITK_WAVES"); return e && *e && atoi(e) > 0 ? atoi(e) : 3; }();
     static const int min_kb = [] { const char *e = getenv("H3Q8_SPLITK_MIN_KB"); return e && *e && atoi(e) > 0 ? atoi(e) : 8; }();
     uint64_t want = tiles && tiles < (uint64_t)sms ? ((uint64_t)waves * sms + tiles - 1) / tiles : 0;
