@@ -4,27 +4,29 @@
  *
  * A cluster of two CTAs computes a 256 x 256 output tile with `tcgen05.mma.cta_group::2`
  * exactly as gemm_tcgen05_pair_kernel does, but the weight arrives as int8: each CTA's TMA
- * brings its own 128 weight rows of a k-block as 64 raw bytes per row, dequantiser warps
- * (two groups of four on alternate k-blocks) turn them into the bf16 operand tile (128-byte rows, 128-byte swizzle) with the
- * reference's arithmetic, bf16(float(q) * scale) (src/metal/shaders.metal:825-827), and the
- * leader's MMA issuer consumes the converted tiles of BOTH CTAs.
+ * brings its own 128 weight rows as 128 raw bytes per row (two k-blocks of 64), dequantiser warps
+ * (two groups of four on alternate 128-wide blocks) turn them into two bf16 operand tiles (128-byte rows, 128-byte
+ * swizzle) with the reference's arithmetic, bf16(float(q) * scale) (src/metal/shaders.metal:825-827), and the
+ * leader's MMA issuer consumes the converted tiles of BOTH CTAs.  The hand-off covers 128 elements of K because
+ * its fixed cost -- two waits, a proxy fence and an arrival per warp -- is a quarter of the conversion time of a
+ * 64-wide block, and the dequantisers are what the tensor core waits for.
  *
  * Why two CTAs: a CTA converts only its own 128 of the tile's 256 weight rows, i.e. half
  * of the conversions per SM and MMA clock of a one-CTA 128 x 256 tile, and its tensor core
  * reads half of the B operand from its own shared memory.
  *
  * Per CTA and k-block (64 elements of K, 512 MMA clocks at full rate):
- *   TMA writes    A 16 KB (bf16, 128-byte swizzle) + raw W 8 KB (int8, 64-byte swizzle)
+ *   TMA writes    A 16 KB (bf16, 128-byte swizzle) + raw W 8 KB (int8, 128-byte swizzle, 16 KB per two k-blocks)
  *   dequantisers  read 8 KB, write 16 KB (converted ring)
  *   tensor core   reads A 16 KB + converted W 16 KB
  *
  * Barriers (count; who arrives):
  *   afull[s]   leader only; 1 + tx bytes of both CTAs' A tiles      (producers of both CTAs)
  *   aempty[s]  per CTA;     1   tcgen05.commit of the leader, sent to both CTAs
- *   rfull[s]   per CTA;     1 + tx bytes of the CTA's own raw tile   (its own producer)
+ *   rfull[s]   per CTA;     1 + tx bytes of the CTA's own raw tile   (its own producer)          per two k-blocks
  *   rempty[s]  per CTA;     4   the warps of the group that converts the tile, once it is in registers
- *   bfull[c]   leader only; 8   one arrival per warp of that group in both CTAs
- *   bempty[c]  per CTA;     1   tcgen05.commit of the leader, sent to both CTAs
+ *   bfull[c]   leader only; 8   one arrival per warp of that group in both CTAs                 per two k-blocks
+ *   bempty[c]  per CTA;     1   tcgen05.commit of the leader, sent to both CTAs                per two k-blocks
  *   tfull[a] / tempty[a]    as in the bf16 pair kernel
  * Every wait is bounded; a role that gives up raises the CTA's abort flag and all roles
  * fall through to the common exit, where the status word is set and TMEM is freed.
@@ -37,11 +39,12 @@ namespace h3q8 {
 struct PairW8A16Config {
     static constexpr int BM = 256, BN = 256, BKE = 64;
     static constexpr int A_BYTES = 128 * 128;            /* this CTA's 128 rows of X, 64 bf16 each       */
-    static constexpr int RAW_BYTES = 128 * 64;           /* this CTA's 128 weight rows, 64 int8 each     */
-    static constexpr int B_BYTES = 128 * 128;            /* converted tile                               */
+    static constexpr int KSUB = 2;                       /* k-blocks per weight hand-off                 */
+    static constexpr int RAW_BYTES = 128 * 64 * KSUB;    /* this CTA's 128 weight rows, 128 int8 each    */
+    static constexpr int B_BYTES = 128 * 128;            /* converted tile of one k-block                */
     /* three rings: a raw tile is free again as soon as it has been converted, the X tile and the converted tile only
      * when the MMAs that read them are done; raw tiles are small, so that ring is the deep one */
-    static constexpr int A_STAGES = 5, RAW_STAGES = 8, CONV_BUFFERS = 5;
+    static constexpr int A_STAGES = 5, RAW_STAGES = 3, CONV_BUFFERS = 3;   /* raw and converted: units of KSUB k-blocks */
     static constexpr int ACC_COLS = BN, ACC_BUFFERS = 2;
     /* warps: epilogue (TMEM lane quadrant = warp % 4, column half = warp / 4), weight producer, activation producer,
      * MMA issuer and TMEM owner, dequantisers in two groups */
@@ -53,7 +56,7 @@ struct PairW8A16Config {
     static_assert((EPILOGUE_WARPS == 4 || EPILOGUE_WARPS == 8) && (GROUP_WARPS == 4 || GROUP_WARPS == 8), "role layout");
     static constexpr int WARPS = FIRST_DEQUANT_WARP + DEQUANT_WARPS, THREADS = WARPS * 32;
     static constexpr int BARRIERS = 2 * A_STAGES + 2 * RAW_STAGES + 2 * CONV_BUFFERS + 2 * ACC_BUFFERS;
-    static constexpr int SMEM_BYTES = A_STAGES * A_BYTES + RAW_STAGES * RAW_BYTES + CONV_BUFFERS * B_BYTES + 1024 + 512;
+    static constexpr int SMEM_BYTES = A_STAGES * A_BYTES + RAW_STAGES * RAW_BYTES + CONV_BUFFERS * KSUB * B_BYTES + 1024 + 512;
     static constexpr uint32_t IDESC = umma_idesc(1, 1, 256, BN);
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
     static_assert(BARRIERS * 8 + 16 <= 512, "barrier block");
@@ -104,7 +107,7 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *a_ring = smem;
     uint8_t *conv = a_ring + C::A_STAGES * C::A_BYTES;
-    uint8_t *raw_ring = conv + C::CONV_BUFFERS * C::B_BYTES;
+    uint8_t *raw_ring = conv + C::CONV_BUFFERS * C::KSUB * C::B_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(raw_ring + C::RAW_STAGES * C::RAW_BYTES);
     uint64_t *afull = bars, *aempty = afull + C::A_STAGES;
     uint64_t *rfull = aempty + C::A_STAGES, *rempty = rfull + C::RAW_STAGES;
@@ -117,6 +120,7 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
     const uint32_t rank = cluster_cta_rank();               /* 0 = leader */
     const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const uint32_t num_kb = (p.K + C::BKE - 1) / C::BKE;
+    const uint32_t num_wb = (num_kb + C::KSUB - 1) / C::KSUB;   /* weight hand-offs per tile */
     const bool swiglu = p.ep.activation == ACT_SWIGLU;
 
     if (threadIdx.x == 0) {
@@ -147,10 +151,10 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
                 tile_coordinates(p, tile, mb, nb);
                 /* SwiGLU: the leader stages 128 gate rows, its peer the matching 128 up rows (weight rows N + n) */
                 const uint32_t b_row = swiglu ? nb * 128 + rank * p.N : nb * C::BN + rank * 128;
-                for (uint32_t kb = 0; kb < num_kb; kb++) {
+                for (uint32_t wb = 0; wb < num_wb; wb++) {
                     if (!wait_or_abort(&rempty[sr.index], sr.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_PRODUCER; break; }
                     mbar_arrive_expect_tx(&rfull[sr.index], C::RAW_BYTES);
-                    tma_load_2d(raw_ring + sr.index * C::RAW_BYTES, &map_b, &rfull[sr.index], (int32_t)(kb * C::BKE), (int32_t)b_row);
+                    tma_load_2d(raw_ring + sr.index * C::RAW_BYTES, &map_b, &rfull[sr.index], (int32_t)(wb * C::KSUB * C::BKE), (int32_t)b_row);
                     sr.advance(C::RAW_STAGES);
                 }
             }
@@ -180,17 +184,23 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
                 if (!wait_or_abort(&tempty[acc.index], acc.phase ^ 1, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
                 tc_fence_after_sync();
                 const uint32_t d = tmem_base + acc.index * C::ACC_COLS;
-                for (uint32_t kb = 0; kb < num_kb; kb++) {
-                    if (!wait_or_abort(&afull[st.index], st.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                for (uint32_t wb = 0; wb < num_wb && !failure; wb++) {
                     if (!wait_or_abort(&bfull[cv.index], cv.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
-                    tc_fence_after_sync();
-                    const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(a_ring + st.index * C::A_BYTES));
-                    const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(conv + cv.index * C::B_BYTES));
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; k4++) umma_bf16_pair(d, a_desc + 2 * k4, b_desc + 2 * k4, C::IDESC, kb | k4);
-                    umma_commit_pair(&aempty[st.index], 3);   /* frees the X tile in both CTAs         */
-                    umma_commit_pair(&bempty[cv.index], 3);   /* frees the converted tile in both CTAs */
-                    st.advance(C::A_STAGES);
+                    for (int sub = 0; sub < C::KSUB; sub++) {
+                        const uint32_t kb = wb * C::KSUB + sub;
+                        if (kb >= num_kb) break;
+                        if (!wait_or_abort(&afull[st.index], st.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
+                        tc_fence_after_sync();
+                        const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(a_ring + st.index * C::A_BYTES));
+                        const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(conv + (cv.index * C::KSUB + sub) * C::B_BYTES));
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; k4++) umma_bf16_pair(d, a_desc + 2 * k4, b_desc + 2 * k4, C::IDESC, kb | k4);
+                        umma_commit_pair(&aempty[st.index], 3);   /* frees the X tile in both CTAs */
+                        st.advance(C::A_STAGES);
+                    }
+                    if (failure) break;
+                    umma_commit_pair(&bempty[cv.index], 3);       /* frees the converted tiles in both CTAs */
                     cv.advance(C::CONV_BUFFERS);
                 }
                 if (failure) break;
@@ -200,17 +210,15 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
         }
     } else if (warp >= C::FIRST_DEQUANT_WARP) {
         /* ------------------------------------------------ dequantisers (both CTAs) */
-        /* Two groups of warps take alternate k-blocks.  With four warps per group thread t owns weight row t of this
-         * CTA's 128 (with eight, half h = t / 128 of row t % 128): 16-byte loads from the raw tile (64-byte rows, 64-byte
-         * swizzle), 16 conversions per load, 16-byte stores into the operand tile (128-byte rows, 128-byte swizzle);
-         * consecutive lanes take consecutive rows, which keeps both swizzles free of bank conflicts.  A warp pays one
-         * wait, one proxy fence and one arrival per TWO k-blocks, and while one group sits in its fence the other
-         * converts. */
+        /* Two groups of four warps take alternate weight blocks of 128 k-values.  Thread t owns weight row t of this
+         * CTA's 128: eight 16-byte loads from the raw tile (128-byte rows, 128-byte swizzle), 16 conversions per load,
+         * 16-byte stores into the two operand tiles (128-byte rows, 128-byte swizzle); consecutive lanes take
+         * consecutive rows, which keeps both swizzles free of bank conflicts.  A warp pays two waits, one proxy fence
+         * and one arrival per block, and while one group sits in its fence the other converts. */
+        static_assert(C::GROUP_WARPS == 4 && C::KSUB == 2, "one thread per weight row, two k-blocks per hand-off");
         const uint32_t group = (warp - C::FIRST_DEQUANT_WARP) / C::GROUP_WARPS;
-        constexpr int HALVES = C::GROUP_WARPS / 4, CHUNKS = 4 / HALVES;   /* 16-byte raw vectors per thread */
-        const uint32_t t = threadIdx.x - (C::FIRST_DEQUANT_WARP + C::GROUP_WARPS * group) * 32;
-        const uint32_t r = t & 127, h = t >> 7;
-        const uint32_t raw_twist = (r >> 1) & 3, conv_twist = r & 7;
+        const uint32_t r = threadIdx.x - (C::FIRST_DEQUANT_WARP + C::GROUP_WARPS * group) * 32;
+        const uint32_t twist = r & 7;
         const uint32_t width = p.scale_group ? p.scale_group : p.K;
         const uint32_t leader_bfull = map_to_cta(smem_u32(bfull), 0);
         auto scale_pointer = [&](uint32_t tile, bool &live) {
@@ -221,47 +229,55 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
             const size_t scale_row = swiglu ? (size_t)rank * p.N + n : n;                  /* row of the weight matrix */
             return p.w_scales + (live ? scale_row : 0) * p.scale_groups;
         };
+        /* the scales of the two k-blocks of weight block wb (the same one unless the scale group is 64) */
+        auto scales_of = [&](const float *row, bool row_live, uint32_t wb, float &s0, float &s1) {
+            const uint32_t k0 = wb * C::KSUB * C::BKE, k1 = k0 + C::BKE;
+            s0 = row_live ? row[k0 / width] : 0.0f;
+            s1 = row_live && k1 < p.K ? row[k1 / width] : s0;
+        };
         PipeState st, cv;
-        uint32_t turn = 0;                                  /* k-blocks seen so far, across tiles */
+        uint32_t turn = 0;                                  /* weight blocks seen so far, across tiles */
         bool live = false;
         const float *row_scales = pair < total_tiles ? scale_pointer(pair, live) : p.w_scales;
-        float first_scale = live ? row_scales[0] : 0.0f;   /* fetched one tile ahead */
+        float first0 = 0.0f, first1 = 0.0f;                 /* block 0 of the coming tile, fetched one tile ahead */
+        if (pair < total_tiles) scales_of(row_scales, live, 0, first0, first1);
         for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
             const float *scales_now = row_scales;
             const bool live_now = live;
-            float upcoming = first_scale;
-            const uint32_t mine_first = (turn & 1u) == group ? 0u : 1u;   /* this group's first k-block of the tile */
-            if (p.scale_groups > 1 && mine_first && live_now && mine_first < num_kb) upcoming = scales_now[(mine_first * C::BKE) / width];
+            float upcoming0 = first0, upcoming1 = first1;
+            const uint32_t mine_first = (turn & 1u) == group ? 0u : 1u;   /* this group's first block of the tile */
+            if (p.scale_groups > 1 && mine_first && mine_first < num_wb) scales_of(scales_now, live_now, mine_first, upcoming0, upcoming1);
             if (tile + pairs < total_tiles) {
                 row_scales = scale_pointer(tile + pairs, live);
-                first_scale = live ? row_scales[0] : 0.0f;
+                scales_of(row_scales, live, 0, first0, first1);
             }
-            for (uint32_t kb = 0; kb < num_kb; kb++, turn++) {
+            for (uint32_t wb = 0; wb < num_wb; wb++, turn++) {
                 if ((turn & 1u) != group) { st.advance(C::RAW_STAGES); cv.advance(C::CONV_BUFFERS); continue; }
-                const float scale = upcoming;
-                if (p.scale_groups > 1 && kb + 2 < num_kb && live_now) upcoming = scales_now[((kb + 2) * C::BKE) / width];
+                const float scale[2] = {upcoming0, upcoming1};
+                if (p.scale_groups > 1 && wb + 2 < num_wb) scales_of(scales_now, live_now, wb + 2, upcoming0, upcoming1);
                 bool ready = wait_or_abort(&rfull[st.index], st.phase, abort_flag);
                 ready = ready && wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_DEQUANT; break; }
-                const uint8_t *raw = raw_ring + st.index * C::RAW_BYTES + r * 64;
-                uint8_t *dst = conv + cv.index * C::B_BYTES + r * 128;
-                uint4 q[CHUNKS];
+                const uint8_t *raw = raw_ring + st.index * C::RAW_BYTES + r * 128;
+                uint8_t *dst = conv + cv.index * C::KSUB * C::B_BYTES + r * 128;
+                uint4 q[8];
 #pragma unroll
-                for (int c = 0; c < CHUNKS; c++) q[c] = *reinterpret_cast<const uint4 *>(raw + (((CHUNKS * h + c) ^ raw_twist) << 4));
+                for (int c = 0; c < 8; c++) q[c] = *reinterpret_cast<const uint4 *>(raw + ((c ^ twist) << 4));
                 /* the raw tile is in registers: its slot may be refilled */
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&rempty[st.index]);
 #pragma unroll
-                for (int c = 0; c < CHUNKS; c++) {
+                for (int c = 0; c < 8; c++) {
                     uint4 lo, hi;
-                    dequant16<PACKED>(q[c], scale, lo, hi);
-                    *reinterpret_cast<uint4 *>(dst + (((2 * (CHUNKS * h + c)) ^ conv_twist) << 4)) = lo;
-                    *reinterpret_cast<uint4 *>(dst + (((2 * (CHUNKS * h + c) + 1) ^ conv_twist) << 4)) = hi;
+                    dequant16<PACKED>(q[c], scale[c >> 2], lo, hi);
+                    uint8_t *tile_row = dst + (c >> 2) * C::B_BYTES;
+                    *reinterpret_cast<uint4 *>(tile_row + (((2 * (c & 3)) ^ twist) << 4)) = lo;
+                    *reinterpret_cast<uint4 *>(tile_row + (((2 * (c & 3) + 1) ^ twist) << 4)) = hi;
                 }
-                /* The converted tile is read by the tensor core of THIS SM (each CTA supplies its own half of B), so all
+                /* The converted tiles are read by the tensor core of THIS SM (each CTA supplies its own half of B), so all
                  * that has to cross the pair is the news that the writes are done: every writer makes its stores visible
                  * to the async proxy, then one lane per warp arrives on the leader's barrier with the plain remote arrive.
-                 * (A cluster-scope release on this arrival is a memory barrier of about 900 clocks per warp and k-block,
+                 * (A cluster-scope release on this arrival is a memory barrier of about 900 clocks per warp and hand-off,
                  * which alone holds the kernel to a third of the MMA rate.) */
                 fence_proxy_async_smem();
                 __syncwarp();

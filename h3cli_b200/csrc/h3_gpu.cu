@@ -58,7 +58,7 @@ struct h3_gpu {
     int quant_mode = 0;         /* 0 off, 1 W8A16, 2 W8A8 */
     uint32_t group = 0;
     bool group_set = false;
-    int w8a16_scratch_rows = 1; /* rows at or above which W8A16 dequantises to scratch first; 0 = never */
+    int w8a16_scratch_rows = -1; /* rows at or above which W8A16 dequantises to scratch first; 0 = never; -1 = by shape */
     void *arena[4] = {nullptr, nullptr, nullptr, nullptr}; /* 0 int8 activations, 1 activation scales, 2 bf16 weight scratch, 3 split-K partial sums */
     size_t arena_bytes[4] = {0, 0, 0, 0};
     int skinny_direct = 1;      /* W8A16 with at most 128 rows: main-loop dequantisation + split-K (the weight is read once as int8) */
@@ -238,10 +238,8 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
     const char *skinny = getenv("H3Q8_SKINNY_DIRECT");
     if (skinny && *skinny) g->skinny_direct = atoi(skinny);
     const char *policy = getenv("H3Q8_W8A16_SCRATCH_ROWS");
-    /* dequantise-then-GEMM is the default: one pass over the weight (about 1 % of a 32 400-row projection) buys the bf16
-     * kernel's rate, while main-loop dequantisation is bound by shared-memory bandwidth (80 KB instead of 64 KB per k-block
-     * and SM); 0 selects the main-loop kernels */
-    g->w8a16_scratch_rows = policy && *policy ? atoi(policy) : 1;
+    /* unset: the policy is chosen per problem (w8a16_to_scratch); a number fixes the row threshold, 0 the main-loop kernels */
+    g->w8a16_scratch_rows = policy && *policy ? atoi(policy) : -1;
     bool ok = cudaSetDevice(device) == cudaSuccess &&
               cudaStreamCreateWithFlags(&g->compute, cudaStreamNonBlocking) == cudaSuccess &&
               cudaStreamCreateWithFlags(&g->copy, cudaStreamNonBlocking) == cudaSuccess &&
@@ -1083,6 +1081,17 @@ static float mlp_activation_clip() {
 /* ------------------------------------------------------------------ linears */
 static size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
 
+/* Which of the two W8A16 policies a problem of more than 128 rows takes.  Dequantise-then-GEMM pays one pass over the
+ * weight (3 bytes of HBM traffic per element and a launch) and then runs at the bf16 kernel's rate; main-loop
+ * dequantisation pays nothing up front but is bound by shared-memory bandwidth (80 KB instead of 64 KB per k-block and
+ * SM), about three quarters of that rate.  The up-front pass is the larger cost only while the GEMM itself is short:
+ * few rows and a short K. */
+static bool w8a16_to_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q) {
+    if (q.activation == H3Q8_ACT_SWIGLU) return g->w8a16_scratch_rows != 0;
+    if (g->w8a16_scratch_rows < 0) return q.rows > 512 || q.input_dim > 4096;
+    return g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows;
+}
+
 /* Scratch a problem needs from the context arenas: [0] int8 activations, [1] their scales, [2] bf16 weight,
  * [3] split-K partial sums (problems of at most 128 rows are spread over all SMs). */
 static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size_t need[4]) {
@@ -1098,7 +1107,7 @@ static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size
     } else if (q.weight->q8) {
         const size_t skinny = g->skinny_direct && !swiglu && q.rows <= 128
                             ? h3q8_linear_workspace_bytes(H3Q8_MODE_W8A16, q.rows, q.input_dim, q.output_dim) : 0;
-        if (q.input_dim % 16 == 0 && !skinny && g->w8a16_scratch_rows && (swiglu || q.rows >= (uint32_t)g->w8a16_scratch_rows)) {
+        if (q.input_dim % 16 == 0 && !skinny && w8a16_to_scratch(g, q)) {
             need[2] = round256((size_t)q.output_dim * (swiglu ? 2 : 1) * q.input_dim * 2);
         } else mode = H3Q8_MODE_W8A16;
     }

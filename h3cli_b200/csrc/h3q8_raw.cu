@@ -195,8 +195,8 @@ static int launch_pair_w8a16(const h3q8_linear_desc &d, const GemmParams &params
     p = params;
     const bool swiglu = d.activation == H3Q8_ACT_SWIGLU; /* weight rows [gate N | up N], 128 outputs per tile */
     if (!make_map(&args.map_a[0], d.input, 2, d.rows, d.input_dim, C::BKE, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
-    if (!make_map(&args.map_b[0], d.weight, 1, (uint64_t)d.output_dim * (swiglu ? 2 : 1), d.input_dim, C::BKE, 128,
-                  CU_TENSOR_MAP_SWIZZLE_64B)) return 0;
+    if (!make_map(&args.map_b[0], d.weight, 1, (uint64_t)d.output_dim * (swiglu ? 2 : 1), d.input_dim, C::KSUB * C::BKE, 128,
+                  CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
     p.m_blocks = (d.rows + C::BM - 1) / C::BM;
     p.n_blocks = swiglu ? (d.output_dim + 127) / 128 : (d.output_dim + C::BN - 1) / C::BN;
     p.tiles = p.m_blocks * p.n_blocks;

@@ -384,10 +384,12 @@ int h3q8_gpu_tensor_wait(h3_gpu_tensor *tensor); /* host waits for the tensor's 
 int h3q8_gpu_tensor_download_async(h3_gpu_tensor *tensor, void *host, size_t bytes);
 /* Rows at or above which a W8A16 linear first dequantises the weight into
  * context scratch and runs the bf16 GEMM (the reference's policy 0,
- * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop.  Default 1
- * (every call), or H3Q8_W8A16_SCRATCH_ROWS from the environment.  Problems of at most 128
- * rows are the exception: they read the int8 weight once with main-loop dequantisation
- * and split-K (H3Q8_SKINNY_DIRECT=0 turns the exception off). */
+ * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop.  Without this call
+ * (and without H3Q8_W8A16_SCRATCH_ROWS in the environment) the policy follows the shape:
+ * main-loop dequantisation for at most 512 rows with input_dim <= 4096, where one pass over
+ * the weight costs more than the slower main loop, scratch otherwise.  Problems of at most
+ * 128 rows read the int8 weight once with main-loop dequantisation and split-K under every
+ * setting (H3Q8_SKINNY_DIRECT=0 turns that off). */
 int h3q8_gpu_set_w8a16_scratch_rows(h3_gpu *gpu, uint32_t rows);
 /* A linear cut along K, or across GPUs (the tensor-parallel FFN): h3q8_gpu_linear_partial_f32 stores the fp32 partial
  * sums [rows, output_dim] of one K slice (bf16 or W8A16 weights, no epilogue term); the caller adds the slices in fp32
