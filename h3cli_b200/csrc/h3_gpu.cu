@@ -1088,7 +1088,7 @@ static size_t round256(size_t n) { return (n + 255) & ~(size_t)255; }
  * few rows and a short K. */
 static bool w8a16_to_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q) {
     if (q.activation == H3Q8_ACT_SWIGLU) return g->w8a16_scratch_rows != 0;
-    if (g->w8a16_scratch_rows < 0) return q.rows > 512 || q.input_dim > 4096;
+    if (g->w8a16_scratch_rows < 0) return q.rows > 1024 || q.input_dim > 4096;
     return g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows;
 }
 

@@ -386,7 +386,7 @@ int h3q8_gpu_tensor_download_async(h3_gpu_tensor *tensor, void *host, size_t byt
  * context scratch and runs the bf16 GEMM (the reference's policy 0,
  * src/metal/q8_host.inc:75-88); 0 = always dequantise in the main loop.  Without this call
  * (and without H3Q8_W8A16_SCRATCH_ROWS in the environment) the policy follows the shape:
- * main-loop dequantisation for at most 512 rows with input_dim <= 4096, where one pass over
+ * main-loop dequantisation for at most 1024 rows with input_dim <= 4096, where one pass over
  * the weight costs more than the slower main loop, scratch otherwise.  Problems of at most
  * 128 rows read the int8 weight once with main-loop dequantisation and split-K under every
  * setting (H3Q8_SKINNY_DIRECT=0 turns that off). */
