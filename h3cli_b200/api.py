@@ -13,6 +13,7 @@ MODE_BF16, MODE_W8A16, MODE_W8A8 = 0, 1, 2
 ACT_NONE, ACT_GELU_TANH, ACT_SWIGLU = 0, 1, 2
 KERNEL_AUTO, KERNEL_PLAIN, KERNEL_TCGEN05, KERNEL_TCGEN05_M256, KERNEL_TCGEN05_N128, KERNEL_TCGEN05_PAIR = 0, 1, 2, 3, 4, 5
 KERNEL_TCGEN05_SPLITK = 6
+KERNEL_TCGEN05_SKINNY = 7
 F32, BF16, I8, U32, F16 = 0, 1, 2, 3, 4
 HOST_VISIBLE, DEVICE_ONLY, HOST_PINNED = 0, 1, 2
 

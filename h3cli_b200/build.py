@@ -46,7 +46,7 @@ def build(force=False, verbose=False):
     dit_o = os.path.join(build_dir, "dit_linear.o")
     run(["gcc", "-O2", "-std=c11", "-fPIC", "-D_GNU_SOURCE", "-Wall", "-I", include, "-c", os.path.join(CSRC, "dit_linear.c"), "-o", dit_o])
     objects = [pack_o, cache_o, plan_o, dit_o]
-    for unit in ("h3q8_raw.cu", "h3_gpu.cu", "h3q8_static.cu", "h3q8_pair_grouped.cu"):
+    for unit in ("h3q8_raw.cu", "h3_gpu.cu", "h3q8_static.cu", "h3q8_pair_grouped.cu", "h3q8_skinny.cu"):
         obj = os.path.join(build_dir, unit.replace(".cu", ".o"))
         run([_nvcc(), *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-I", include, "-I", CSRC, "-c",
              os.path.join(CSRC, unit), "-o", obj])

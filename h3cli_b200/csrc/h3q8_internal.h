@@ -9,4 +9,7 @@ uint32_t static_status_take();          /* error word inside the static scratch 
 struct PairArgs;
 /* grouped-scale two-CTA W8A8 kernel (its own translation unit; every fp32 step is an explicit __fmul_rn / __fadd_rn) */
 int launch_pair_grouped_kernel(const PairArgs &args, bool magic, bool wide, int sms, void *stream);
+struct SkinnyArgs;
+/* weight-streaming kernel for at most 64 rows: K split over a cluster, partial sums reduced through distributed shared memory */
+int launch_skinny_kernel(SkinnyArgs &args, uint32_t mode, int sms, void *stream);
 }

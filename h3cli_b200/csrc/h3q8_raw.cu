@@ -11,6 +11,7 @@
 
 #include "h3q8.h"
 #include "h3q8_internal.h"
+#include "gemm_tcgen05_skinny.cuh"
 #include "kernels_misc.cuh"
 
 namespace h3q8 {
@@ -329,6 +330,20 @@ static int launch_splitk(const h3q8_linear_desc &d, GemmParams p, DeviceState *d
     return cuda_ok(e != cudaSuccess ? e : cudaGetLastError(), "tcgen05 split-K linear launch");
 }
 
+static int launch_skinny(const h3q8_linear_desc &d, const GemmParams &p, DeviceState *dev, cudaStream_t stream) {
+    SkinnyArgs args;
+    memset(&args, 0, sizeof args);
+    args.p = p;
+    args.tokens16 = (d.rows + 15u) & ~15u;
+    const uint32_t w_bytes = d.mode == H3Q8_MODE_BF16 ? 2 : 1, x_bytes = d.mode == H3Q8_MODE_W8A8 ? 1 : 2;
+    /* 128-byte operand rows: 64 bf16 or 128 int8 (the raw W8A16 tile covers two 64-wide k-blocks) */
+    if (!make_map(&args.map_w, d.weight, w_bytes, d.output_dim, d.input_dim, 128 / w_bytes, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    /* token tiles: 64 rows, or exactly the padded row count where shared memory is tight (W8A16 keeps four converted weight tiles) */
+    if (!make_map(&args.map_x, d.input, x_bytes, d.rows, d.input_dim, 128 / x_bytes, d.mode == H3Q8_MODE_W8A16 ? args.tokens16 : 64,
+                  CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    return launch_skinny_kernel(args, d.mode, dev->sms, stream);   /* chooses the K split */
+}
+
 template <int MODE>
 static int launch_plain(const h3q8_linear_desc &d, const GemmParams &p, cudaStream_t stream) {
     dim3 grid((d.output_dim + 63) / 64, (d.rows + 63) / 64);
@@ -342,6 +357,7 @@ static int launch_mode(const h3q8_linear_desc &d, const GemmParams &p, uint32_t 
     const bool grouped8 = MODE == MODE_W8A8 && p.scale_group != 0;
     if (kernel == H3Q8_KERNEL_PLAIN) return launch_plain<MODE>(d, p, stream);
     if (kernel == H3Q8_KERNEL_TCGEN05_SPLITK) return launch_splitk<MODE>(d, p, dev, stream);
+    if (kernel == H3Q8_KERNEL_TCGEN05_SKINNY) return launch_skinny(d, p, dev, stream);
     if (grouped8) {
         if (MODE != MODE_W8A8) return fail("grouped W8A8 reached a non-W8A8 launch");
         if (kernel == H3Q8_KERNEL_TCGEN05_PAIR)
@@ -421,7 +437,10 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     const bool grouped_pair_ok = d.mode == H3Q8_MODE_W8A8 && p.scale_group && p.scale_group % 128 == 0 &&
                                  d.input_dim % p.scale_group == 0 && !swiglu && !d.rope;
     kernel = d.kernel;
-    if (kernel > H3Q8_KERNEL_TCGEN05_SPLITK) return fail("linear: unknown kernel selector %u", kernel);
+    if (kernel > H3Q8_KERNEL_TCGEN05_SKINNY) return fail("linear: unknown kernel selector %u", kernel);
+    /* the weight-streaming kernel: at most 64 rows, per-channel int8 scales, bias / GELU / gate / residual epilogue */
+    const bool skinny_ok = d.rows <= 64 && !(d.mode == H3Q8_MODE_W8A8 && p.scale_group) && !swiglu && !d.rope && !d.accumulators &&
+                           d.output;
     /* split-K: raw sums go through the workspace, so no per-group combine, second accumulator, rotary epilogue or dump */
     const bool splitk_ok = !(d.mode == H3Q8_MODE_W8A8 && p.scale_group) && !swiglu && !d.rope && !d.accumulators && d.workspace &&
                            aligned16(d.workspace);
@@ -435,8 +454,9 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
         /* SwiGLU runs on the two-CTA kernel (gate rows in one CTA, up rows in its peer) or on the plain kernel */
         /* one row tile: the weight is streamed once and the problem is bandwidth bound, so spread K over the idle SMs */
         uint32_t splits, kb_per_split;
-        if (kernel != H3Q8_KERNEL_PLAIN && d.rows <= 128 && splitk_ok &&
-            plan_splitk(d.mode, d.rows, d.input_dim, d.output_dim, dev->sms, d.workspace_bytes, splits, kb_per_split))
+        if (kernel != H3Q8_KERNEL_PLAIN && skinny_ok) kernel = H3Q8_KERNEL_TCGEN05_SKINNY;
+        else if (kernel != H3Q8_KERNEL_PLAIN && d.rows <= 128 && splitk_ok &&
+                 plan_splitk(d.mode, d.rows, d.input_dim, d.output_dim, dev->sms, d.workspace_bytes, splits, kb_per_split))
             kernel = H3Q8_KERNEL_TCGEN05_SPLITK;
         if (swiglu) kernel = tma_ok ? H3Q8_KERNEL_TCGEN05_PAIR : H3Q8_KERNEL_PLAIN;
         if (d.rope) kernel = H3Q8_KERNEL_TCGEN05_PAIR;
@@ -455,6 +475,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
         return fail("linear: the two-CTA W8A8 kernel takes scale groups that are multiples of 128 and divide K");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && d.mode == H3Q8_MODE_W8A16 && d.accumulators) {
         return fail("linear: the two-CTA W8A16 kernel has no accumulator dump");
+    } else if (kernel == H3Q8_KERNEL_TCGEN05_SKINNY && !skinny_ok) {
+        return fail("linear: the weight-streaming kernel takes at most 64 rows, ungrouped W8A8 scales, and no SwiGLU / rotary epilogue / accumulator dump");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_SPLITK && !splitk_ok) {
         return fail("linear: split-K takes ungrouped scales, no SwiGLU / rotary epilogue / accumulator dump, and a 16-byte aligned workspace");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {

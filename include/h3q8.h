@@ -104,9 +104,13 @@ enum { /* kernel selection; AUTO picks by shape */
     H3Q8_KERNEL_TCGEN05_N128 = 4, /* tcgen05/TMA kernel, 128 x 128 tiles            */
     H3Q8_KERNEL_TCGEN05_PAIR = 5, /* two-CTA tcgen05 kernel, 256 x 256 tiles per CTA
                                      pair (BF16 and W8A8 per-channel modes)         */
-    H3Q8_KERNEL_TCGEN05_SPLITK = 6 /* skinny M: 128 x 128 tiles, K split over several
+    H3Q8_KERNEL_TCGEN05_SPLITK = 6, /* skinny M: 128 x 128 tiles, K split over several
                                      CTAs per tile, partial sums in `workspace`, then
                                      a finishing kernel (weight-bandwidth bound)     */
+    H3Q8_KERNEL_TCGEN05_SKINNY = 7 /* at most 64 rows: the weight is the MMA's wide
+                                     operand, K split over a thread-block cluster,
+                                     partial sums reduced through distributed shared
+                                     memory; one launch, no workspace                */
 };
 
 /* QKV epilogue (src/cuda/cuda_kernels.cuh:988-1045 with the grouped column layout of

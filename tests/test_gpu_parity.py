@@ -351,7 +351,8 @@ def test_skinny_split_k(gpu, oracle, mode, M, N, K, kernel):
     launches = lib.h3q8_kernel_launches()
     gpu.raw_linear(mode=mode_id, rows=M, input_dim=K, output_dim=N, weight_group=group, activation=act, kernel=kernel, output=out,
                    workspace=workspace, workspace_bytes=nbytes, **t)
-    assert gpu.raw_status() == 0 and lib.h3q8_kernel_launches() - launches == 2      # split GEMM + finishing kernel
+    # split GEMM + finishing kernel; up to 64 rows AUTO prefers the one-launch weight-streaming kernel
+    assert gpu.raw_status() == 0 and lib.h3q8_kernel_launches() - launches == (1 if kernel == h.KERNEL_AUTO and M <= 64 else 2)
     got = out.read()
     assert (got[M * N:] == 0x3F80).all(), "wrote past the end of the output"
     if mode == "w8a8" and not act:
@@ -362,6 +363,49 @@ def test_skinny_split_k(gpu, oracle, mode, M, N, K, kernel):
         gpu.raw_linear(mode=mode_id, rows=M, input_dim=K, output_dim=N, weight_group=group, activation=act,
                        kernel=h.KERNEL_TCGEN05_SPLITK, output=out, workspace=workspace, workspace_bytes=M * N * 4, **t)
     for tensor in list(t.values()) + [out, workspace]:
+        tensor.free()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 3072, 3072), (16, 3072, 3072), (16, 12288, 3072), (16, 3072, 12288), (33, 520, 1536),
+                                   (64, 1536, 12288), (47, 256, 16000), (5, 136, 1040), (17, 128, 128), (64, 8, 4096)])
+@pytest.mark.parametrize("mode", ["bf16", "w8a16", "w8a16g64", "w8a16g128", "w8a8"])
+def test_skinny_weight_streaming(gpu, oracle, mode, M, N, K):
+    """At most 64 rows: the weight is the MMA's wide operand, K is split over a thread-block cluster and the partial
+    sums are reduced through distributed shared memory in ascending split order -- one launch, no workspace.
+    int32 partial sums are exact, so W8A8 stays bit-equal to the oracle; ragged N, K tails and every epilogue term."""
+    group = {"w8a16g64": 64, "w8a16g128": 128}.get(mode, 0)
+    if group and K % group:
+        pytest.skip("group width must divide K")
+    x, wq, ws = operands(67, M, N, K, group, outliers=mode == "w8a8")
+    bias, gate, res, act = epilogue_operands(67, M, N, "bgr" if M % 2 else "ba")
+    lib = h.library()
+    mode_id = h.MODE_BF16 if mode == "bf16" else h.MODE_W8A8 if mode == "w8a8" else h.MODE_W8A16
+    if mode == "bf16":
+        wb = oracle.q8_dequant(wq, ws, 0)
+        want = oracle.linear(oracle.MODE_BF16, x, wb, bias=bias, gate=gate, residual=res, activation=act)
+        t = upload(gpu, input=x, weight=wb, bias=bias, gate=gate, residual=res)
+    elif mode == "w8a8":
+        xq, xs = oracle.quantize_rows(x)
+        want = oracle.linear(oracle.MODE_W8A8, xq, wq, ws[:, 0].copy(), 0, x_scales=xs, bias=bias, gate=gate, residual=res, activation=act, fast=True)
+        t = upload(gpu, input=xq, weight=wq, weight_scales=ws[:, 0].copy(), input_scales=xs, bias=bias, gate=gate, residual=res)
+    else:
+        want = oracle.linear(oracle.MODE_W8A16, x, wq, ws, group, bias=bias, gate=gate, residual=res, activation=act)
+        t = upload(gpu, input=x, weight=wq, weight_scales=ws, bias=bias, gate=gate, residual=res)
+    out = gpu.tensor_from_bf16(np.full(M * N + GUARD, 0x3F80, np.uint16))
+    launches = lib.h3q8_kernel_launches()
+    gpu.raw_linear(mode=mode_id, rows=M, input_dim=K, output_dim=N, weight_group=group, activation=act,
+                   kernel=h.KERNEL_TCGEN05_SKINNY, output=out, **t)
+    assert gpu.raw_status() == 0 and lib.h3q8_kernel_launches() - launches == 1
+    got = out.read()
+    assert (got[M * N:] == 0x3F80).all(), "wrote past the end of the output"
+    if mode == "w8a8" and not act:
+        assert (got[:M * N].reshape(M, N) == want).all()
+    else:
+        check_bf16(got[:M * N].reshape(M, N), want)
+    with pytest.raises(h.H3Error):                   # more rows than the kernel's token operand holds
+        gpu.raw_linear(mode=mode_id, rows=65, input_dim=K, output_dim=N, weight_group=group, activation=act,
+                       kernel=h.KERNEL_TCGEN05_SKINNY, output=out, **t)
+    for tensor in list(t.values()) + [out]:
         tensor.free()
 
 
