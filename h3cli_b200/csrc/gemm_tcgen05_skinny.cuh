@@ -11,6 +11,8 @@
  *   - K is split over the CTAs of a thread-block cluster (1 to 8) so that tiles x splits
  *     fills the machine; each CTA streams its K range through a deep TMA ring (eight 16 KB
  *     weight tiles in flight per SM);
+ *   - the four K steps of a k-block accumulate into four separate TMEM accumulators, because MMAs
+ *     this narrow are latency-bound and only overlap when they do not chain on one accumulator;
  *   - the partial sums never leave the chip: each CTA writes its [tokens x 128] partial tile
  *     into its own shared memory, the cluster synchronises once, and CTA s sums token rows
  *     s, s + splits, ... over all CTAs in ascending split order through distributed shared
@@ -20,7 +22,7 @@
  * Modes: bf16 x bf16, W8A8 (int8 x int8 -> int32, per-token and per-channel scales in the
  * epilogue) and W8A16 (int8 weights dequantised in the main loop, bf16(float(q) * scale),
  * src/metal/shaders.metal:825-827, by two groups of four warps on alternate 128-wide blocks
- * of K, exactly as in the two-CTA W8A16 kernel).
+ * of K, with the conversion of the two-CTA W8A16 kernel).
  *
  * Every mbarrier wait is bounded; a role that gives up raises the CTA's abort flag, all roles
  * fall through to the two cluster barriers and the common exit, the status word is set and
@@ -51,18 +53,22 @@ struct SkinnyConfig {
     /* rings in K units */
     static constexpr int STAGES = 8;                              /* X (and W unless W8A16); W8A16 uses as many of them as
                                                                      its 32 KB token region holds at the call's row count */
-    static constexpr int RAW_STAGES = MODE == MODE_W8A16 ? 4 : 0;
-    static constexpr int CONV_BUFFERS = MODE == MODE_W8A16 ? 4 : 0;  /* two per dequantiser group: converting never waits for an MMA */
+    /* W8A16: two groups of four dequantiser warps take alternate units, one converted pair each; eight raw tiles keep
+     * 128 KB of the weight stream in flight.  (Four groups, or four converted pairs, measured the same or slower.) */
+    static constexpr int GROUPS = 2;
+    static constexpr int RAW_STAGES = MODE == MODE_W8A16 ? 8 : 0;
+    static constexpr int CONV_BUFFERS = MODE == MODE_W8A16 ? GROUPS : 0;
     static constexpr int X_REGION = 32 * 1024;                    /* W8A16: token tiles of tokens16 rows                */
     static constexpr int STAGE_BYTES = MODE == MODE_W8A16 ? X_REGION / STAGES : X_BYTES + W_BYTES;
     static constexpr int EPILOGUE_WARPS = 4, PRODUCER_WARP = 4, MMA_WARP = 5, FIRST_DEQUANT_WARP = 6;
-    static constexpr int GROUP_WARPS = 4, DEQUANT_WARPS = MODE == MODE_W8A16 ? 2 * GROUP_WARPS : 0;
+    static constexpr int GROUP_WARPS = 4, DEQUANT_WARPS = MODE == MODE_W8A16 ? GROUPS * GROUP_WARPS : 0;
     static constexpr int WARPS = FIRST_DEQUANT_WARP + DEQUANT_WARPS, THREADS = WARPS * 32;
     static constexpr int RING_BYTES = STAGES * STAGE_BYTES + RAW_STAGES * RAW_BYTES + CONV_BUFFERS * SUB * W_BYTES;
     static constexpr int PARTIAL_BYTES = MAX_TOKENS * 128 * 4;   /* aliases the rings once the main loop is done    */
     static constexpr int BARRIERS = 2 * STAGES + 2 * RAW_STAGES + 2 * CONV_BUFFERS + 1;
     static constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
-    static constexpr int TMEM_COLUMNS = 64;
+    static constexpr int ACCUMULATORS = 4;      /* independent partial accumulators, see the MMA issuer */
+    static constexpr int TMEM_COLUMNS = ACCUMULATORS * MAX_TOKENS;
     static_assert(PARTIAL_BYTES <= RING_BYTES, "the partial tile lives in the drained rings");
     static_assert(SMEM_BYTES <= 227 * 1024 && BARRIERS * 8 + 16 <= 512, "shared memory budget");
 };
@@ -162,8 +168,10 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
         /* ------------------------------------------------ MMA issuer */
         if (lane == 0 && unit_begin < unit_end) {
             const uint32_t idesc = MODE == MODE_W8A8 ? umma_idesc(2, 1, 128, tokens16) : umma_idesc(1, 1, 128, tokens16);
+            /* The four K steps of a k-block go to four accumulators (columns j * tokens16), so that MMAs this narrow do not
+             * chain on one accumulator; the epilogue adds the four in a fixed order.  Each MMA still reads its 4 KB of
+             * weights from shared memory, about 60 clocks, which is the floor of this formulation. */
             PipeState st, cv;
-            uint32_t accumulate = 0;
             for (uint32_t u = unit_begin; u < unit_end && !failure; u++) {
                 if (!wait_or_abort(&full[st.index], st.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
                 if (MODE == MODE_W8A16 && !wait_or_abort(&bfull[cv.index], cv.phase, abort_flag)) { failure = STATUS_WAIT_MMA; break; }
@@ -175,11 +183,11 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
                     const uint8_t *w_tile = MODE == MODE_W8A16 ? conv + (cv.index * C::SUB + sub) * C::W_BYTES : stage;
                     const uint8_t *x_tile = MODE == MODE_W8A16 ? stage + sub * x_tile_bytes : stage + C::W_BYTES;
                     const uint64_t w_desc = umma_smem_desc_sw128(smem_u32(w_tile)), x_desc = umma_smem_desc_sw128(smem_u32(x_tile));
+                    const uint32_t accumulate = u > unit_begin || sub > 0;
 #pragma unroll
                     for (int k4 = 0; k4 < 4; k4++) {
-                        if (MODE == MODE_W8A8) umma_i8(tmem_base, w_desc + 2 * k4, x_desc + 2 * k4, idesc, accumulate);
-                        else umma_bf16(tmem_base, w_desc + 2 * k4, x_desc + 2 * k4, idesc, accumulate);
-                        accumulate = 1;
+                        if (MODE == MODE_W8A8) umma_i8(tmem_base + k4 * tokens16, w_desc + 2 * k4, x_desc + 2 * k4, idesc, accumulate);
+                        else umma_bf16(tmem_base + k4 * tokens16, w_desc + 2 * k4, x_desc + 2 * k4, idesc, accumulate);
                     }
                 }
                 umma_commit(&empty[st.index]);
@@ -189,7 +197,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
             if (!failure) umma_commit(tfull);
         }
     } else if (MODE == MODE_W8A16 && warp >= C::FIRST_DEQUANT_WARP) {
-        /* ------------------------------------------------ dequantisers: two groups on alternate units */
+        /* ------------------------------------------------ dequantisers: group g converts units g, g + GROUPS, ... */
         const uint32_t group = (warp - C::FIRST_DEQUANT_WARP) / C::GROUP_WARPS;
         const uint32_t r = threadIdx.x - (C::FIRST_DEQUANT_WARP + C::GROUP_WARPS * group) * 32;   /* weight row of the tile */
         const uint32_t twist = r & 7;
@@ -205,9 +213,9 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
         float upcoming0 = 0.0f, upcoming1 = 0.0f;
         if (unit_begin + group < unit_end) scales_of(unit_begin + group, upcoming0, upcoming1);
         for (uint32_t u = unit_begin; u < unit_end; u++) {
-            if (((u - unit_begin) & 1u) != group) { sr.advance(C::RAW_STAGES); cv.advance(C::CONV_BUFFERS); continue; }
+            if ((u - unit_begin) % C::GROUPS != group) { sr.advance(C::RAW_STAGES); cv.advance(C::CONV_BUFFERS); continue; }
             const float scale[2] = {upcoming0, upcoming1};
-            if (p.scale_groups > 1 && u + 2 < unit_end) scales_of(u + 2, upcoming0, upcoming1);
+            if (p.scale_groups > 1 && u + C::GROUPS < unit_end) scales_of(u + C::GROUPS, upcoming0, upcoming1);
             bool ready = wait_or_abort(&rfull[sr.index], sr.phase, abort_flag);
             ready = ready && wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
             if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_DEQUANT; break; }
@@ -245,8 +253,17 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
         for (uint32_t c = 0; c < tokens16 / 16; c++) {
             uint32_t v[16];
             if (unit_begin < unit_end && !failure) {
+                uint32_t more[3][16];
                 tmem_load_32x16(tmem_base + ((warp * 32u) << 16) + c * 16, v);
+#pragma unroll
+                for (int j = 1; j < C::ACCUMULATORS; j++) tmem_load_32x16(tmem_base + ((warp * 32u) << 16) + j * tokens16 + c * 16, more[j - 1]);
                 tmem_load_wait();
+#pragma unroll
+                for (int j = 1; j < C::ACCUMULATORS; j++)
+#pragma unroll
+                    for (int i = 0; i < 16; i++)
+                        v[i] = MODE == MODE_W8A8 ? v[i] + more[j - 1][i]
+                                                 : __float_as_uint(__fadd_rn(__uint_as_float(v[i]), __uint_as_float(more[j - 1][i])));
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; j++) v[j] = 0;       /* a K slice without work contributes zeros */
@@ -273,15 +290,6 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
             const uint32_t m = split + (item >> 4) * splits, col = (item & 15) * 8, n = n0 + col;
             if (n >= p.N) continue;
             const uint32_t own = smem_u32(partial + m * 128 + col);
-            uint4 v[8][2];
-#pragma unroll
-            for (int s = 0; s < 8; s++) {
-                if ((uint32_t)s < splits) {
-                    const uint32_t peer = map_to_cta(own, s);
-                    v[s][0] = load_cluster_u128(peer);
-                    v[s][1] = load_cluster_u128(peer + 16);
-                } else v[s][0] = v[s][1] = make_uint4(0, 0, 0, 0);
-            }
             uint32_t bias[4] = {0, 0, 0, 0}, gate[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u}, res[4] = {0, 0, 0, 0};
             if (p.ep.bias) *reinterpret_cast<uint4 *>(bias) = *reinterpret_cast<const uint4 *>(p.ep.bias + n);
             if (p.ep.gate) *reinterpret_cast<uint4 *>(gate) = *reinterpret_cast<const uint4 *>(p.ep.gate + n);
@@ -292,22 +300,40 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
                 const float4 s0 = *reinterpret_cast<const float4 *>(p.w_scales + n), s1 = *reinterpret_cast<const float4 *>(p.w_scales + n + 4);
                 const float ws[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
                 int32_t sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (uint32_t first = 0; first < splits; first += 4) {           /* four CTAs' sums in flight at a time */
+                    uint4 v[4][2];
 #pragma unroll
-                for (int s = 0; s < 8; s++) {
-                    const uint32_t w[8] = {v[s][0].x, v[s][0].y, v[s][0].z, v[s][0].w, v[s][1].x, v[s][1].y, v[s][1].z, v[s][1].w};
+                    for (int s = 0; s < 4; s++) {
+                        const uint32_t peer = map_to_cta(own, first + s < splits ? first + s : 0);
+                        v[s][0] = first + s < splits ? load_cluster_u128(peer) : make_uint4(0, 0, 0, 0);
+                        v[s][1] = first + s < splits ? load_cluster_u128(peer + 16) : make_uint4(0, 0, 0, 0);
+                    }
 #pragma unroll
-                    for (int j = 0; j < 8; j++) sum[j] += (int32_t)w[j];
+                    for (int s = 0; s < 4; s++) {
+                        const uint32_t w[8] = {v[s][0].x, v[s][0].y, v[s][0].z, v[s][0].w, v[s][1].x, v[s][1].y, v[s][1].z, v[s][1].w};
+#pragma unroll
+                        for (int j = 0; j < 8; j++) sum[j] += (int32_t)w[j];
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 8; j++) lin[j] = __fmul_rn(__fmul_rn((float)sum[j], a_scale), ws[j]);
             } else {
+                for (uint32_t first = 0; first < splits; first += 4) {
+                    uint4 v[4][2];
 #pragma unroll
-                for (int s = 0; s < 8; s++) {
-                    const uint32_t w[8] = {v[s][0].x, v[s][0].y, v[s][0].z, v[s][0].w, v[s][1].x, v[s][1].y, v[s][1].z, v[s][1].w};
+                    for (int s = 0; s < 4; s++) {
+                        const uint32_t peer = map_to_cta(own, first + s < splits ? first + s : 0);
+                        v[s][0] = first + s < splits ? load_cluster_u128(peer) : make_uint4(0, 0, 0, 0);
+                        v[s][1] = first + s < splits ? load_cluster_u128(peer + 16) : make_uint4(0, 0, 0, 0);
+                    }
 #pragma unroll
-                    for (int j = 0; j < 8; j++)
-                        if (s == 0) lin[j] = __uint_as_float(w[j]);
-                        else if ((uint32_t)s < splits) lin[j] = __fadd_rn(lin[j], __uint_as_float(w[j]));
+                    for (int s = 0; s < 4; s++) {
+                        const uint32_t w[8] = {v[s][0].x, v[s][0].y, v[s][0].z, v[s][0].w, v[s][1].x, v[s][1].y, v[s][1].z, v[s][1].w};
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            if (first + s == 0) lin[j] = __uint_as_float(w[j]);
+                            else if (first + s < splits) lin[j] = __fadd_rn(lin[j], __uint_as_float(w[j]));
+                    }
                 }
             }
             uint32_t packed[4];
