@@ -163,6 +163,7 @@ def main():
                          "(config 5): M=219,600 rows sharded over the GPUs, --layers layers of group-128 weights streamed "
                          "from pinned host memory through two device slots")
     ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--kernel", type=int, default=0, help="--case --graph 1: H3Q8_KERNEL_* selector of the raw call (0 = automatic)")
     ap.add_argument("--graph", type=int, default=0, help="--case: time raw h3q8_linear calls replayed from a CUDA graph (device time of skinny problems)")
     ap.add_argument("--stream-gather", type=int, default=0,
                     help="--workload stream at N > 1: each rank uploads 1/N of a layer, NCCL all-gather assembles it in the local slot")
@@ -1054,25 +1055,33 @@ def run_case(args, gpu, lib, stream, device_bf16):
         mode = {"w8a16": h.MODE_W8A16, "w8a8": h.MODE_W8A8}[args.mode]
         nbytes = lib.h3q8_linear_workspace_bytes(mode, rows, k, n)
         workspace = gpu.tensor_alloc(max(nbytes, 256), 2)
-        d = LinearDesc(mode=mode, rows=rows, input_dim=k, output_dim=n, input=x.device_pointer, weight=weight.device_pointer,
-                       weight_scales=weight.device_pointer + ((wrows * k + 15) & ~15), weight_group=group,
-                       gate=gate.device_pointer if gate else None, residual=residual.device_pointer if residual else None,
-                       activation=1 if "a" in spec else 0, output=out.device_pointer, workspace=workspace.device_pointer if nbytes else None,
-                       workspace_bytes=nbytes)
+        # The weight is the traffic: consecutive calls read DIFFERENT copies of it, 384 MB in all (three times the L2),
+        # so that every call streams its weight from HBM instead of finding the previous call's copy in L2.
+        copies = max(1, min(args.steps, -(-384 * 1024 * 1024 // (wrows * k))))
+        weights = [weight] + [gpu.q8_from_host(wq, ws, group) for _ in range(copies - 1)]
+        descs = []
         if mode == h.MODE_W8A8:
             xq, xs = gpu.tensor_new_i8(rows * k), gpu.tensor_new_f32(rows)
             assert lib.h3q8_quantize_rows(x.device_pointer, xq.device_pointer, xs.device_pointer, rows, rows, k, 1.0, gpu.stream)
-            d.input, d.input_scales = xq.device_pointer, xs.device_pointer
+        for w in weights:
+            d = LinearDesc(mode=mode, rows=rows, input_dim=k, output_dim=n, input=x.device_pointer, weight=w.device_pointer,
+                           weight_scales=w.device_pointer + ((wrows * k + 15) & ~15), weight_group=group,
+                           gate=gate.device_pointer if gate else None, residual=residual.device_pointer if residual else None,
+                           activation=1 if "a" in spec else 0, output=out.device_pointer,
+                           workspace=workspace.device_pointer if nbytes else None, workspace_bytes=nbytes, kernel=args.kernel)
+            if mode == h.MODE_W8A8:
+                d.input, d.input_scales = xq.device_pointer, xs.device_pointer
+            descs.append(d)
         side = torch.cuda.Stream()
         with torch.cuda.stream(side):
-            for _ in range(3):
-                assert lib.h3q8_linear(ctypes.byref(d), side.cuda_stream), lib.h3q8_last_error()
+            for i in range(3):
+                assert lib.h3q8_linear(ctypes.byref(descs[i % copies]), side.cuda_stream), lib.h3q8_last_error()
         torch.cuda.synchronize()
         before = lib.h3q8_kernel_launches()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
-            for _ in range(args.steps):
-                assert lib.h3q8_linear(ctypes.byref(d), side.cuda_stream), lib.h3q8_last_error()
+            for i in range(args.steps):
+                assert lib.h3q8_linear(ctypes.byref(descs[i % copies]), side.cuda_stream), lib.h3q8_last_error()
         per_step = (lib.h3q8_kernel_launches() - before) // args.steps
         graph.replay()
         torch.cuda.synchronize()
@@ -1086,6 +1095,7 @@ def run_case(args, gpu, lib, stream, device_bf16):
             best = ms if best is None or ms < best else best
         assert lib.h3q8_device_status(None) == 0
         print(json.dumps({"case": name, "mode": args.mode, "group": group, "rows": rows, "k": k, "n": n, "timing": "cuda graph replay",
+                          "l2": "calls rotate over %d copies of the weight (%d MB in all): every call reads its weight from HBM" % (copies, copies * wrows * k >> 20),
                           "kernels_per_call": int(per_step), "ms": best, "tflops": 2.0 * rows * k * wrows / best / 1e9,
                           "weight_gbs": wrows * k / best / 1e6, "workspace_bytes": int(nbytes)}), flush=True)
         gpu.free()
