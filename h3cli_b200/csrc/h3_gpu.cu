@@ -1108,7 +1108,8 @@ static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size
         /* few rows: the int8 weight is read once with main-loop dequantisation (weight-streaming kernel up to 64 rows,
          * split-K with a workspace up to 128) */
         const size_t skinny = !g->skinny_direct || swiglu || q.rows > 128 ? 0
-                            : q.rows <= 64 ? 1 : h3q8_linear_workspace_bytes(H3Q8_MODE_W8A16, q.rows, q.input_dim, q.output_dim);
+                            : q.rows <= 64 ? (uint64_t)q.input_dim * q.output_dim >= (1u << 20)   /* a weight worth streaming */
+                            : h3q8_linear_workspace_bytes(H3Q8_MODE_W8A16, q.rows, q.input_dim, q.output_dim);
         if (q.input_dim % 16 == 0 && !skinny && w8a16_to_scratch(g, q)) {
             need[2] = round256((size_t)q.output_dim * (swiglu ? 2 : 1) * q.input_dim * 2);
         } else mode = H3Q8_MODE_W8A16;
