@@ -926,6 +926,7 @@ def test_profile_report_lines(oracle, monkeypatch, capfd):
     def run():
         gpu = h.Gpu()
         gpu.quant_configure(1)
+        gpu.set_w8a16_scratch_rows(1)                  # the conversion category needs the dequantise-to-scratch policy
         h.library().h3_gpu_profile_set_label(gpu.handle, b"unit")
         weight = gpu.q8_from_host(wq, ws, 0)
         tx, out = gpu.tensor_new_bf16(rows * cols), gpu.tensor_new_bf16(rows * n)
