@@ -1224,6 +1224,66 @@ def test_weight_streaming_double_buffered(oracle):
     gpu.free()
 
 
+def test_config5_full_rows_streamed_layers(oracle):
+    """Config 5 at its full row count: M = 219 600 tokens, hidden 3072, FFN 12288, W8A16 group-128 weights streamed
+    layer by layer from pinned host memory through two device slots (two layers here: attention output with gate and
+    residual, then FFN-up with GELU and FFN-down with gate and residual).  24 sampled rows per projection against the
+    oracle; the concatenation property of row sharding is covered by test_config1_single_w8a16."""
+    M, H, F, group = 219600, 3072, 12288, 128
+    gpu = h.Gpu()
+    gpu.quant_configure(1)
+    rng = np.random.default_rng(55)
+    def bf16(shape, mean=0.0, std=1.0):
+        return synth.to_bf16(rng.standard_normal(shape, dtype=np.float32) * np.float32(std) + np.float32(mean)).reshape(shape)
+    x, res, gate = bf16((M, H)), bf16((M, H)), bf16((H,), 1.0, 0.1)
+    specs = [[(H, H)], [(F, H), (H, F)]]                    # layer 0: out projection; layer 1: FFN-up, FFN-down
+    blobs, weights = [], []
+    for layer, shapes in enumerate(specs):
+        parts, kept = [], []
+        for i, (n, k) in enumerate(shapes):
+            wq, ws = synth.int8_weights(60 + layer, 2 + i, n, k), synth.lognormal_scales(60 + layer, 6 + i, n, k // group)
+            blob = h.q8_blob(wq, ws, group)
+            kept.append((wq, ws, sum(part.size for part in parts)))
+            parts.append(np.concatenate([blob, np.zeros(-blob.size % 256, np.uint8)]))
+        blobs.append(np.concatenate(parts))
+        weights.append(kept)
+    slot_bytes = max(blob.size for blob in blobs)
+    host, pointer, view = pinned_bytes(gpu, len(blobs) * slot_bytes)
+    for layer, blob in enumerate(blobs):
+        view[layer * slot_bytes:layer * slot_bytes + blob.size] = blob
+    stream = gpu.weight_stream(slot_bytes, 2)
+    tx, tres, tgate = gpu.tensor_from_bf16(x), gpu.tensor_from_bf16(res), gpu.tensor_from_bf16(gate)
+    attn, hidden, down = gpu.tensor_new_bf16(M * H), gpu.tensor_new_bf16(M * F), gpu.tensor_new_bf16(M * H)
+    views = []
+    slot = stream.prefetch(pointer, slot_bytes)
+    gpu.begin()
+    upcoming = stream.prefetch(pointer + slot_bytes, slot_bytes)
+    stream.acquire(slot)
+    w_out = stream.view(slot, weights[0][0][2], H, H, group)
+    gpu.linear_fused_bf16(attn, tx, w_out, None, tgate, tres, M, H, H, 0)
+    stream.release(slot)
+    gpu.continue_()
+    stream.acquire(upcoming)
+    w_up = stream.view(upcoming, weights[1][0][2], F, H, group)
+    w_down = stream.view(upcoming, weights[1][1][2], H, F, group)
+    gpu.linear_fused_bf16(hidden, attn, w_up, None, None, None, M, H, F, h.ACT_GELU_TANH)
+    gpu.linear_fused_bf16(down, hidden, w_down, None, tgate, attn, M, F, H, 0)
+    stream.release(upcoming)
+    gpu.submit()
+    views += [w_out, w_up, w_down]
+    rows = sample_rows(M, 24, 5)
+    got_attn, got_hidden, got_down = (t.read().reshape(M, -1)[rows] for t in (attn, hidden, down))
+    check_bf16(got_attn, oracle.linear(oracle.MODE_W8A16, x[rows], weights[0][0][0], weights[0][0][1], group, gate=gate, residual=res[rows]))
+    check_bf16(got_hidden, oracle.linear(oracle.MODE_W8A16, got_attn, weights[1][0][0], weights[1][0][1], group, activation=1))
+    check_bf16(got_down, oracle.linear(oracle.MODE_W8A16, got_hidden, weights[1][1][0], weights[1][1][1], group, gate=gate, residual=got_attn))
+    assert gpu.stats().streamed_bytes == 2 * slot_bytes
+    for t in views + [tx, tres, tgate, attn, hidden, down]:
+        t.free()
+    stream.free()
+    host.free()
+    gpu.free()
+
+
 # --------------------------------------------------------------------------- interface behaviour
 def test_int8_operator_family_like_the_reference(oracle):
     """h3_gpu_quantize_weight_int8 + h3_gpu_linear_int8_bf16 (src/metal/gpu.m:3174-3249):
