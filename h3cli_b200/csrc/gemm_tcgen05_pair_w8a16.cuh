@@ -34,6 +34,11 @@
 #pragma once
 #include "gemm_tcgen05_pair.cuh"
 
+/* dequantiser groups; three measured slightly slower than two (the bound is shared-memory bandwidth, not the conversion) */
+#ifndef H3Q8_W8A16_GROUPS
+#define H3Q8_W8A16_GROUPS 2
+#endif
+
 namespace h3q8 {
 
 struct PairW8A16Config {
@@ -52,7 +57,7 @@ struct PairW8A16Config {
      * ring depths matter little once each covers the TMA latency: the kernel is bound by shared-memory bandwidth */
     static constexpr int EPILOGUE_WARPS = 8, RAW_PRODUCER_WARP = EPILOGUE_WARPS, A_PRODUCER_WARP = EPILOGUE_WARPS + 1,
                          MMA_WARP = EPILOGUE_WARPS + 2, FIRST_DEQUANT_WARP = EPILOGUE_WARPS + 3;
-    static constexpr int GROUP_WARPS = 4, DEQUANT_WARPS = 2 * GROUP_WARPS;
+    static constexpr int GROUPS = H3Q8_W8A16_GROUPS, GROUP_WARPS = 4, DEQUANT_WARPS = GROUPS * GROUP_WARPS;
     static_assert((EPILOGUE_WARPS == 4 || EPILOGUE_WARPS == 8) && (GROUP_WARPS == 4 || GROUP_WARPS == 8), "role layout");
     static constexpr int WARPS = FIRST_DEQUANT_WARP + DEQUANT_WARPS, THREADS = WARPS * 32;
     static constexpr int BARRIERS = 2 * A_STAGES + 2 * RAW_STAGES + 2 * CONV_BUFFERS + 2 * ACC_BUFFERS;
@@ -245,16 +250,16 @@ gemm_tcgen05_pair_w8a16_kernel(const __grid_constant__ PairArgs args) {
             const float *scales_now = row_scales;
             const bool live_now = live;
             float upcoming0 = first0, upcoming1 = first1;
-            const uint32_t mine_first = (turn & 1u) == group ? 0u : 1u;   /* this group's first block of the tile */
+            const uint32_t mine_first = (group + C::GROUPS - turn % C::GROUPS) % C::GROUPS;   /* this group's first block of the tile */
             if (p.scale_groups > 1 && mine_first && mine_first < num_wb) scales_of(scales_now, live_now, mine_first, upcoming0, upcoming1);
             if (tile + pairs < total_tiles) {
                 row_scales = scale_pointer(tile + pairs, live);
                 scales_of(row_scales, live, 0, first0, first1);
             }
             for (uint32_t wb = 0; wb < num_wb; wb++, turn++) {
-                if ((turn & 1u) != group) { st.advance(C::RAW_STAGES); cv.advance(C::CONV_BUFFERS); continue; }
+                if (turn % C::GROUPS != group) { st.advance(C::RAW_STAGES); cv.advance(C::CONV_BUFFERS); continue; }
                 const float scale[2] = {upcoming0, upcoming1};
-                if (p.scale_groups > 1 && wb + 2 < num_wb) scales_of(scales_now, live_now, wb + 2, upcoming0, upcoming1);
+                if (p.scale_groups > 1 && wb + C::GROUPS < num_wb) scales_of(scales_now, live_now, wb + C::GROUPS, upcoming0, upcoming1);
                 bool ready = wait_or_abort(&rfull[st.index], st.phase, abort_flag);
                 ready = ready && wait_or_abort(&bempty[cv.index], cv.phase ^ 1, abort_flag);
                 if (!__all_sync(0xffffffffu, ready)) { failure = STATUS_WAIT_DEQUANT; break; }
