@@ -37,6 +37,8 @@ REAL_LAYERS = [("real_qkv", 5376, 21504, ""), ("real_qkv_rope", 5376, 21504, "q"
 # name, K, N, epilogue
 LAYERS = [("qkv", HIDDEN, 3 * HIDDEN, ""), ("attn_out", HIDDEN, HIDDEN, "gr"),
           ("ffn_up", HIDDEN, FFN, "a"), ("ffn_down", FFN, HIDDEN, "gr")]
+# BASELINE configs 1 and 3: one linear, K = N = 3072, bias (and GELU-tanh for config 3); --rows 4096
+CONFIG_CASES = [("config1", HIDDEN, HIDDEN, "b"), ("config3", HIDDEN, HIDDEN, "ba")]
 FLOP_PER_STEP = sum(2.0 * M_TOKENS * k * n for _, k, n, _ in LAYERS)
 METRIC = "q8_dit_block_linear_tflops"
 UNIT = "TFLOP/s"
@@ -163,6 +165,7 @@ def main():
                          "(config 5): M=219,600 rows sharded over the GPUs, --layers layers of group-128 weights streamed "
                          "from pinned host memory through two device slots")
     ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--flush-l2", type=int, default=0, help="--case: write 256 MB between iterations and time each call on its own (cold L2)")
     ap.add_argument("--kernel", type=int, default=0, help="--case --graph 1: H3Q8_KERNEL_* selector of the raw call (0 = automatic)")
     ap.add_argument("--graph", type=int, default=0, help="--case: time raw h3q8_linear calls replayed from a CUDA graph (device time of skinny problems)")
     ap.add_argument("--stream-gather", type=int, default=0,
@@ -1028,7 +1031,7 @@ def run_helpers(args, gpu, lib, stream, device_bf16):
 def run_case(args, gpu, lib, stream, device_bf16):
     """One projection at --rows rows: the small workload used under ncu."""
     import torch
-    name, k, n, spec = next(layer for layer in LAYERS + REAL_LAYERS if layer[0] == args.case)
+    name, k, n, spec = next(layer for layer in LAYERS + REAL_LAYERS + CONFIG_CASES if layer[0] == args.case)
     rows = args.rows
     real = name.startswith("real_")
     wrows = 2 * n if "s" in spec else n
@@ -1040,6 +1043,7 @@ def run_case(args, gpu, lib, stream, device_bf16):
     x, out = device_bf16(rows, k, seed=1), gpu.tensor_new_bf16(rows * n)
     residual = device_bf16(rows, n, seed=3) if "r" in spec else None
     gate = device_bf16(1, n, 1.0, 0.1, seed=4) if "g" in spec else None
+    bias = device_bf16(1, n, 0.0, 0.02, seed=9) if "b" in spec else None
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if "q" in spec:   # QKV projection with per-head RMS norm + RoPE in the epilogue: 56 heads x 128, rotary half 48
         heads, half = n // 384, 48
@@ -1100,19 +1104,38 @@ def run_case(args, gpu, lib, stream, device_bf16):
                           "weight_gbs": wrows * k / best / 1e6, "workspace_bytes": int(nbytes)}), flush=True)
         gpu.free()
         return
+    def call():
+        if "q" in spec:
+            gpu.grouped_qkv_linear_rope_bf16(q, kk, v, None, x, weight, qn, kn, cos, sin, rows, k, heads, 128, half, 1e-5)
+        else:
+            gpu.linear_fused_bf16(out, x, weight, bias, gate, residual, rows, k, n, 2 if "s" in spec else 1 if "a" in spec else 0)
+
     gpu.begin()
     for i in range(args.warmup + args.steps):
         if i == args.warmup:
             start.record(stream)
-        if "q" in spec:
-            gpu.grouped_qkv_linear_rope_bf16(q, kk, v, None, x, weight, qn, kn, cos, sin, rows, k, heads, 128, half, 1e-5)
-            continue
-        gpu.linear_fused_bf16(out, x, weight, None, gate, residual, rows, k, n, 2 if "s" in spec else 1 if "a" in spec else 0)
+        call()
     stop.record(stream)
     gpu.submit()
     ms = start.elapsed_time(stop) / args.steps
-    print(json.dumps({"case": name, "mode": args.mode, "group": group, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * wrows / ms / 1e9, "weight_gbs": wrows * k / ms / 1e6,
-                      "launches": int(lib.h3q8_kernel_launches())}), flush=True)
+    record = {"case": name, "mode": args.mode, "group": group, "rows": rows, "k": k, "n": n, "ms": ms, "tflops": 2.0 * rows * k * wrows / ms / 1e9,
+              "weight_gbs": wrows * k / ms / 1e6, "launches": int(lib.h3q8_kernel_launches())}
+    if args.flush_l2:
+        # cold L2: 256 MB are written on the same stream between calls, and every call is timed on its own
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+        pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+        gpu.begin()
+        for first, last in pairs:
+            with torch.cuda.stream(stream):
+                flush.zero_()
+            first.record(stream)
+            call()
+            last.record(stream)
+        gpu.submit()
+        cold = sorted(first.elapsed_time(last) for first, last in pairs)
+        record.update({"ms_cold_l2_median": cold[len(cold) // 2], "ms_cold_l2_min": cold[0],
+                       "tflops_cold_l2": 2.0 * rows * k * wrows / cold[len(cold) // 2] / 1e9, "l2": "256 MB written between calls"})
+    print(json.dumps(record), flush=True)
     gpu.free()
 
 

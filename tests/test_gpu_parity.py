@@ -630,12 +630,16 @@ def test_config2_block_stack(oracle):
         gpu.free()
 
 
+@pytest.mark.parametrize("shape", ["proj", "qkv", "ffn_up"])
 @pytest.mark.parametrize("quant_mode", [1, 2])
-def test_config4_grouped_call(oracle, quant_mode):
+def test_config4_grouped_call(oracle, quant_mode, shape):
     """Video (M = 2 x 32 400, K=N=3072) and audio (M = 2 x 1 152, K=N=1536) problems with separate
     weight sets in ONE GEMM launch, at the configuration's full row counts: after the per-problem
-    conversion kernels exactly one more kernel is launched; sampled rows against the oracle."""
-    specs = [(2 * 32400, 3072, 3072), (2 * 1152, 1536, 1536)]
+    conversion kernels exactly one more kernel is launched; sampled rows against the oracle.
+    "qkv" and "ffn_up" are the same launch with the QKV (N = 3 x hidden) and FFN-up (N = 4 x hidden)
+    widths of both streams."""
+    factor = {"proj": 1, "qkv": 3, "ffn_up": 4}[shape]
+    specs = [(2 * 32400, factor * 3072, 3072), (2 * 1152, factor * 1536, 1536)]
     gpu = h.Gpu()
     gpu.quant_configure(quant_mode)
     gpu.set_w8a16_scratch_rows(1)
