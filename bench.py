@@ -157,7 +157,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="h3q8")
-    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS] + ["helpers", "grouped_streams", "real_block_int8"],
+    ap.add_argument("--case", default=None, choices=[name for name, _, _, _ in LAYERS + REAL_LAYERS + CONFIG_CASES] + ["helpers", "grouped_streams", "real_block_int8"],
                     help="profiling aid: run only this projection (with --rows) and print a short line")
     ap.add_argument("--rows", type=int, default=M_TOKENS, help="rows per GPU for --case")
     ap.add_argument("--workload", default="block", choices=["block", "stream", "tp_ffn"],

@@ -33,6 +33,7 @@ class LinearDesc(C.Structure):
         ("input_scales", C.c_void_p), ("bias", C.c_void_p), ("gate", C.c_void_p), ("residual", C.c_void_p),
         ("activation", C.c_uint32), ("output", C.c_void_p), ("accumulators", C.c_void_p), ("kernel", C.c_uint32),
         ("input_group", C.c_uint32), ("rope", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("after_producer", C.c_uint32),
     ]
 
 

@@ -56,6 +56,9 @@ struct GemmParams {
      * producer that leaves out the very first operand load, so that a wait runs out and the error path is exercised */
     long long wait_limit;
     uint32_t skip_first_load;
+    /* launched as a programmatic dependent of the kernel that writes one of the operands: the producer role waits for
+     * that grid (griddepcontrol.wait) before its first load */
+    uint32_t wait_previous;
 };
 
 template <int MODE, int BN, int MT, bool GROUPED>

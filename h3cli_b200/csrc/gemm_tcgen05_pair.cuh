@@ -107,6 +107,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
 
     if (warp == C::PRODUCER_WARP) {
         if (lane == 0) {
+            if (args.p[0].wait_previous) grid_dependency_wait();   /* an operand is still being written by the previous kernel */
             PipeState st;
             for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
                 uint32_t local, mb, nb;

@@ -61,6 +61,7 @@ struct h3_gpu {
     int w8a16_scratch_rows = -1; /* rows at or above which W8A16 dequantises to scratch first; 0 = never; -1 = by shape */
     void *arena[4] = {nullptr, nullptr, nullptr, nullptr}; /* 0 int8 activations, 1 activation scales, 2 bf16 weight scratch, 3 split-K partial sums */
     size_t arena_bytes[4] = {0, 0, 0, 0};
+    int dependent_launch = 1;   /* GEMMs start as programmatic dependents of their conversion kernel; H3Q8_DEPENDENT_LAUNCH=0 turns it off */
     int skinny_direct = 1;      /* W8A16 with at most 128 rows: main-loop dequantisation + split-K (the weight is read once as int8) */
     uint32_t *flags = nullptr;  /* [0] kernel wait status, [1] non-finite seen */
     unsigned long long *diagnostics = nullptr;   /* [0] clipped, [1] non-zero values quantised to zero; H3_QUANT_DIAGNOSTICS=1 */
@@ -235,6 +236,8 @@ extern "C" h3_gpu *h3_gpu_create(const char *, char *error, size_t error_size) {
         g->allocation_budget = g->weight_options.allocation_limit;
     }
     g->profiling = getenv("H3_PROFILE") != nullptr;
+    const char *dependent = getenv("H3Q8_DEPENDENT_LAUNCH");
+    if (dependent && *dependent) g->dependent_launch = atoi(dependent);
     const char *skinny = getenv("H3Q8_SKINNY_DIRECT");
     if (skinny && *skinny) g->skinny_direct = atoi(skinny);
     const char *policy = getenv("H3Q8_W8A16_SCRATCH_ROWS");
@@ -1092,6 +1095,14 @@ static bool w8a16_to_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q) {
     return g->w8a16_scratch_rows && q.rows >= (uint32_t)g->w8a16_scratch_rows;
 }
 
+/* Whether the GEMM of a problem starts as a programmatic dependent of its conversion kernel (set-up overlapped with
+ * that kernel's tail).  Worth 2-3 us per call, which is 3-4 % of a 4 096-row projection; at 32 400 rows it is lost in the
+ * noise for K = 3 072 and costs 1 % at K = 12 288, where the early-resident GEMM blocks take thread slots from a
+ * conversion grid of many waves.  Never with profiling: the event between the two kernels breaks the dependency. */
+static bool dependent_launch(const h3_gpu *g, const h3_gpu_linear_problem &q) {
+    return g->dependent_launch && !g->profiling && q.rows <= 8192;
+}
+
 /* Scratch a problem needs from the context arenas: [0] int8 activations, [1] their scales, [2] bf16 weight,
  * [3] split-K partial sums (problems of at most 128 rows are spread over all SMs). */
 static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size_t need[4]) {
@@ -1194,6 +1205,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
                 d.mode = H3Q8_MODE_W8A8;
                 d.input = xq;
                 d.input_scales = xs;
+                d.after_producer = dependent_launch(g, q);   /* the quantiser is the kernel right before the GEMM */
             } else if (need[2]) {
                 /* policy 0 of the reference: dequantise once, then a bf16 GEMM (src/metal/q8_host.inc:75-88) */
                 uint16_t *wb = (uint16_t *)((char *)g->arena[2] + offset[2]);
@@ -1207,6 +1219,7 @@ static int linear_dispatch_many(h3_gpu *g, const h3_gpu_linear_problem *problems
                 d.weight = wb;
                 d.weight_scales = nullptr;
                 d.weight_group = 0;
+                d.after_producer = dependent_launch(g, q);   /* the dequantiser is the kernel right before the GEMM */
             } else d.mode = H3Q8_MODE_W8A16;
             g->stats.q8_dispatches++;
             g->stats.quant_projection_dispatches++;

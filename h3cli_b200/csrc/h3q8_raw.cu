@@ -181,9 +181,29 @@ static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, 
         clusters[device] = active < dev->sms / 2 ? active : dev->sms / 2;
     }
     const uint32_t pairs = tiles < (uint32_t)clusters[device] ? tiles : (uint32_t)clusters[device];
-    kernel<<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(args);
+    bool dependent = false;
+    for (uint32_t i = 0; i < count; i++) dependent = dependent || params[i].wait_previous;
+    args.p[0].wait_previous = dependent;
+    if (!dependent) {
+        kernel<<<2 * pairs, C::THREADS, C::SMEM_BYTES, stream>>>(args);
+        count_launch(1);
+        return cuda_ok(cudaGetLastError(), "tcgen05 pair linear launch");
+    }
+    /* programmatic dependent of the conversion kernel enqueued just before: resident and set up while that kernel
+     * drains; its producer role waits for the conversion's completion before the first operand load */
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(2 * pairs);
+    config.blockDim = dim3(C::THREADS);
+    config.dynamicSmemBytes = C::SMEM_BYTES;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, kernel, args);
     count_launch(1);
-    return cuda_ok(cudaGetLastError(), "tcgen05 pair linear launch");
+    return cuda_ok(e != cudaSuccess ? e : cudaGetLastError(), "tcgen05 pair linear launch");
 }
 
 /* W8A16 with main-loop dequantisation on the two-CTA tile (one problem per launch). */
@@ -417,6 +437,7 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     p.w_scales = d.weight_scales; p.a_scales = d.input_scales;
     p.ep.bias = d.bias; p.ep.gate = d.gate; p.ep.residual = d.residual; p.ep.activation = d.activation;
     p.out = d.output; p.acc_dump = d.accumulators; p.status = dev->status;
+    p.wait_previous = d.after_producer != 0;
     p.wait_limit = injected_wait_limit.load(std::memory_order_relaxed);
     p.skip_first_load = injected_skip_first_load.load(std::memory_order_relaxed);
     if (d.rope) {

@@ -66,6 +66,7 @@ static __global__ void __launch_bounds__(256) quantize_rows_kernel(const uint16_
                                                             float *__restrict__ scales, uint32_t rows, uint32_t columns,
                                                             float clip, uint32_t *nonfinite) {
     __shared__ uint32_t scratch[8];
+    grid_dependency_trigger();   /* the GEMM that consumes these rows may set itself up while this grid drains */
     const uint32_t row = blockIdx.x;
     int8_t *q = out + (size_t)row * columns;
     const bool vec = (columns & 7u) == 0;
@@ -133,6 +134,7 @@ template <int ITERS>
 static __global__ void __launch_bounds__(256) quantize_segments_warp_kernel(const uint16_t *__restrict__ in, int8_t *__restrict__ out,
                                                                      float *__restrict__ scales, uint64_t live, uint64_t total,
                                                                      uint32_t segment, float clip, uint32_t *nonfinite) {
+    grid_dependency_trigger();   /* the GEMM that consumes these rows may set itself up while this grid drains */
     const uint64_t s = (uint64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (s >= total) return;
     const uint32_t lane = threadIdx.x & 31, vectors = segment / 8;
@@ -420,6 +422,7 @@ static __global__ void __launch_bounds__(256) q8_pack_rows_kernel(const uint16_t
 static __global__ void __launch_bounds__(256) q8_dequant_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                                                          uint16_t *__restrict__ out, uint32_t rows, uint32_t columns,
                                                          uint32_t width, uint32_t groups) {
+    grid_dependency_trigger();   /* a GEMM launched as a programmatic dependent may set itself up while this grid drains */
     const uint32_t row = blockIdx.y;
     const int8_t *src = q + (size_t)row * columns;
     uint16_t *dst = out + (size_t)row * columns;

@@ -57,6 +57,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
     }
 }
 
+/* Programmatic dependent launch: a grid launched with that attribute may become resident while its predecessor in the
+ * stream still runs; grid_dependency_wait returns once the predecessor has completed and its writes are visible (at once
+ * when the grid was launched in ordinary stream order); grid_dependency_trigger lets dependents become resident early. */
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 /* --------------------------------------------------------------------- TMA */
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");

@@ -158,6 +158,10 @@ typedef struct {
     void *workspace;          /* optional device scratch (16-byte aligned) for split-K partial sums: with it, problems of
                                  at most 128 rows spread over all SMs (AUTO); needs splits * rows * output_dim * 4 bytes  */
     size_t workspace_bytes;
+    uint32_t after_producer;  /* 1: an operand of this call (the dequantised weight, the quantised activations) is written
+                                 by the kernel enqueued immediately before on the same stream.  The two-CTA kernels are
+                                 then launched as a programmatic dependent: their set-up overlaps that kernel's tail and
+                                 their first operand load waits for its completion.  0 = ordinary stream order. */
 } h3q8_linear_desc;
 /* Bytes of workspace that let a rows x output_dim x input_dim problem use every SM (0 when split-K would not help). */
 size_t h3q8_linear_workspace_bytes(uint32_t mode, uint32_t rows, uint32_t input_dim, uint32_t output_dim);
