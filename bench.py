@@ -173,6 +173,8 @@ def main():
     ap.add_argument("--group", type=int, default=-1, help="weight scale group for --case (default: 64 for real W8A16 shapes, else per channel)")
     ap.add_argument("--e2e-depth", type=int, default=4, help="end-to-end steps in flight (buffer sets)")
     ap.add_argument("--e2e-slices", type=int, default=1, help="row slices per end-to-end step (copy/compute overlap inside a step)")
+    ap.add_argument("--e2e-edge-slices", type=int, default=4, help="row slices of the FIRST and LAST end-to-end step of a run: the pipeline "
+                    "fills and drains a slice at a time instead of a whole batch at a time")
     ap.add_argument("--no-subrecords", action="store_true", help="default run: skip the w8a8 / config5_stream / tp_ffn sub-records")
     ap.add_argument("--mode", default="w8a16", choices=["w8a16", "w8a8"],
                     help="w8a16 (default, BASELINE config 2) or the W8A8 variant: per-token int8 activations, int8 MMAs")
@@ -443,18 +445,33 @@ def measure_block(args, gpu, mode, dev, steps=None):
     E2E_CHUNKS = args.e2e_slices
     DEPTH = max(1, args.e2e_depth)
     host_out = [host_y] + [torch.empty(M_TOKENS * HIDDEN, dtype=torch.int16).pin_memory() for _ in range(DEPTH - 1)]
-    sets = []
-    for _ in range(DEPTH):
+    def new_set(chunks):
         slices = []
-        for begin, end in sharding.all_ranges(M_TOKENS, E2E_CHUNKS):
+        for begin, end in sharding.all_ranges(M_TOKENS, chunks):
             rows = end - begin
             slices.append(dict(rows=rows, offset=begin * HIDDEN * 2, x=gpu.tensor_new_bf16(rows * HIDDEN),
                                qkv=gpu.tensor_new_bf16(rows * 3 * HIDDEN), h1=gpu.tensor_new_bf16(rows * HIDDEN),
                                up=gpu.tensor_new_bf16(rows * FFN), y=gpu.tensor_new_bf16(rows * HIDDEN)))
-        sets.append(slices)
+        return slices
 
-    def enqueue_e2e(index):
-        slices, out = sets[index % DEPTH], host_out[index % DEPTH]
+    sets = [new_set(E2E_CHUNKS) for _ in range(DEPTH)]
+    # The first batch of a run cannot hide its upload behind anything and the last cannot hide its download: those two
+    # batches are cut into EDGE row slices (own tensors), so compute starts after the first slice has arrived and the
+    # last slice's download is all that trails the last GEMM.  Batches in between stay whole: a slice costs a second
+    # pass of the weight dequantiser and smaller GEMMs, which only pays where nothing else overlaps the copy.
+    EDGE = max(1, args.e2e_edge_slices)
+    edge_sets = [new_set(EDGE), new_set(EDGE)] if EDGE != E2E_CHUNKS else None
+    plan = {}                                         # step index -> tensor set in use
+
+    def enqueue_e2e(index, count):
+        if edge_sets and index == 0:
+            slices = edge_sets[0]
+        elif edge_sets and index == count - 1 and count > 1:
+            slices = edge_sets[1]
+        else:
+            slices = sets[index % DEPTH]
+        plan[index] = slices
+        out = host_out[index % DEPTH]
         for c in slices:
             c["x"].upload_async(host_x.data_ptr() + c["offset"], c["rows"] * HIDDEN * 2)
         for c in slices:
@@ -467,7 +484,7 @@ def measure_block(args, gpu, mode, dev, steps=None):
             c["y"].download_async(out.data_ptr() + c["offset"], rows * HIDDEN * 2)
 
     def finish_e2e(index):
-        for c in sets[index % DEPTH]:
+        for c in plan.pop(index):
             c["y"].wait()                             # this step's block output is in host memory
 
     def run_e2e(count, depth):
@@ -475,7 +492,7 @@ def measure_block(args, gpu, mode, dev, steps=None):
         begin = time.perf_counter()
         gpu.begin()                                   # one command scope; h3_gpu_continue commits each slice
         for i in range(count):
-            enqueue_e2e(i)
+            enqueue_e2e(i, count)
             if i >= depth - 1:
                 finish_e2e(i - (depth - 1))
         for i in range(max(0, count - (depth - 1)), count):
@@ -502,7 +519,7 @@ def measure_block(args, gpu, mode, dev, steps=None):
     gpu.set_profiling(False)
     e2e_value = world * FLOP_PER_STEP * steps / e_seconds / 1e12
     h2d_seconds, d2h_seconds = copies_after.h2d_seconds - copies_before.h2d_seconds, copies_after.d2h_seconds - copies_before.d2h_seconds
-    for slices in sets:
+    for slices in sets + (edge_sets or []):
         for c in slices:
             for key in ("x", "qkv", "h1", "up", "y"):
                 c[key].free()
@@ -551,7 +568,8 @@ def measure_block(args, gpu, mode, dev, steps=None):
                         "the DiT block calls them, " + str(E2E_CHUNKS) + " row slices so copies overlap compute) -> h3q8_gpu_tensor_download_async -> "
                         "pinned host y -> h3q8_gpu_tensor_wait; steps are independent batches with " + str(DEPTH) + " buffer sets: "
                         "later steps are enqueued before the host waits for step i's output (ms_per_step_one_at_a_time: no "
-                        "step in flight behind the current one); host wall clock over all steps, max over ranks; h2d_gbs / d2h_gbs: "
+                        "step in flight behind the current one); the first and the last batch of the run are cut into " + str(EDGE) +
+                        " row slices so that the pipeline fills and drains a slice at a time; host wall clock over all steps, max over ranks; h2d_gbs / d2h_gbs: "
                         "bytes / CUDA-event time of this rank's copies; the process is bound to the CPUs of the GPU's NUMA node "
                         "before its pinned buffers are allocated"},
         "gpu_launches": int(launches),
