@@ -11,13 +11,14 @@
  *   - K is split over the CTAs of a thread-block cluster (1 to 8) so that tiles x splits
  *     fills the machine; each CTA streams its K range through a deep TMA ring (eight 16 KB
  *     weight tiles in flight per SM);
- *   - the four K steps of a k-block accumulate into four separate TMEM accumulators, because MMAs
- *     this narrow are latency-bound and only overlap when they do not chain on one accumulator;
+ *   - the four K steps of a k-block accumulate into four separate TMEM accumulators, so that
+ *     consecutive narrow MMAs do not chain on one accumulator (the epilogue adds the four);
  *   - the partial sums never leave the chip: each CTA writes its [tokens x 128] partial tile
  *     into its own shared memory, the cluster synchronises once, and CTA s sums token rows
  *     s, s + splits, ... over all CTAs in ascending split order through distributed shared
- *     memory, eight channels per thread and step (int32 exactly, fp32 in one fixed order: results do not depend on scheduling),
- *     runs the usual epilogue and stores bf16 -- one launch, no workspace.
+ *     memory, eight channels per thread and step (int32 exactly, fp32 in one fixed order:
+ *     results do not depend on scheduling), runs the usual epilogue and stores bf16 -- one
+ *     launch, no workspace.
  *
  * Modes: bf16 x bf16, W8A8 (int8 x int8 -> int32, per-token and per-channel scales in the
  * epilogue) and W8A16 (int8 weights dequantised in the main loop, bf16(float(q) * scale),

@@ -366,6 +366,35 @@ def test_skinny_split_k(gpu, oracle, mode, M, N, K, kernel):
         tensor.free()
 
 
+def test_gemm_as_programmatic_dependent_of_its_dequantiser(gpu, oracle):
+    """h3q8_linear_desc.after_producer: the dequantiser writes the bf16 weight into ONE scratch buffer and the two-CTA
+    GEMM enqueued right behind it is launched as a programmatic dependent.  Two weight sets alternate through the same
+    scratch for 40 calls; if the GEMM's first load did not wait for the dequantiser it would multiply by the other set
+    (or a mixture), so every output is compared with the ordinary-launch result bit for bit."""
+    M, N, K = 1024, 768, 1024
+    lib = h.library()
+    sets, wants, outs = [], [], []
+    x = synth.activations(81, 1, M, K).reshape(M, K)
+    tx = gpu.tensor_from_bf16(x)
+    scratch = gpu.tensor_new_bf16(N * K)
+    for i in range(2):
+        wq, ws = synth.int8_weights(82 + i, 2, N, K), synth.lognormal_scales(82 + i, 3, N, 1)
+        sets.append(upload(gpu, weight=wq, weight_scales=ws))
+        wants.append(raw_linear(gpu, h.MODE_BF16, x, oracle.q8_dequant(wq, ws, 0), kernel=h.KERNEL_TCGEN05_PAIR))
+        check_bf16(wants[i], oracle.linear(oracle.MODE_W8A16, x, wq, ws, 0))
+    outs = [gpu.tensor_new_bf16(M * N) for _ in range(40)]
+    for i, out in enumerate(outs):
+        t = sets[i % 2]
+        assert lib.h3q8_q8_dequant(t["weight"].device_pointer, t["weight_scales"].device_pointer, scratch.device_pointer, N, K, 0, gpu.stream)
+        gpu.raw_linear(mode=h.MODE_BF16, rows=M, input_dim=K, output_dim=N, input=tx, weight=scratch, output=out,
+                       kernel=h.KERNEL_TCGEN05_PAIR, after_producer=1)
+    assert gpu.raw_status() == 0
+    for i, out in enumerate(outs):
+        assert (out.read().reshape(M, N) == wants[i % 2]).all(), i
+    for tensor in outs + [tx, scratch] + [v for t in sets for v in t.values()]:
+        tensor.free()
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 3072, 3072), (16, 3072, 3072), (16, 12288, 3072), (16, 3072, 12288), (33, 520, 1536),
                                    (64, 1536, 12288), (47, 256, 16000), (5, 136, 1040), (17, 128, 128), (64, 8, 4096)])
 @pytest.mark.parametrize("mode", ["bf16", "w8a16", "w8a16g64", "w8a16g128", "w8a8"])
