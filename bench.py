@@ -587,9 +587,11 @@ def measure_block(args, gpu, mode, dev, steps=None):
 def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local, standalone=True):
     """The optional tensor-parallel FFN: every rank sees all M rows; FFN-up is column-parallel (rank r owns FFN
     features [f0, f1), GELU stays local), FFN-down is row-parallel over the same features and stores fp32 partial
-    sums, one NCCL all-reduce per block adds them in fp32, and the finishing call applies gate + residual with the
-    single bf16 rounding -- so the result meets the same tolerance as the unsharded fused call.  The rows are cut
-    into chunks so the all-reduce of chunk c (communication stream) overlaps the GEMMs of chunk c+1."""
+    sums.  The one all-reduce per block is issued as its two halves so that the bf16 rounding sits between them: a
+    reduce-scatter adds the partial sums in fp32 and leaves every rank 1/N of the rows, the finishing call applies
+    gate + residual and the single bf16 rounding to those rows, and an all-gather distributes the bf16 result --
+    the same sums as an fp32 all-reduce, three quarters of its bytes on the wire and 1/N of the finishing work per
+    rank.  The rows are cut into chunks so the communication of chunk c overlaps the GEMMs of chunk c+1."""
     import torch
     import torch.distributed as dist
     from h3cli_b200 import sharding
@@ -606,14 +608,29 @@ def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local, standalo
     gate = device_bf16(1, HIDDEN, 1.0, 0.1, seed=4, replicated=True)
     comm = torch.cuda.Stream()
     parts = []
-    for c, (begin, end) in enumerate(sharding.all_ranges(rows_total, chunks)):
-        rows = end - begin
+    # chunk sizes are multiples of 8 * world rows, so that every rank's share of a chunk is whole and 16-byte aligned
+    quantum = 8 * world
+    per_chunk = max(quantum, rows_total // chunks // quantum * quantum)
+    bounds = [min(rows_total, c * per_chunk) for c in range(chunks)] + [rows_total]
+    if (rows_total - bounds[-2]) % world:
+        raise SystemExit("tp_ffn: --rows must be a multiple of the rank count")
+    for c in range(chunks):
+        rows = bounds[c + 1] - bounds[c]
+        if rows <= 0:
+            continue
         part = dict(rows=rows, x=device_bf16(rows, HIDDEN, seed=10 + c, replicated=True),
                     residual=device_bf16(rows, HIDDEN, seed=20 + c, replicated=True), hidden=gpu.tensor_new_bf16(rows * width),
                     partial=gpu.tensor_new_f32(rows * HIDDEN), y=gpu.tensor_new_bf16(rows * HIDDEN))
+        share = rows // world                               # rows of this chunk that this rank finishes
+        part["share"], part["first"] = share, rank * share
         part["view"] = torch.as_tensor(_Span32(part["partial"].device_pointer, rows * HIDDEN), device=f"cuda:{local}")
+        part["y_view"] = torch.as_tensor(_Span16(part["y"].device_pointer, rows * HIDDEN), device=f"cuda:{local}").view(torch.bfloat16)
+        if world > 1:
+            part["reduced"] = gpu.tensor_new_f32(share * HIDDEN)
+            part["reduced_view"] = torch.as_tensor(_Span32(part["reduced"].device_pointer, share * HIDDEN), device=f"cuda:{local}")
         parts.append(part)
     reduce_events = []
+    comm_pointer = comm.cuda_stream
 
     def one_block(timed=False):
         for p in parts:
@@ -626,14 +643,22 @@ def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local, standalo
                     if timed:
                         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                         e0.record(comm)
-                    dist.all_reduce(p["view"])              # fp32 sum over the ranks, in place
+                    dist.reduce_scatter_tensor(p["reduced_view"], p["view"])     # fp32 sums; this rank keeps its rows
+                    offset = p["first"] * HIDDEN * 2
+                    # gate + residual + the one bf16 rounding, on this rank's rows, on the communication stream
+                    assert lib.h3q8_linear_finish(p["reduced"].device_pointer, p["share"], HIDDEN, None, gate.device_pointer,
+                                                  p["residual"].device_pointer + offset, 0, p["y"].device_pointer + offset,
+                                                  comm_pointer), lib.h3q8_last_error()
+                    share = p["share"] * HIDDEN
+                    dist.all_gather_into_tensor(p["y_view"], p["y_view"][rank * share:(rank + 1) * share])
                     if timed:
                         e1.record(comm)
                         reduce_events.append((e0, e1))
-        for p in parts:                                     # gate + residual + the one bf16 rounding on the reduced sums
-            if world > 1:
-                stream.wait_stream(comm)
-            gpu.linear_finish_bf16(p["y"], p["partial"], None, gate, p["residual"], p["rows"], HIDDEN, 0)
+        if world > 1:
+            stream.wait_stream(comm)
+        else:
+            for p in parts:
+                gpu.linear_finish_bf16(p["y"], p["partial"], None, gate, p["residual"], p["rows"], HIDDEN, 0)
         gpu.continue_()
 
     gpu.begin()
@@ -678,9 +703,11 @@ def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local, standalo
         plain, plain_tp = gpu.tensor_new_bf16(p["rows"] * HIDDEN), gpu.tensor_new_bf16(p["rows"] * HIDDEN)
         gpu.begin()
         gpu.linear_fused_bf16(plain, hidden, full_down, None, None, None, p["rows"], FFN, HIDDEN, 0)
-        gpu.linear_finish_bf16(plain_tp, p["partial"], None, None, None, p["rows"], HIDDEN, 0)
+        # the reduced fp32 sums this rank holds: all rows on one GPU, its share of the chunk (the first rows on rank 0) otherwise
+        sums, held = (p["reduced"], p["share"]) if world > 1 else (p["partial"], p["rows"])
+        gpu.linear_finish_bf16(plain_tp, sums, None, None, None, held, HIDDEN, 0)
         gpu.submit()
-        linear_ulp, linear_rel = ulps(plain_tp.read(), plain.read())
+        linear_ulp, linear_rel = ulps(plain_tp.read()[:held * HIDDEN], plain.read()[:held * HIDDEN])
         report = {"rel_l2": final_rel, "max_bf16_ulp": float(final_ulp.max()), "fraction_beyond_2_ulp": float((final_ulp > 2.0).mean()),
                   "projection_only": {"rel_l2": linear_rel, "max_bf16_ulp": float(linear_ulp.max()),
                                       "fraction_not_bit_equal": float((linear_ulp > 0).mean())},
@@ -697,14 +724,17 @@ def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local, standalo
         record = {
             "metric": METRIC, "workload": "tp_ffn", "value": flop / t / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "ms_per_block_ffn": t / args.steps * 1e3, "rows": rows_total, "ffn_features_this_rank": width, "row_chunks": chunks,
-            "allreduce_bytes_per_block": rows_total * HIDDEN * 4 if world > 1 else 0, "allreduce_ms_per_block_comm_stream": reduce_ms,
+            "allreduce_bytes_per_block": rows_total * HIDDEN * (4 + 2) if world > 1 else 0, "allreduce_ms_per_block_comm_stream": reduce_ms,
+            "collective": "reduce_scatter (fp32 partial sums) -> finish own rows -> all_gather (bf16 result)",
             "scaling": "strong", "dtype": "bf16", "data": "synthetic", "parity_vs_unsharded_fused_call": report,
             "config": {"workload": "tensor-parallel FFN (optional variant): FFN-up column-parallel with local GELU, FFN-down "
-                                   "row-parallel into fp32 partial sums, one NCCL all-reduce (fp32) per block, chunked over rows and "
-                                   "overlapped with the next chunk's GEMMs, gate + residual + bf16 rounding after the reduction"}}
+                                   "row-parallel into fp32 partial sums, one all-reduce per block issued as NCCL reduce-scatter (fp32) + "
+                                   "all-gather (bf16) with gate + residual + the bf16 rounding between the two, chunked over rows "
+                                   "and overlapped with the next chunk's GEMMs"}}
     for p in parts:
-        for key in ("x", "residual", "hidden", "partial", "y"):
-            p[key].free()
+        for key in ("x", "residual", "hidden", "partial", "y", "reduced"):
+            if key in p:
+                p[key].free()
     for t in (up_slice, down_slice, gate):
         t.free()
     if standalone:
