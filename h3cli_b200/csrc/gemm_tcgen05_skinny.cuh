@@ -1,6 +1,6 @@
-/* Linears of at most 64 token rows: the weight is the wide operand.
+/* Linears of at most 128 token rows: the weight is the wide operand.
  *
- *   out[m, n] = epilogue( sum_k X[m, k] * W[n, k] )        rows (m) <= 64
+ *   out[m, n] = epilogue( sum_k X[m, k] * W[n, k] )        rows (m) <= 128
  *
  * With so few rows the weight matrix is streamed once and the problem is bound by HBM, so the
  * kernel is built around the weight stream instead of around an output tile:
@@ -9,8 +9,9 @@
  *     real output channel), its N side the token rows padded to a multiple of 16, so the
  *     accumulator is [128 channels x tokens] and all 128 epilogue threads have work;
  *   - K is split over the CTAs of a thread-block cluster (1 to 8) so that tiles x splits
- *     fills the machine; each CTA streams its K range through a deep TMA ring (eight 16 KB
- *     weight tiles in flight per SM);
+ *     fills the machine; each CTA streams its K range through a deep TMA ring (up to eight
+ *     16 KB weight tiles in flight per SM; the token tile beside each is as tall as the call's
+ *     padded row count, so few rows leave the shared memory to the weight stream);
  *   - the four K steps of a k-block accumulate into four separate TMEM accumulators, so that
  *     consecutive narrow MMAs do not chain on one accumulator (the epilogue adds the four);
  *   - the partial sums never leave the chip: each CTA writes its [tokens x 128] partial tile
@@ -44,27 +45,26 @@ struct SkinnyArgs {
 
 template <int MODE>
 struct SkinnyConfig {
-    static constexpr int MAX_TOKENS = 64;
+    static constexpr int MAX_TOKENS = 128;
     static constexpr int BKE = MODE == MODE_W8A8 ? 128 : 64;     /* K elements per 128-byte operand row             */
     static constexpr int SUB = MODE == MODE_W8A16 ? 2 : 1;       /* k-blocks per K unit (weight hand-off)           */
     static constexpr int UNIT = BKE * SUB;                        /* K elements per unit                             */
     static constexpr int W_BYTES = 128 * 128;                     /* weight operand tile of one k-block              */
-    static constexpr int X_BYTES = MAX_TOKENS * 128;              /* token operand tile of one k-block               */
     static constexpr int RAW_BYTES = 128 * 128;                   /* W8A16: 128 rows x 128 int8 (one unit)           */
     /* rings in K units */
-    static constexpr int STAGES = 8;                              /* X (and W unless W8A16); W8A16 uses as many of them as
-                                                                     its 32 KB token region holds at the call's row count */
-    /* W8A16: two groups of four dequantiser warps take alternate units, one converted pair each; eight raw tiles keep
-     * 128 KB of the weight stream in flight.  (Four groups, or four converted pairs, measured the same or slower.) */
+    static constexpr int STAGES = 8;                              /* at most; as many as the stage region holds at the
+                                                                     call's row count (a token tile is tokens16 x 128 B) */
+    /* W8A16: two groups of four dequantiser warps take alternate units, one converted pair each.  (Four groups, four
+     * converted pairs or eight raw tiles measured the same or slower: the main loop, not the stream, is its bound.) */
     static constexpr int GROUPS = 2;
-    static constexpr int RAW_STAGES = MODE == MODE_W8A16 ? 8 : 0;
+    static constexpr int RAW_STAGES = MODE == MODE_W8A16 ? 5 : 0;
     static constexpr int CONV_BUFFERS = MODE == MODE_W8A16 ? GROUPS : 0;
-    static constexpr int X_REGION = 32 * 1024;                    /* W8A16: token tiles of tokens16 rows                */
-    static constexpr int STAGE_BYTES = MODE == MODE_W8A16 ? X_REGION / STAGES : X_BYTES + W_BYTES;
+    /* stage region: token tiles only (W8A16, 64 KB) or weight tile + token tile (192 KB) */
+    static constexpr int STAGE_REGION = MODE == MODE_W8A16 ? 64 * 1024 : 192 * 1024;
     static constexpr int EPILOGUE_WARPS = 4, PRODUCER_WARP = 4, MMA_WARP = 5, FIRST_DEQUANT_WARP = 6;
     static constexpr int GROUP_WARPS = 4, DEQUANT_WARPS = MODE == MODE_W8A16 ? GROUPS * GROUP_WARPS : 0;
     static constexpr int WARPS = FIRST_DEQUANT_WARP + DEQUANT_WARPS, THREADS = WARPS * 32;
-    static constexpr int RING_BYTES = STAGES * STAGE_BYTES + RAW_STAGES * RAW_BYTES + CONV_BUFFERS * SUB * W_BYTES;
+    static constexpr int RING_BYTES = STAGE_REGION + RAW_STAGES * RAW_BYTES + CONV_BUFFERS * SUB * W_BYTES;
     static constexpr int PARTIAL_BYTES = MAX_TOKENS * 128 * 4;   /* aliases the rings once the main loop is done    */
     static constexpr int BARRIERS = 2 * STAGES + 2 * RAW_STAGES + 2 * CONV_BUFFERS + 1;
     static constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
@@ -94,7 +94,7 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *ring = smem;                                             /* per stage: [W tile] X tile(s)            */
-    uint8_t *conv = ring + C::STAGES * C::STAGE_BYTES;                /* W8A16: converted weight tiles            */
+    uint8_t *conv = ring + C::STAGE_REGION;                           /* W8A16: converted weight tiles            */
     uint8_t *raw_ring = conv + C::CONV_BUFFERS * C::SUB * C::W_BYTES; /* W8A16: raw int8 weight tiles             */
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::RING_BYTES);
     uint64_t *full = bars, *empty = full + C::STAGES;
@@ -114,10 +114,10 @@ gemm_tcgen05_skinny_kernel(const __grid_constant__ SkinnyArgs args) {
     const uint32_t unit_end = min(units, unit_begin + args.units_per_split);
     const uint32_t num_kb = (p.K + C::BKE - 1) / C::BKE;
     const uint32_t tokens16 = args.tokens16;
-    /* W8A16: a token tile holds tokens16 rows (the TMA box of the call), a stage the tiles of one unit */
-    const uint32_t x_tile_bytes = MODE == MODE_W8A16 ? tokens16 * 128 : C::X_BYTES;
-    const uint32_t stage_bytes = MODE == MODE_W8A16 ? C::SUB * x_tile_bytes : C::STAGE_BYTES;
-    const uint32_t stages = MODE == MODE_W8A16 ? min((uint32_t)C::STAGES, C::X_REGION / stage_bytes) : C::STAGES;
+    /* a token tile holds tokens16 rows (the TMA box of the call); a stage holds the tiles of one unit */
+    const uint32_t x_tile_bytes = tokens16 * 128;
+    const uint32_t stage_bytes = MODE == MODE_W8A16 ? C::SUB * x_tile_bytes : C::W_BYTES + x_tile_bytes;
+    const uint32_t stages = min((uint32_t)C::STAGES, C::STAGE_REGION / stage_bytes);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }

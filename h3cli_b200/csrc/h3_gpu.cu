@@ -1116,17 +1116,14 @@ static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size
         need[1] = round256(padded * sizeof(float));
         mode = H3Q8_MODE_W8A8;
     } else if (q.weight->q8) {
-        /* few rows: the int8 weight is read once with main-loop dequantisation (weight-streaming kernel up to 64 rows,
-         * split-K with a workspace up to 128) */
-        const size_t skinny = !g->skinny_direct || swiglu || q.rows > 128 ? 0
-                            : q.rows <= 64 ? (uint64_t)q.input_dim * q.output_dim >= (1u << 20)   /* a weight worth streaming */
-                            : h3q8_linear_workspace_bytes(H3Q8_MODE_W8A16, q.rows, q.input_dim, q.output_dim);
+        /* few rows: the int8 weight is read once with main-loop dequantisation (the weight-streaming kernel), when the
+         * weight is large enough for that to matter */
+        const bool skinny = g->skinny_direct && !swiglu && q.rows <= 128 && (uint64_t)q.input_dim * q.output_dim >= (1u << 20);
         if (q.input_dim % 16 == 0 && !skinny && w8a16_to_scratch(g, q)) {
             need[2] = round256((size_t)q.output_dim * (swiglu ? 2 : 1) * q.input_dim * 2);
         } else mode = H3Q8_MODE_W8A16;
     }
-    if (!swiglu && q.rows <= 128 && !(mode == H3Q8_MODE_W8A8 && q.weight->q8_group))
-        need[3] = round256(h3q8_linear_workspace_bytes(mode, q.rows, q.input_dim, q.output_dim));
+    (void)mode;   /* problems of at most 128 rows run on the weight-streaming kernel, which needs no split-K workspace */
 }
 
 /* The linear operators: validate every problem, run the conversion kernels each needs

@@ -359,9 +359,8 @@ static int launch_skinny(const h3q8_linear_desc &d, const GemmParams &p, DeviceS
     const uint32_t w_bytes = d.mode == H3Q8_MODE_BF16 ? 2 : 1, x_bytes = d.mode == H3Q8_MODE_W8A8 ? 1 : 2;
     /* 128-byte operand rows: 64 bf16 or 128 int8 (the raw W8A16 tile covers two 64-wide k-blocks) */
     if (!make_map(&args.map_w, d.weight, w_bytes, d.output_dim, d.input_dim, 128 / w_bytes, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
-    /* token tiles: 64 rows, or exactly the padded row count where shared memory is tight (W8A16 keeps four converted weight tiles) */
-    if (!make_map(&args.map_x, d.input, x_bytes, d.rows, d.input_dim, 128 / x_bytes, d.mode == H3Q8_MODE_W8A16 ? args.tokens16 : 64,
-                  CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
+    /* token tiles are exactly as tall as the padded row count, which leaves the shared memory to the weight stream */
+    if (!make_map(&args.map_x, d.input, x_bytes, d.rows, d.input_dim, 128 / x_bytes, args.tokens16, CU_TENSOR_MAP_SWIZZLE_128B)) return 0;
     return launch_skinny_kernel(args, d.mode, dev->sms, stream);   /* chooses the K split */
 }
 
@@ -460,8 +459,8 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
                                  d.input_dim % p.scale_group == 0 && !swiglu && !d.rope;
     kernel = d.kernel;
     if (kernel > H3Q8_KERNEL_TCGEN05_SKINNY) return fail("linear: unknown kernel selector %u", kernel);
-    /* the weight-streaming kernel: at most 64 rows, per-channel int8 scales, bias / GELU / gate / residual epilogue */
-    const bool skinny_ok = d.rows <= 64 && !(d.mode == H3Q8_MODE_W8A8 && p.scale_group) && !swiglu && !d.rope && !d.accumulators &&
+    /* the weight-streaming kernel: at most 128 rows, per-channel int8 scales, bias / GELU / gate / residual epilogue */
+    const bool skinny_ok = d.rows <= 128 && !(d.mode == H3Q8_MODE_W8A8 && p.scale_group) && !swiglu && !d.rope && !d.accumulators &&
                            d.output;
     /* split-K: raw sums go through the workspace, so no per-group combine, second accumulator, rotary epilogue or dump */
     const bool splitk_ok = !(d.mode == H3Q8_MODE_W8A8 && p.scale_group) && !swiglu && !d.rope && !d.accumulators && d.workspace &&
@@ -498,7 +497,7 @@ static int plan_linear(const h3q8_linear_desc &d, GemmParams &p, uint32_t &kerne
     } else if (kernel == H3Q8_KERNEL_TCGEN05_PAIR && d.mode == H3Q8_MODE_W8A16 && d.accumulators) {
         return fail("linear: the two-CTA W8A16 kernel has no accumulator dump");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_SKINNY && !skinny_ok) {
-        return fail("linear: the weight-streaming kernel takes at most 64 rows, ungrouped W8A8 scales, and no SwiGLU / rotary epilogue / accumulator dump");
+        return fail("linear: the weight-streaming kernel takes at most 128 rows, ungrouped W8A8 scales, and no SwiGLU / rotary epilogue / accumulator dump");
     } else if (kernel == H3Q8_KERNEL_TCGEN05_SPLITK && !splitk_ok) {
         return fail("linear: split-K takes ungrouped scales, no SwiGLU / rotary epilogue / accumulator dump, and a 16-byte aligned workspace");
     } else if (kernel != H3Q8_KERNEL_PLAIN && !tma_ok) {

@@ -107,7 +107,7 @@ enum { /* kernel selection; AUTO picks by shape */
     H3Q8_KERNEL_TCGEN05_SPLITK = 6, /* skinny M: 128 x 128 tiles, K split over several
                                      CTAs per tile, partial sums in `workspace`, then
                                      a finishing kernel (weight-bandwidth bound)     */
-    H3Q8_KERNEL_TCGEN05_SKINNY = 7 /* at most 64 rows: the weight is the MMA's wide
+    H3Q8_KERNEL_TCGEN05_SKINNY = 7 /* at most 128 rows: the weight is the MMA's wide
                                      operand, K split over a thread-block cluster,
                                      partial sums reduced through distributed shared
                                      memory; one launch, no workspace                */
@@ -155,8 +155,9 @@ typedef struct {
                                  src/metal/shaders.metal:2663-2742); 0 = one scale per token   */
     const h3q8_rope_desc *rope; /* optional QKV norm + rotary epilogue; output may then be NULL
                                  (when given it also receives the plain bf16 projection)       */
-    void *workspace;          /* optional device scratch (16-byte aligned) for split-K partial sums: with it, problems of
-                                 at most 128 rows spread over all SMs (AUTO); needs splits * rows * output_dim * 4 bytes  */
+    void *workspace;          /* device scratch (16-byte aligned) for H3Q8_KERNEL_TCGEN05_SPLITK: splits * rows * output_dim * 4
+                                 bytes of partial sums.  AUTO does not need it: problems of at most 128 rows run on the
+                                 weight-streaming kernel, which reduces on chip                                         */
     size_t workspace_bytes;
     uint32_t after_producer;  /* 1: an operand of this call (the dequantised weight, the quantised activations) is written
                                  by the kernel enqueued immediately before on the same stream.  The two-CTA kernels are

@@ -351,8 +351,8 @@ def test_skinny_split_k(gpu, oracle, mode, M, N, K, kernel):
     launches = lib.h3q8_kernel_launches()
     gpu.raw_linear(mode=mode_id, rows=M, input_dim=K, output_dim=N, weight_group=group, activation=act, kernel=kernel, output=out,
                    workspace=workspace, workspace_bytes=nbytes, **t)
-    # split GEMM + finishing kernel; up to 64 rows AUTO prefers the one-launch weight-streaming kernel
-    assert gpu.raw_status() == 0 and lib.h3q8_kernel_launches() - launches == (1 if kernel == h.KERNEL_AUTO and M <= 64 else 2)
+    # split GEMM + finishing kernel; AUTO prefers the one-launch weight-streaming kernel
+    assert gpu.raw_status() == 0 and lib.h3q8_kernel_launches() - launches == (1 if kernel == h.KERNEL_AUTO else 2)
     got = out.read()
     assert (got[M * N:] == 0x3F80).all(), "wrote past the end of the output"
     if mode == "w8a8" and not act:
@@ -396,10 +396,11 @@ def test_gemm_as_programmatic_dependent_of_its_dequantiser(gpu, oracle):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 3072, 3072), (16, 3072, 3072), (16, 12288, 3072), (16, 3072, 12288), (33, 520, 1536),
-                                   (64, 1536, 12288), (47, 256, 16000), (5, 136, 1040), (17, 128, 128), (64, 8, 4096)])
+                                   (64, 1536, 12288), (47, 256, 16000), (5, 136, 1040), (17, 128, 128), (64, 8, 4096),
+                                   (65, 3072, 3072), (100, 520, 1536), (128, 1536, 12288), (128, 3072, 3072)])
 @pytest.mark.parametrize("mode", ["bf16", "w8a16", "w8a16g64", "w8a16g128", "w8a8"])
 def test_skinny_weight_streaming(gpu, oracle, mode, M, N, K):
-    """At most 64 rows: the weight is the MMA's wide operand, K is split over a thread-block cluster and the partial
+    """At most 128 rows: the weight is the MMA's wide operand, K is split over a thread-block cluster and the partial
     sums are reduced through distributed shared memory in ascending split order -- one launch, no workspace.
     int32 partial sums are exact, so W8A8 stays bit-equal to the oracle; ragged N, K tails and every epilogue term."""
     group = {"w8a16g64": 64, "w8a16g128": 128}.get(mode, 0)
@@ -432,7 +433,7 @@ def test_skinny_weight_streaming(gpu, oracle, mode, M, N, K):
     else:
         check_bf16(got[:M * N].reshape(M, N), want)
     with pytest.raises(h.H3Error):                   # more rows than the kernel's token operand holds
-        gpu.raw_linear(mode=mode_id, rows=65, input_dim=K, output_dim=N, weight_group=group, activation=act,
+        gpu.raw_linear(mode=mode_id, rows=129, input_dim=K, output_dim=N, weight_group=group, activation=act,
                        kernel=h.KERNEL_TCGEN05_SKINNY, output=out, **t)
     for tensor in list(t.values()) + [out]:
         tensor.free()
