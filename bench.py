@@ -609,15 +609,8 @@ def run_tp_ffn(args, gpu, lib, stream, device_bf16, rank, world, local, standalo
     comm = torch.cuda.Stream()
     parts = []
     # chunk sizes are multiples of 8 * world rows, so that every rank's share of a chunk is whole and 16-byte aligned
-    quantum = 8 * world
-    per_chunk = max(quantum, rows_total // chunks // quantum * quantum)
-    bounds = [min(rows_total, c * per_chunk) for c in range(chunks)] + [rows_total]
-    if (rows_total - bounds[-2]) % world:
-        raise SystemExit("tp_ffn: --rows must be a multiple of the rank count")
-    for c in range(chunks):
-        rows = bounds[c + 1] - bounds[c]
-        if rows <= 0:
-            continue
+    for c, (begin, end) in enumerate(sharding.reduce_chunks(rows_total, chunks, world)):
+        rows = end - begin
         part = dict(rows=rows, x=device_bf16(rows, HIDDEN, seed=10 + c, replicated=True),
                     residual=device_bf16(rows, HIDDEN, seed=20 + c, replicated=True), hidden=gpu.tensor_new_bf16(rows * width),
                     partial=gpu.tensor_new_f32(rows * HIDDEN), y=gpu.tensor_new_bf16(rows * HIDDEN))

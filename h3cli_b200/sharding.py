@@ -48,3 +48,19 @@ def feature_range(features, rank, world, tile=128):
         raise ValueError("FFN width must be a multiple of tile * world")
     width = features // world
     return rank * width, (rank + 1) * width
+
+
+def reduce_chunks(rows, chunks, world, quantum=8):
+    """Row chunks [begin, end) of the tensor-parallel FFN's reduction: the partial sums of a chunk are reduce-scattered,
+    every rank finishes rows/world of it and the results are all-gathered while the next chunk computes.  Every chunk
+    is a multiple of `quantum * world` rows (a rank's share is then whole and keeps 16-byte aligned rows) except the
+    last, which takes the remainder and must still divide by `world`."""
+    if world < 1 or chunks < 1 or rows < 1:
+        raise ValueError("invalid chunking")
+    unit = quantum * world
+    per_chunk = max(unit, rows // chunks // unit * unit)
+    bounds = [min(rows, c * per_chunk) for c in range(chunks)] + [rows]
+    out = [(b, e) for b, e in zip(bounds, bounds[1:]) if e > b]
+    if any((e - b) % world for b, e in out):
+        raise ValueError("rows must be a multiple of the rank count")
+    return out

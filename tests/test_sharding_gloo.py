@@ -79,6 +79,18 @@ def _worker(rank, world, port, result_queue):
     dist.destroy_process_group()
 
 
+def test_reduce_chunks_give_every_rank_a_whole_share():
+    for rows in (32400, 4096, 219600, 64, 8):
+        for world in (1, 2, 4, 8):
+            for chunks in (1, 4):
+                got = sharding.reduce_chunks(rows, chunks, world)
+                assert got[0][0] == 0 and got[-1][1] == rows and all(a[1] == b[0] for a, b in zip(got, got[1:]))
+                assert all((e - b) % world == 0 for b, e in got)
+                assert all((e - b) % (8 * world) == 0 for b, e in got[:-1])
+    with pytest.raises(ValueError):
+        sharding.reduce_chunks(32401, 4, 2)
+
+
 def test_blob_and_feature_splits():
     for total in (0, 1, 255, 256, 116785152, 116785153):
         for world in (1, 2, 4, 8):
