@@ -59,10 +59,10 @@ struct h3_gpu {
     uint32_t group = 0;
     bool group_set = false;
     int w8a16_scratch_rows = -1; /* rows at or above which W8A16 dequantises to scratch first; 0 = never; -1 = by shape */
-    void *arena[4] = {nullptr, nullptr, nullptr, nullptr}; /* 0 int8 activations, 1 activation scales, 2 bf16 weight scratch, 3 split-K partial sums */
+    void *arena[4] = {nullptr, nullptr, nullptr, nullptr}; /* 0 int8 activations, 1 activation scales, 2 bf16 weight scratch, 3 reserved for a split-K workspace (unused: few-row problems reduce on chip) */
     size_t arena_bytes[4] = {0, 0, 0, 0};
     int dependent_launch = 1;   /* GEMMs start as programmatic dependents of their conversion kernel; H3Q8_DEPENDENT_LAUNCH=0 turns it off */
-    int skinny_direct = 1;      /* W8A16 with at most 128 rows: main-loop dequantisation + split-K (the weight is read once as int8) */
+    int skinny_direct = 1;      /* W8A16 with at most 128 rows: main-loop dequantisation on the weight-streaming kernel (the weight is read once as int8) */
     uint32_t *flags = nullptr;  /* [0] kernel wait status, [1] non-finite seen */
     unsigned long long *diagnostics = nullptr;   /* [0] clipped, [1] non-zero values quantised to zero; H3_QUANT_DIAGNOSTICS=1 */
     void *bounce[2] = {nullptr, nullptr};
@@ -1104,7 +1104,7 @@ static bool dependent_launch(const h3_gpu *g, const h3_gpu_linear_problem &q) {
 }
 
 /* Scratch a problem needs from the context arenas: [0] int8 activations, [1] their scales, [2] bf16 weight,
- * [3] split-K partial sums (problems of at most 128 rows are spread over all SMs). */
+ * [3] nothing any more (problems of at most 128 rows reduce their K slices on chip). */
 static void linear_scratch(const h3_gpu *g, const h3_gpu_linear_problem &q, size_t need[4]) {
     need[0] = need[1] = need[2] = need[3] = 0;
     if (!q.weight) return;
