@@ -188,3 +188,61 @@ def test_w8a8_activation_group_scales(oracle):
         total = value if total is None else (total + value).astype(np.float32)
     assert (oracle.f32_to_bf16(total).reshape(5, 7) == out).all()
     assert (oracle.linear(oracle.MODE_W8A8, xq[:5], wq, ws, 0, x_scales=xs[:5], input_group=1024, fast=True) == out).all()
+
+
+def test_restatement_against_reference_cuda_kernel_outputs(oracle):
+    """tests/golden/reference_kernels.npz holds outputs of the reference's OWN CUDA element kernels
+    (src/cuda/cuda_kernels.cuh compiled unmodified, run on a B200 by tests/golden/make_reference_kernel_golden.py).
+    The CPU restatement is held to them here with the bounds the GPU tests use beside the live kernels: gate, add-style
+    IEEE steps and the v stream bit for bit; tanhf / expf / rsqrtf results within one bf16 step (a CPU's libm and
+    1/sqrt against the GPU's)."""
+    g = np.load(os.path.join(GOLDEN, "reference_kernels.npz"))
+    f32 = lambda bits: oracle.bf16_to_f32(np.asarray(bits, np.uint16))
+
+    def steps_apart(a, b):
+        ordered = lambda bits: np.where(bits.astype(np.int32) & 0x8000, -(bits.astype(np.int32) & 0x7FFF), bits.astype(np.int32))
+        return np.abs(ordered(np.asarray(a)) - ordered(np.asarray(b)))
+
+    def within_one_step(a, b, floor):
+        x, y = f32(a).astype(np.float64), f32(b).astype(np.float64)
+        step = 2.0 ** (np.floor(np.log2(np.maximum(np.maximum(np.abs(x), np.abs(y)), floor))) - 7)
+        return bool((np.abs(x - y) <= step).all())
+
+    # GELU-tanh over every bf16 input (src/cuda/cuda_kernels.cuh:879-902)
+    bits = np.arange(65536, dtype=np.uint32).astype(np.uint16)
+    finite = np.isfinite(f32(bits))
+    apart = steps_apart(oracle.gelu_tanh_bf16(bits)[finite], g["gelu_out"][finite])
+    assert apart.max() <= 1 and (apart != 0).mean() < 2e-3
+    # gate * branch + residual (:973-986): separate IEEE multiply and add, bit for bit
+    for i in range(2):
+        res, branch, mod, row_map = g[f"gate{i}_res"], g[f"gate{i}_branch"], g[f"gate{i}_mod"], g[f"gate{i}_map"]
+        product = f32(branch) * f32(mod[row_map, 2, :])
+        assert (oracle.f32_to_bf16(f32(res) + product) == g[f"gate{i}_out"]).all()
+    # SwiGLU on a stored [rows, 2 * width] tensor (:1047-1059)
+    fused = g["swiglu_in"]
+    width = fused.shape[1] // 2
+    gate, up = f32(fused[:, :width]), f32(fused[:, width:])
+    apart = steps_apart(oracle.f32_to_bf16(gate / (np.float32(1) + np.exp(-gate, dtype=np.float32)) * up), g["swiglu_out"])
+    assert apart.max() <= 1 and (apart != 0).mean() < 5e-3
+    # grouped QKV: per-head RMS norm + rotary embedding (:988-1045)
+    for i, (heads, half) in enumerate([(2, 48), (3, 64)]):
+        got = oracle.grouped_qkv_rope(g[f"rope{i}_qkv"], g[f"rope{i}_qn"], g[f"rope{i}_kn"], g[f"rope{i}_cos"], g[f"rope{i}_sin"],
+                                      heads, 128, half, 1e-5)
+        for mine, theirs in zip(got, (g[f"rope{i}_q"], g[f"rope{i}_k"], g[f"rope{i}_v"])):
+            assert within_one_step(mine, theirs, 1.0)
+        assert (got[2] == g[f"rope{i}_v"]).all()
+    # gate -> AdaLN -> per-row int8 (:973-986, 936-971; src/metal/shaders.metal:1434-1459)
+    for i in range(3):
+        res, branch, mod, norm_w, row_map = (g[f"chain{i}_{k}"] for k in ("res", "branch", "mod", "norm", "map"))
+        rows = res.shape[0]
+        padded = (rows + 127) // 128 * 128
+        o_gated, o_norm, o_q, _ = oracle.gate_adaln_quantize(res, branch, mod, norm_w, mod, row_map, padded, 6, 2, 3, 4, 1e-5)
+        assert (o_gated == g[f"chain{i}_gated"]).all()
+        assert within_one_step(o_norm, g[f"chain{i}_adaln"], 0.25)
+        want_q, _ = oracle.quantize_rows(g[f"chain{i}_adaln"], padded)
+        assert np.abs(o_q.astype(np.int32) - want_q.astype(np.int32)).max() <= 1
+    # the reference's small bf16 linear (:762-794): fp32 fmaf chain against the FP64-dot restatement
+    from parity import check_bf16
+    for i in range(3):
+        bias = g[f"linear{i}_bias"]
+        check_bf16(oracle.linear(oracle.MODE_BF16, g[f"linear{i}_x"], g[f"linear{i}_w"], bias=bias if bias.size else None), g[f"linear{i}_out"])
