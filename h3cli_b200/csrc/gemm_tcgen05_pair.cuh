@@ -34,7 +34,14 @@
 
 namespace h3q8 {
 
-template <int MODE>
+/* EPILOGUE_WARPS: 8 = each warp a column half of the tile, 16 = a column quarter (the rotary epilogue keeps a whole
+ * 128-wide head row per thread and stays at 8).  Sixteen warps cover the TMEM and global-memory latencies of the
+ * epilogue better; they pay where the epilogue is exposed: int8 tiles, whose main loop is half as long for the same
+ * epilogue (measured on one box at M = 32 400: QKV 2 302 -> 2 513, attention-out 1 770 -> 1 842, FFN-up 2 154 -> 2 487,
+ * FFN-down 2 319 -> 2 296 TOP/s; the 4 096-row W8A8 linear 58.1 -> 45.1 us), and bf16 problems of few tile waves, where
+ * the last tile's epilogue is not hidden (4 096 x 3 072 x 3 072: 66.9 -> 63.8 us).  At M = 32 400 the bf16 kernel loses
+ * 1 % with sixteen, so the launcher picks by mode and row count. */
+template <int MODE, bool ROPE = false, int EPILOGUE_WARPS_ = 8>
 struct PairConfig {
     static constexpr int BM = 256, BN = 256;           /* per pair */
     static constexpr int ROW_BYTES = 128;
@@ -44,7 +51,9 @@ struct PairConfig {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = 6;
     static constexpr int ACC_COLS = BN, ACC_BUFFERS = 2;
-    static constexpr int EPILOGUE_WARPS = 8, PRODUCER_WARP = 8, MMA_WARP = 9, WARPS = 10, THREADS = WARPS * 32;
+    static constexpr int EPILOGUE_WARPS = EPILOGUE_WARPS_;
+    static constexpr int PRODUCER_WARP = EPILOGUE_WARPS, MMA_WARP = EPILOGUE_WARPS + 1, WARPS = EPILOGUE_WARPS + 2, THREADS = WARPS * 32;
+    static_assert(EPILOGUE_WARPS == 8 || (EPILOGUE_WARPS == 16 && !ROPE), "column halves, or quarters for the plain epilogues");
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
     static constexpr uint32_t IDESC = MODE == MODE_W8A8 ? umma_idesc(2, 1, 256, BN) : umma_idesc(1, 1, 256, BN);
     static_assert(MODE == MODE_BF16 || MODE == MODE_W8A8, "pair kernel: bf16 or int8 operands");
@@ -70,10 +79,10 @@ __device__ __forceinline__ uint32_t locate_problem(const PairArgs &args, uint32_
 
 /* ROPE selects the QKV norm + rotary epilogue (its own instantiation: it keeps a whole
  * 128-wide head row in registers, which the other epilogues should not pay for). */
-template <int MODE, bool ROPE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<MODE>::THREADS, 1)
+template <int MODE, bool ROPE, int EPILOGUE_WARPS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairConfig<MODE, ROPE, EPILOGUE_WARPS>::THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
-    using C = PairConfig<MODE>;
+    using C = PairConfig<MODE, ROPE, EPILOGUE_WARPS>;
     const uint32_t total_tiles = args.tile_start[args.count];
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -162,7 +171,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
         }
     } else {
         /* epilogue: this CTA's 128 rows, TMEM lane quadrant warp % 4, column half warp / 4 */
-        constexpr int HALF_CHUNKS = C::BN / 64;
+        constexpr int SPLIT = C::EPILOGUE_WARPS / 4;          /* column parts of the tile: halves or quarters */
+        constexpr int HALF_CHUNKS = C::BN / 32 / SPLIT;        /* 32-column chunks per warp */
+        static_assert(!ROPE || SPLIT == 2, "the rotary epilogue owns a 128-column group per warp");
         const uint32_t quadrant = warp & 3, half = warp >> 2;
         PipeState acc;
         for (uint32_t tile = pair; tile < total_tiles && !failure; tile += pairs) {
@@ -229,8 +240,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ PairArgs args) {
             } else if (!ROPE && swiglu) {
                 /* accumulator columns 0..127 hold the gate, 128..255 the up projection of the same 128 outputs */
 #pragma unroll 1
-                for (int hc = 0; hc < 2; hc++) {
-                    const int c = half * 2 + hc;
+                for (int hc = 0; hc < 4 / SPLIT; hc++) {
+                    const int c = half * (4 / SPLIT) + hc;
                     uint32_t vg[32], vu[32];
                     const uint32_t taddr = tmem_base + ((quadrant * 32u) << 16) + acc.index * C::ACC_COLS + c * 32;
                     tmem_load_32x32(taddr, vg);

@@ -129,9 +129,9 @@ static int launch_tcgen05(const h3q8_linear_desc &d, GemmParams p, DeviceState *
 
 /* Two-CTA clusters: the grid is twice the number of clusters that can be resident at once. */
 /* `count` problems (1..PAIR_MAX_PROBLEMS) of one operand mode in ONE launch. */
-template <int MODE, bool ROPE = false>
-static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, uint32_t count, DeviceState *dev, cudaStream_t stream) {
-    using C = PairConfig<MODE>;
+template <int MODE, bool ROPE, int EPILOGUE_WARPS>
+static int launch_pair_with(const h3q8_linear_desc *descs, const GemmParams *params, uint32_t count, DeviceState *dev, cudaStream_t stream) {
+    using C = PairConfig<MODE, ROPE, EPILOGUE_WARPS>;
     static_assert(sizeof(PairArgs) <= 4000, "kernel parameter block too large");
     PairArgs args;
     memset(&args, 0, sizeof args);
@@ -159,7 +159,7 @@ static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, 
         tiles += p.tiles;
     }
     args.tile_start[count] = tiles;
-    auto kernel = gemm_tcgen05_pair_kernel<MODE, ROPE>;
+    auto kernel = gemm_tcgen05_pair_kernel<MODE, ROPE, EPILOGUE_WARPS>;
     static int clusters[64] = {};
     int device = 0;
     cudaGetDevice(&device);
@@ -204,6 +204,21 @@ static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, 
     cudaError_t e = cudaLaunchKernelEx(&config, kernel, args);
     count_launch(1);
     return cuda_ok(e != cudaSuccess ? e : cudaGetLastError(), "tcgen05 pair linear launch");
+}
+
+/* Epilogue warps by mode and size: sixteen for int8 tiles (their main loop is half as long for the same epilogue) and
+ * for bf16 problems of few tile waves (the last tile's epilogue is exposed), eight for large bf16 problems and for the
+ * rotary epilogue. */
+template <int MODE, bool ROPE = false>
+static int launch_pair(const h3q8_linear_desc *descs, const GemmParams *params, uint32_t count, DeviceState *dev, cudaStream_t stream) {
+    if constexpr (ROPE) return launch_pair_with<MODE, true, 8>(descs, params, count, dev, stream);
+    else if constexpr (MODE == MODE_W8A8) return launch_pair_with<MODE, false, 16>(descs, params, count, dev, stream);
+    else {
+        uint64_t rows = 0;
+        for (uint32_t i = 0; i < count; i++) rows += descs[i].rows;
+        return rows <= 8192 ? launch_pair_with<MODE, false, 16>(descs, params, count, dev, stream)
+                            : launch_pair_with<MODE, false, 8>(descs, params, count, dev, stream);
+    }
 }
 
 /* W8A16 with main-loop dequantisation on the two-CTA tile (one problem per launch). */
