@@ -31,9 +31,12 @@ def build(force=False, verbose=False):
     """Builds h3cli_b200/libh3q8.so if any source is newer; returns its path."""
     include = os.path.join(ROOT, "include")
     sources = [os.path.join(CSRC, f) for f in sorted(os.listdir(CSRC))] + [os.path.join(include, "h3q8.h"), __file__]
-    if not force and not _stale(LIB, sources):
-        return LIB
     build_dir = os.path.join(HERE, "_build")
+    stamp = os.path.join(build_dir, "nvcc_flags.txt")      # a library built with other flags (H3Q8_NVCC_EXTRA) is stale too
+    flags = " ".join(NVCC_FLAGS)
+    same_flags = os.path.exists(stamp) and open(stamp).read() == flags
+    if not force and same_flags and not _stale(LIB, sources):
+        return LIB
     os.makedirs(build_dir, exist_ok=True)
     pack_o = os.path.join(build_dir, "q8_pack.o")
     run = lambda cmd: subprocess.run(cmd, check=True, stdout=None if verbose else subprocess.DEVNULL)
@@ -52,6 +55,8 @@ def build(force=False, verbose=False):
              os.path.join(CSRC, unit), "-o", obj])
         objects.append(obj)
     run([_nvcc(), "-shared", "-o", LIB, *objects, "-lm"])
+    with open(stamp, "w") as f:
+        f.write(flags)
     # the artifact preparation tool links the library it sits beside
     run(["gcc", "-O2", "-std=c11", "-I", include, os.path.join(CSRC, "q8_prepare.c"), "-o", PREPARE, "-L", HERE, "-lh3q8",
          "-Wl,-rpath,$ORIGIN"])
