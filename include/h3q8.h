@@ -102,8 +102,10 @@ enum { /* kernel selection; AUTO picks by shape */
     H3Q8_KERNEL_TCGEN05 = 2,   /* tcgen05/TMA kernel, 128 x 256 tiles               */
     H3Q8_KERNEL_TCGEN05_M256 = 3, /* tcgen05/TMA kernel, 256 x 256 tiles            */
     H3Q8_KERNEL_TCGEN05_N128 = 4, /* tcgen05/TMA kernel, 128 x 128 tiles            */
-    H3Q8_KERNEL_TCGEN05_PAIR = 5, /* two-CTA tcgen05 kernel, 256 x 256 tiles per CTA
-                                     pair (BF16 and W8A8 per-channel modes)         */
+    H3Q8_KERNEL_TCGEN05_PAIR = 5, /* two-CTA tcgen05 kernels, 256 x 256 tiles per CTA
+                                     pair: BF16, W8A8 (per-channel, or scale groups of
+                                     128 * n on 256 x 128 tiles), W8A16 with the
+                                     dequantisation in the main loop; more than 128 rows */
     H3Q8_KERNEL_TCGEN05_SPLITK = 6, /* skinny M: 128 x 128 tiles, K split over several
                                      CTAs per tile, partial sums in `workspace`, then
                                      a finishing kernel (weight-bandwidth bound)     */
